@@ -1,0 +1,203 @@
+/*
+ * simnets_b200.h -- C ABI of the B200 (sm_100a) Similarity / MEX operator library.
+ *
+ * Every entry point is plain C: pointers, sizes, POD descriptors.  Device entry
+ * points enqueue work on the caller's CUDA stream (passed as void* so that this
+ * header needs no CUDA include), never synchronise, never allocate and never
+ * free: the caller owns all buffers, including the scratch workspace whose size
+ * the *_workspace_bytes queries return.  Return value: 0 on success, a negative
+ * SIMNETS_E_* code for a rejected call, a positive cudaError_t for a launch
+ * failure.  simnets_status_string() renders either.
+ *
+ * Tensors are dense row-major NCHW, float32 (dtype 0) or float64 (dtype 1).
+ *
+ * Each declaration cites the interface of the reference implementation
+ * (HUJI-Deep/simnets-tf, paths relative to that project) that it stands in for.
+ */
+#ifndef SIMNETS_B200_H
+#define SIMNETS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SIMNETS_API __attribute__((visibility("default")))
+
+/* ---- status codes ------------------------------------------------------ */
+enum {
+    SIMNETS_OK = 0,
+    SIMNETS_E_NULL = -1,          /* a required pointer is NULL                   */
+    SIMNETS_E_DESC = -2,          /* descriptor fails the reference's validation  */
+    SIMNETS_E_DTYPE = -3,         /* dtype is neither float32 (0) nor float64 (1) */
+    SIMNETS_E_WORKSPACE = -4,     /* workspace missing or too small               */
+    SIMNETS_E_UNSUPPORTED = -5,   /* valid, but outside what this build handles   */
+    SIMNETS_E_TOO_LARGE = -6      /* exceeds a fixed capacity (static scratch)    */
+};
+
+enum { SIMNETS_F32 = 0, SIMNETS_F64 = 1 };
+enum { SIMNETS_SIM_L1 = 0, SIMNETS_SIM_L2 = 1 };
+
+/* ---- descriptor flags --------------------------------------------------- */
+/* Gradient outputs are overwritten by default, as the reference does
+ * (src/kernels/similarity_grad_kernel_cpu.cpp:62,176; mex_grad_kernel_cpu.cpp:249).
+ * With ACCUMULATE the parameter-gradient entry points add into the destination,
+ * so that a data-parallel step can point them straight at its gradient bucket. */
+#define SIMNETS_FLAG_ACCUMULATE        (1u << 0)
+/* Use the one-thread-per-output kernels for every shape (slow, shape-agnostic). */
+#define SIMNETS_FLAG_FORCE_DIRECT      (1u << 1)
+/* MEX only: never use the factorised evaluation, always the per-term exp form. */
+#define SIMNETS_FLAG_MEX_EXACT         (1u << 2)
+/* Similarity, L2 + normalization_term without ignore_nan_input: the reference's
+ * fast op adds -0.5*K*log(2*pi) to the whole output tensor inside its batch loop
+ * (src/kernels/similarity_kernel_cpu.cpp:118-120), so sample n receives the
+ * constant (batch - n) times.  By default this library adds it once per element,
+ * which is what the reference's own SimilarityRef op does
+ * (src/kernels/similarity_ref_kernel_cpu.cpp:89-93); this flag reproduces the
+ * fast op's behaviour instead. */
+#define SIMNETS_FLAG_SIM_BATCH_CONST_QUIRK (1u << 3)
+/* Similarity, extension without a reference counterpart: L1 with NaN inputs
+ * skipped (term contributes 0).  Requires similarity_function == L1. */
+#define SIMNETS_FLAG_SIM_L1_SKIP_NAN   (1u << 4)
+
+/* ---- Similarity ---------------------------------------------------------- */
+/* Mirrors the attrs of the Similarity op family (src/ops/similarity_op.cpp:61-75)
+ * and the dimensions SimilarityKernelCommon::CalculateDimensions derives
+ * (include/kernels/similarity_kernel_common.hpp:113-164).
+ * templates / weights: [num_instances, channels, block_h, block_w]. */
+typedef struct simnets_sim_desc {
+    int32_t dtype;
+    int32_t batch, channels, height, width;
+    int32_t num_instances;
+    int32_t block_h, block_w;
+    int32_t stride_h, stride_w;
+    int32_t pad_h, pad_w;
+    int32_t similarity_function;        /* SIMNETS_SIM_L1 | SIMNETS_SIM_L2 */
+    int32_t normalization_term;
+    int32_t ignore_nan_input;
+    float   normalization_term_fudge;
+    float   out_of_bounds_value;
+    uint32_t flags;
+} simnets_sim_desc;
+
+/* Output height/width: floor((in + 2*pad - block)/stride) + 1
+ * (include/utils/im2col.hpp:101-108 with round_down = true;
+ *  shape function SimilarityShape, src/ops/similarity_op.cpp:8-53).
+ * Also performs the constructor's attr validation
+ * (include/kernels/similarity_kernel_common.hpp:84-110). */
+SIMNETS_API int simnets_similarity_output_dims(const simnets_sim_desc* d, int32_t* out_h, int32_t* out_w);
+
+SIMNETS_API size_t simnets_similarity_workspace_bytes(const simnets_sim_desc* d);
+
+/* Similarity forward: y[batch, num_instances, out_h, out_w].
+ * Replaces SimilarityKernelGPU<T>::Compute (src/kernels/similarity_kernel_gpu.cu:24-133),
+ * oracle SimilarityKernelCPU<T>::Compute (src/kernels/similarity_kernel_cpu.cpp:19-122). */
+SIMNETS_API int simnets_similarity_forward(const simnets_sim_desc* d,
+                                           const void* x, const void* templates, const void* weights,
+                                           void* y, void* workspace, size_t workspace_bytes, void* stream);
+
+/* dL/dinput.  Replaces SimilarityInputGradKernelGPU (src/kernels/similarity_grad_kernel_gpu.cu:155-269),
+ * oracle SimilarityInputGradKernelCPU (src/kernels/similarity_grad_kernel_cpu.cpp:158-270). */
+SIMNETS_API int simnets_similarity_input_grad(const simnets_sim_desc* d,
+                                              const void* x, const void* templates, const void* weights,
+                                              const void* dy, void* dx,
+                                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* dL/dtemplates and dL/dweights, summed over batch and positions.
+ * Replaces SimilarityParametersGradKernelGPU (src/kernels/similarity_grad_kernel_gpu.cu:24-143),
+ * oracle SimilarityParametersGradKernelCPU (src/kernels/similarity_grad_kernel_cpu.cpp:23-146). */
+SIMNETS_API int simnets_similarity_params_grad(const simnets_sim_desc* d,
+                                               const void* x, const void* templates, const void* weights,
+                                               const void* dy, void* dtemplates, void* dweights,
+                                               void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- MEX ------------------------------------------------------------------ */
+/* Mirrors the attrs of the Mex op family (src/ops/mex_op.cpp:58-74).  padding and
+ * strides may hold -1 ("whole image dimension", src/kernels/mex_kernel_common.cpp:8-27);
+ * the region lists have length 1 ([d] means [-1, d, d]) or 3.
+ * offsets: [num_regions, num_instances, block_c, block_h, block_w]. */
+typedef struct simnets_mex_desc {
+    int32_t dtype;
+    int32_t batch, channels, height, width;
+    int32_t num_instances;
+    int32_t blocks[3];                  /* c, h, w */
+    int32_t strides[3];
+    int32_t padding[3];
+    float   epsilon;                    /* may be +inf / -inf */
+    int32_t softmax_mode;
+    float   blocks_out_of_bounds_value;
+    int32_t blocks_round_down;
+    int32_t use_unshared_regions;
+    int32_t shared_offset_region[3];
+    int32_t n_shared_offset_region;     /* 1 or 3 */
+    int32_t unshared_offset_region[3];
+    int32_t n_unshared_offset_region;   /* 1 or 3 */
+    uint32_t flags;
+} simnets_mex_desc;
+
+/* Everything MexDimensionsData::CalculateDimensions computes
+ * (src/kernels/mex_kernel_common.cpp:63-158, include/kernels/mex_kernel_common.hpp:11-58). */
+typedef struct simnets_mex_geometry {
+    int32_t block_c, block_h, block_w;
+    int32_t stride_c, stride_h, stride_w;
+    int32_t pad_c, pad_h, pad_w;
+    int32_t channels_out, height_out, width_out;
+    int32_t channels_out_total;         /* channels_out * num_instances */
+    int32_t region_c, region_h, region_w;     /* shared_offsets_region_*: extent of one region */
+    int32_t offsets_c, offsets_h, offsets_w;  /* number of regions along each axis */
+    int32_t num_regions, region_size;
+    int32_t M, K, N;
+    int32_t is_1x1;
+} simnets_mex_geometry;
+
+/* Host only.  Validates like MEXKernelCommon's constructor and
+ * CalculateDimensionsWithConext (src/kernels/mex_kernel_common.cpp:29-58,161-170). */
+SIMNETS_API int simnets_mex_dims(const simnets_mex_desc* d, simnets_mex_geometry* out);
+
+/* Host only.  Same symbol, argument order and return value (num_regions, or -1) as the
+ * reference's helper library libmex_dims_helper.so (src/kernels/mex_dims_helper.cpp:8-44),
+ * which python/simnets/ops/mex.py:17-38 calls through ctypes.  A padding / strides list of
+ * length 1 is broadcast to three entries (the reference reads past the end of such a list). */
+SIMNETS_API int get_mex_offsets_nregions(int n_input_dim, const int* input_dim,
+                                         int n_padding, const int* padding,
+                                         int n_strides, const int* strides,
+                                         int num_instances, int blocks_round_down, int use_unshared_regions,
+                                         int n_blocks, const int* blocks,
+                                         int n_shared_offset_region, const int* shared_offset_region,
+                                         int n_unshared_offset_region, const int* unshared_offset_region);
+
+SIMNETS_API size_t simnets_mex_workspace_bytes(const simnets_mex_desc* d);
+
+/* MEX forward: y[batch, num_instances * channels_out, height_out, width_out].
+ * Replaces MEXKernelGPU<T>::Compute (src/kernels/mex_kernel_gpu.cu:60-159),
+ * oracle MEXKernelCPU<T>::Compute + mex_forward_cpu (src/kernels/mex_kernel_cpu.cpp:11-38,60-159). */
+SIMNETS_API int simnets_mex_forward(const simnets_mex_desc* d,
+                                    const void* x, const void* offsets, void* y,
+                                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* dL/dinput.  Replaces MEXGradInputKernelGPU (src/kernels/mex_grad_kernel_gpu.cu:23-205),
+ * oracle MEXGradInputKernelCPU (src/kernels/mex_grad_kernel_cpu.cpp:23-209). */
+SIMNETS_API int simnets_mex_input_grad(const simnets_mex_desc* d,
+                                       const void* x, const void* offsets, const void* y, const void* dy,
+                                       void* dx, void* workspace, size_t workspace_bytes, void* stream);
+
+/* dL/doffsets, summed over batch and region positions.
+ * Replaces MEXGradOffsetsKernelGPU (src/kernels/mex_grad_kernel_gpu.cu:207-374),
+ * oracle MEXGradOffsetsKernelCPU (src/kernels/mex_grad_kernel_cpu.cpp:211-370). */
+SIMNETS_API int simnets_mex_offsets_grad(const simnets_mex_desc* d,
+                                         const void* x, const void* offsets, const void* y, const void* dy,
+                                         void* doffsets, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- misc ----------------------------------------------------------------- */
+SIMNETS_API const char* simnets_status_string(int status);
+/* Number of kernels this library has launched in this process (all devices). */
+SIMNETS_API uint64_t simnets_launch_count(void);
+/* ABI version of this header. */
+SIMNETS_API int simnets_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SIMNETS_B200_H */
