@@ -1,0 +1,189 @@
+// C ABI of the library (include/simnets_b200.h): validates descriptors, picks a kernel family and
+// enqueues it on the caller's stream.  No entry point here allocates, frees or synchronises.
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include "simnets_b200.h"
+#include "host_dims.hpp"
+#include "kernels.cuh"
+
+namespace simnets {
+static std::atomic<uint64_t> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(uint64_t(n), std::memory_order_relaxed); }
+}  // namespace simnets
+
+using namespace simnets;
+
+namespace {
+inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
+inline int from_cuda(cudaError_t e) { return e == cudaSuccess ? SIMNETS_OK : int(e); }
+}  // namespace
+
+extern "C" {
+
+int simnets_abi_version(void) { return 1; }
+uint64_t simnets_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* simnets_status_string(int status) {
+    switch (status) {
+    case SIMNETS_OK: return "ok";
+    case SIMNETS_E_NULL: return "a required pointer is NULL";
+    case SIMNETS_E_DESC: return "invalid descriptor (fails the operator's attribute / shape validation)";
+    case SIMNETS_E_DTYPE: return "dtype must be float32 (0) or float64 (1)";
+    case SIMNETS_E_WORKSPACE: return "workspace missing or smaller than the *_workspace_bytes query";
+    case SIMNETS_E_UNSUPPORTED: return "valid descriptor outside the supported index range";
+    case SIMNETS_E_TOO_LARGE: return "problem exceeds the fixed capacity of this entry point";
+    default: break;
+    }
+    if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
+    return "unknown status";
+}
+
+/* ------------------------------------------------------------- Similarity */
+int simnets_similarity_output_dims(const simnets_sim_desc* d, int32_t* out_h, int32_t* out_w) {
+    SimGeo g;
+    const int rc = sim_geometry(d, &g);
+    if (rc) return rc;
+    if (!out_h || !out_w) return SIMNETS_E_NULL;
+    *out_h = g.oh; *out_w = g.ow;
+    return SIMNETS_OK;
+}
+
+size_t simnets_similarity_workspace_bytes(const simnets_sim_desc* d) {
+    SimGeo g;
+    if (sim_geometry(d, &g)) return 0;
+    return sim_workspace_bytes(g, d->dtype == SIMNETS_F64, d->flags);
+}
+
+int simnets_similarity_forward(const simnets_sim_desc* d, const void* x, const void* t, const void* w, void* y,
+                               void* ws, size_t ws_bytes, void* stream) {
+    SimGeo g;
+    const int rc = sim_geometry(d, &g);
+    if (rc) return rc;
+    if (!x || !t || !w || !y) return SIMNETS_E_NULL;
+    const bool f64 = d->dtype == SIMNETS_F64;
+    if (sim_use_tiled(g, f64, d->flags)) {
+        if (!ws || ws_bytes < sim_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;
+        return from_cuda(launch_sim_fwd_tiled(g, (const float*)x, (const float*)t, (const float*)w, (float*)y, ws, as_stream(stream)));
+    }
+    return from_cuda(launch_sim_fwd_direct(g, f64, x, t, w, y, as_stream(stream)));
+}
+
+int simnets_similarity_input_grad(const simnets_sim_desc* d, const void* x, const void* t, const void* w, const void* dy,
+                                  void* dx, void* ws, size_t ws_bytes, void* stream) {
+    SimGeo g;
+    const int rc = sim_geometry(d, &g);
+    if (rc) return rc;
+    if (!x || !t || !w || !dy || !dx) return SIMNETS_E_NULL;
+    const bool f64 = d->dtype == SIMNETS_F64;
+    if (sim_use_tiled(g, f64, d->flags)) {
+        if (!ws || ws_bytes < sim_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;
+        return from_cuda(launch_sim_dx_tiled(g, (const float*)x, (const float*)t, (const float*)w, (const float*)dy, (float*)dx, ws, as_stream(stream)));
+    }
+    return from_cuda(launch_sim_dx_direct(g, f64, x, t, w, dy, dx, as_stream(stream)));
+}
+
+int simnets_similarity_params_grad(const simnets_sim_desc* d, const void* x, const void* t, const void* w, const void* dy,
+                                   void* dt, void* dw, void* ws, size_t ws_bytes, void* stream) {
+    SimGeo g;
+    const int rc = sim_geometry(d, &g);
+    if (rc) return rc;
+    if (!x || !t || !w || !dy || !dt || !dw) return SIMNETS_E_NULL;
+    const bool f64 = d->dtype == SIMNETS_F64;
+    const bool acc = (d->flags & SIMNETS_FLAG_ACCUMULATE) != 0;
+    if (sim_use_tiled(g, f64, d->flags)) {
+        if (!ws || ws_bytes < sim_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;
+        return from_cuda(launch_sim_dparams_tiled(g, (const float*)x, (const float*)t, (const float*)w, (const float*)dy,
+                                                  (float*)dt, (float*)dw, acc, ws, as_stream(stream)));
+    }
+    return from_cuda(launch_sim_dparams_direct(g, f64, x, t, w, dy, dt, dw, acc, as_stream(stream)));
+}
+
+/* -------------------------------------------------------------------- MEX */
+int simnets_mex_dims(const simnets_mex_desc* d, simnets_mex_geometry* out) {
+    if (!out) return SIMNETS_E_NULL;
+    return mex_geometry(d, out, nullptr);
+}
+
+int get_mex_offsets_nregions(int n_input_dim, const int* input_dim, int n_padding, const int* padding, int n_strides,
+                             const int* strides, int num_instances, int blocks_round_down, int use_unshared_regions,
+                             int n_blocks, const int* blocks, int n_shared, const int* shared, int n_unshared,
+                             const int* unshared) {
+    if (!input_dim || !padding || !strides || !blocks || !shared || !unshared) return -1;
+    if (n_input_dim != 3 || n_blocks != 3) return -1;
+    if ((n_shared != 1 && n_shared != 3) || (n_unshared != 1 && n_unshared != 3)) return -1;
+    simnets_mex_desc d = {};
+    d.dtype = SIMNETS_F32;
+    d.batch = 1; d.channels = input_dim[0]; d.height = input_dim[1]; d.width = input_dim[2];
+    d.num_instances = num_instances;
+    auto three = [](int n, const int* v, int32_t* dst) {
+        if (n == 1) { dst[0] = dst[1] = dst[2] = v[0]; return true; }          // broadcast
+        if (n == 2) { dst[0] = -1; dst[1] = v[0]; dst[2] = v[1]; return true; } // as ExpandDimSpec prepends -1
+        if (n == 3) { dst[0] = v[0]; dst[1] = v[1]; dst[2] = v[2]; return true; }
+        return false;
+    };
+    if (!three(n_padding, padding, d.padding) || !three(n_strides, strides, d.strides)) return -1;
+    for (int a = 0; a < 3; ++a) d.blocks[a] = blocks[a];
+    d.epsilon = 1.0f;
+    d.blocks_round_down = blocks_round_down > 0;
+    d.use_unshared_regions = use_unshared_regions > 0;
+    for (int a = 0; a < n_shared; ++a) d.shared_offset_region[a] = shared[a];
+    d.n_shared_offset_region = n_shared;
+    for (int a = 0; a < n_unshared; ++a) d.unshared_offset_region[a] = unshared[a];
+    d.n_unshared_offset_region = n_unshared;
+    simnets_mex_geometry g;
+    if (mex_geometry(&d, &g, nullptr)) return -1;
+    return g.num_regions;
+}
+
+size_t simnets_mex_workspace_bytes(const simnets_mex_desc* d) {
+    MexGeo g;
+    if (mex_geometry(d, nullptr, &g)) return 0;
+    return mex_workspace_bytes(g, d->dtype == SIMNETS_F64, d->flags);
+}
+
+int simnets_mex_forward(const simnets_mex_desc* d, const void* x, const void* off, void* y, void* ws, size_t ws_bytes, void* stream) {
+    MexGeo g;
+    const int rc = mex_geometry(d, nullptr, &g);
+    if (rc) return rc;
+    if (!x || !off || !y) return SIMNETS_E_NULL;
+    const bool f64 = d->dtype == SIMNETS_F64;
+    if (mex_use_tiled(g, f64, d->flags)) {
+        if (!ws || ws_bytes < mex_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;
+        return from_cuda(launch_mex_fwd_tiled(g, (const float*)x, (const float*)off, (float*)y, ws, d->flags, as_stream(stream)));
+    }
+    return from_cuda(launch_mex_fwd_direct(g, f64, x, off, y, as_stream(stream)));
+}
+
+int simnets_mex_input_grad(const simnets_mex_desc* d, const void* x, const void* off, const void* y, const void* dy, void* dx,
+                           void* ws, size_t ws_bytes, void* stream) {
+    MexGeo g;
+    const int rc = mex_geometry(d, nullptr, &g);
+    if (rc) return rc;
+    if (!x || !off || !y || !dy || !dx) return SIMNETS_E_NULL;
+    const bool f64 = d->dtype == SIMNETS_F64;
+    if (mex_use_tiled(g, f64, d->flags)) {
+        if (!ws || ws_bytes < mex_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;
+        return from_cuda(launch_mex_dx_tiled(g, (const float*)x, (const float*)off, (const float*)y, (const float*)dy, (float*)dx,
+                                             ws, d->flags, as_stream(stream)));
+    }
+    return from_cuda(launch_mex_dx_direct(g, f64, x, off, y, dy, dx, as_stream(stream)));
+}
+
+int simnets_mex_offsets_grad(const simnets_mex_desc* d, const void* x, const void* off, const void* y, const void* dy,
+                             void* doff, void* ws, size_t ws_bytes, void* stream) {
+    MexGeo g;
+    const int rc = mex_geometry(d, nullptr, &g);
+    if (rc) return rc;
+    if (!x || !off || !y || !dy || !doff) return SIMNETS_E_NULL;
+    const bool f64 = d->dtype == SIMNETS_F64;
+    const bool acc = (d->flags & SIMNETS_FLAG_ACCUMULATE) != 0;
+    if (mex_use_tiled(g, f64, d->flags)) {
+        if (!ws || ws_bytes < mex_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;
+        return from_cuda(launch_mex_doff_tiled(g, (const float*)x, (const float*)off, (const float*)y, (const float*)dy,
+                                               (float*)doff, acc, ws, d->flags, as_stream(stream)));
+    }
+    return from_cuda(launch_mex_doff_direct(g, f64, x, off, y, dy, doff, acc, as_stream(stream)));
+}
+
+}  // extern "C"

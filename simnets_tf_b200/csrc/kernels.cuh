@@ -1,0 +1,38 @@
+// Internal launch interface between the C ABI layer (api.cu) and the kernel translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include "geometry.cuh"
+
+namespace simnets {
+
+void count_launch(int n = 1);
+
+// direct_kernels.cu -- any shape, float32 and float64
+cudaError_t launch_sim_fwd_direct(const SimGeo&, bool f64, const void* x, const void* t, const void* w, void* y, cudaStream_t);
+cudaError_t launch_sim_dx_direct(const SimGeo&, bool f64, const void* x, const void* t, const void* w, const void* dy, void* dx, cudaStream_t);
+cudaError_t launch_sim_dparams_direct(const SimGeo&, bool f64, const void* x, const void* t, const void* w, const void* dy,
+                                      void* dt, void* dw, bool accumulate, cudaStream_t);
+cudaError_t launch_mex_fwd_direct(const MexGeo&, bool f64, const void* x, const void* off, void* y, cudaStream_t);
+cudaError_t launch_mex_dx_direct(const MexGeo&, bool f64, const void* x, const void* off, const void* y, const void* dy, void* dx, cudaStream_t);
+cudaError_t launch_mex_doff_direct(const MexGeo&, bool f64, const void* x, const void* off, const void* y, const void* dy,
+                                   void* doff, bool accumulate, cudaStream_t);
+
+}  // namespace simnets
+
+namespace simnets {
+// tiled_*.cu -- float32 generalized-GEMM tile kernels for the hot shapes
+bool sim_use_tiled(const SimGeo&, bool f64, uint32_t flags);
+size_t sim_workspace_bytes(const SimGeo&, bool f64, uint32_t flags);
+cudaError_t launch_sim_fwd_tiled(const SimGeo&, const float* x, const float* t, const float* w, float* y, void* ws, cudaStream_t);
+cudaError_t launch_sim_dx_tiled(const SimGeo&, const float* x, const float* t, const float* w, const float* dy, float* dx, void* ws, cudaStream_t);
+cudaError_t launch_sim_dparams_tiled(const SimGeo&, const float* x, const float* t, const float* w, const float* dy,
+                                     float* dt, float* dw, bool accumulate, void* ws, cudaStream_t);
+bool mex_use_tiled(const MexGeo&, bool f64, uint32_t flags);
+size_t mex_workspace_bytes(const MexGeo&, bool f64, uint32_t flags);
+cudaError_t launch_mex_fwd_tiled(const MexGeo&, const float* x, const float* off, float* y, void* ws, uint32_t flags, cudaStream_t);
+cudaError_t launch_mex_dx_tiled(const MexGeo&, const float* x, const float* off, const float* y, const float* dy, float* dx,
+                                void* ws, uint32_t flags, cudaStream_t);
+cudaError_t launch_mex_doff_tiled(const MexGeo&, const float* x, const float* off, const float* y, const float* dy, float* doff,
+                                  bool accumulate, void* ws, uint32_t flags, cudaStream_t);
+}  // namespace simnets

@@ -1,0 +1,170 @@
+"""`mex` and its gradient ops, with the signature of the reference's python wrapper
+(HUJI-Deep/simnets-tf python/simnets/ops/mex.py:114-195), its `_mex_dims_helper` (:17-38),
+`_expand_dim_specification` (:84-112) and the gradient wiring of `_mex_grad` (:47-81).
+"""
+import ctypes as C
+
+import torch
+
+from .. import _lib, abi
+from .._torch_glue import dtype_code, require_cuda, stream_ptr, workspace
+
+_DEFAULTS = dict(softmax_mode=False, padding=[0, 0, 0], strides=[1, 1, 1], blocks=[1, 1, 1], epsilon=1.0,
+                 blocks_out_of_bounds_value=0.0, blocks_round_down=True, use_unshared_regions=True,
+                 shared_offset_region=[-1], unshared_offset_region=[-1])
+
+
+def _attrs(**given):
+    """Op attrs with the op registration's defaults (reference src/ops/mex_op.cpp:58-74) for every None."""
+    out = dict(_DEFAULTS)
+    for k, v in given.items():
+        if v is not None:
+            out[k] = v
+    return out
+
+
+def _mex_dims_helper(input_dim, num_instances, blocks, padding=[0], strides=[1], blocks_round_down=True,
+                     use_unshared_regions=True, shared_offset_region=[-1], unshared_offset_region=[-1]):
+    """Number of offset regions for an input of shape `input_dim` = [C, H, W] (or -1 if invalid)."""
+    args = []
+
+    def add_array(l):
+        l = [int(e) for e in l]
+        args.extend([C.c_int(len(l)), (C.c_int * len(l))(*l)])
+
+    add_array(input_dim)
+    add_array(padding)
+    add_array(strides)
+    args.extend([C.c_int(num_instances), C.c_int(blocks_round_down), C.c_int(use_unshared_regions)])
+    add_array(blocks)
+    add_array(shared_offset_region)
+    add_array(unshared_offset_region)
+    return _lib.lib().get_mex_offsets_nregions(*args)
+
+
+def _expand_dim_specification(image_shape, dim_spec):
+    """Expand a 2- or 3-long dimension specification: prepend -1 to a pair, then replace every -1
+    with the corresponding image dimension (`image_shape` has 3 entries, or 4 with the batch)."""
+    if len(dim_spec) != 2 and len(dim_spec) != 3:
+        raise ValueError('Bad dimensions specifications, should be a list of two or three, got %s' % dim_spec)
+    image_shape = list(image_shape)
+    if len(image_shape) == 3:
+        image_shape = [None] + image_shape
+    dim_spec = list(dim_spec)
+    if len(dim_spec) == 2:
+        dim_spec = [-1] + dim_spec
+    for i in range(3):
+        if dim_spec[i] == -1:
+            dim_spec[i] = image_shape[i + 1]
+    return dim_spec
+
+
+def _desc(input, num_instances, attrs, flags=0):
+    if input.dim() != 4:
+        raise ValueError("input must be 4-D")
+    return abi.make_mex_desc(input.shape, num_instances, attrs["softmax_mode"], attrs["padding"], attrs["strides"],
+                             attrs["blocks"], attrs["epsilon"], attrs["blocks_out_of_bounds_value"], attrs["blocks_round_down"],
+                             attrs["use_unshared_regions"], attrs["shared_offset_region"], attrs["unshared_offset_region"],
+                             dtype=dtype_code(input), flags=flags)
+
+
+def _geometry(d):
+    g = abi.MexGeometry()
+    _lib.check(_lib.lib().simnets_mex_dims(C.byref(d), C.byref(g)))
+    return g
+
+
+def _check_offsets(offsets, g, num_instances):
+    want = (g.num_regions, num_instances, g.block_c, g.block_h, g.block_w)
+    if tuple(offsets.shape) != want:
+        raise ValueError("offsets must have shape %s, got %s" % (want, tuple(offsets.shape)))
+
+
+def _ws(d, dev):
+    n = _lib.lib().simnets_mex_workspace_bytes(C.byref(d))
+    buf = workspace(dev, n)
+    return buf.data_ptr(), buf.numel()
+
+
+def mex_forward(input, offsets, num_instances, flags=0, **attrs):
+    """The `Mex` op: [batch, num_instances * channels_out, height_out, width_out]."""
+    attrs = _attrs(**attrs)
+    dev = require_cuda(input, offsets)
+    input, offsets = input.contiguous(), offsets.contiguous()
+    d = _desc(input, num_instances, attrs, flags)
+    g = _geometry(d)
+    _check_offsets(offsets, g, num_instances)
+    y = torch.empty((input.shape[0], g.channels_out_total, g.height_out, g.width_out), dtype=input.dtype, device=dev)
+    with torch.cuda.device(dev):
+        ws, n = _ws(d, dev)
+        _lib.check(_lib.lib().simnets_mex_forward(C.byref(d), input.data_ptr(), offsets.data_ptr(), y.data_ptr(), ws, n, stream_ptr(dev)))
+    return y
+
+
+def mex_input_grad(input, offsets, orig_output, output_grad, num_instances, flags=0, **attrs):
+    """The `MexInputGrad` op."""
+    attrs = _attrs(**attrs)
+    dev = require_cuda(input, offsets, orig_output, output_grad)
+    input, offsets, y, dy = input.contiguous(), offsets.contiguous(), orig_output.contiguous(), output_grad.contiguous()
+    d = _desc(input, num_instances, attrs, flags)
+    _check_offsets(offsets, _geometry(d), num_instances)
+    dx = torch.empty_like(input)
+    with torch.cuda.device(dev):
+        ws, n = _ws(d, dev)
+        _lib.check(_lib.lib().simnets_mex_input_grad(C.byref(d), input.data_ptr(), offsets.data_ptr(), y.data_ptr(), dy.data_ptr(),
+                                                     dx.data_ptr(), ws, n, stream_ptr(dev)))
+    return dx
+
+
+def mex_offsets_grad(input, offsets, orig_output, output_grad, num_instances, flags=0, out=None, **attrs):
+    """The `MexOffsetsGrad` op.  `out` / FLAG_ACCUMULATE as in `similarity_parameters_grad`."""
+    attrs = _attrs(**attrs)
+    dev = require_cuda(input, offsets, orig_output, output_grad)
+    input, offsets, y, dy = input.contiguous(), offsets.contiguous(), orig_output.contiguous(), output_grad.contiguous()
+    d = _desc(input, num_instances, attrs, flags)
+    _check_offsets(offsets, _geometry(d), num_instances)
+    if out is None:
+        doff = torch.empty_like(offsets)
+    else:
+        doff = out
+        assert doff.is_contiguous() and doff.numel() == offsets.numel()
+    with torch.cuda.device(dev):
+        ws, n = _ws(d, dev)
+        _lib.check(_lib.lib().simnets_mex_offsets_grad(C.byref(d), input.data_ptr(), offsets.data_ptr(), y.data_ptr(), dy.data_ptr(),
+                                                       doff.data_ptr(), ws, n, stream_ptr(dev)))
+    return doff
+
+
+class _Mex(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, input, offsets, num_instances, attrs):
+        y = mex_forward(input, offsets, num_instances, **attrs)
+        ctx.attrs, ctx.num_instances = attrs, num_instances
+        ctx.save_for_backward(input, offsets, y)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad):
+        input, offsets, y = ctx.saved_tensors
+        gi = go = None
+        if ctx.needs_input_grad[0]:
+            gi = mex_input_grad(input, offsets, y, grad, ctx.num_instances, **ctx.attrs)
+        if ctx.needs_input_grad[1]:
+            go = mex_offsets_grad(input, offsets, y, grad, ctx.num_instances, **ctx.attrs)
+        return gi, go, None, None
+
+
+def mex(input, offsets, num_instances, softmax_mode=None, padding=None, strides=None, blocks=None, epsilon=None,
+        blocks_out_of_bounds_value=None, blocks_round_down=None, use_unshared_regions=None, shared_offset_region=None,
+        unshared_offset_region=None, name=None):
+    """Computes the MEX layer given a 4-D `input` and 5-D `offsets`
+    ([num_regions, num_instances, block_c, block_h, block_w]).
+
+    Same arguments, defaults and result as the reference's `simnets.ops.mex.mex`; `name` is accepted
+    and ignored.  Differentiable w.r.t. `input` and `offsets`.
+    """
+    attrs = _attrs(softmax_mode=softmax_mode, padding=padding, strides=strides, blocks=blocks, epsilon=epsilon,
+                   blocks_out_of_bounds_value=blocks_out_of_bounds_value, blocks_round_down=blocks_round_down,
+                   use_unshared_regions=use_unshared_regions, shared_offset_region=shared_offset_region,
+                   unshared_offset_region=unshared_offset_region)
+    return _Mex.apply(input, offsets, num_instances, attrs)

@@ -1,0 +1,121 @@
+"""GPU parity of the MEX op family against the CPU oracle, through the C ABI."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+import gpu_util
+from simnets_tf_b200 import abi
+from simnets_tf_b200.ops import mex as mex_ops
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("c", cases.MEX_SMALL, ids=lambda c: c["name"])
+def test_small_grid(port, c):
+    gpu_util.check_mex(port, c, f64_tiebreak=True)
+
+
+@pytest.mark.parametrize("c", cases.MEX_SMALL, ids=lambda c: c["name"])
+def test_small_grid_direct_kernels(port, c):
+    gpu_util.check_mex(port, c, flags=abi.FLAG_FORCE_DIRECT, f64_tiebreak=True)
+
+
+@pytest.mark.parametrize("c", cases.MEX_SMALL, ids=lambda c: c["name"])
+def test_small_grid_exact_evaluation(port, c):
+    gpu_util.check_mex(port, c, flags=abi.FLAG_MEX_EXACT, f64_tiebreak=True)
+
+
+@pytest.mark.parametrize("c", cases.MEX_SMALL[::3], ids=lambda c: c["name"])
+def test_small_grid_float64(port, c):
+    gpu_util.check_mex(port, c, dtype=abi.F64, tol=1e-12)
+
+
+@pytest.mark.parametrize("c", cases.MEX_CONFIGS, ids=lambda c: c["name"])
+def test_baseline_configs(port, c):
+    errs = gpu_util.check_mex(port, c, f64_tiebreak=True)
+    print(c["name"], errs)
+
+
+def test_golden_vectors(cuda_lib):
+    """The committed vectors were produced by the reference project's own CPU templates."""
+    golden = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "mex_small.npz"))
+    by_name = {c["name"]: c for c in cases.MEX_SMALL}
+    for name in sorted({k.split("/")[0] for k in golden.files}):
+        c = by_name[name]
+        g = {k: golden["%s/%s" % (name, k)] for k in ("x", "off", "dy", "y", "dx", "doff")}
+        xd, od, dyd, yd = (gpu_util.dev(g[k]) for k in ("x", "off", "dy", "y"))
+        attrs = cases.mex_attrs(c)
+        cases.assert_parity(mex_ops.mex_forward(xd, od, c["M"], **attrs).cpu().numpy(), g["y"], what=name + " y")
+        cases.assert_parity(mex_ops.mex_input_grad(xd, od, yd, dyd, c["M"], **attrs).cpu().numpy(), g["dx"], what=name + " dx")
+        cases.assert_parity(mex_ops.mex_offsets_grad(xd, od, yd, dyd, c["M"], **attrs).cpu().numpy(), g["doff"], tol=2e-5, what=name + " doff")
+
+
+def test_autograd_wiring_matches_grad_ops(port):
+    """`mex(...)` is differentiable and its backward is the two grad ops (reference ops/mex.py:47-81)."""
+    c = next(c for c in cases.MEX_SMALL if c["name"] == "blocks_bug")
+    d = cases.mex_desc(c)
+    x, off, dy = cases.mex_inputs(c, port.mex_offsets_shape(d), port.mex_out_shape(d))
+    xd, od = (gpu_util.dev(a).requires_grad_(True) for a in (x, off))
+    y = mex_ops.mex(xd, od, c["M"], **cases.mex_attrs(c))
+    y.backward(gpu_util.dev(dy))
+    ry = port.mex_forward(d, x, off)
+    cases.assert_parity(xd.grad.cpu().numpy(), port.mex_input_grad(d, x, off, ry, dy), tol=2e-5, what="dx")
+    cases.assert_parity(od.grad.cpu().numpy(), port.mex_offsets_grad(d, x, off, ry, dy), tol=2e-5, what="doff")
+
+
+def test_wide_dynamic_range_takes_the_exact_route(port):
+    """Offsets and inputs spanning hundreds of units (and -inf entries) would underflow a factorised
+    evaluation; results must still match the oracle, whichever route the library picks."""
+    c = cases.mex_case("range", (2, 6, 6, 6), 5, (6, 1, 1), (6, 1, 1), softmax=True, unshared_region=(2,), seed=77)
+    d = cases.mex_desc(c)
+    x, off, dy = cases.mex_inputs(c, port.mex_offsets_shape(d), port.mex_out_shape(d))
+    x = (x * 150).astype(np.float32)
+    off = (off * 150).astype(np.float32)
+    off[0, 0, 0] = -np.inf
+    x[0, 1, 2, 2] = -np.inf
+    xd, od, dyd = (gpu_util.dev(a) for a in (x, off, dy))
+    ry = port.mex_forward(d, x, off)
+    attrs = cases.mex_attrs(c)
+    cases.assert_parity(mex_ops.mex_forward(xd, od, c["M"], **attrs).cpu().numpy(), ry, what="y")
+    ryd = gpu_util.dev(ry)
+    cases.assert_parity(mex_ops.mex_input_grad(xd, od, ryd, dyd, c["M"], **attrs).cpu().numpy(),
+                        port.mex_input_grad(d, x, off, ry, dy), what="dx")
+    cases.assert_parity(mex_ops.mex_offsets_grad(xd, od, ryd, dyd, c["M"], **attrs).cpu().numpy(),
+                        port.mex_offsets_grad(d, x, off, ry, dy), what="doff")
+
+
+def test_full_size_properties():
+    """Config-4 MEX at full output size (4 GiB): properties that need no oracle.
+    (1) with all offsets equal to a constant a and softmax_mode, y = a + logsumexp_eps(block), checked
+    against torch on a slice; (2) a sample's output does not depend on its batch neighbours;
+    (3) per-block softmax weights sum to one, so sum over taps of dx equals sum of dy per block."""
+    torch.manual_seed(0)
+    B, C, H, M = 256, 256, 32, 256
+    x = torch.randn(B, C, H, H, device="cuda")
+    attrs = dict(softmax_mode=True, blocks=[4, 2, 2], strides=[4, 2, 2], epsilon=0.5, use_unshared_regions=False,
+                 shared_offset_region=[-1])
+    off = torch.full((1, M, 4, 2, 2), 0.25, device="cuda")
+    y = mex_ops.mex_forward(x, off, M, **attrs)
+    assert y.shape == (B, M * 64, 16, 16)
+    blocks = x[:2].reshape(2, 64, 4, 16, 2, 16, 2).permute(0, 1, 3, 5, 2, 4, 6).reshape(2, 64, 16, 16, 16)
+    want = 0.25 + torch.logsumexp(0.5 * blocks.double(), dim=-1) / 0.5
+    got = y[:2].reshape(2, M, 64, 16, 16)
+    assert cases.rel_err(got[:, 0].cpu().numpy(), want.cpu().numpy()) < 1e-5
+    assert cases.rel_err(got[:, M - 1].cpu().numpy(), want.cpu().numpy()) < 1e-5
+    del got, want, blocks
+    y_tail = mex_ops.mex_forward(x[B - 2:], off, M, **attrs)
+    assert torch.equal(y[B - 2:], y_tail)
+    del y_tail
+    nb = 8
+    off2 = 0.1 * torch.randn(1, M, 4, 2, 2, device="cuda")
+    y2 = mex_ops.mex_forward(x[:nb], off2, M, **attrs)
+    dy = torch.randn_like(y2)
+    dx = mex_ops.mex_input_grad(x[:nb], off2, y2, dy, M, **attrs)
+    per_block_dx = dx.reshape(nb, 64, 4, 16, 2, 16, 2).sum(dim=(2, 4, 6))
+    per_block_dy = dy.reshape(nb, M, 64, 16, 16).sum(dim=1)
+    assert cases.rel_err(per_block_dx.cpu().numpy(), per_block_dy.cpu().numpy()) < 1e-4
+    doff = mex_ops.mex_offsets_grad(x[:nb], off2, y2, dy, M, **attrs)
+    assert cases.rel_err(doff.sum(dim=(2, 3, 4)).flatten().cpu().numpy(), dy.reshape(nb, M, -1).sum(dim=(0, 2)).cpu().numpy()) < 1e-4
