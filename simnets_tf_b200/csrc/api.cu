@@ -60,7 +60,7 @@ int simnets_similarity_forward(const simnets_sim_desc* d, const void* x, const v
     SimGeo g;
     const int rc = sim_geometry(d, &g);
     if (rc) return rc;
-    if (!x || !t || !w || !y) return SIMNETS_E_NULL;
+    if (!t || !w || (g.B > 0 && (!x || !y))) return SIMNETS_E_NULL;   // batch-sized tensors may be NULL when batch == 0
     const bool f64 = d->dtype == SIMNETS_F64;
     if (sim_use_tiled(g, f64, d->flags)) {
         if (!ws || ws_bytes < sim_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;
@@ -74,7 +74,7 @@ int simnets_similarity_input_grad(const simnets_sim_desc* d, const void* x, cons
     SimGeo g;
     const int rc = sim_geometry(d, &g);
     if (rc) return rc;
-    if (!x || !t || !w || !dy || !dx) return SIMNETS_E_NULL;
+    if (!t || !w || (g.B > 0 && (!x || !dy || !dx))) return SIMNETS_E_NULL;
     const bool f64 = d->dtype == SIMNETS_F64;
     if (sim_use_tiled(g, f64, d->flags)) {
         if (!ws || ws_bytes < sim_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;
@@ -88,7 +88,7 @@ int simnets_similarity_params_grad(const simnets_sim_desc* d, const void* x, con
     SimGeo g;
     const int rc = sim_geometry(d, &g);
     if (rc) return rc;
-    if (!x || !t || !w || !dy || !dt || !dw) return SIMNETS_E_NULL;
+    if (!t || !w || !dt || !dw || (g.B > 0 && (!x || !dy))) return SIMNETS_E_NULL;
     const bool f64 = d->dtype == SIMNETS_F64;
     const bool acc = (d->flags & SIMNETS_FLAG_ACCUMULATE) != 0;
     if (sim_use_tiled(g, f64, d->flags)) {
@@ -146,7 +146,7 @@ int simnets_mex_forward(const simnets_mex_desc* d, const void* x, const void* of
     MexGeo g;
     const int rc = mex_geometry(d, nullptr, &g);
     if (rc) return rc;
-    if (!x || !off || !y) return SIMNETS_E_NULL;
+    if (!off || (g.B > 0 && (!x || !y))) return SIMNETS_E_NULL;
     const bool f64 = d->dtype == SIMNETS_F64;
     if (mex_use_tiled(g, f64, d->flags)) {
         if (!ws || ws_bytes < mex_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;
@@ -160,7 +160,7 @@ int simnets_mex_input_grad(const simnets_mex_desc* d, const void* x, const void*
     MexGeo g;
     const int rc = mex_geometry(d, nullptr, &g);
     if (rc) return rc;
-    if (!x || !off || !y || !dy || !dx) return SIMNETS_E_NULL;
+    if (!off || (g.B > 0 && (!x || !y || !dy || !dx))) return SIMNETS_E_NULL;
     const bool f64 = d->dtype == SIMNETS_F64;
     if (mex_use_tiled(g, f64, d->flags)) {
         if (!ws || ws_bytes < mex_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;
@@ -175,7 +175,7 @@ int simnets_mex_offsets_grad(const simnets_mex_desc* d, const void* x, const voi
     MexGeo g;
     const int rc = mex_geometry(d, nullptr, &g);
     if (rc) return rc;
-    if (!x || !off || !y || !dy || !doff) return SIMNETS_E_NULL;
+    if (!off || !doff || (g.B > 0 && (!x || !y || !dy))) return SIMNETS_E_NULL;
     const bool f64 = d->dtype == SIMNETS_F64;
     const bool acc = (d->flags & SIMNETS_FLAG_ACCUMULATE) != 0;
     if (mex_use_tiled(g, f64, d->flags)) {

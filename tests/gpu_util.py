@@ -1,12 +1,14 @@
 """Helpers of the GPU parity tests: run one op family through the torch-facing wrappers (which call
 the C ABI) and compare every output with the CPU oracle under the acceptance rule of cases.py."""
+import importlib
+
 import numpy as np
 import torch
 
 import cases
 from simnets_tf_b200 import abi
-from simnets_tf_b200.ops import mex as mex_ops
-from simnets_tf_b200.ops import similarity as sim_ops
+mex_ops = importlib.import_module("simnets_tf_b200.ops.mex")
+sim_ops = importlib.import_module("simnets_tf_b200.ops.similarity")
 
 
 def dev(a, dtype=torch.float32):

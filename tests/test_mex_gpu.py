@@ -1,6 +1,8 @@
 """GPU parity of the MEX op family against the CPU oracle, through the C ABI."""
 import os
 
+import importlib
+
 import numpy as np
 import pytest
 import torch
@@ -8,7 +10,7 @@ import torch
 import cases
 import gpu_util
 from simnets_tf_b200 import abi
-from simnets_tf_b200.ops import mex as mex_ops
+mex_ops = importlib.import_module("simnets_tf_b200.ops.mex")
 
 pytestmark = pytest.mark.gpu
 

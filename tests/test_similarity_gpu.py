@@ -1,6 +1,8 @@
 """GPU parity of the Similarity op family against the CPU oracle, through the C ABI."""
 import os
 
+import importlib
+
 import numpy as np
 import pytest
 import torch
@@ -8,7 +10,7 @@ import torch
 import cases
 import gpu_util
 from simnets_tf_b200 import abi
-from simnets_tf_b200.ops import similarity as sim_ops
+sim_ops = importlib.import_module("simnets_tf_b200.ops.similarity")
 
 pytestmark = pytest.mark.gpu
 
