@@ -39,3 +39,49 @@ def workspace(dev, nbytes):
         buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)
         _WORKSPACES[key] = buf
     return buf
+
+
+class OpProfile(object):
+    """Optional per-op device timing: when enabled, every operator call is bracketed by CUDA events on
+    the stream it launches on, together with the algorithmic bytes and term count of that call."""
+
+    def __init__(self):
+        self.enabled = False
+        self.rows = {}
+
+    def start(self):
+        self.enabled, self.rows = True, {}
+
+    def stop(self):
+        """Stop recording and return {key: dict(calls, ms, bytes, terms)} (synchronises)."""
+        self.enabled = False
+        torch.cuda.synchronize()
+        out = {}
+        for key, recs in self.rows.items():
+            out[key] = dict(calls=len(recs), ms=sum(s.elapsed_time(e) for s, e, _, _ in recs),
+                            bytes=sum(r[2] for r in recs), terms=sum(r[3] for r in recs))
+        self.rows = {}
+        return out
+
+
+PROFILE = OpProfile()
+
+
+class timed(object):
+    """`with timed(op, signature, algorithmic_bytes, terms):` around one C-ABI call."""
+
+    def __init__(self, op, sig, nbytes, terms):
+        self.key, self.nbytes, self.terms = "%s[%s]" % (op, sig), nbytes, terms
+
+    def __enter__(self):
+        if PROFILE.enabled:
+            self.s = torch.cuda.Event(enable_timing=True)
+            self.e = torch.cuda.Event(enable_timing=True)
+            self.s.record()
+        return self
+
+    def __exit__(self, *exc):
+        if PROFILE.enabled and exc[0] is None:
+            self.e.record()
+            PROFILE.rows.setdefault(self.key, []).append((self.s, self.e, self.nbytes, self.terms))
+        return False

@@ -1,0 +1,186 @@
+"""Layer classes with the constructor arguments, attribute handling and `get_config` keys of the
+reference's Keras layers (HUJI-Deep/simnets-tf python/simnets/keras.py:19-188).
+
+Keras and TensorFlow are not part of this stack; the layers are `torch.nn.Module`s that create their
+variables on first call (the counterpart of Keras' `build(input_shape)`) and run the CUDA operators.
+`perform_unsupervised_init` (k-means / GMM / PCA initialisation, pure TensorFlow graph code in the
+reference) is outside this library.
+"""
+import math
+
+import numpy as np
+import torch
+
+from .ops.mex import _expand_dim_specification, _mex_dims_helper
+from .ops.mex import mex as _mex
+from .ops.similarity import similarity as _similarity
+
+
+def _init_tensor(spec, shape, device, dtype, generator=None):
+    """Keras initializer names the reference's layers use ('random_normal' = N(0, 0.05), 'ones', 'zeros')
+    or a callable `(shape, dtype) -> array-like`."""
+    if callable(spec):
+        return torch.as_tensor(np.asarray(spec(shape, dtype=None)), dtype=dtype).to(device)
+    name = str(spec).lower()
+    if name == "ones":
+        return torch.ones(shape, dtype=dtype, device=device)
+    if name == "zeros":
+        return torch.zeros(shape, dtype=dtype, device=device)
+    if name == "random_normal":
+        return (0.05 * torch.randn(shape, dtype=dtype, device="cpu", generator=generator)).to(device)
+    raise ValueError("unknown initializer %r" % (spec,))
+
+
+class Similarity(torch.nn.Module):
+    """Similarity layer; `weights` enter the op as their absolute value, as in the reference's `call`."""
+
+    def __init__(self, num_instances=None, similarity_function='L2', strides=[1, 1], blocks=[3, 3], padding='SAME',
+                 normalization_term=False, normalization_term_fudge=0.001, ignore_nan_input=False,
+                 out_of_bounds_value=0, templates_initializer='random_normal', weights_initializer='ones',
+                 channels_last=False, **kwargs):
+        super(Similarity, self).__init__()
+        assert num_instances is not None
+        self.num_instances = num_instances
+        self.similarity_function = similarity_function
+        self.strides = list(strides)
+        self.blocks = list(blocks)
+        if isinstance(padding, str):
+            if padding.upper() not in ['SAME', 'VALID']:
+                raise ValueError('Padding must be one of SAME, VALID (or a list of ints)')
+            self.padding = [0, 0] if padding.upper() == 'VALID' else [e // 2 for e in blocks]
+        else:
+            self.padding = list(padding)
+        self.normalization_term = normalization_term
+        self.normalization_term_fudge = normalization_term_fudge
+        self.ignore_nan_input = ignore_nan_input
+        self.out_of_bounds_value = out_of_bounds_value
+        self.templates_initializer = templates_initializer
+        self.weights_initializer = weights_initializer
+        self.channels_last = channels_last
+        self.generator = kwargs.pop("generator", None)
+        self.sweights = None
+        self.templates = None
+
+    def build(self, input_shape, device=None, dtype=torch.float32):
+        num_channels = input_shape[3] if self.channels_last else input_shape[1]
+        shape = (self.num_instances, num_channels, self.blocks[0], self.blocks[1])
+        self.sweights = torch.nn.Parameter(_init_tensor(self.weights_initializer, shape, device, dtype, self.generator))
+        self.templates = torch.nn.Parameter(_init_tensor(self.templates_initializer, shape, device, dtype, self.generator))
+
+    def forward(self, x):
+        if self.templates is None:
+            self.build(tuple(x.shape), x.device, x.dtype)
+        if self.channels_last:
+            x = x.permute(0, 3, 1, 2)
+        y = _similarity(x, self.templates, torch.abs(self.sweights), similarity_function=self.similarity_function,
+                        blocks=self.blocks, strides=self.strides, padding=self.padding,
+                        normalization_term=self.normalization_term,
+                        normalization_term_fudge=self.normalization_term_fudge,
+                        ignore_nan_input=self.ignore_nan_input, out_of_bounds_value=self.out_of_bounds_value)
+        return y.permute(0, 2, 3, 1) if self.channels_last else y
+
+    def get_config(self):
+        names = ['num_instances', 'similarity_function', 'strides', 'blocks', 'padding', 'normalization_term',
+                 'normalization_term_fudge', 'ignore_nan_input', 'out_of_bounds_value', 'templates_initializer',
+                 'weights_initializer', 'channels_last']
+        return {k: getattr(self, k) for k in names}
+
+
+class DirichletInit(object):
+    """log of Dirichlet(alpha) samples over each (region, instance) block."""
+
+    def __init__(self, alpha=1.0, seed=None):
+        self.alpha = alpha
+        self.rng = np.random.default_rng(seed)
+
+    def __call__(self, shape, dtype=None):
+        num_regions, num_instances, block_c, block_h, block_w = shape
+        k = block_c * block_h * block_w
+        init = self.rng.dirichlet([self.alpha] * k, size=(num_regions, num_instances))
+        with np.errstate(divide="ignore"):
+            init = np.log(init)
+        return init.reshape(shape).astype(np.float32 if dtype is None else dtype)
+
+    def get_config(self):
+        return {'alpha': self.alpha}
+
+
+dirichlet_init = DirichletInit
+
+
+class Mex(torch.nn.Module):
+    """MEX layer; `normalize_offsets` subtracts a per-(region, instance) logsumexp from the offsets variable."""
+
+    def __init__(self, num_instances=None, padding=[0, 0, 0], strides=[1, 1, 1], blocks=[1, 1, 1],
+                 epsilon=1.0, use_unshared_regions=True, shared_offset_region=[-1],
+                 unshared_offset_region=[-1], softmax_mode=False, blocks_out_of_bounds_value=0.0,
+                 blocks_round_down=True, normalize_offsets=False, offsets_initializer=None,
+                 channels_last=False, **kwargs):
+        super(Mex, self).__init__()
+        assert num_instances is not None
+        self.num_instances = num_instances
+        self.padding = padding
+        self.strides = list(strides)
+        self.blocks = list(blocks)
+        self.epsilon = epsilon
+        self.use_unshared_regions = use_unshared_regions
+        self.shared_offset_region = list(shared_offset_region)
+        self.unshared_offset_region = list(unshared_offset_region)
+        self.softmax_mode = softmax_mode
+        self.blocks_out_of_bounds_value = blocks_out_of_bounds_value
+        self.blocks_round_down = blocks_round_down
+        self.normalize_offsets = normalize_offsets
+        if offsets_initializer is None or (isinstance(offsets_initializer, str) and offsets_initializer == 'dirichlet'):
+            offsets_initializer = dirichlet_init()
+        self.offsets_initializer = offsets_initializer
+        self.channels_last = channels_last
+        self.offsets = None
+
+    def build(self, input_shape, device=None, dtype=torch.float32):
+        input_shape = list(input_shape)
+        if self.channels_last:
+            input_shape = [input_shape[0], input_shape[3], input_shape[1], input_shape[2]]
+        self.blocks = _expand_dim_specification(input_shape, self.blocks)
+        if isinstance(self.padding, str):
+            if self.padding.upper() not in ['SAME', 'VALID']:
+                raise ValueError('Padding must be one of SAME, VALID (or a list of ints)')
+            self.padding = [0, 0, 0] if self.padding.upper() == 'VALID' else [e // 2 for e in self.blocks]
+        nregions = _mex_dims_helper(input_shape[1:], self.num_instances, blocks=self.blocks, padding=self.padding,
+                                    strides=self.strides, use_unshared_regions=self.use_unshared_regions,
+                                    shared_offset_region=self.shared_offset_region,
+                                    blocks_round_down=self.blocks_round_down,
+                                    unshared_offset_region=self.unshared_offset_region)
+        if nregions < 0:
+            raise ValueError("invalid MEX geometry for input shape %s" % (input_shape,))
+        shape = (nregions, self.num_instances) + tuple(self.blocks)
+        self.offsets = torch.nn.Parameter(_init_tensor(self.offsets_initializer, shape, device, dtype))
+
+    def effective_offsets(self):
+        if not self.normalize_offsets:
+            return self.offsets
+        flat = self.offsets.reshape(self.offsets.shape[0] * self.offsets.shape[1], -1)
+        return (flat - torch.logsumexp(flat, dim=1, keepdim=True)).reshape(self.offsets.shape)
+
+    def forward(self, x):
+        if self.offsets is None:
+            self.build(tuple(x.shape), x.device, x.dtype)
+        if self.channels_last:
+            x = x.permute(0, 3, 1, 2)
+        y = _mex(x, self.effective_offsets(), self.num_instances, blocks=self.blocks, padding=self.padding,
+                 strides=self.strides, use_unshared_regions=self.use_unshared_regions,
+                 shared_offset_region=self.shared_offset_region,
+                 blocks_out_of_bounds_value=self.blocks_out_of_bounds_value,
+                 blocks_round_down=self.blocks_round_down,
+                 unshared_offset_region=self.unshared_offset_region,
+                 epsilon=self.epsilon, softmax_mode=self.softmax_mode)
+        return y.permute(0, 2, 3, 1) if self.channels_last else y
+
+    def get_config(self):
+        names = ['num_instances', 'padding', 'strides', 'blocks', 'epsilon', 'use_unshared_regions', 'shared_offset_region',
+                 'unshared_offset_region', 'softmax_mode', 'blocks_out_of_bounds_value', 'blocks_round_down',
+                 'normalize_offsets', 'offsets_initializer', 'channels_last']
+        return {k: getattr(self, k) for k in names}
+
+
+def perform_unsupervised_init(model, kind='gmm', layers=[], data=None, batch_size=None):
+    raise NotImplementedError("unsupervised (k-means / GMM / PCA) initialisation is not part of the B200 operator library")

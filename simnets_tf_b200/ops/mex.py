@@ -7,7 +7,7 @@ import ctypes as C
 import torch
 
 from .. import _lib, abi
-from .._torch_glue import dtype_code, require_cuda, stream_ptr, workspace
+from .._torch_glue import dtype_code, require_cuda, stream_ptr, timed, workspace
 
 _DEFAULTS = dict(softmax_mode=False, padding=[0, 0, 0], strides=[1, 1, 1], blocks=[1, 1, 1], epsilon=1.0,
                  blocks_out_of_bounds_value=0.0, blocks_round_down=True, use_unshared_regions=True,
@@ -80,6 +80,15 @@ def _check_offsets(offsets, g, num_instances):
         raise ValueError("offsets must have shape %s, got %s" % (want, tuple(offsets.shape)))
 
 
+def _cost(d, g, kind):
+    """(signature, algorithmic bytes, terms) of one call: bytes = every input read once + every output written once."""
+    x, o, y = d.batch * d.channels * d.height * d.width, g.num_regions * g.M * g.K, d.batch * g.M * g.N
+    e = 4 if d.dtype == abi.F32 else 8
+    nbytes = {"fwd": x + o + y, "dx": 2 * x + o + 2 * y, "doff": x + 2 * o + 2 * y}[kind] * e
+    sig = "B%d C%d %dx%d M%d K%d N%d R%d" % (d.batch, d.channels, d.height, d.width, g.M, g.K, g.N, g.num_regions)
+    return sig, nbytes, y * g.K
+
+
 def _ws(d, dev):
     n = _lib.lib().simnets_mex_workspace_bytes(C.byref(d))
     buf = workspace(dev, n)
@@ -97,7 +106,8 @@ def mex_forward(input, offsets, num_instances, flags=0, **attrs):
     y = torch.empty((input.shape[0], g.channels_out_total, g.height_out, g.width_out), dtype=input.dtype, device=dev)
     with torch.cuda.device(dev):
         ws, n = _ws(d, dev)
-        _lib.check(_lib.lib().simnets_mex_forward(C.byref(d), input.data_ptr(), offsets.data_ptr(), y.data_ptr(), ws, n, stream_ptr(dev)))
+        with timed("mex_forward", *_cost(d, g, "fwd")):
+            _lib.check(_lib.lib().simnets_mex_forward(C.byref(d), input.data_ptr(), offsets.data_ptr(), y.data_ptr(), ws, n, stream_ptr(dev)))
     return y
 
 
@@ -107,12 +117,14 @@ def mex_input_grad(input, offsets, orig_output, output_grad, num_instances, flag
     dev = require_cuda(input, offsets, orig_output, output_grad)
     input, offsets, y, dy = input.contiguous(), offsets.contiguous(), orig_output.contiguous(), output_grad.contiguous()
     d = _desc(input, num_instances, attrs, flags)
-    _check_offsets(offsets, _geometry(d), num_instances)
+    g = _geometry(d)
+    _check_offsets(offsets, g, num_instances)
     dx = torch.empty_like(input)
     with torch.cuda.device(dev):
         ws, n = _ws(d, dev)
-        _lib.check(_lib.lib().simnets_mex_input_grad(C.byref(d), input.data_ptr(), offsets.data_ptr(), y.data_ptr(), dy.data_ptr(),
-                                                     dx.data_ptr(), ws, n, stream_ptr(dev)))
+        with timed("mex_input_grad", *_cost(d, g, "dx")):
+            _lib.check(_lib.lib().simnets_mex_input_grad(C.byref(d), input.data_ptr(), offsets.data_ptr(), y.data_ptr(), dy.data_ptr(),
+                                                         dx.data_ptr(), ws, n, stream_ptr(dev)))
     return dx
 
 
@@ -122,7 +134,8 @@ def mex_offsets_grad(input, offsets, orig_output, output_grad, num_instances, fl
     dev = require_cuda(input, offsets, orig_output, output_grad)
     input, offsets, y, dy = input.contiguous(), offsets.contiguous(), orig_output.contiguous(), output_grad.contiguous()
     d = _desc(input, num_instances, attrs, flags)
-    _check_offsets(offsets, _geometry(d), num_instances)
+    g = _geometry(d)
+    _check_offsets(offsets, g, num_instances)
     if out is None:
         doff = torch.empty_like(offsets)
     else:
@@ -130,8 +143,9 @@ def mex_offsets_grad(input, offsets, orig_output, output_grad, num_instances, fl
         assert doff.is_contiguous() and doff.numel() == offsets.numel()
     with torch.cuda.device(dev):
         ws, n = _ws(d, dev)
-        _lib.check(_lib.lib().simnets_mex_offsets_grad(C.byref(d), input.data_ptr(), offsets.data_ptr(), y.data_ptr(), dy.data_ptr(),
-                                                       doff.data_ptr(), ws, n, stream_ptr(dev)))
+        with timed("mex_offsets_grad", *_cost(d, g, "doff")):
+            _lib.check(_lib.lib().simnets_mex_offsets_grad(C.byref(d), input.data_ptr(), offsets.data_ptr(), y.data_ptr(), dy.data_ptr(),
+                                                           doff.data_ptr(), ws, n, stream_ptr(dev)))
     return doff
 
 

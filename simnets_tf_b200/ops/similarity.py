@@ -8,7 +8,7 @@ import ctypes as C
 import torch
 
 from .. import _lib, abi
-from .._torch_glue import dtype_code, require_cuda, stream_ptr, workspace
+from .._torch_glue import dtype_code, require_cuda, stream_ptr, timed, workspace
 
 _DEFAULTS = dict(similarity_function="L2", blocks=[3, 3], strides=[2, 2], padding=[0, 0], normalization_term=False,
                  normalization_term_fudge=0.001, ignore_nan_input=False, out_of_bounds_value=0.0)
@@ -38,6 +38,15 @@ def _desc(input, templates, weights, attrs, flags=0):
                              attrs["ignore_nan_input"], attrs["out_of_bounds_value"], dtype=dtype_code(input), flags=flags)
 
 
+def _cost(d, y_numel, kind):
+    """(signature, algorithmic bytes, terms) of one call: bytes = every input read once + every output written once."""
+    k = d.channels * d.block_h * d.block_w
+    x, p, e = d.batch * d.channels * d.height * d.width, d.num_instances * k, 4 if d.dtype == abi.F32 else 8
+    nbytes = {"fwd": x + 2 * p + y_numel, "dx": 2 * x + 2 * p + y_numel, "dp": x + y_numel + 4 * p}[kind] * e
+    sig = "B%d C%d %dx%d M%d K%d" % (d.batch, d.channels, d.height, d.width, d.num_instances, k)
+    return sig, nbytes, y_numel * k
+
+
 def _ws(d, dev):
     n = _lib.lib().simnets_similarity_workspace_bytes(C.byref(d))
     buf = workspace(dev, n)
@@ -55,8 +64,9 @@ def similarity_forward(input, templates, weights, flags=0, **attrs):
     y = torch.empty((input.shape[0], templates.shape[0], oh.value, ow.value), dtype=input.dtype, device=dev)
     with torch.cuda.device(dev):
         ws, n = _ws(d, dev)
-        _lib.check(_lib.lib().simnets_similarity_forward(C.byref(d), input.data_ptr(), templates.data_ptr(), weights.data_ptr(),
-                                                         y.data_ptr(), ws, n, stream_ptr(dev)))
+        with timed("similarity_forward", *_cost(d, y.numel(), "fwd")):
+            _lib.check(_lib.lib().simnets_similarity_forward(C.byref(d), input.data_ptr(), templates.data_ptr(), weights.data_ptr(),
+                                                             y.data_ptr(), ws, n, stream_ptr(dev)))
     return y
 
 
@@ -69,8 +79,9 @@ def similarity_input_grad(input, templates, weights, input_grad, flags=0, **attr
     dx = torch.empty_like(input)
     with torch.cuda.device(dev):
         ws, n = _ws(d, dev)
-        _lib.check(_lib.lib().simnets_similarity_input_grad(C.byref(d), input.data_ptr(), templates.data_ptr(), weights.data_ptr(),
-                                                            dy.data_ptr(), dx.data_ptr(), ws, n, stream_ptr(dev)))
+        with timed("similarity_input_grad", *_cost(d, dy.numel(), "dx")):
+            _lib.check(_lib.lib().simnets_similarity_input_grad(C.byref(d), input.data_ptr(), templates.data_ptr(), weights.data_ptr(),
+                                                                dy.data_ptr(), dx.data_ptr(), ws, n, stream_ptr(dev)))
     return dx
 
 
@@ -90,8 +101,9 @@ def similarity_parameters_grad(input, templates, weights, output_grad, flags=0, 
         assert dt.is_contiguous() and dw.is_contiguous() and dt.numel() == templates.numel() and dw.numel() == weights.numel()
     with torch.cuda.device(dev):
         ws, n = _ws(d, dev)
-        _lib.check(_lib.lib().simnets_similarity_params_grad(C.byref(d), input.data_ptr(), templates.data_ptr(), weights.data_ptr(),
-                                                             dy.data_ptr(), dt.data_ptr(), dw.data_ptr(), ws, n, stream_ptr(dev)))
+        with timed("similarity_params_grad", *_cost(d, dy.numel(), "dp")):
+            _lib.check(_lib.lib().simnets_similarity_params_grad(C.byref(d), input.data_ptr(), templates.data_ptr(), weights.data_ptr(),
+                                                                 dy.data_ptr(), dt.data_ptr(), dw.data_ptr(), ws, n, stream_ptr(dev)))
     return dt, dw
 
 
