@@ -25,8 +25,9 @@ def host_cores():
 
 
 class CpuOps(object):
-    def __init__(self, oracle, threads=1):
+    def __init__(self, oracle, threads=1, dtype=abi.F32):
         self.o = oracle
+        self.dtype = dtype
         self.threads = max(1, int(threads))
         self.pool = ThreadPoolExecutor(self.threads) if self.threads > 1 else None
 
@@ -45,7 +46,7 @@ class CpuOps(object):
     def _sd(self, kw, shape):
         return abi.make_sim_desc(shape, kw["num_instances"], kw.get("similarity_function", "L2"), kw["blocks"], kw["strides"],
                                  kw["padding"], kw.get("normalization_term", False), kw.get("normalization_term_fudge", 0.001),
-                                 kw.get("ignore_nan_input", False), kw.get("out_of_bounds_value", 0.0))
+                                 kw.get("ignore_nan_input", False), kw.get("out_of_bounds_value", 0.0), dtype=self.dtype)
 
     def sim_fwd(self, kw, x, t, w):
         return np.concatenate(self._map(lambda a, b: self.o.similarity_forward(self._sd(kw, x[a:b].shape), x[a:b], t, w), len(x)))
@@ -63,7 +64,7 @@ class CpuOps(object):
                                  kw.get("strides", [1, 1, 1]), kw["blocks"], kw.get("epsilon", 1.0),
                                  kw.get("blocks_out_of_bounds_value", 0.0), kw.get("blocks_round_down", True),
                                  kw.get("use_unshared_regions", True), kw.get("shared_offset_region", [-1]),
-                                 kw.get("unshared_offset_region", [-1]))
+                                 kw.get("unshared_offset_region", [-1]), dtype=self.dtype)
 
     def mex_fwd(self, kw, x, off):
         return np.concatenate(self._map(lambda a, b: self.o.mex_forward(self._md(kw, x[a:b].shape), x[a:b], off), len(x)))
@@ -113,15 +114,16 @@ class _MexFn(torch.autograd.Function):
 class CpuSimNet(object):
     """Same parameters (by seed) and same arithmetic order of layers as `simnets_tf_b200.simnet.SimNet`."""
 
-    def __init__(self, spec, oracle, seed=0, threads=1):
+    def __init__(self, spec, oracle, seed=0, threads=1, dtype=np.float32):
         self.spec = spec
-        self.ops = CpuOps(oracle, threads)
+        self.dtype = np.dtype(dtype)
+        self.ops = CpuOps(oracle, threads, abi.F64 if self.dtype == np.float64 else abi.F32)
         self.params = []
         for entry, values in zip(spec["layers"], init_parameters(spec, seed)):
             if values is None:
                 self.params.append(None)
             else:
-                self.params.append({k: torch.from_numpy(v.copy()).requires_grad_(True) for k, v in values.items()})
+                self.params.append({k: torch.from_numpy(v.astype(self.dtype)).requires_grad_(True) for k, v in values.items()})
 
     def parameters(self):
         """In the order torch lists them for SimNet: per layer (weights, templates) / (offsets)."""
@@ -155,7 +157,7 @@ class CpuSimNet(object):
         """One forward + backward; returns (loss, [gradients in parameters() order])."""
         for p in self.parameters():
             p.grad = None
-        logits = self.forward(torch.from_numpy(np.ascontiguousarray(x)))
+        logits = self.forward(torch.from_numpy(np.ascontiguousarray(x, dtype=self.dtype)))
         loss = F.cross_entropy(logits, torch.from_numpy(np.asarray(labels)).long(), reduction="sum") / float(global_batch or len(x))
         loss.backward()
         return float(loss.detach()), [p.grad.numpy() for p in self.parameters()]

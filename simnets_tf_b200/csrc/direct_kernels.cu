@@ -166,7 +166,8 @@ __device__ __forceinline__ T mex_tap(const MexGeo& g, const T* __restrict__ xs, 
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads) mex_fwd_direct(MexGeo g, const T* __restrict__ x, const T* __restrict__ off, T* __restrict__ y) {
+__global__ void __launch_bounds__(kThreads) mex_fwd_direct(MexGeo g, const T* __restrict__ x, const T* __restrict__ off, T* __restrict__ y, const int* __restrict__ gate) {
+    if (gate && *gate == 0) return;
     const long long total = (long long)g.B * g.M * g.N;
     const T oob = T(g.oob), eps = T(g.eps), cst = T(g.cst);
     for (long long idx = blockIdx.x * (long long)kThreads + threadIdx.x; idx < total; idx += (long long)gridDim.x * kThreads) {
@@ -200,7 +201,8 @@ __device__ __forceinline__ T mex_weight(const MexGeo& g, T eps, T cst, T data, T
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads) mex_dx_direct(MexGeo g, const T* __restrict__ x, const T* __restrict__ off,
-                                                          const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx) {
+                                                          const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx, const int* __restrict__ gate) {
+    if (gate && *gate == 0) return;
     const long long total = (long long)g.B * g.C * g.H * g.W;
     const T eps = T(g.eps), cst = T(g.cst);
     for (long long idx = blockIdx.x * (long long)kThreads + threadIdx.x; idx < total; idx += (long long)gridDim.x * kThreads) {
@@ -240,8 +242,9 @@ __global__ void __launch_bounds__(kThreads) mex_dx_direct(MexGeo g, const T* __r
 template <typename T>
 __global__ void __launch_bounds__(kThreads) mex_doff_direct(MexGeo g, const T* __restrict__ x, const T* __restrict__ off,
                                                             const T* __restrict__ y, const T* __restrict__ dy,
-                                                            T* __restrict__ doff, int accumulate) {
+                                                            T* __restrict__ doff, int accumulate, const int* __restrict__ gate) {
     __shared__ T smem[kThreads];
+    if (gate && *gate == 0) return;
     const int rmk = blockIdx.x;
     const int k = rmk % g.K, m = (rmk / g.K) % g.M, r = rmk / (g.K * g.M);
     const T o = off[rmk], oob = T(g.oob), eps = T(g.eps), cst = T(g.cst);
@@ -300,32 +303,32 @@ cudaError_t launch_sim_dparams_direct(const SimGeo& g, bool f64, const void* x, 
     return cudaGetLastError();
 }
 
-cudaError_t launch_mex_fwd_direct(const MexGeo& g, bool f64, const void* x, const void* off, void* y, cudaStream_t s) {
+cudaError_t launch_mex_fwd_direct(const MexGeo& g, bool f64, const void* x, const void* off, void* y, cudaStream_t s, const int* gate) {
     const long long total = (long long)g.B * g.M * g.N;
     if (total == 0) return cudaSuccess;
     SIMNETS_DTYPE_SWITCH(f64,
-        (mex_fwd_direct<float><<<grid_for(total), kThreads, 0, s>>>(g, (const float*)x, (const float*)off, (float*)y)),
-        (mex_fwd_direct<double><<<grid_for(total), kThreads, 0, s>>>(g, (const double*)x, (const double*)off, (double*)y)));
+        (mex_fwd_direct<float><<<grid_for(total), kThreads, 0, s>>>(g, (const float*)x, (const float*)off, (float*)y, gate)),
+        (mex_fwd_direct<double><<<grid_for(total), kThreads, 0, s>>>(g, (const double*)x, (const double*)off, (double*)y, gate)));
     count_launch();
     return cudaGetLastError();
 }
 
-cudaError_t launch_mex_dx_direct(const MexGeo& g, bool f64, const void* x, const void* off, const void* y, const void* dy, void* dx, cudaStream_t s) {
+cudaError_t launch_mex_dx_direct(const MexGeo& g, bool f64, const void* x, const void* off, const void* y, const void* dy, void* dx, cudaStream_t s, const int* gate) {
     const long long total = (long long)g.B * g.C * g.H * g.W;
     if (total == 0) return cudaSuccess;
     SIMNETS_DTYPE_SWITCH(f64,
-        (mex_dx_direct<float><<<grid_for(total), kThreads, 0, s>>>(g, (const float*)x, (const float*)off, (const float*)y, (const float*)dy, (float*)dx)),
-        (mex_dx_direct<double><<<grid_for(total), kThreads, 0, s>>>(g, (const double*)x, (const double*)off, (const double*)y, (const double*)dy, (double*)dx)));
+        (mex_dx_direct<float><<<grid_for(total), kThreads, 0, s>>>(g, (const float*)x, (const float*)off, (const float*)y, (const float*)dy, (float*)dx, gate)),
+        (mex_dx_direct<double><<<grid_for(total), kThreads, 0, s>>>(g, (const double*)x, (const double*)off, (const double*)y, (const double*)dy, (double*)dx, gate)));
     count_launch();
     return cudaGetLastError();
 }
 
 cudaError_t launch_mex_doff_direct(const MexGeo& g, bool f64, const void* x, const void* off, const void* y, const void* dy,
-                                   void* doff, bool accumulate, cudaStream_t s) {
+                                   void* doff, bool accumulate, cudaStream_t s, const int* gate) {
     const int blocks = g.R * g.M * g.K;
     SIMNETS_DTYPE_SWITCH(f64,
-        (mex_doff_direct<float><<<blocks, kThreads, 0, s>>>(g, (const float*)x, (const float*)off, (const float*)y, (const float*)dy, (float*)doff, accumulate)),
-        (mex_doff_direct<double><<<blocks, kThreads, 0, s>>>(g, (const double*)x, (const double*)off, (const double*)y, (const double*)dy, (double*)doff, accumulate)));
+        (mex_doff_direct<float><<<blocks, kThreads, 0, s>>>(g, (const float*)x, (const float*)off, (const float*)y, (const float*)dy, (float*)doff, accumulate, gate)),
+        (mex_doff_direct<double><<<blocks, kThreads, 0, s>>>(g, (const double*)x, (const double*)off, (const double*)y, (const double*)dy, (double*)doff, accumulate, gate)));
     count_launch();
     return cudaGetLastError();
 }

@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <math_constants.h>
+#include "simnets_b200.h"
 #include "geometry.cuh"
 
 namespace simnets {
@@ -13,10 +14,12 @@ cudaError_t launch_sim_fwd_direct(const SimGeo&, bool f64, const void* x, const 
 cudaError_t launch_sim_dx_direct(const SimGeo&, bool f64, const void* x, const void* t, const void* w, const void* dy, void* dx, cudaStream_t);
 cudaError_t launch_sim_dparams_direct(const SimGeo&, bool f64, const void* x, const void* t, const void* w, const void* dy,
                                       void* dt, void* dw, bool accumulate, cudaStream_t);
-cudaError_t launch_mex_fwd_direct(const MexGeo&, bool f64, const void* x, const void* off, void* y, cudaStream_t);
-cudaError_t launch_mex_dx_direct(const MexGeo&, bool f64, const void* x, const void* off, const void* y, const void* dy, void* dx, cudaStream_t);
+// MEX launchers take an optional device flag: with `gate` non-null the kernel runs only if *gate != 0
+cudaError_t launch_mex_fwd_direct(const MexGeo&, bool f64, const void* x, const void* off, void* y, cudaStream_t, const int* gate = nullptr);
+cudaError_t launch_mex_dx_direct(const MexGeo&, bool f64, const void* x, const void* off, const void* y, const void* dy, void* dx, cudaStream_t,
+                                 const int* gate = nullptr);
 cudaError_t launch_mex_doff_direct(const MexGeo&, bool f64, const void* x, const void* off, const void* y, const void* dy,
-                                   void* doff, bool accumulate, cudaStream_t);
+                                   void* doff, bool accumulate, cudaStream_t, const int* gate = nullptr);
 
 }  // namespace simnets
 

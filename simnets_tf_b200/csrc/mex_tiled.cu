@@ -1,0 +1,539 @@
+// MEX forward / input-gradient / offsets-gradient as factorised generalized GEMMs (float32).
+//
+// The reference evaluates y[m,j] = mx + log(sum_k exp(eps*(x[k,j] + o[m,k] - mx)) + c)/eps with one
+// exp per (m, k, j) term (HUJI-Deep/simnets-tf src/kernels/mex_kernel_cpu.cpp:11-38,
+// include/utils/mex_utils.hpp:10-29): M*N*K exponentials per sample, which binds the kernel to the
+// special-function unit, not to memory.  Here the exponent is split per operand:
+//
+//     exp(eps*(x[k,j] + o[m,k])) = exp(eps*(x[k,j] - mx[j])) * exp(eps*(o[m,k] - mo[m])) * exp(eps*(mx[j] + mo[m]))
+//          Ex[k,j] in (0,1]  ^                 Eo[m,k] in (0,1]  ^
+//
+// with mx[j] = max_k x[k,j] and mo[m] = max_k o[m,k] (min for eps < 0), so that
+//     S[m,j] = sum_k Eo[m,k] * Ex[k,j]          -- a plain FP32 GEMM, K*N + M*K exponentials in total
+//     y[m,j] = mx[j] + mo[m] + (log S[m,j] + c)/eps
+// and, with the softmax weight p = Eo*Ex*G,  G[m,j] = exp(eps*(mx[j] + mo[m] - y[m,j]) + c)
+// (mex_utils.hpp:31-56 computes p = exp(eps*(x + o - y) + c) directly),
+//     dX patch[k,j] = Ex[k,j] * sum_m Eo[m,k] * (dy*G)[m,j]
+//     dO[m,k]       = Eo[m,k] * sum_j (dy*G)[m,j] * Ex[k,j].
+// S >= exp(-|eps| * (max_k o - min_k o)) whenever the offsets are finite, so the factorisation cannot
+// underflow if |eps| * spread(o) <= 60; a prepass checks exactly that and raises a device flag
+// otherwise, in which case these kernels return at once and the exact one-exp-per-term kernels
+// (direct_kernels.cu), launched right behind them and gated on the same flag, do the work.
+//
+// Offset regions (shared / unshared) never move data: a CTA works on the positions of ONE region,
+// enumerated in the region-local order of the reference's split_patches (mex_utils.hpp:69-116).
+#include "kernels.cuh"
+#include "tile.cuh"
+
+namespace simnets {
+
+namespace {
+
+constexpr float kSafeSpread = 60.0f;
+
+struct MexWs {           // workspace carve-up, every part 256-byte aligned
+    int* flag;           // != 0: factorisation unsafe, take the exact kernels
+    float* mo;           // [R][M]
+    float* eo;           // [R][M][K]   Eo, offsets layout
+    float* eot;          // [R][K][M]   Eo transposed
+    float* mx;           // [B][N]
+    float* part;         // [S][R][M][K] split-q partial sums of the offsets gradient
+    size_t bytes;
+};
+
+__host__ inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+constexpr int kDoffTile = 64, kDoffKC = 32;
+
+__host__ int doff_splits(const MexGeo& g) {
+    const long long P = (long long)g.B * g.rs;
+    const long long chunks = (P + kDoffKC - 1) / kDoffKC;
+    const long long tiles = (long long)((g.M + kDoffTile - 1) / kDoffTile) * ((g.K + kDoffTile - 1) / kDoffTile) * g.R;
+    long long s = (148 * 2 + tiles - 1) / tiles;
+    if (s > chunks) s = chunks;
+    if (s < 1) s = 1;
+    if (s > 64) s = 64;
+    return int(s);
+}
+
+__host__ MexWs carve(const MexGeo& g, void* base) {
+    MexWs w;
+    char* p = static_cast<char*>(base);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { char* r = p ? p + off : nullptr; off += align256(bytes); return r; };
+    w.flag = reinterpret_cast<int*>(take(16));
+    w.mo = reinterpret_cast<float*>(take(sizeof(float) * g.R * g.M));
+    w.eo = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.M * g.K));
+    w.eot = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.M * g.K));
+    w.mx = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.B * g.N));
+    w.part = reinterpret_cast<float*>(take(sizeof(float) * (size_t)doff_splits(g) * g.R * g.M * g.K));
+    w.bytes = off;
+    return w;
+}
+
+// ------------------------------------------------------------------ prepasses
+// One block per (region, instance): stabiliser mo, Eo in both layouts, and the safety flag.
+__global__ void __launch_bounds__(128) mex_prep_offsets(MexGeo g, const float* __restrict__ off, float* __restrict__ mo,
+                                                        float* __restrict__ eo, float* __restrict__ eot, int* __restrict__ flag) {
+    __shared__ float s_hi[128], s_lo[128];
+    __shared__ int s_bad[128];
+    const int rm = blockIdx.x, r = rm / g.M, m = rm % g.M;
+    const float* o = off + (size_t)rm * g.K;
+    float hi = -CUDART_INF_F, lo = CUDART_INF_F;
+    int bad = 0;
+    for (int k = threadIdx.x; k < g.K; k += 128) {
+        const float v = o[k];
+        if (!isfinite(v)) bad = 1;
+        hi = fmaxf(hi, v); lo = fminf(lo, v);
+    }
+    s_hi[threadIdx.x] = hi; s_lo[threadIdx.x] = lo; s_bad[threadIdx.x] = bad;
+    __syncthreads();
+    for (int s = 64; s > 0; s >>= 1) {
+        if (threadIdx.x < s) {
+            s_hi[threadIdx.x] = fmaxf(s_hi[threadIdx.x], s_hi[threadIdx.x + s]);
+            s_lo[threadIdx.x] = fminf(s_lo[threadIdx.x], s_lo[threadIdx.x + s]);
+            s_bad[threadIdx.x] |= s_bad[threadIdx.x + s];
+        }
+        __syncthreads();
+    }
+    hi = s_hi[0]; lo = s_lo[0]; bad = s_bad[0];
+    const float eps = float(g.eps);
+    const float ref = eps > 0.f ? hi : lo;
+    if (threadIdx.x == 0) {
+        mo[rm] = ref;
+        if (bad || !(fabsf(eps) * (hi - lo) <= kSafeSpread)) atomicOr(flag, 1);
+    }
+    for (int k = threadIdx.x; k < g.K; k += 128) {
+        const float e = fast_exp(eps * (o[k] - ref));
+        eo[(size_t)rm * g.K + k] = e;
+        eot[((size_t)r * g.K + k) * g.M + m] = e;
+    }
+}
+
+struct Tap { int c, h, w; };
+
+template <bool SPATIAL1>
+__device__ __forceinline__ Tap tap_of(const MexGeo& g, int k) {
+    Tap t;
+    if (SPATIAL1) { t.c = k; t.h = 0; t.w = 0; }
+    else { t.w = k % g.bw; const int q = k / g.bw; t.h = q % g.bh; t.c = q / g.bh; }
+    return t;
+}
+
+// value of tap k of the patch whose corner is (c0, h0, w0) in sample xs
+template <bool SPATIAL1>
+__device__ __forceinline__ float patch_value(const MexGeo& g, const float* __restrict__ xs, int c0, int h0, int w0, int k, float oob) {
+    const Tap t = tap_of<SPATIAL1>(g, k);
+    const int cc = c0 + t.c, hh = h0 + t.h, ww = w0 + t.w;
+    if (cc >= 0 && cc < g.C && hh >= 0 && hh < g.H && ww >= 0 && ww < g.W) return __ldg(xs + ((size_t)cc * g.H + hh) * g.W + ww);
+    return oob;
+}
+
+// mx[n][pos] = max (eps > 0) or min (eps < 0) over the K taps of the patch at pos; NaN taps are ignored,
+// as the reference's max pass ignores them (std::max(acc, NaN) keeps acc).
+template <bool SPATIAL1>
+__global__ void __launch_bounds__(256) mex_colmax(MexGeo g, const float* __restrict__ x, float* __restrict__ mx, const int* __restrict__ flag) {
+    if (*flag) return;
+    const long long total = (long long)g.B * g.N;
+    const bool up = g.eps > 0;
+    const float oob = float(g.oob);
+    for (long long idx = blockIdx.x * 256LL + threadIdx.x; idx < total; idx += (long long)gridDim.x * 256) {
+        const int pos = int(idx % g.N), n = int(idx / g.N);
+        const int w = pos % g.Wo, h = (pos / g.Wo) % g.Ho, c = pos / (g.Wo * g.Ho);
+        const float* xs = x + (size_t)n * g.C * g.H * g.W;
+        const int c0 = c * g.sc - g.pc, h0 = h * g.sh - g.ph, w0 = w * g.sw - g.pw;
+        float v = up ? -CUDART_INF_F : CUDART_INF_F;
+        for (int k = 0; k < g.K; ++k) {
+            const float t = patch_value<SPATIAL1>(g, xs, c0, h0, w0, k, oob);
+            v = up ? fmaxf(v, t) : fminf(v, t);
+        }
+        mx[idx] = v;
+    }
+}
+
+// Per-column (= one output position of one sample) bookkeeping shared by the tile kernels.
+struct Column {
+    long long base;      // n*M*N + pos : offset of y[n, 0, pos]; -1 for a position outside the output grid
+    int n, c0, h0, w0;   // sample and patch corner in the input
+    float mx;
+};
+
+// j-th position (over the whole batch) of region r -> Column
+__device__ __forceinline__ Column column_of(const MexGeo& g, int r, long long jl, long long P, const float* __restrict__ mx) {
+    Column c;
+    c.base = -1; c.n = 0; c.c0 = c.h0 = c.w0 = 0; c.mx = 0.f;
+    if (jl >= P) return c;
+    const int n = int(jl / g.rs), l = int(jl % g.rs);
+    const int pos = mex_region_position(g, r, l);
+    if (pos < 0) return c;
+    const int w = pos % g.Wo, h = (pos / g.Wo) % g.Ho, cc = pos / (g.Wo * g.Ho);
+    c.n = n; c.c0 = cc * g.sc - g.pc; c.h0 = h * g.sh - g.ph; c.w0 = w * g.sw - g.pw;
+    c.base = (long long)n * g.M * g.N + pos;
+    c.mx = mx[(long long)n * g.N + pos];
+    return c;
+}
+
+// ------------------------------------------------------------------- forward
+// C[i = m, j = position] = sum_{q = k} EoT[k][m] * Ex[k][j]
+template <int TM, bool SPATIAL1>
+__global__ void __launch_bounds__(256) mex_fwd_tiled(MexGeo g, const float* __restrict__ x, const float* __restrict__ eot,
+                                                     const float* __restrict__ mo, const float* __restrict__ mx,
+                                                     float* __restrict__ y, const int* __restrict__ flag) {
+    using Cfg = TileCfg<TM, 128, 8, TM / 16, 8, 1, 1>;
+    static_assert(Cfg::THREADS == 256, "256 threads");
+    if (*flag) return;
+    __shared__ __align__(16) float smem[Cfg::SMEM_FLOATS];
+    __shared__ Column cols[Cfg::TN];
+    const long long P = (long long)g.B * g.rs;                 // positions of one region over the batch
+    const int mtiles = (g.M + TM - 1) / TM;
+    int bid = blockIdx.x;
+    const int r = bid % g.R; bid /= g.R;
+    const int mt = bid % mtiles;
+    const long long jt = bid / mtiles;
+    const int i0 = mt * TM;
+    const long long j0 = jt * Cfg::TN;
+    if (threadIdx.x < Cfg::TN) cols[threadIdx.x] = column_of(g, r, j0 + threadIdx.x, P, mx);
+    __syncthreads();
+
+    const TileThread<Cfg> t;
+    const float eps = float(g.eps), oob = float(g.oob);
+    // staging roles: element e of a chunk = (kk, lane) with lane fastest (contiguous global reads)
+    const int s_lane = threadIdx.x % 128, s_k = threadIdx.x / 128;          // TM or TN lanes, 2 k-rows per pass
+    const Column sc = cols[s_lane];
+    const float* xs = x + (size_t)sc.n * g.C * g.H * g.W;
+    const float* arow = eot + (size_t)r * g.K * g.M;
+    float ra[Cfg::A_PER], rb[Cfg::B_PER];
+    constexpr int A_LANES = TM, A_ROWS = 256 / TM;                            // rows of the chunk one pass covers
+    const int a_lane = threadIdx.x % A_LANES, a_k = threadIdx.x / A_LANES;
+
+    float acc[Cfg::RM][Cfg::RN];
+#pragma unroll
+    for (int r_ = 0; r_ < Cfg::RM; ++r_)
+#pragma unroll
+        for (int c_ = 0; c_ < Cfg::RN; ++c_) acc[r_][c_] = 0.f;
+
+    auto fetchA = [&](int chunk) {
+#pragma unroll
+        for (int s = 0; s < Cfg::A_PER; ++s) {
+            const int k = chunk * Cfg::KC + a_k + s * A_ROWS, m = i0 + a_lane;
+            ra[s] = (k < g.K && m < g.M) ? __ldg(arow + (size_t)k * g.M + m) : 0.f;
+        }
+    };
+    auto fetchB = [&](int chunk) {
+#pragma unroll
+        for (int s = 0; s < Cfg::B_PER; ++s) {
+            const int k = chunk * Cfg::KC + s_k + s * 2;
+            rb[s] = (k < g.K && sc.base >= 0) ? patch_value<SPATIAL1>(g, xs, sc.c0, sc.h0, sc.w0, k, oob) : -CUDART_INF_F * (eps > 0 ? 1.f : -1.f);
+        }
+    };
+    auto commitA = [&](float* As) {
+#pragma unroll
+        for (int s = 0; s < Cfg::A_PER; ++s) As[(a_k + s * A_ROWS) * TM + a_lane] = ra[s];
+    };
+    auto commitB = [&](float* Bs) {
+#pragma unroll
+        for (int s = 0; s < Cfg::B_PER; ++s) {
+            // padding rows of the last chunk and dead columns hold -inf*sign(eps): exp() gives exactly 0
+            const float e = (sc.base >= 0) ? fast_exp(eps * (rb[s] - sc.mx)) : 0.f;
+            Bs[(s_k + s * 2) * Cfg::TN + s_lane] = e;
+        }
+    };
+    auto comb = [&](int r_, int c_, const float (&a)[1], const float (&b)[1]) { acc[r_][c_] = fmaf(a[0], b[0], acc[r_][c_]); };
+    tile_mainloop<Cfg, false, false>(smem, (g.K + Cfg::KC - 1) / Cfg::KC, t, fetchA, fetchB, commitA, commitB, comb);
+
+    const float inv_eps = 1.f / eps, cst = float(g.cst);
+#pragma unroll
+    for (int r_ = 0; r_ < Cfg::RM; ++r_) {
+        const int m = i0 + t.row(r_);
+        if (m >= g.M) continue;
+        const float mom = mo[r * g.M + m];
+#pragma unroll
+        for (int c_ = 0; c_ < Cfg::RN; ++c_) {
+            const Column& col = cols[t.col(c_)];
+            if (col.base < 0) continue;
+            __stcs(y + col.base + (long long)m * g.N, col.mx + mom + (fast_log(acc[r_][c_]) + cst) * inv_eps);
+        }
+    }
+}
+
+// ------------------------------------------------------------ input gradient
+// C[i = k, j = position] = sum_{q = m} Eo[m][k] * (dy*G)[m][j];  dx[tap k of position j] = Ex[k][j] * C
+// (taps of different positions never coincide: the host only takes this kernel when blocks do not overlap).
+template <int TM, bool SPATIAL1>
+__global__ void __launch_bounds__(256) mex_dx_tiled(MexGeo g, const float* __restrict__ x, const float* __restrict__ eo,
+                                                    const float* __restrict__ mo, const float* __restrict__ mx,
+                                                    const float* __restrict__ y, const float* __restrict__ dy,
+                                                    float* __restrict__ dx, const int* __restrict__ flag) {
+    using Cfg = TileCfg<TM, 128, 8, TM / 16, 8, 1, 1>;
+    if (*flag) return;
+    __shared__ __align__(16) float smem[Cfg::SMEM_FLOATS];
+    __shared__ Column cols[Cfg::TN];
+    const long long P = (long long)g.B * g.rs;
+    const int ktiles = (g.K + TM - 1) / TM;
+    int bid = blockIdx.x;
+    const int r = bid % g.R; bid /= g.R;
+    const int kt = bid % ktiles;
+    const long long jt = bid / ktiles;
+    const int i0 = kt * TM;
+    const long long j0 = jt * Cfg::TN;
+    if (threadIdx.x < Cfg::TN) cols[threadIdx.x] = column_of(g, r, j0 + threadIdx.x, P, mx);
+    __syncthreads();
+
+    const TileThread<Cfg> t;
+    const float eps = float(g.eps), cst = float(g.cst), oob = float(g.oob);
+    const int s_lane = threadIdx.x % 128, s_k = threadIdx.x / 128;
+    const Column sc = cols[s_lane];
+    constexpr int A_LANES = TM, A_ROWS = 256 / TM;
+    const int a_lane = threadIdx.x % A_LANES, a_k = threadIdx.x / A_LANES;
+    const float* arow = eo + (size_t)r * g.M * g.K;
+    const float* mor = mo + r * g.M;
+    float ra[Cfg::A_PER], rby[Cfg::B_PER], rbg[Cfg::B_PER], rbm[Cfg::B_PER];
+
+    float acc[Cfg::RM][Cfg::RN];
+#pragma unroll
+    for (int r_ = 0; r_ < Cfg::RM; ++r_)
+#pragma unroll
+        for (int c_ = 0; c_ < Cfg::RN; ++c_) acc[r_][c_] = 0.f;
+
+    auto fetchA = [&](int chunk) {
+#pragma unroll
+        for (int s = 0; s < Cfg::A_PER; ++s) {
+            const int m = chunk * Cfg::KC + a_k + s * A_ROWS, k = i0 + a_lane;
+            ra[s] = (m < g.M && k < g.K) ? __ldg(arow + (size_t)m * g.K + k) : 0.f;
+        }
+    };
+    auto fetchB = [&](int chunk) {
+#pragma unroll
+        for (int s = 0; s < Cfg::B_PER; ++s) {
+            const int m = chunk * Cfg::KC + s_k + s * 2;
+            const bool ok = m < g.M && sc.base >= 0;
+            rby[s] = ok ? __ldcs(y + sc.base + (long long)m * g.N) : 0.f;
+            rbg[s] = ok ? __ldcs(dy + sc.base + (long long)m * g.N) : 0.f;
+            rbm[s] = ok ? __ldg(mor + m) : 0.f;
+        }
+    };
+    auto commitA = [&](float* As) {
+#pragma unroll
+        for (int s = 0; s < Cfg::A_PER; ++s) As[(a_k + s * A_ROWS) * TM + a_lane] = ra[s];
+    };
+    auto commitB = [&](float* Bs) {
+#pragma unroll
+        for (int s = 0; s < Cfg::B_PER; ++s) {
+            const int m = s_k + s * 2;      // row inside the chunk; rows past M carry dy = 0
+            Bs[m * Cfg::TN + s_lane] = rbg[s] * fast_exp(eps * (sc.mx + rbm[s] - rby[s]) + cst);
+        }
+    };
+    auto comb = [&](int r_, int c_, const float (&a)[1], const float (&b)[1]) { acc[r_][c_] = fmaf(a[0], b[0], acc[r_][c_]); };
+    tile_mainloop<Cfg, false, false>(smem, (g.M + Cfg::KC - 1) / Cfg::KC, t, fetchA, fetchB, commitA, commitB, comb);
+
+#pragma unroll
+    for (int c_ = 0; c_ < Cfg::RN; ++c_) {
+        const Column& col = cols[t.col(c_)];
+        if (col.base < 0) continue;
+        const size_t sample = (size_t)col.n * g.C * g.H * g.W;
+#pragma unroll
+        for (int r_ = 0; r_ < Cfg::RM; ++r_) {
+            const int k = i0 + t.row(r_);
+            if (k >= g.K) continue;
+            const Tap tp = tap_of<SPATIAL1>(g, k);
+            const int cc = col.c0 + tp.c, hh = col.h0 + tp.h, ww = col.w0 + tp.w;
+            if (cc < 0 || cc >= g.C || hh < 0 || hh >= g.H || ww < 0 || ww >= g.W) continue;
+            const size_t a = sample + ((size_t)cc * g.H + hh) * g.W + ww;
+            dx[a] = fast_exp(eps * (__ldg(x + a) - col.mx)) * acc[r_][c_];
+        }
+    }
+    (void)oob;
+}
+
+// ---------------------------------------------------------- offsets gradient
+// C[i = m, j = k] = sum_{q = positions of region r in this split} (dy*G)[m][q] * Ex[k][q]; both operands
+// are contiguous along q in memory, so they are stored transposed (swizzled stages).
+template <bool SPATIAL1>
+__global__ void __launch_bounds__(256) mex_doff_tiled(MexGeo g, const float* __restrict__ x, const float* __restrict__ mo,
+                                                      const float* __restrict__ mx, const float* __restrict__ y,
+                                                      const float* __restrict__ dy, float* __restrict__ part, int splits,
+                                                      const int* __restrict__ flag) {
+    using Cfg = TileCfg<kDoffTile, kDoffTile, kDoffKC, 4, 4, 1, 1>;
+    static_assert(Cfg::THREADS == 256, "256 threads");
+    if (*flag) return;
+    __shared__ __align__(16) float smem[Cfg::SMEM_FLOATS];
+    const long long P = (long long)g.B * g.rs;
+    const int mtiles = (g.M + kDoffTile - 1) / kDoffTile, ktiles = (g.K + kDoffTile - 1) / kDoffTile;
+    int bid = blockIdx.x;
+    const int kt = bid % ktiles; bid /= ktiles;
+    const int mt = bid % mtiles; bid /= mtiles;
+    const int r = bid % g.R;
+    const int split = bid / g.R;
+    const int i0 = mt * kDoffTile, jk0 = kt * kDoffTile;
+    const long long chunks = (P + kDoffKC - 1) / kDoffKC;
+    const long long c_begin = chunks * split / splits, c_end = chunks * (split + 1) / splits;
+
+    const TileThread<Cfg> t;
+    const float eps = float(g.eps), cst = float(g.cst), oob = float(g.oob);
+    const int qq = threadIdx.x % 32, e0 = threadIdx.x / 32;         // this thread stages q = qq, rows e0 + 8*s
+    const float* mor = mo + r * g.M;
+    Column cur;                                                     // the position this thread stages in the fetched chunk
+    float ray[Cfg::A_PER], rag[Cfg::A_PER], rbx[Cfg::B_PER];
+
+    float acc[4][4];
+#pragma unroll
+    for (int r_ = 0; r_ < 4; ++r_)
+#pragma unroll
+        for (int c_ = 0; c_ < 4; ++c_) acc[r_][c_] = 0.f;
+
+    auto fetchA = [&](int chunk) {
+        cur = column_of(g, r, (c_begin + chunk) * kDoffKC + qq, P, mx);
+#pragma unroll
+        for (int s = 0; s < Cfg::A_PER; ++s) {
+            const int m = i0 + e0 + 8 * s;
+            const bool ok = cur.base >= 0 && m < g.M;
+            ray[s] = ok ? __ldcs(y + cur.base + (long long)m * g.N) : 0.f;
+            rag[s] = ok ? __ldcs(dy + cur.base + (long long)m * g.N) : 0.f;
+        }
+    };
+    auto fetchB = [&](int) {
+        const float* xs = x + (size_t)cur.n * g.C * g.H * g.W;
+#pragma unroll
+        for (int s = 0; s < Cfg::B_PER; ++s) {
+            const int k = jk0 + e0 + 8 * s;
+            rbx[s] = (cur.base >= 0 && k < g.K) ? patch_value<SPATIAL1>(g, xs, cur.c0, cur.h0, cur.w0, k, oob) : 0.f;
+        }
+    };
+    auto commitA = [&](float* As) {
+#pragma unroll
+        for (int s = 0; s < Cfg::A_PER; ++s) {
+            const int e = e0 + 8 * s, m = i0 + e;
+            const float mom = m < g.M ? __ldg(mor + m) : 0.f;
+            As[stage_offset<kDoffTile, true>(qq, e)] = rag[s] * fast_exp(eps * (cur.mx + mom - ray[s]) + cst);
+        }
+    };
+    auto commitB = [&](float* Bs) {
+#pragma unroll
+        for (int s = 0; s < Cfg::B_PER; ++s) {
+            const int e = e0 + 8 * s;
+            Bs[stage_offset<kDoffTile, true>(qq, e)] = (cur.base >= 0 && jk0 + e < g.K) ? fast_exp(eps * (rbx[s] - cur.mx)) : 0.f;
+        }
+    };
+    auto comb = [&](int r_, int c_, const float (&a)[1], const float (&b)[1]) { acc[r_][c_] = fmaf(a[0], b[0], acc[r_][c_]); };
+    tile_mainloop<Cfg, true, true>(smem, int(c_end - c_begin), t, fetchA, fetchB, commitA, commitB, comb);
+
+    float* dst = part + ((size_t)split * g.R + r) * g.M * g.K;
+#pragma unroll
+    for (int r_ = 0; r_ < 4; ++r_) {
+        const int m = i0 + t.row(r_);
+        if (m >= g.M) continue;
+#pragma unroll
+        for (int c_ = 0; c_ < 4; ++c_) {
+            const int k = jk0 + t.col(c_);
+            if (k < g.K) dst[(size_t)m * g.K + k] = acc[r_][c_];
+        }
+    }
+}
+
+// doff[r][m][k] (+)= Eo[r][m][k] * sum over splits, in split order (deterministic)
+__global__ void __launch_bounds__(256) mex_doff_reduce(long long n, int splits, const float* __restrict__ part, const float* __restrict__ eo,
+                                                       float* __restrict__ doff, int accumulate, const int* __restrict__ flag) {
+    if (*flag) return;
+    for (long long i = blockIdx.x * 256LL + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
+        float s = 0.f;
+        for (int p = 0; p < splits; ++p) s += part[(size_t)p * n + i];
+        s *= eo[i];
+        doff[i] = accumulate ? doff[i] + s : s;
+    }
+}
+
+bool blocks_disjoint(const MexGeo& g) { return g.sc >= g.bc && g.sh >= g.bh && g.sw >= g.bw; }
+
+bool blocks_cover_input(const MexGeo& g) {
+    auto full = [](int dim, int block, int stride, int pad) { return stride == block && pad == 0 && dim % block == 0; };
+    return full(g.C, g.bc, g.sc, g.pc) && full(g.H, g.bh, g.sh, g.ph) && full(g.W, g.bw, g.sw, g.pw);
+}
+
+cudaError_t run_prepasses(const MexGeo& g, const MexWs& w, const float* x, const float* off, cudaStream_t s) {
+    cudaError_t e = cudaMemsetAsync(w.flag, 0, 16, s);
+    if (e != cudaSuccess) return e;
+    mex_prep_offsets<<<g.R * g.M, 128, 0, s>>>(g, off, w.mo, w.eo, w.eot, w.flag);
+    const long long total = (long long)g.B * g.N;
+    const int grid = int(std::min<long long>((total + 255) / 256, 148LL * 16));
+    if (g.bh == 1 && g.bw == 1) mex_colmax<true><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
+    else mex_colmax<false><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
+    count_launch(2);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool mex_use_tiled(const MexGeo& g, bool f64, uint32_t flags) {
+    if (f64 || !g.finite || g.B == 0) return false;
+    if (flags & (SIMNETS_FLAG_FORCE_DIRECT | SIMNETS_FLAG_MEX_EXACT)) return false;
+    return true;
+}
+
+size_t mex_workspace_bytes(const MexGeo& g, bool f64, uint32_t flags) {
+    if (!mex_use_tiled(g, f64, flags)) return 256;
+    return carve(g, nullptr).bytes;
+}
+
+cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* off, float* y, void* ws, uint32_t, cudaStream_t s) {
+    const MexWs w = carve(g, ws);
+    cudaError_t e = run_prepasses(g, w, x, off, s);
+    if (e != cudaSuccess) return e;
+    const long long P = (long long)g.B * g.rs;
+    const bool sp1 = g.bh == 1 && g.bw == 1;
+    const bool wide = g.M > 64;
+    const long long jtiles = (P + 127) / 128;
+    const long long blocks = jtiles * ((g.M + (wide ? 127 : 63)) / (wide ? 128 : 64)) * g.R;
+    if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+#define FWD(TM, SP) mex_fwd_tiled<TM, SP><<<int(blocks), 256, 0, s>>>(g, x, w.eot, w.mo, w.mx, y, w.flag)
+    if (wide) { if (sp1) FWD(128, true); else FWD(128, false); }
+    else { if (sp1) FWD(64, true); else FWD(64, false); }
+#undef FWD
+    count_launch();
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);       // runs only if the flag was raised
+}
+
+cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* dx,
+                                void* ws, uint32_t, cudaStream_t s) {
+    if (!blocks_disjoint(g)) return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, nullptr);
+    const MexWs w = carve(g, ws);
+    cudaError_t e = run_prepasses(g, w, x, off, s);
+    if (e != cudaSuccess) return e;
+    if (!blocks_cover_input(g)) {
+        e = cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)g.B * g.C * g.H * g.W, s);
+        if (e != cudaSuccess) return e;
+    }
+    const long long P = (long long)g.B * g.rs;
+    const bool sp1 = g.bh == 1 && g.bw == 1;
+    const bool wide = g.K > 64;
+    const long long blocks = ((P + 127) / 128) * ((g.K + (wide ? 127 : 63)) / (wide ? 128 : 64)) * g.R;
+    if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+#define DX(TM, SP) mex_dx_tiled<TM, SP><<<int(blocks), 256, 0, s>>>(g, x, w.eo, w.mo, w.mx, y, dy, dx, w.flag)
+    if (wide) { if (sp1) DX(128, true); else DX(128, false); }
+    else { if (sp1) DX(64, true); else DX(64, false); }
+#undef DX
+    count_launch();
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
+}
+
+cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* doff,
+                                  bool accumulate, void* ws, uint32_t, cudaStream_t s) {
+    const MexWs w = carve(g, ws);
+    cudaError_t e = run_prepasses(g, w, x, off, s);
+    if (e != cudaSuccess) return e;
+    const int splits = doff_splits(g);
+    const long long blocks = (long long)((g.M + kDoffTile - 1) / kDoffTile) * ((g.K + kDoffTile - 1) / kDoffTile) * g.R * splits;
+    if (g.bh == 1 && g.bw == 1) mex_doff_tiled<true><<<int(blocks), 256, 0, s>>>(g, x, w.mo, w.mx, y, dy, w.part, splits, w.flag);
+    else mex_doff_tiled<false><<<int(blocks), 256, 0, s>>>(g, x, w.mo, w.mx, y, dy, w.part, splits, w.flag);
+    const long long n = (long long)g.R * g.M * g.K;
+    mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, splits, w.part, w.eo, doff, accumulate, w.flag);
+    count_launch(2);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
+}
+
+}  // namespace simnets

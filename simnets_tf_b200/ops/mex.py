@@ -7,6 +7,7 @@ import ctypes as C
 import torch
 
 from .. import _lib, abi
+from .. import _torch_glue
 from .._torch_glue import dtype_code, require_cuda, stream_ptr, timed, workspace
 
 _DEFAULTS = dict(softmax_mode=False, padding=[0, 0, 0], strides=[1, 1, 1], blocks=[1, 1, 1], epsilon=1.0,
@@ -65,7 +66,7 @@ def _desc(input, num_instances, attrs, flags=0):
     return abi.make_mex_desc(input.shape, num_instances, attrs["softmax_mode"], attrs["padding"], attrs["strides"],
                              attrs["blocks"], attrs["epsilon"], attrs["blocks_out_of_bounds_value"], attrs["blocks_round_down"],
                              attrs["use_unshared_regions"], attrs["shared_offset_region"], attrs["unshared_offset_region"],
-                             dtype=dtype_code(input), flags=flags)
+                             dtype=dtype_code(input), flags=flags | _torch_glue.DEFAULT_FLAGS)
 
 
 def _geometry(d):

@@ -8,6 +8,7 @@ import ctypes as C
 import torch
 
 from .. import _lib, abi
+from .. import _torch_glue
 from .._torch_glue import dtype_code, require_cuda, stream_ptr, timed, workspace
 
 _DEFAULTS = dict(similarity_function="L2", blocks=[3, 3], strides=[2, 2], padding=[0, 0], normalization_term=False,
@@ -35,7 +36,7 @@ def _desc(input, templates, weights, attrs, flags=0):
         raise ValueError("templates spatial shape %s does not match blocks %s" % (list(templates.shape[2:]), blocks))
     return abi.make_sim_desc(input.shape, templates.shape[0], attrs["similarity_function"], blocks, attrs["strides"],
                              attrs["padding"], attrs["normalization_term"], attrs["normalization_term_fudge"],
-                             attrs["ignore_nan_input"], attrs["out_of_bounds_value"], dtype=dtype_code(input), flags=flags)
+                             attrs["ignore_nan_input"], attrs["out_of_bounds_value"], dtype=dtype_code(input), flags=flags | _torch_glue.DEFAULT_FLAGS)
 
 
 def _cost(d, y_numel, kind):

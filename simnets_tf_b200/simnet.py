@@ -86,20 +86,20 @@ def init_parameters(spec, seed):
 class SimNet(torch.nn.Module):
     """A specification instantiated on the CUDA operators."""
 
-    def __init__(self, spec, seed=0, device="cuda"):
+    def __init__(self, spec, seed=0, device="cuda", dtype=torch.float32):
         super(SimNet, self).__init__()
         self.spec = spec
         mods, init = [], init_parameters(spec, seed)
         for entry, values in zip(spec["layers"], init):
             if entry[0] == "similarity":
                 m = layers.Similarity(**entry[1])
-                m.templates = torch.nn.Parameter(torch.from_numpy(values["templates"]).to(device))
-                m.sweights = torch.nn.Parameter(torch.from_numpy(values["weights"]).to(device))
+                m.sweights = torch.nn.Parameter(torch.from_numpy(values["weights"]).to(device=device, dtype=dtype))      # same order as build()
+                m.templates = torch.nn.Parameter(torch.from_numpy(values["templates"]).to(device=device, dtype=dtype))
                 mods.append(m)
             elif entry[0] == "mex":
                 m = layers.Mex(**entry[1])
                 m.blocks = list(values["offsets"].shape[2:])
-                m.offsets = torch.nn.Parameter(torch.from_numpy(values["offsets"]).to(device))
+                m.offsets = torch.nn.Parameter(torch.from_numpy(values["offsets"]).to(device=device, dtype=dtype))
                 mods.append(m)
             else:
                 mods.append(None)

@@ -11,24 +11,47 @@ from simnets_tf_b200.simnet import SPECS, SimNet
 pytestmark = pytest.mark.gpu
 
 
+def _run_gpu(spec, x, labels, dtype):
+    net = SimNet(spec, seed=5, device="cuda", dtype=dtype)
+    bucket = dp.GradBucket(net.parameters())
+    bucket.zero()
+    xd = torch.from_numpy(x).to(device="cuda", dtype=dtype)
+    with torch.no_grad():
+        logits = net(xd).cpu().numpy()
+    loss = net.loss(xd, torch.from_numpy(labels).cuda())
+    loss.backward()
+    for p in net.parameters():
+        assert p.grad.data_ptr() >= bucket.flat.data_ptr()          # gradients live inside the flat bucket
+    return logits, float(loss.detach()), [p.grad.cpu().numpy() for p in net.parameters()]
+
+
 @pytest.mark.parametrize("name,batch", [("cfg3", 6), ("cfg5", 4)])
 def test_network_step_matches_cpu_oracle(port, name, batch):
+    """Network-level gradients pass through the normalize_offsets backward, which cancels almost all of
+    each offsets gradient, so float32 rounding is amplified far beyond 1e-5 on BOTH sides.  Hence:
+    (1) float64 on the GPU must agree with the float64 oracle to 1e-7 (the same amplification acts on 1e-16; proves the wiring and the math);
+    (2) float32 on the GPU must be no farther from the float64 oracle than 3x the float32 oracle is."""
     from oracle.simnet_cpu import CpuSimNet
     spec = SPECS[name]
     rng = np.random.default_rng(11)
     x = rng.uniform(-0.5, 0.5, size=(batch,) + tuple(spec["input_shape"])).astype(np.float32)
     labels = rng.integers(0, spec["classes"], size=batch)
-    cpu = CpuSimNet(spec, port, seed=5, threads=2)
-    ref_loss, ref_grads = cpu.step(x, labels)
-    net = SimNet(spec, seed=5, device="cuda")
-    bucket = dp.GradBucket(net.parameters())
-    bucket.zero()
-    loss = net.loss(torch.from_numpy(x).cuda(), torch.from_numpy(labels).cuda())
-    loss.backward()
-    assert abs(float(loss) - ref_loss) <= 1e-5 * abs(ref_loss)
-    params = list(net.parameters())
-    assert len(params) == len(ref_grads)
-    assert sum(p.numel() for p in params) == {"cfg3": 701696, "cfg5": 773504}[name]
-    for i, (p, g) in enumerate(zip(params, ref_grads)):
-        assert p.grad.data_ptr() >= bucket.flat.data_ptr()          # gradients live inside the flat bucket
-        cases.assert_parity(p.grad.cpu().numpy(), g, tol=5e-5, what="%s grad %d %s" % (name, i, tuple(p.shape)))
+    cpu64 = CpuSimNet(spec, port, seed=5, threads=2, dtype=np.float64)
+    loss64, grads64 = cpu64.step(x, labels)
+    logits64 = cpu64.forward(torch.from_numpy(x.astype(np.float64))).detach().numpy()
+    cpu32 = CpuSimNet(spec, port, seed=5, threads=2)
+    loss32, grads32 = cpu32.step(x, labels)
+
+    g_logits, g_loss, g_grads = _run_gpu(spec, x, labels, torch.float64)
+    cases.assert_parity(g_logits, logits64, tol=1e-10, what=name + " f64 logits")
+    assert abs(g_loss - loss64) <= 1e-10 * max(1.0, float(np.abs(logits64).max()))
+    assert sum(g.size for g in g_grads) == {"cfg3": 701696, "cfg5": 773504}[name]
+    for i, (a, b) in enumerate(zip(g_grads, grads64)):
+        cases.assert_parity(a, b, tol=1e-7, what="%s f64 grad %d %s" % (name, i, a.shape))
+
+    f_logits, f_loss, f_grads = _run_gpu(spec, x, labels, torch.float32)
+    cases.assert_parity(f_logits, logits64.astype(np.float32), tol=1e-5, what=name + " f32 logits")
+    assert abs(f_loss - loss64) <= 2e-5 * max(1.0, float(np.abs(logits64).max()))
+    for i, (a, b32, b64) in enumerate(zip(f_grads, grads32, grads64)):
+        ours, ref = cases.rel_err(a, b64), cases.rel_err(b32, b64)
+        assert ours <= max(5e-5, 3 * ref), "%s f32 grad %d %s: %.3g from the f64 oracle, f32 oracle %.3g" % (name, i, a.shape, ours, ref)
