@@ -1,0 +1,420 @@
+// Similarity forward and parameter gradients as implicit-im2col generalized GEMMs (float32).
+//
+//   forward   y[n, m, pos]   = sum_k f(t[m,k], w[m,k], patch[k, (n,pos)])              i = m, j = position, q = tap
+//   params    (dT, dW)[m, k] = sum_{n,pos} g(dy[n,m,pos], patch[k,(n,pos)], t, w)      i = m, j = tap,      q = position
+//
+// with the reference's element functors (HUJI-Deep/simnets-tf include/utils/similarity_utils.hpp:17-119).
+// The patch matrix of the reference (src/utils/im2col.cpp:247-280) is never built: a tap table gives, for
+// each k = (c, kh, kw), its offset inside a sample and its (kh, kw); a position gives its patch corner.
+// NaN handling costs no branch in the inner loop: while an input value is staged into shared memory a NaN
+// becomes (value 0, mask 0) and the mask multiplies the term (ignore_nan_input modes); in the other modes
+// the NaN itself is staged and propagates through the arithmetic exactly as in the reference.
+// Per-(m,k) constants (0.5*log(w + fudge) - 0.5*log(2*pi), -w, -0.5*w) are computed once by a prepass,
+// which also lays the parameters out tap-major so that the forward kernel's loads are contiguous.
+#include "kernels.cuh"
+#include "tile.cuh"
+
+namespace simnets {
+
+namespace {
+
+constexpr double kLog2Pi = 1.8378770664093454835606594728112;
+constexpr int kDpTile = 64, kDpKC = 32;
+
+struct SimWs {
+    float* planes;   // [3][K][M]: t, scale (-w or -0.5w), per-term constant
+    float* cm;       // [M] per-instance constant added once per output
+    int2* taps;      // [K]: {offset of tap inside a sample, (kh << 16) | kw}
+    float* part;     // [S][3][M][K] split partial sums of the parameter gradients
+    size_t bytes;
+};
+
+__host__ inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+__host__ int dp_splits(const SimGeo& g) {
+    const long long P = (long long)g.B * g.N;
+    const long long chunks = (P + kDpKC - 1) / kDpKC;
+    const long long tiles = (long long)((g.M + kDpTile - 1) / kDpTile) * ((g.K + kDpTile - 1) / kDpTile);
+    long long s = (148 * 2 + tiles - 1) / tiles;
+    if (s > chunks) s = chunks;
+    if (s < 1) s = 1;
+    if (s > 512) s = 512;
+    return int(s);
+}
+
+__host__ SimWs carve(const SimGeo& g, void* base) {
+    SimWs w;
+    char* p = static_cast<char*>(base);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { char* r = p ? p + off : nullptr; off += align256(bytes); return r; };
+    w.planes = reinterpret_cast<float*>(take(sizeof(float) * 3 * (size_t)g.K * g.M));
+    w.cm = reinterpret_cast<float*>(take(sizeof(float) * g.M));
+    w.taps = reinterpret_cast<int2*>(take(sizeof(int2) * g.K));
+    w.part = reinterpret_cast<float*>(take(sizeof(float) * 3 * (size_t)dp_splits(g) * g.M * g.K));
+    w.bytes = off;
+    return w;
+}
+
+// One block per instance m: tap-major parameter planes, the per-instance constant, and (block 0) the tap table.
+__global__ void __launch_bounds__(128) sim_prep(SimGeo g, const float* __restrict__ tm, const float* __restrict__ wt,
+                                                float* __restrict__ planes, float* __restrict__ cm, int2* __restrict__ taps) {
+    __shared__ float red[128];
+    const int m = blockIdx.x;
+    const float fudge = float(g.fudge);
+    const size_t plane = (size_t)g.K * g.M;
+    float csum = 0.f;
+    for (int k = threadIdx.x; k < g.K; k += 128) {
+        const float t = tm[(size_t)m * g.K + k], w = wt[(size_t)m * g.K + k];
+        float scale = -w, c = 0.f;
+        if (g.mode == SIM_L2N) { scale = -0.5f * w; csum += 0.5f * logf(w + fudge); }
+        if (g.mode == SIM_L2N_NAN) { scale = -0.5f * w; c = float(0.5 * (double(logf(w + fudge)) - kLog2Pi)); }
+        planes[(size_t)k * g.M + m] = t;
+        planes[plane + (size_t)k * g.M + m] = scale;
+        planes[2 * plane + (size_t)k * g.M + m] = c;
+        if (m == 0) {
+            const int kw = k % g.bw, kh = (k / g.bw) % g.bh, c_ = k / (g.bw * g.bh);
+            taps[k] = make_int2((c_ * g.H + kh) * g.W + kw, (kh << 16) | kw);
+        }
+    }
+    red[threadIdx.x] = csum;
+    __syncthreads();
+    for (int s = 64; s > 0; s >>= 1) {
+        if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) cm[m] = g.mode == SIM_L2N ? red[0] + float(-0.5 * double(g.K) * kLog2Pi) : 0.f;
+}
+
+struct SimColumn {
+    long long base;     // n*M*N + pos, or -1 past the end
+    int n, h0, w0;      // sample, patch corner
+};
+
+__device__ __forceinline__ SimColumn sim_column(const SimGeo& g, long long j, long long P) {
+    SimColumn c;
+    c.base = -1; c.n = 0; c.h0 = c.w0 = 0;
+    if (j >= P) return c;
+    const int n = int(j / g.N), pos = int(j % g.N);
+    c.n = n;
+    c.h0 = (pos / g.ow) * g.sh - g.ph;
+    c.w0 = (pos % g.ow) * g.sw - g.pw;
+    c.base = (long long)n * g.M * g.N + pos;
+    return c;
+}
+
+__device__ __forceinline__ float sim_tap_value(const SimGeo& g, const float* __restrict__ xs, const SimColumn& col, int2 tap, float oob) {
+    const int hh = col.h0 + (tap.y >> 16), ww = col.w0 + (tap.y & 0xffff);
+    if (hh >= 0 && hh < g.H && ww >= 0 && ww < g.W) return __ldg(xs + tap.x + col.h0 * g.W + col.w0);
+    return oob;
+}
+
+// ------------------------------------------------------------------- forward
+// MODE is a SimMode; NA = parameter planes used, NB = input planes (value [, mask]).
+template <int MODE> struct FwdPlanes {
+    static constexpr int NA = MODE == SIM_L2N_NAN ? 3 : 2;
+    static constexpr int NB = (MODE == SIM_L2N_NAN || MODE == SIM_L1_SKIP) ? 2 : 1;
+};
+
+template <int TM, int MODE>
+__global__ void __launch_bounds__(256) sim_fwd_tiled(SimGeo g, const float* __restrict__ x, const float* __restrict__ planes,
+                                                     const float* __restrict__ cm, const int2* __restrict__ taps, float* __restrict__ y) {
+    constexpr int NA = FwdPlanes<MODE>::NA, NB = FwdPlanes<MODE>::NB;
+    using Cfg = TileCfg<TM, 128, 8, TM / 16, 8, NA, NB>;
+    static_assert(Cfg::THREADS == 256, "256 threads");
+    __shared__ __align__(16) float smem[Cfg::SMEM_FLOATS];
+    __shared__ SimColumn cols[Cfg::TN];
+    const long long P = (long long)g.B * g.N;
+    const int mtiles = (g.M + TM - 1) / TM;
+    const int mt = blockIdx.x % mtiles;
+    const long long jt = blockIdx.x / mtiles;
+    const int i0 = mt * TM;
+    const long long j0 = jt * Cfg::TN;
+    if (threadIdx.x < Cfg::TN) cols[threadIdx.x] = sim_column(g, j0 + threadIdx.x, P);
+    __syncthreads();
+
+    const TileThread<Cfg> t;
+    const float oob = float(g.oob);
+    const size_t plane = (size_t)g.K * g.M;
+    const int s_lane = threadIdx.x % 128, s_k = threadIdx.x / 128;
+    const SimColumn sc = cols[s_lane];
+    const float* xs = x + (size_t)sc.n * g.C * g.H * g.W;
+    constexpr int A_ROWS = 256 / TM;
+    const int a_lane = threadIdx.x % TM, a_k = threadIdx.x / TM;
+    float ra[Cfg::A_PER][NA], rb[Cfg::B_PER];
+
+    float acc[Cfg::RM][Cfg::RN];
+#pragma unroll
+    for (int r_ = 0; r_ < Cfg::RM; ++r_)
+#pragma unroll
+        for (int c_ = 0; c_ < Cfg::RN; ++c_) acc[r_][c_] = 0.f;
+
+    auto fetchA = [&](int chunk) {
+#pragma unroll
+        for (int s = 0; s < Cfg::A_PER; ++s) {
+            const int k = chunk * Cfg::KC + a_k + s * A_ROWS, m = i0 + a_lane;
+            const bool ok = k < g.K && m < g.M;
+#pragma unroll
+            for (int p = 0; p < NA; ++p) ra[s][p] = ok ? __ldg(planes + p * plane + (size_t)k * g.M + m) : 0.f;
+        }
+    };
+    auto fetchB = [&](int chunk) {
+#pragma unroll
+        for (int s = 0; s < Cfg::B_PER; ++s) {
+            const int k = chunk * Cfg::KC + s_k + s * 2;
+            // rows past K pair a zero scale / zero constant with a finite value: the term is exactly 0
+            rb[s] = (k < g.K && sc.base >= 0) ? sim_tap_value(g, xs, sc, __ldg(taps + k), oob) : 0.f;
+        }
+    };
+    auto commitA = [&](float* As) {
+#pragma unroll
+        for (int s = 0; s < Cfg::A_PER; ++s)
+#pragma unroll
+            for (int p = 0; p < NA; ++p) As[p * Cfg::KC * TM + (a_k + s * A_ROWS) * TM + a_lane] = ra[s][p];
+    };
+    auto commitB = [&](float* Bs) {
+#pragma unroll
+        for (int s = 0; s < Cfg::B_PER; ++s) {
+            const int o = (s_k + s * 2) * Cfg::TN + s_lane;
+            if (NB == 2) {
+                const bool nan = rb[s] != rb[s];
+                Bs[o] = nan ? 0.f : rb[s];
+                Bs[Cfg::KC * Cfg::TN + o] = nan ? 0.f : 1.f;
+            } else {
+                Bs[o] = rb[s];
+            }
+        }
+    };
+    auto comb = [&](int r_, int c_, const float (&a)[NA], const float (&b)[NB]) {
+        const float d = a[0] - b[0];
+        if (MODE == SIM_L1) acc[r_][c_] = fmaf(a[1], fabsf(d), acc[r_][c_]);
+        else if (MODE == SIM_L1_SKIP) acc[r_][c_] = fmaf(a[1], fabsf(d) * b[NB - 1], acc[r_][c_]);
+        else if (MODE == SIM_L2N_NAN) acc[r_][c_] = fmaf(b[NB - 1], fmaf(a[1] * d, d, a[NA - 1]), acc[r_][c_]);
+        else acc[r_][c_] = fmaf(a[1] * d, d, acc[r_][c_]);
+    };
+    tile_mainloop<Cfg, false, false>(smem, (g.K + Cfg::KC - 1) / Cfg::KC, t, fetchA, fetchB, commitA, commitB, comb);
+
+#pragma unroll
+    for (int r_ = 0; r_ < Cfg::RM; ++r_) {
+        const int m = i0 + t.row(r_);
+        if (m >= g.M) continue;
+        const float cmm = cm[m];
+#pragma unroll
+        for (int c_ = 0; c_ < Cfg::RN; ++c_) {
+            const SimColumn& col = cols[t.col(c_)];
+            if (col.base < 0) continue;
+            float v = acc[r_][c_];
+            if (MODE == SIM_L2N) {
+                v += cmm;
+                if (g.batch_quirk) v += float(-0.5 * double(g.K) * kLog2Pi) * float(g.B - col.n - 1);
+            }
+            __stcs(y + col.base + (long long)m * g.N, v);
+        }
+    }
+}
+
+// -------------------------------------------------------- parameter gradients
+// Accumulators per output (m, k): sT = sum a*d, sW = sum a*d*d (L1: a*sign(d), a*|d|), sN = sum a*mask,
+// with a = dy and d = mask*(x - t).  Both operands are contiguous along q (positions) in memory.
+template <int MODE>
+__global__ void __launch_bounds__(256) sim_dparams_tiled(SimGeo g, const float* __restrict__ x, const float* __restrict__ tm,
+                                                         const float* __restrict__ dy, const int2* __restrict__ taps,
+                                                         float* __restrict__ part, int splits) {
+    constexpr bool MASKED = MODE == SIM_L2N_NAN || MODE == SIM_L1_SKIP;
+    constexpr bool NORM = MODE == SIM_L2N || MODE == SIM_L2N_NAN;
+    constexpr bool L1 = MODE == SIM_L1 || MODE == SIM_L1_SKIP;
+    constexpr int NB = MASKED ? 2 : 1;
+    using Cfg = TileCfg<kDpTile, kDpTile, kDpKC, 4, 4, 1, NB>;
+    static_assert(Cfg::THREADS == 256, "256 threads");
+    __shared__ __align__(16) float smem[Cfg::SMEM_FLOATS];
+    const long long P = (long long)g.B * g.N;
+    const int ktiles = (g.K + kDpTile - 1) / kDpTile, mtiles = (g.M + kDpTile - 1) / kDpTile;
+    int bid = blockIdx.x;
+    const int kt = bid % ktiles; bid /= ktiles;
+    const int mt = bid % mtiles;
+    const int split = bid / mtiles;
+    const int i0 = mt * kDpTile, jk0 = kt * kDpTile;
+    const long long chunks = (P + kDpKC - 1) / kDpKC;
+    const long long c_begin = chunks * split / splits, c_end = chunks * (split + 1) / splits;
+
+    const TileThread<Cfg> t;
+    const float oob = float(g.oob);
+    const int qq = threadIdx.x % 32, e0 = threadIdx.x / 32;
+    SimColumn cur;
+    float ra[Cfg::A_PER], rb[Cfg::B_PER];
+    int2 mytaps[Cfg::B_PER];
+#pragma unroll
+    for (int s = 0; s < Cfg::B_PER; ++s) {
+        const int k = jk0 + e0 + 8 * s;
+        mytaps[s] = k < g.K ? taps[k] : make_int2(0, 0);
+    }
+    float tt[4][4];
+#pragma unroll
+    for (int r_ = 0; r_ < 4; ++r_)
+#pragma unroll
+        for (int c_ = 0; c_ < 4; ++c_) {
+            const int m = i0 + t.row(r_), k = jk0 + t.col(c_);
+            tt[r_][c_] = (m < g.M && k < g.K) ? tm[(size_t)m * g.K + k] : 0.f;
+        }
+    float sT[4][4], sW[4][4], sN[4][4];
+#pragma unroll
+    for (int r_ = 0; r_ < 4; ++r_)
+#pragma unroll
+        for (int c_ = 0; c_ < 4; ++c_) { sT[r_][c_] = 0.f; sW[r_][c_] = 0.f; sN[r_][c_] = 0.f; }
+
+    auto fetchA = [&](int chunk) {
+        cur = sim_column(g, (c_begin + chunk) * kDpKC + qq, P);
+#pragma unroll
+        for (int s = 0; s < Cfg::A_PER; ++s) {
+            const int m = i0 + e0 + 8 * s;
+            ra[s] = (cur.base >= 0 && m < g.M) ? __ldcs(dy + cur.base + (long long)m * g.N) : 0.f;
+        }
+    };
+    auto fetchB = [&](int) {
+        const float* xs = x + (size_t)cur.n * g.C * g.H * g.W;
+#pragma unroll
+        for (int s = 0; s < Cfg::B_PER; ++s) {
+            const int k = jk0 + e0 + 8 * s;
+            // dead positions carry dy = 0 and a finite value, so every term they touch is exactly 0
+            rb[s] = (cur.base >= 0 && k < g.K) ? sim_tap_value(g, xs, cur, mytaps[s], oob) : 0.f;
+        }
+    };
+    auto commitA = [&](float* As) {
+#pragma unroll
+        for (int s = 0; s < Cfg::A_PER; ++s) As[stage_offset<kDpTile, true>(qq, e0 + 8 * s)] = ra[s];
+    };
+    auto commitB = [&](float* Bs) {
+#pragma unroll
+        for (int s = 0; s < Cfg::B_PER; ++s) {
+            const int o = stage_offset<kDpTile, true>(qq, e0 + 8 * s);
+            if (MASKED) {
+                const bool nan = rb[s] != rb[s];
+                Bs[o] = nan ? 0.f : rb[s];
+                Bs[Cfg::KC * Cfg::TN + o] = (nan || cur.base < 0) ? 0.f : 1.f;
+            } else {
+                Bs[o] = rb[s];
+            }
+        }
+    };
+    auto comb = [&](int r_, int c_, const float (&a)[1], const float (&b)[NB]) {
+        const float d = MASKED ? fmaf(-tt[r_][c_], b[NB - 1], b[0]) : b[0] - tt[r_][c_];
+        if (L1) {
+            const float sg = float((0.f < d) - (d < 0.f));
+            sT[r_][c_] = fmaf(a[0], sg, sT[r_][c_]);
+            sW[r_][c_] = fmaf(a[0], fabsf(d), sW[r_][c_]);
+        } else {
+            const float u = a[0] * d;
+            sT[r_][c_] += u;
+            sW[r_][c_] = fmaf(u, d, sW[r_][c_]);
+            if (NORM) sN[r_][c_] = MASKED ? fmaf(a[0], b[NB - 1], sN[r_][c_]) : sN[r_][c_] + a[0];
+        }
+    };
+    tile_mainloop<Cfg, true, true>(smem, int(c_end - c_begin), t, fetchA, fetchB, commitA, commitB, comb);
+
+    const size_t mk = (size_t)g.M * g.K;
+    float* dst = part + (size_t)split * 3 * mk;
+#pragma unroll
+    for (int r_ = 0; r_ < 4; ++r_) {
+        const int m = i0 + t.row(r_);
+        if (m >= g.M) continue;
+#pragma unroll
+        for (int c_ = 0; c_ < 4; ++c_) {
+            const int k = jk0 + t.col(c_);
+            if (k >= g.K) continue;
+            dst[(size_t)m * g.K + k] = sT[r_][c_];
+            dst[mk + (size_t)m * g.K + k] = sW[r_][c_];
+            if (NORM) dst[2 * mk + (size_t)m * g.K + k] = sN[r_][c_];
+        }
+    }
+}
+
+// Sums the split partials in split order and applies the per-parameter factors of the backward functors.
+__global__ void __launch_bounds__(256) sim_dparams_reduce(SimGeo g, int splits, const float* __restrict__ part,
+                                                          const float* __restrict__ wt, float* __restrict__ dt, float* __restrict__ dw,
+                                                          int accumulate) {
+    const int mk = g.M * g.K;
+    const float fudge = float(g.fudge);
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < mk; i += gridDim.x * 256) {
+        float a = 0.f, b = 0.f, c = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float* p = part + (size_t)s * 3 * mk;
+            a += p[i]; b += p[mk + i];
+            if (g.mode == SIM_L2N || g.mode == SIM_L2N_NAN) c += p[2 * mk + i];
+        }
+        const float w = wt[i];
+        float gt, gw;
+        if (g.mode == SIM_L1 || g.mode == SIM_L1_SKIP) { gt = w * a; gw = -b; }
+        else if (g.mode == SIM_L2) { gt = 2.f * w * a; gw = -b; }
+        else { gt = w * a; gw = 0.5f * (c / (w + fudge) - b); }
+        dt[i] = accumulate ? dt[i] + gt : gt;
+        dw[i] = accumulate ? dw[i] + gw : gw;
+    }
+}
+
+void launch_prep(const SimGeo& g, const SimWs& w, const float* t, const float* wt, cudaStream_t s) {
+    sim_prep<<<g.M, 128, 0, s>>>(g, t, wt, w.planes, w.cm, w.taps);
+    count_launch();
+}
+
+}  // namespace
+
+bool sim_use_tiled(const SimGeo& g, bool f64, uint32_t flags) {
+    if (f64 || g.B == 0) return false;
+    if (flags & SIMNETS_FLAG_FORCE_DIRECT) return false;
+    if (g.bh >= 32768 || g.bw >= 32768) return false;
+    return true;
+}
+
+size_t sim_workspace_bytes(const SimGeo& g, bool f64, uint32_t flags) {
+    if (!sim_use_tiled(g, f64, flags)) return 256;
+    return carve(g, nullptr).bytes;
+}
+
+cudaError_t launch_sim_fwd_tiled(const SimGeo& g, const float* x, const float* t, const float* w, float* y, void* ws, cudaStream_t s) {
+    const SimWs W = carve(g, ws);
+    launch_prep(g, W, t, w, s);
+    const long long P = (long long)g.B * g.N;
+    const bool wide = g.M > 64;
+    const long long blocks = ((P + 127) / 128) * ((g.M + (wide ? 127 : 63)) / (wide ? 128 : 64));
+    if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+#define FWD(TM, MODE) sim_fwd_tiled<TM, MODE><<<int(blocks), 256, 0, s>>>(g, x, W.planes, W.cm, W.taps, y)
+#define FWD_MODES(TM)                                        \
+    switch (g.mode) {                                        \
+    case SIM_L1: FWD(TM, SIM_L1); break;                     \
+    case SIM_L1_SKIP: FWD(TM, SIM_L1_SKIP); break;           \
+    case SIM_L2: FWD(TM, SIM_L2); break;                     \
+    case SIM_L2N: FWD(TM, SIM_L2N); break;                   \
+    default: FWD(TM, SIM_L2N_NAN); break;                    \
+    }
+    if (wide) { FWD_MODES(128) } else { FWD_MODES(64) }
+#undef FWD_MODES
+#undef FWD
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_sim_dx_tiled(const SimGeo& g, const float* x, const float* t, const float* w, const float* dy, float* dx, void*, cudaStream_t s) {
+    return launch_sim_dx_direct(g, false, x, t, w, dy, dx, s);
+}
+
+cudaError_t launch_sim_dparams_tiled(const SimGeo& g, const float* x, const float* t, const float* w, const float* dy,
+                                     float* dt, float* dw, bool accumulate, void* ws, cudaStream_t s) {
+    const SimWs W = carve(g, ws);
+    launch_prep(g, W, t, w, s);
+    const int splits = dp_splits(g);
+    const int blocks = ((g.M + kDpTile - 1) / kDpTile) * ((g.K + kDpTile - 1) / kDpTile) * splits;
+#define DP(MODE) sim_dparams_tiled<MODE><<<blocks, 256, 0, s>>>(g, x, t, dy, W.taps, W.part, splits)
+    switch (g.mode) {
+    case SIM_L1: DP(SIM_L1); break;
+    case SIM_L1_SKIP: DP(SIM_L1_SKIP); break;
+    case SIM_L2: DP(SIM_L2); break;
+    case SIM_L2N: DP(SIM_L2N); break;
+    default: DP(SIM_L2N_NAN); break;
+    }
+#undef DP
+    const int mk = g.M * g.K;
+    sim_dparams_reduce<<<std::min((mk + 255) / 256, 148 * 8), 256, 0, s>>>(g, splits, W.part, w, dt, dw, accumulate);
+    count_launch(2);
+    return cudaGetLastError();
+}
+
+}  // namespace simnets
