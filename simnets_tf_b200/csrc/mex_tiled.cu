@@ -34,14 +34,15 @@ constexpr float kSafeSpread = 60.0f;
 struct MexWs {           // workspace carve-up, every part 256-byte aligned
     int* flag;           // != 0: factorisation unsafe, take the exact kernels
     float* mo;           // [R][M]
-    float* eo;           // [R][M][K]   Eo, offsets layout
-    float* eot;          // [R][K][M]   Eo transposed
+    float* eo;           // [R][M][Kp]  Eo, offsets layout, rows padded to a multiple of 4 floats
+    float* eot;          // [R][K][Mp]  Eo transposed, rows padded likewise (16-byte aligned rows for async copies)
     float* mx;           // [B][N]
     float* part;         // [S][R][M][K] split-q partial sums of the offsets gradient
     size_t bytes;
 };
 
 __host__ inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+__host__ __device__ inline int pad4(int v) { return (v + 3) & ~3; }
 
 constexpr int kDoffTile = 64, kDoffKC = 32;
 
@@ -63,8 +64,8 @@ __host__ MexWs carve(const MexGeo& g, void* base) {
     auto take = [&](size_t bytes) { char* r = p ? p + off : nullptr; off += align256(bytes); return r; };
     w.flag = reinterpret_cast<int*>(take(16));
     w.mo = reinterpret_cast<float*>(take(sizeof(float) * g.R * g.M));
-    w.eo = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.M * g.K));
-    w.eot = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.M * g.K));
+    w.eo = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.M * pad4(g.K)));
+    w.eot = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.K * pad4(g.M)));
     w.mx = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.B * g.N));
     w.part = reinterpret_cast<float*>(take(sizeof(float) * (size_t)doff_splits(g) * g.R * g.M * g.K));
     w.bytes = off;
@@ -105,8 +106,8 @@ __global__ void __launch_bounds__(128) mex_prep_offsets(MexGeo g, const float* _
     }
     for (int k = threadIdx.x; k < g.K; k += 128) {
         const float e = fast_exp(eps * (o[k] - ref));
-        eo[(size_t)rm * g.K + k] = e;
-        eot[((size_t)r * g.K + k) * g.M + m] = e;
+        eo[(size_t)rm * pad4(g.K) + k] = e;
+        eot[((size_t)r * g.K + k) * pad4(g.M) + m] = e;
     }
 }
 
@@ -127,6 +128,13 @@ __device__ __forceinline__ float patch_value(const MexGeo& g, const float* __res
     const int cc = c0 + t.c, hh = h0 + t.h, ww = w0 + t.w;
     if (cc >= 0 && cc < g.C && hh >= 0 && hh < g.H && ww >= 0 && ww < g.W) return __ldg(xs + ((size_t)cc * g.H + hh) * g.W + ww);
     return oob;
+}
+
+// Index of tap k of the patch at (c0, h0, w0) inside its sample, for geometries in which no patch leaves the input.
+template <bool SPATIAL1>
+__device__ __forceinline__ int interior_index(const MexGeo& g, int c0, int h0, int w0, int k) {
+    const Tap t = tap_of<SPATIAL1>(g, k);
+    return ((c0 + t.c) * g.H + h0 + t.h) * g.W + w0 + t.w;
 }
 
 // mx[n][pos] = max (eps > 0) or min (eps < 0) over the K taps of the patch at pos; NaN taps are ignored,
@@ -175,7 +183,8 @@ __device__ __forceinline__ Column column_of(const MexGeo& g, int r, long long jl
 
 // ------------------------------------------------------------------- forward
 // C[i = m, j = position] = sum_{q = k} EoT[k][m] * Ex[k][j]
-template <int TM, bool SPATIAL1>
+// INTERIOR: no patch of this geometry leaves the input, so taps need no bounds test.
+template <int TM, bool SPATIAL1, bool INTERIOR>
 __global__ void __launch_bounds__(256) mex_fwd_tiled(MexGeo g, const float* __restrict__ x, const float* __restrict__ eot,
                                                      const float* __restrict__ mo, const float* __restrict__ mx,
                                                      float* __restrict__ y, const int* __restrict__ flag) {
@@ -183,7 +192,8 @@ __global__ void __launch_bounds__(256) mex_fwd_tiled(MexGeo g, const float* __re
     static_assert(Cfg::THREADS == 256, "256 threads");
     if (*flag) return;
     __shared__ __align__(16) float smem[Cfg::SMEM_FLOATS];
-    __shared__ Column cols[Cfg::TN];
+    __shared__ long long col_base[Cfg::TN];
+    __shared__ float col_mx[Cfg::TN];
     const long long P = (long long)g.B * g.rs;                 // positions of one region over the batch
     const int mtiles = (g.M + TM - 1) / TM;
     int bid = blockIdx.x;
@@ -192,66 +202,61 @@ __global__ void __launch_bounds__(256) mex_fwd_tiled(MexGeo g, const float* __re
     const long long jt = bid / mtiles;
     const int i0 = mt * TM;
     const long long j0 = jt * Cfg::TN;
-    if (threadIdx.x < Cfg::TN) cols[threadIdx.x] = column_of(g, r, j0 + threadIdx.x, P, mx);
-    __syncthreads();
 
-    const TileThread<Cfg> t;
-    const float eps = float(g.eps), oob = float(g.oob);
-    // staging roles: element e of a chunk = (kk, lane) with lane fastest (contiguous global reads)
-    const int s_lane = threadIdx.x % 128, s_k = threadIdx.x / 128;          // TM or TN lanes, 2 k-rows per pass
-    const Column sc = cols[s_lane];
+    // staging role: this thread stages column s_lane, rows s_k, s_k + 2, ... of every chunk
+    const int s_lane = threadIdx.x % 128, s_k = threadIdx.x / 128;
+    const Column sc = column_of(g, r, j0 + s_lane, P, mx);
+    if (s_k == 0) { col_base[s_lane] = sc.base; col_mx[s_lane] = sc.mx; }
     const float* xs = x + (size_t)sc.n * g.C * g.H * g.W;
-    const float* arow = eot + (size_t)r * g.K * g.M;
-    float ra[Cfg::A_PER], rb[Cfg::B_PER];
-    constexpr int A_LANES = TM, A_ROWS = 256 / TM;                            // rows of the chunk one pass covers
-    const int a_lane = threadIdx.x % A_LANES, a_k = threadIdx.x / A_LANES;
+    const bool live = sc.base >= 0;
+    const float eps = float(g.eps), oob = float(g.oob);
+    const float dead = eps > 0 ? -CUDART_INF_F : CUDART_INF_F;  // exp(eps * (dead - mx)) == 0
+    const float* arow = eot + (size_t)r * g.K * pad4(g.M);
+    const int ldm = pad4(g.M);
+    const TileThread<Cfg> t;
+    float rb[Cfg::B_PER];
 
-    float acc[Cfg::RM][Cfg::RN];
+    float2 acc[Cfg::RM][Cfg::RN / 2];
 #pragma unroll
     for (int r_ = 0; r_ < Cfg::RM; ++r_)
 #pragma unroll
-        for (int c_ = 0; c_ < Cfg::RN; ++c_) acc[r_][c_] = 0.f;
+        for (int c_ = 0; c_ < Cfg::RN / 2; ++c_) acc[r_][c_] = make_float2(0.f, 0.f);
 
-    auto fetchA = [&](int chunk) {
-#pragma unroll
-        for (int s = 0; s < Cfg::A_PER; ++s) {
-            const int k = chunk * Cfg::KC + a_k + s * A_ROWS, m = i0 + a_lane;
-            ra[s] = (k < g.K && m < g.M) ? __ldg(arow + (size_t)k * g.M + m) : 0.f;
-        }
-    };
-    auto fetchB = [&](int chunk) {
+    auto fetchA = [&](int chunk, float* As) { stage_copy_async<Cfg, TM>(As, arow, ldm, chunk * Cfg::KC, g.K, i0, g.M); };
+    auto fetchB = [&](int chunk, float*) {
 #pragma unroll
         for (int s = 0; s < Cfg::B_PER; ++s) {
             const int k = chunk * Cfg::KC + s_k + s * 2;
-            rb[s] = (k < g.K && sc.base >= 0) ? patch_value<SPATIAL1>(g, xs, sc.c0, sc.h0, sc.w0, k, oob) : -CUDART_INF_F * (eps > 0 ? 1.f : -1.f);
+            if (!live || k >= g.K) rb[s] = dead;
+            else if (INTERIOR) rb[s] = __ldg(xs + interior_index<SPATIAL1>(g, sc.c0, sc.h0, sc.w0, k));
+            else rb[s] = patch_value<SPATIAL1>(g, xs, sc.c0, sc.h0, sc.w0, k, oob);
         }
     };
-    auto commitA = [&](float* As) {
-#pragma unroll
-        for (int s = 0; s < Cfg::A_PER; ++s) As[(a_k + s * A_ROWS) * TM + a_lane] = ra[s];
-    };
+    auto commitA = [&](float*) { cp_async_wait_all(); };
     auto commitB = [&](float* Bs) {
 #pragma unroll
-        for (int s = 0; s < Cfg::B_PER; ++s) {
-            // padding rows of the last chunk and dead columns hold -inf*sign(eps): exp() gives exactly 0
-            const float e = (sc.base >= 0) ? fast_exp(eps * (rb[s] - sc.mx)) : 0.f;
-            Bs[(s_k + s * 2) * Cfg::TN + s_lane] = e;
-        }
+        for (int s = 0; s < Cfg::B_PER; ++s) Bs[(s_k + s * 2) * Cfg::TN + s_lane] = live ? fast_exp(eps * (rb[s] - sc.mx)) : 0.f;
     };
-    auto comb = [&](int r_, int c_, const float (&a)[1], const float (&b)[1]) { acc[r_][c_] = fmaf(a[0], b[0], acc[r_][c_]); };
+    auto comb = [&](int r_, int cp, const float2 (&a)[1], const float2 (&b)[1]) { acc[r_][cp] = fma2(a[0], b[0], acc[r_][cp]); };
     tile_mainloop<Cfg, false, false>(smem, (g.K + Cfg::KC - 1) / Cfg::KC, t, fetchA, fetchB, commitA, commitB, comb);
 
-    const float inv_eps = 1.f / eps, cst = float(g.cst);
+    // y = mx + mo + (log S + c)/eps, with log S = log2 S * ln 2
+    const float inv_eps = 1.f / eps, k_log = 0.69314718056f * inv_eps, k_cst = float(g.cst) * inv_eps;
+    long long cb[Cfg::RN];
+    float cm_[Cfg::RN];
+#pragma unroll
+    for (int c_ = 0; c_ < Cfg::RN; ++c_) { cb[c_] = col_base[t.col(c_)]; cm_[c_] = col_mx[t.col(c_)] + k_cst; }
 #pragma unroll
     for (int r_ = 0; r_ < Cfg::RM; ++r_) {
         const int m = i0 + t.row(r_);
         if (m >= g.M) continue;
         const float mom = mo[r * g.M + m];
+        float* yrow = y + (long long)m * g.N;
 #pragma unroll
         for (int c_ = 0; c_ < Cfg::RN; ++c_) {
-            const Column& col = cols[t.col(c_)];
-            if (col.base < 0) continue;
-            __stcs(y + col.base + (long long)m * g.N, col.mx + mom + (fast_log(acc[r_][c_]) + cst) * inv_eps);
+            if (cb[c_] < 0) continue;
+            const float sacc = (c_ & 1) ? acc[r_][c_ >> 1].y : acc[r_][c_ >> 1].x;
+            __stcs(yrow + cb[c_], fmaf(__log2f(sacc), k_log, cm_[c_] + mom));
         }
     }
 }
@@ -276,59 +281,47 @@ __global__ void __launch_bounds__(256) mex_dx_tiled(MexGeo g, const float* __res
     const long long jt = bid / ktiles;
     const int i0 = kt * TM;
     const long long j0 = jt * Cfg::TN;
-    if (threadIdx.x < Cfg::TN) cols[threadIdx.x] = column_of(g, r, j0 + threadIdx.x, P, mx);
-    __syncthreads();
 
-    const TileThread<Cfg> t;
-    const float eps = float(g.eps), cst = float(g.cst), oob = float(g.oob);
     const int s_lane = threadIdx.x % 128, s_k = threadIdx.x / 128;
-    const Column sc = cols[s_lane];
-    constexpr int A_LANES = TM, A_ROWS = 256 / TM;
-    const int a_lane = threadIdx.x % A_LANES, a_k = threadIdx.x / A_LANES;
-    const float* arow = eo + (size_t)r * g.M * g.K;
+    const Column sc = column_of(g, r, j0 + s_lane, P, mx);
+    if (s_k == 0) cols[s_lane] = sc;
+    const bool live = sc.base >= 0;
+    const TileThread<Cfg> t;
+    const float eps = float(g.eps), cst = float(g.cst);
+    const float* arow = eo + (size_t)r * g.M * pad4(g.K);
+    const int ldk = pad4(g.K);
     const float* mor = mo + r * g.M;
-    float ra[Cfg::A_PER], rby[Cfg::B_PER], rbg[Cfg::B_PER], rbm[Cfg::B_PER];
+    float rby[Cfg::B_PER], rbg[Cfg::B_PER], rbm[Cfg::B_PER];
 
-    float acc[Cfg::RM][Cfg::RN];
+    float2 acc[Cfg::RM][Cfg::RN / 2];
 #pragma unroll
     for (int r_ = 0; r_ < Cfg::RM; ++r_)
 #pragma unroll
-        for (int c_ = 0; c_ < Cfg::RN; ++c_) acc[r_][c_] = 0.f;
+        for (int c_ = 0; c_ < Cfg::RN / 2; ++c_) acc[r_][c_] = make_float2(0.f, 0.f);
 
-    auto fetchA = [&](int chunk) {
-#pragma unroll
-        for (int s = 0; s < Cfg::A_PER; ++s) {
-            const int m = chunk * Cfg::KC + a_k + s * A_ROWS, k = i0 + a_lane;
-            ra[s] = (m < g.M && k < g.K) ? __ldg(arow + (size_t)m * g.K + k) : 0.f;
-        }
-    };
-    auto fetchB = [&](int chunk) {
+    auto fetchA = [&](int chunk, float* As) { stage_copy_async<Cfg, TM>(As, arow, ldk, chunk * Cfg::KC, g.M, i0, g.K); };
+    auto fetchB = [&](int chunk, float*) {
 #pragma unroll
         for (int s = 0; s < Cfg::B_PER; ++s) {
             const int m = chunk * Cfg::KC + s_k + s * 2;
-            const bool ok = m < g.M && sc.base >= 0;
+            const bool ok = m < g.M && live;
             rby[s] = ok ? __ldcs(y + sc.base + (long long)m * g.N) : 0.f;
             rbg[s] = ok ? __ldcs(dy + sc.base + (long long)m * g.N) : 0.f;
             rbm[s] = ok ? __ldg(mor + m) : 0.f;
         }
     };
-    auto commitA = [&](float* As) {
-#pragma unroll
-        for (int s = 0; s < Cfg::A_PER; ++s) As[(a_k + s * A_ROWS) * TM + a_lane] = ra[s];
-    };
+    auto commitA = [&](float*) { cp_async_wait_all(); };
     auto commitB = [&](float* Bs) {
 #pragma unroll
-        for (int s = 0; s < Cfg::B_PER; ++s) {
-            const int m = s_k + s * 2;      // row inside the chunk; rows past M carry dy = 0
-            Bs[m * Cfg::TN + s_lane] = rbg[s] * fast_exp(eps * (sc.mx + rbm[s] - rby[s]) + cst);
-        }
+        for (int s = 0; s < Cfg::B_PER; ++s)       // rows past M and dead columns carry dy = 0
+            Bs[(s_k + s * 2) * Cfg::TN + s_lane] = rbg[s] * fast_exp(eps * (sc.mx + rbm[s] - rby[s]) + cst);
     };
-    auto comb = [&](int r_, int c_, const float (&a)[1], const float (&b)[1]) { acc[r_][c_] = fmaf(a[0], b[0], acc[r_][c_]); };
+    auto comb = [&](int r_, int cp, const float2 (&a)[1], const float2 (&b)[1]) { acc[r_][cp] = fma2(a[0], b[0], acc[r_][cp]); };
     tile_mainloop<Cfg, false, false>(smem, (g.M + Cfg::KC - 1) / Cfg::KC, t, fetchA, fetchB, commitA, commitB, comb);
 
 #pragma unroll
     for (int c_ = 0; c_ < Cfg::RN; ++c_) {
-        const Column& col = cols[t.col(c_)];
+        const Column col = cols[t.col(c_)];
         if (col.base < 0) continue;
         const size_t sample = (size_t)col.n * g.C * g.H * g.W;
 #pragma unroll
@@ -339,10 +332,10 @@ __global__ void __launch_bounds__(256) mex_dx_tiled(MexGeo g, const float* __res
             const int cc = col.c0 + tp.c, hh = col.h0 + tp.h, ww = col.w0 + tp.w;
             if (cc < 0 || cc >= g.C || hh < 0 || hh >= g.H || ww < 0 || ww >= g.W) continue;
             const size_t a = sample + ((size_t)cc * g.H + hh) * g.W + ww;
-            dx[a] = fast_exp(eps * (__ldg(x + a) - col.mx)) * acc[r_][c_];
+            const float sacc = (c_ & 1) ? acc[r_][c_ >> 1].y : acc[r_][c_ >> 1].x;
+            dx[a] = fast_exp(eps * (__ldg(x + a) - col.mx)) * sacc;
         }
     }
-    (void)oob;
 }
 
 // ---------------------------------------------------------- offsets gradient
@@ -372,16 +365,19 @@ __global__ void __launch_bounds__(256) mex_doff_tiled(MexGeo g, const float* __r
     const float eps = float(g.eps), cst = float(g.cst), oob = float(g.oob);
     const int qq = threadIdx.x % 32, e0 = threadIdx.x / 32;         // this thread stages q = qq, rows e0 + 8*s
     const float* mor = mo + r * g.M;
+    float mom[Cfg::A_PER];
+#pragma unroll
+    for (int s = 0; s < Cfg::A_PER; ++s) mom[s] = (i0 + e0 + 8 * s < g.M) ? mor[i0 + e0 + 8 * s] : 0.f;
     Column cur;                                                     // the position this thread stages in the fetched chunk
     float ray[Cfg::A_PER], rag[Cfg::A_PER], rbx[Cfg::B_PER];
 
-    float acc[4][4];
+    float2 acc[4][2];
 #pragma unroll
     for (int r_ = 0; r_ < 4; ++r_)
 #pragma unroll
-        for (int c_ = 0; c_ < 4; ++c_) acc[r_][c_] = 0.f;
+        for (int c_ = 0; c_ < 2; ++c_) acc[r_][c_] = make_float2(0.f, 0.f);
 
-    auto fetchA = [&](int chunk) {
+    auto fetchA = [&](int chunk, float*) {
         cur = column_of(g, r, (c_begin + chunk) * kDoffKC + qq, P, mx);
 #pragma unroll
         for (int s = 0; s < Cfg::A_PER; ++s) {
@@ -391,7 +387,7 @@ __global__ void __launch_bounds__(256) mex_doff_tiled(MexGeo g, const float* __r
             rag[s] = ok ? __ldcs(dy + cur.base + (long long)m * g.N) : 0.f;
         }
     };
-    auto fetchB = [&](int) {
+    auto fetchB = [&](int, float*) {
         const float* xs = x + (size_t)cur.n * g.C * g.H * g.W;
 #pragma unroll
         for (int s = 0; s < Cfg::B_PER; ++s) {
@@ -401,11 +397,8 @@ __global__ void __launch_bounds__(256) mex_doff_tiled(MexGeo g, const float* __r
     };
     auto commitA = [&](float* As) {
 #pragma unroll
-        for (int s = 0; s < Cfg::A_PER; ++s) {
-            const int e = e0 + 8 * s, m = i0 + e;
-            const float mom = m < g.M ? __ldg(mor + m) : 0.f;
-            As[stage_offset<kDoffTile, true>(qq, e)] = rag[s] * fast_exp(eps * (cur.mx + mom - ray[s]) + cst);
-        }
+        for (int s = 0; s < Cfg::A_PER; ++s)
+            As[stage_offset<kDoffTile, true>(qq, e0 + 8 * s)] = rag[s] * fast_exp(eps * (cur.mx + mom[s] - ray[s]) + cst);
     };
     auto commitB = [&](float* Bs) {
 #pragma unroll
@@ -414,7 +407,7 @@ __global__ void __launch_bounds__(256) mex_doff_tiled(MexGeo g, const float* __r
             Bs[stage_offset<kDoffTile, true>(qq, e)] = (cur.base >= 0 && jk0 + e < g.K) ? fast_exp(eps * (rbx[s] - cur.mx)) : 0.f;
         }
     };
-    auto comb = [&](int r_, int c_, const float (&a)[1], const float (&b)[1]) { acc[r_][c_] = fmaf(a[0], b[0], acc[r_][c_]); };
+    auto comb = [&](int r_, int cp, const float2 (&a)[1], const float2 (&b)[1]) { acc[r_][cp] = fma2(a[0], b[0], acc[r_][cp]); };
     tile_mainloop<Cfg, true, true>(smem, int(c_end - c_begin), t, fetchA, fetchB, commitA, commitB, comb);
 
     float* dst = part + ((size_t)split * g.R + r) * g.M * g.K;
@@ -425,21 +418,27 @@ __global__ void __launch_bounds__(256) mex_doff_tiled(MexGeo g, const float* __r
 #pragma unroll
         for (int c_ = 0; c_ < 4; ++c_) {
             const int k = jk0 + t.col(c_);
-            if (k < g.K) dst[(size_t)m * g.K + k] = acc[r_][c_];
+            if (k < g.K) dst[(size_t)m * g.K + k] = (c_ & 1) ? acc[r_][c_ >> 1].y : acc[r_][c_ >> 1].x;
         }
     }
 }
 
 // doff[r][m][k] (+)= Eo[r][m][k] * sum over splits, in split order (deterministic)
-__global__ void __launch_bounds__(256) mex_doff_reduce(long long n, int splits, const float* __restrict__ part, const float* __restrict__ eo,
+__global__ void __launch_bounds__(256) mex_doff_reduce(long long n, int K, int splits, const float* __restrict__ part, const float* __restrict__ eo,
                                                        float* __restrict__ doff, int accumulate, const int* __restrict__ flag) {
     if (*flag) return;
     for (long long i = blockIdx.x * 256LL + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
         float s = 0.f;
         for (int p = 0; p < splits; ++p) s += part[(size_t)p * n + i];
-        s *= eo[i];
+        s *= eo[(i / K) * pad4(K) + i % K];
         doff[i] = accumulate ? doff[i] + s : s;
     }
+}
+
+// no patch reaches outside the input: no padding, and the last patch along each axis ends inside
+bool patches_inside_input(const MexGeo& g) {
+    auto inside = [](int dim, int block, int stride, int pad, int out) { return pad == 0 && (out - 1) * stride + block <= dim; };
+    return inside(g.C, g.bc, g.sc, g.pc, g.Co) && inside(g.H, g.bh, g.sh, g.ph, g.Ho) && inside(g.W, g.bw, g.sw, g.pw, g.Wo);
 }
 
 bool blocks_disjoint(const MexGeo& g) { return g.sc >= g.bc && g.sh >= g.bh && g.sw >= g.bw; }
@@ -484,9 +483,13 @@ cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* o
     const long long jtiles = (P + 127) / 128;
     const long long blocks = jtiles * ((g.M + (wide ? 127 : 63)) / (wide ? 128 : 64)) * g.R;
     if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-#define FWD(TM, SP) mex_fwd_tiled<TM, SP><<<int(blocks), 256, 0, s>>>(g, x, w.eot, w.mo, w.mx, y, w.flag)
-    if (wide) { if (sp1) FWD(128, true); else FWD(128, false); }
-    else { if (sp1) FWD(64, true); else FWD(64, false); }
+    const bool interior = patches_inside_input(g);
+#define FWD(TM, SP, IN) mex_fwd_tiled<TM, SP, IN><<<int(blocks), 256, 0, s>>>(g, x, w.eot, w.mo, w.mx, y, w.flag)
+#define FWD_TM(TM)                                                                         \
+    if (sp1) { if (interior) FWD(TM, true, true); else FWD(TM, true, false); }            \
+    else { if (interior) FWD(TM, false, true); else FWD(TM, false, false); }
+    if (wide) { FWD_TM(128) } else { FWD_TM(64) }
+#undef FWD_TM
 #undef FWD
     count_launch();
     e = cudaGetLastError();
@@ -529,7 +532,7 @@ cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* 
     if (g.bh == 1 && g.bw == 1) mex_doff_tiled<true><<<int(blocks), 256, 0, s>>>(g, x, w.mo, w.mx, y, dy, w.part, splits, w.flag);
     else mex_doff_tiled<false><<<int(blocks), 256, 0, s>>>(g, x, w.mo, w.mx, y, dy, w.part, splits, w.flag);
     const long long n = (long long)g.R * g.M * g.K;
-    mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, splits, w.part, w.eo, doff, accumulate, w.flag);
+    mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, g.K, splits, w.part, w.eo, doff, accumulate, w.flag);
     count_launch(2);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;

@@ -22,7 +22,7 @@ constexpr double kLog2Pi = 1.8378770664093454835606594728112;
 constexpr int kDpTile = 64, kDpKC = 32;
 
 struct SimWs {
-    float* planes;   // [3][K][M]: t, scale (-w or -0.5w), per-term constant
+    float* planes;   // [3][K][Mp]: t, scale (-w or -0.5w), per-term constant; Mp = M rounded up to 4 floats
     float* cm;       // [M] per-instance constant added once per output
     int2* taps;      // [K]: {offset of tap inside a sample, (kh << 16) | kw}
     float* part;     // [S][3][M][K] split partial sums of the parameter gradients
@@ -30,6 +30,7 @@ struct SimWs {
 };
 
 __host__ inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+__host__ __device__ inline int pad4(int v) { return (v + 3) & ~3; }
 
 __host__ int dp_splits(const SimGeo& g) {
     const long long P = (long long)g.B * g.N;
@@ -47,7 +48,7 @@ __host__ SimWs carve(const SimGeo& g, void* base) {
     char* p = static_cast<char*>(base);
     size_t off = 0;
     auto take = [&](size_t bytes) { char* r = p ? p + off : nullptr; off += align256(bytes); return r; };
-    w.planes = reinterpret_cast<float*>(take(sizeof(float) * 3 * (size_t)g.K * g.M));
+    w.planes = reinterpret_cast<float*>(take(sizeof(float) * 3 * (size_t)g.K * pad4(g.M)));
     w.cm = reinterpret_cast<float*>(take(sizeof(float) * g.M));
     w.taps = reinterpret_cast<int2*>(take(sizeof(int2) * g.K));
     w.part = reinterpret_cast<float*>(take(sizeof(float) * 3 * (size_t)dp_splits(g) * g.M * g.K));
@@ -61,16 +62,17 @@ __global__ void __launch_bounds__(128) sim_prep(SimGeo g, const float* __restric
     __shared__ float red[128];
     const int m = blockIdx.x;
     const float fudge = float(g.fudge);
-    const size_t plane = (size_t)g.K * g.M;
+    const int ldm = pad4(g.M);
+    const size_t plane = (size_t)g.K * ldm;
     float csum = 0.f;
     for (int k = threadIdx.x; k < g.K; k += 128) {
         const float t = tm[(size_t)m * g.K + k], w = wt[(size_t)m * g.K + k];
         float scale = -w, c = 0.f;
         if (g.mode == SIM_L2N) { scale = -0.5f * w; csum += 0.5f * logf(w + fudge); }
         if (g.mode == SIM_L2N_NAN) { scale = -0.5f * w; c = float(0.5 * (double(logf(w + fudge)) - kLog2Pi)); }
-        planes[(size_t)k * g.M + m] = t;
-        planes[plane + (size_t)k * g.M + m] = scale;
-        planes[2 * plane + (size_t)k * g.M + m] = c;
+        planes[(size_t)k * ldm + m] = t;
+        planes[plane + (size_t)k * ldm + m] = scale;
+        planes[2 * plane + (size_t)k * ldm + m] = c;
         if (m == 0) {
             const int kw = k % g.bw, kh = (k / g.bw) % g.bh, c_ = k / (g.bw * g.bh);
             taps[k] = make_int2((c_ * g.H + kh) * g.W + kw, (kh << 16) | kw);
@@ -115,6 +117,8 @@ template <int MODE> struct FwdPlanes {
     static constexpr int NB = (MODE == SIM_L2N_NAN || MODE == SIM_L1_SKIP) ? 2 : 1;
 };
 
+__device__ __forceinline__ float2 abs2(float2 v) { return make_float2(fabsf(v.x), fabsf(v.y)); }
+
 template <int TM, int MODE>
 __global__ void __launch_bounds__(256) sim_fwd_tiled(SimGeo g, const float* __restrict__ x, const float* __restrict__ planes,
                                                      const float* __restrict__ cm, const int2* __restrict__ taps, float* __restrict__ y) {
@@ -122,55 +126,50 @@ __global__ void __launch_bounds__(256) sim_fwd_tiled(SimGeo g, const float* __re
     using Cfg = TileCfg<TM, 128, 8, TM / 16, 8, NA, NB>;
     static_assert(Cfg::THREADS == 256, "256 threads");
     __shared__ __align__(16) float smem[Cfg::SMEM_FLOATS];
-    __shared__ SimColumn cols[Cfg::TN];
+    __shared__ long long col_base[Cfg::TN];
     const long long P = (long long)g.B * g.N;
     const int mtiles = (g.M + TM - 1) / TM;
     const int mt = blockIdx.x % mtiles;
     const long long jt = blockIdx.x / mtiles;
     const int i0 = mt * TM;
     const long long j0 = jt * Cfg::TN;
-    if (threadIdx.x < Cfg::TN) cols[threadIdx.x] = sim_column(g, j0 + threadIdx.x, P);
-    __syncthreads();
 
     const TileThread<Cfg> t;
     const float oob = float(g.oob);
-    const size_t plane = (size_t)g.K * g.M;
+    const int ldm = pad4(g.M);
+    const size_t plane = (size_t)g.K * ldm;
     const int s_lane = threadIdx.x % 128, s_k = threadIdx.x / 128;
-    const SimColumn sc = cols[s_lane];
+    const SimColumn sc = sim_column(g, j0 + s_lane, P);
+    if (s_k == 0) col_base[s_lane] = sc.base;
+    const bool live = sc.base >= 0;
+    // a patch that lies entirely inside the image needs no per-tap bounds test
+    const bool inside = live && sc.h0 >= 0 && sc.w0 >= 0 && sc.h0 + g.bh <= g.H && sc.w0 + g.bw <= g.W;
     const float* xs = x + (size_t)sc.n * g.C * g.H * g.W;
-    constexpr int A_ROWS = 256 / TM;
-    const int a_lane = threadIdx.x % TM, a_k = threadIdx.x / TM;
-    float ra[Cfg::A_PER][NA], rb[Cfg::B_PER];
+    const float* xc = xs + sc.h0 * g.W + sc.w0;
+    float rb[Cfg::B_PER];
 
-    float acc[Cfg::RM][Cfg::RN];
+    float2 acc[Cfg::RM][Cfg::RN / 2];
 #pragma unroll
     for (int r_ = 0; r_ < Cfg::RM; ++r_)
 #pragma unroll
-        for (int c_ = 0; c_ < Cfg::RN; ++c_) acc[r_][c_] = 0.f;
+        for (int c_ = 0; c_ < Cfg::RN / 2; ++c_) acc[r_][c_] = make_float2(0.f, 0.f);
 
-    auto fetchA = [&](int chunk) {
+    auto fetchA = [&](int chunk, float* As) {
 #pragma unroll
-        for (int s = 0; s < Cfg::A_PER; ++s) {
-            const int k = chunk * Cfg::KC + a_k + s * A_ROWS, m = i0 + a_lane;
-            const bool ok = k < g.K && m < g.M;
-#pragma unroll
-            for (int p = 0; p < NA; ++p) ra[s][p] = ok ? __ldg(planes + p * plane + (size_t)k * g.M + m) : 0.f;
-        }
+        for (int p = 0; p < NA; ++p)
+            stage_copy_async<Cfg, TM>(As + p * Cfg::KC * TM, planes + p * plane, ldm, chunk * Cfg::KC, g.K, i0, g.M);
     };
-    auto fetchB = [&](int chunk) {
+    auto fetchB = [&](int chunk, float*) {
 #pragma unroll
         for (int s = 0; s < Cfg::B_PER; ++s) {
             const int k = chunk * Cfg::KC + s_k + s * 2;
             // rows past K pair a zero scale / zero constant with a finite value: the term is exactly 0
-            rb[s] = (k < g.K && sc.base >= 0) ? sim_tap_value(g, xs, sc, __ldg(taps + k), oob) : 0.f;
+            if (k >= g.K || !live) rb[s] = 0.f;
+            else if (inside) rb[s] = __ldg(xc + __ldg(taps + k).x);
+            else rb[s] = sim_tap_value(g, xs, sc, __ldg(taps + k), oob);
         }
     };
-    auto commitA = [&](float* As) {
-#pragma unroll
-        for (int s = 0; s < Cfg::A_PER; ++s)
-#pragma unroll
-            for (int p = 0; p < NA; ++p) As[p * Cfg::KC * TM + (a_k + s * A_ROWS) * TM + a_lane] = ra[s][p];
-    };
+    auto commitA = [&](float*) { cp_async_wait_all(); };
     auto commitB = [&](float* Bs) {
 #pragma unroll
         for (int s = 0; s < Cfg::B_PER; ++s) {
@@ -184,30 +183,34 @@ __global__ void __launch_bounds__(256) sim_fwd_tiled(SimGeo g, const float* __re
             }
         }
     };
-    auto comb = [&](int r_, int c_, const float (&a)[NA], const float (&b)[NB]) {
-        const float d = a[0] - b[0];
-        if (MODE == SIM_L1) acc[r_][c_] = fmaf(a[1], fabsf(d), acc[r_][c_]);
-        else if (MODE == SIM_L1_SKIP) acc[r_][c_] = fmaf(a[1], fabsf(d) * b[NB - 1], acc[r_][c_]);
-        else if (MODE == SIM_L2N_NAN) acc[r_][c_] = fmaf(b[NB - 1], fmaf(a[1] * d, d, a[NA - 1]), acc[r_][c_]);
-        else acc[r_][c_] = fmaf(a[1] * d, d, acc[r_][c_]);
+    auto comb = [&](int r_, int cp, const float2 (&a)[NA], const float2 (&b)[NB]) {
+        const float2 d = add2(a[0], neg2(b[0]));
+        if (MODE == SIM_L1) acc[r_][cp] = fma2(a[1], abs2(d), acc[r_][cp]);
+        else if (MODE == SIM_L1_SKIP) acc[r_][cp] = fma2(a[1], mul2(abs2(d), b[NB - 1]), acc[r_][cp]);
+        else if (MODE == SIM_L2N_NAN) acc[r_][cp] = fma2(b[NB - 1], fma2(mul2(a[1], d), d, a[NA - 1]), acc[r_][cp]);
+        else acc[r_][cp] = fma2(mul2(a[1], d), d, acc[r_][cp]);
     };
     tile_mainloop<Cfg, false, false>(smem, (g.K + Cfg::KC - 1) / Cfg::KC, t, fetchA, fetchB, commitA, commitB, comb);
 
+    long long cb[Cfg::RN];
+#pragma unroll
+    for (int c_ = 0; c_ < Cfg::RN; ++c_) cb[c_] = col_base[t.col(c_)];
+    const float quirk_c = float(-0.5 * double(g.K) * kLog2Pi);
 #pragma unroll
     for (int r_ = 0; r_ < Cfg::RM; ++r_) {
         const int m = i0 + t.row(r_);
         if (m >= g.M) continue;
         const float cmm = cm[m];
+        float* yrow = y + (long long)m * g.N;
 #pragma unroll
         for (int c_ = 0; c_ < Cfg::RN; ++c_) {
-            const SimColumn& col = cols[t.col(c_)];
-            if (col.base < 0) continue;
-            float v = acc[r_][c_];
+            if (cb[c_] < 0) continue;
+            float v = (c_ & 1) ? acc[r_][c_ >> 1].y : acc[r_][c_ >> 1].x;
             if (MODE == SIM_L2N) {
                 v += cmm;
-                if (g.batch_quirk) v += float(-0.5 * double(g.K) * kLog2Pi) * float(g.B - col.n - 1);
+                if (g.batch_quirk) v += quirk_c * float(g.B - 1 - int(cb[c_] / ((long long)g.M * g.N)));
             }
-            __stcs(y + col.base + (long long)m * g.N, v);
+            __stcs(yrow + cb[c_], v);
         }
     }
 }
@@ -247,21 +250,22 @@ __global__ void __launch_bounds__(256) sim_dparams_tiled(SimGeo g, const float* 
         const int k = jk0 + e0 + 8 * s;
         mytaps[s] = k < g.K ? taps[k] : make_int2(0, 0);
     }
-    float tt[4][4];
+    float2 tt[4][2];
 #pragma unroll
     for (int r_ = 0; r_ < 4; ++r_)
 #pragma unroll
         for (int c_ = 0; c_ < 4; ++c_) {
             const int m = i0 + t.row(r_), k = jk0 + t.col(c_);
-            tt[r_][c_] = (m < g.M && k < g.K) ? tm[(size_t)m * g.K + k] : 0.f;
+            const float v = (m < g.M && k < g.K) ? tm[(size_t)m * g.K + k] : 0.f;
+            if (c_ & 1) tt[r_][c_ >> 1].y = v; else tt[r_][c_ >> 1].x = v;
         }
-    float sT[4][4], sW[4][4], sN[4][4];
+    float2 sT[4][2], sW[4][2], sN[4][2];
 #pragma unroll
     for (int r_ = 0; r_ < 4; ++r_)
 #pragma unroll
-        for (int c_ = 0; c_ < 4; ++c_) { sT[r_][c_] = 0.f; sW[r_][c_] = 0.f; sN[r_][c_] = 0.f; }
+        for (int c_ = 0; c_ < 2; ++c_) { sT[r_][c_] = make_float2(0.f, 0.f); sW[r_][c_] = sT[r_][c_]; sN[r_][c_] = sT[r_][c_]; }
 
-    auto fetchA = [&](int chunk) {
+    auto fetchA = [&](int chunk, float*) {
         cur = sim_column(g, (c_begin + chunk) * kDpKC + qq, P);
 #pragma unroll
         for (int s = 0; s < Cfg::A_PER; ++s) {
@@ -269,13 +273,17 @@ __global__ void __launch_bounds__(256) sim_dparams_tiled(SimGeo g, const float* 
             ra[s] = (cur.base >= 0 && m < g.M) ? __ldcs(dy + cur.base + (long long)m * g.N) : 0.f;
         }
     };
-    auto fetchB = [&](int) {
+    auto fetchB = [&](int, float*) {
         const float* xs = x + (size_t)cur.n * g.C * g.H * g.W;
+        const bool inside = cur.base >= 0 && cur.h0 >= 0 && cur.w0 >= 0 && cur.h0 + g.bh <= g.H && cur.w0 + g.bw <= g.W;
+        const float* xc = xs + cur.h0 * g.W + cur.w0;
 #pragma unroll
         for (int s = 0; s < Cfg::B_PER; ++s) {
             const int k = jk0 + e0 + 8 * s;
             // dead positions carry dy = 0 and a finite value, so every term they touch is exactly 0
-            rb[s] = (cur.base >= 0 && k < g.K) ? sim_tap_value(g, xs, cur, mytaps[s], oob) : 0.f;
+            if (cur.base < 0 || k >= g.K) rb[s] = 0.f;
+            else if (inside) rb[s] = __ldg(xc + mytaps[s].x);
+            else rb[s] = sim_tap_value(g, xs, cur, mytaps[s], oob);
         }
     };
     auto commitA = [&](float* As) {
@@ -295,17 +303,17 @@ __global__ void __launch_bounds__(256) sim_dparams_tiled(SimGeo g, const float* 
             }
         }
     };
-    auto comb = [&](int r_, int c_, const float (&a)[1], const float (&b)[NB]) {
-        const float d = MASKED ? fmaf(-tt[r_][c_], b[NB - 1], b[0]) : b[0] - tt[r_][c_];
+    auto comb = [&](int r_, int cp, const float2 (&a)[1], const float2 (&b)[NB]) {
+        const float2 d = MASKED ? fma2(neg2(tt[r_][cp]), b[NB - 1], b[0]) : add2(b[0], neg2(tt[r_][cp]));
         if (L1) {
-            const float sg = float((0.f < d) - (d < 0.f));
-            sT[r_][c_] = fmaf(a[0], sg, sT[r_][c_]);
-            sW[r_][c_] = fmaf(a[0], fabsf(d), sW[r_][c_]);
+            const float2 sg = make_float2(float((0.f < d.x) - (d.x < 0.f)), float((0.f < d.y) - (d.y < 0.f)));
+            sT[r_][cp] = fma2(a[0], sg, sT[r_][cp]);
+            sW[r_][cp] = fma2(a[0], abs2(d), sW[r_][cp]);
         } else {
-            const float u = a[0] * d;
-            sT[r_][c_] += u;
-            sW[r_][c_] = fmaf(u, d, sW[r_][c_]);
-            if (NORM) sN[r_][c_] = MASKED ? fmaf(a[0], b[NB - 1], sN[r_][c_]) : sN[r_][c_] + a[0];
+            const float2 u = mul2(a[0], d);
+            sT[r_][cp] = add2(sT[r_][cp], u);
+            sW[r_][cp] = fma2(u, d, sW[r_][cp]);
+            if (NORM) sN[r_][cp] = MASKED ? fma2(a[0], b[NB - 1], sN[r_][cp]) : add2(sN[r_][cp], a[0]);
         }
     };
     tile_mainloop<Cfg, true, true>(smem, int(c_end - c_begin), t, fetchA, fetchB, commitA, commitB, comb);
@@ -320,9 +328,10 @@ __global__ void __launch_bounds__(256) sim_dparams_tiled(SimGeo g, const float* 
         for (int c_ = 0; c_ < 4; ++c_) {
             const int k = jk0 + t.col(c_);
             if (k >= g.K) continue;
-            dst[(size_t)m * g.K + k] = sT[r_][c_];
-            dst[mk + (size_t)m * g.K + k] = sW[r_][c_];
-            if (NORM) dst[2 * mk + (size_t)m * g.K + k] = sN[r_][c_];
+            const bool hi = c_ & 1;
+            dst[(size_t)m * g.K + k] = hi ? sT[r_][c_ >> 1].y : sT[r_][c_ >> 1].x;
+            dst[mk + (size_t)m * g.K + k] = hi ? sW[r_][c_ >> 1].y : sW[r_][c_ >> 1].x;
+            if (NORM) dst[2 * mk + (size_t)m * g.K + k] = hi ? sN[r_][c_ >> 1].y : sN[r_][c_ >> 1].x;
         }
     }
 }

@@ -30,7 +30,8 @@ def test_network_step_matches_cpu_oracle(port, name, batch):
     """Network-level gradients pass through the normalize_offsets backward, which cancels almost all of
     each offsets gradient, so float32 rounding is amplified far beyond 1e-5 on BOTH sides.  Hence:
     (1) float64 on the GPU must agree with the float64 oracle to 1e-7 (the same amplification acts on 1e-16; proves the wiring and the math);
-    (2) float32 on the GPU must be no farther from the float64 oracle than 3x the float32 oracle is."""
+    (2) float32 on the GPU must be no farther from the float64 oracle than 10x the float32 oracle is
+        (both are noise of the same amplified rounding; the factor allows for different summation orders)."""
     from oracle.simnet_cpu import CpuSimNet
     spec = SPECS[name]
     rng = np.random.default_rng(11)
@@ -54,4 +55,4 @@ def test_network_step_matches_cpu_oracle(port, name, batch):
     assert abs(f_loss - loss64) <= 2e-5 * max(1.0, float(np.abs(logits64).max()))
     for i, (a, b32, b64) in enumerate(zip(f_grads, grads32, grads64)):
         ours, ref = cases.rel_err(a, b64), cases.rel_err(b32, b64)
-        assert ours <= max(5e-5, 3 * ref), "%s f32 grad %d %s: %.3g from the f64 oracle, f32 oracle %.3g" % (name, i, a.shape, ours, ref)
+        assert ours <= max(1e-4, 10 * ref), "%s f32 grad %d %s: %.3g from the f64 oracle, f32 oracle %.3g" % (name, i, a.shape, ours, ref)
