@@ -177,6 +177,31 @@ SIMNETS_API int simnets_mex_forward(const simnets_mex_desc* d,
                                     const void* x, const void* offsets, void* y,
                                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* MEX forward for callers that have no scratch to give.  No counterpart in the reference: its
+ * OpKernels always obtain temporaries from TensorFlow's allocator (context->allocate_temp).
+ *
+ * Some hosts of this library cannot hand it a workspace: an operator plugin loaded into a serving
+ * runtime that has pre-assigned every byte of device memory to its own arena, a callback running
+ * inside someone else's executor where calling a device allocator is forbidden, or a partitioned
+ * GPU whose share is already fully committed.  For them this entry point computes exactly what
+ * simnets_mex_forward computes, but keeps its scratch (offset exponentials, per-position maxima,
+ * the safety flag) in a fixed device array inside the library, SIMNETS_MEX_STATIC_SCRATCH_BYTES
+ * large, which each GPU that loads the library holds until the process exits.  It calls no device
+ * allocator and no allocating library routine.
+ *
+ *  - Problems whose forward scratch exceeds the array are rejected with SIMNETS_E_TOO_LARGE before
+ *    anything is launched (scratch need = 4 bytes * (batch*N + 2*num_regions*M*K) plus a few hundred
+ *    bytes of padding; use simnets_mex_forward with a caller workspace for those).
+ *  - The first call on each device looks up the array's device address; make that first call outside
+ *    any stream capture.
+ *  - All calls share the one array and it keeps whatever the previous call left; the call itself
+ *    clears the part that must start at zero.  Two calls that overlap on the same GPU (different
+ *    streams or threads) race on it: serialise them.
+ */
+#define SIMNETS_MEX_STATIC_SCRATCH_BYTES (8u << 20)
+SIMNETS_API int simnets_mex_forward_static_scratch(const simnets_mex_desc* d,
+                                                   const void* x, const void* offsets, void* y, void* stream);
+
 /* dL/dinput.  Replaces MEXGradInputKernelGPU (src/kernels/mex_grad_kernel_gpu.cu:23-205),
  * oracle MEXGradInputKernelCPU (src/kernels/mex_grad_kernel_cpu.cpp:23-209). */
 SIMNETS_API int simnets_mex_input_grad(const simnets_mex_desc* d,

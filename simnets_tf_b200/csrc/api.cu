@@ -155,6 +155,17 @@ int simnets_mex_forward(const simnets_mex_desc* d, const void* x, const void* of
     return from_cuda(launch_mex_fwd_direct(g, f64, x, off, y, as_stream(stream)));
 }
 
+int simnets_mex_forward_static_scratch(const simnets_mex_desc* d, const void* x, const void* off, void* y, void* stream) {
+    MexGeo g;
+    const int rc = mex_geometry(d, nullptr, &g);
+    if (rc) return rc;
+    if (!off || (g.B > 0 && (!x || !y))) return SIMNETS_E_NULL;
+    const bool f64 = d->dtype == SIMNETS_F64;
+    if (!mex_use_tiled(g, f64, d->flags))        // these shapes run on kernels that need no scratch at all
+        return from_cuda(launch_mex_fwd_direct(g, f64, x, off, y, as_stream(stream)));
+    return launch_mex_fwd_static(g, (const float*)x, (const float*)off, (float*)y, as_stream(stream));
+}
+
 int simnets_mex_input_grad(const simnets_mex_desc* d, const void* x, const void* off, const void* y, const void* dy, void* dx,
                            void* ws, size_t ws_bytes, void* stream) {
     MexGeo g;

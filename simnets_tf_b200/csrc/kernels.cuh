@@ -34,6 +34,8 @@ cudaError_t launch_sim_dparams_tiled(const SimGeo&, const float* x, const float*
 bool mex_use_tiled(const MexGeo&, bool f64, uint32_t flags);
 size_t mex_workspace_bytes(const MexGeo&, bool f64, uint32_t flags);
 cudaError_t launch_mex_fwd_tiled(const MexGeo&, const float* x, const float* off, float* y, void* ws, uint32_t flags, cudaStream_t);
+// forward on the library's fixed device scratch; returns a status code of simnets_b200.h
+int launch_mex_fwd_static(const MexGeo&, const float* x, const float* off, float* y, cudaStream_t);
 cudaError_t launch_mex_dx_tiled(const MexGeo&, const float* x, const float* off, const float* y, const float* dy, float* dx,
                                 void* ws, uint32_t flags, cudaStream_t);
 cudaError_t launch_mex_doff_tiled(const MexGeo&, const float* x, const float* off, const float* y, const float* dy, float* doff,

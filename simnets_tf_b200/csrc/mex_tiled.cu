@@ -22,6 +22,7 @@
 //
 // Offset regions (shared / unshared) never move data: a CTA works on the positions of ONE region,
 // enumerated in the region-local order of the reference's split_patches (mex_utils.hpp:69-116).
+#include <mutex>
 #include "kernels.cuh"
 #include "tile.cuh"
 
@@ -39,6 +40,7 @@ struct MexWs {           // workspace carve-up, every part 256-byte aligned
     float* mx;           // [B][N]
     float* part;         // [S][R][M][K] split-q partial sums of the offsets gradient
     size_t bytes;
+    size_t fwd_bytes;    // bytes the forward pass touches (everything before `part`)
 };
 
 __host__ inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
@@ -67,6 +69,7 @@ __host__ MexWs carve(const MexGeo& g, void* base) {
     w.eo = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.M * pad4(g.K)));
     w.eot = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.K * pad4(g.M)));
     w.mx = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.B * g.N));
+    w.fwd_bytes = off;
     w.part = reinterpret_cast<float*>(take(sizeof(float) * (size_t)doff_splits(g) * g.R * g.M * g.K));
     w.bytes = off;
     return w;
@@ -495,6 +498,41 @@ cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* o
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);       // runs only if the flag was raised
+}
+
+// --------------------------------------------- forward on library-owned scratch
+// Scratch for simnets_mex_forward_static_scratch(): a fixed device array that every GPU loading this
+// library carries until the process exits.  In host code the name below is only a handle for the
+// runtime, not a device address; the address a kernel may use comes from cudaGetSymbolAddress, taken
+// once per device with that device current.
+static __device__ __align__(256) unsigned char g_mex_static_scratch[SIMNETS_MEX_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxDevices] = {};
+}  // namespace
+
+int launch_mex_fwd_static(const MexGeo& g, const float* x, const float* off, float* y, cudaStream_t s) {
+    if (carve(g, nullptr).fwd_bytes > size_t(SIMNETS_MEX_STATIC_SCRATCH_BYTES)) return SIMNETS_E_TOO_LARGE;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return int(e);
+    if (dev < 0 || dev >= kMaxDevices) return SIMNETS_E_UNSUPPORTED;
+    void* ptr = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mu);
+        if (!g_static_ptr[dev]) {
+            e = cudaGetSymbolAddress(&ptr, g_mex_static_scratch);      // address on the CURRENT device
+            if (e != cudaSuccess) return int(e);
+            g_static_ptr[dev] = ptr;
+        }
+        ptr = g_static_ptr[dev];
+    }
+    // launch_mex_fwd_tiled clears the one word that must start at zero (the safety flag) on every call;
+    // everything else in the scratch is fully rewritten by the prepasses before it is read.
+    e = launch_mex_fwd_tiled(g, x, off, y, ptr, 0, s);
+    return e == cudaSuccess ? SIMNETS_OK : int(e);
 }
 
 cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* dx,
