@@ -34,6 +34,13 @@ cudaError_t launch_sim_dparams_tiled(const SimGeo&, const float* x, const float*
 bool mex_use_tiled(const MexGeo&, bool f64, uint32_t flags);
 size_t mex_workspace_bytes(const MexGeo&, bool f64, uint32_t flags);
 cudaError_t launch_mex_fwd_tiled(const MexGeo&, const float* x, const float* off, float* y, void* ws, uint32_t flags, cudaStream_t);
+// mex_smallm.cu -- one CTA per position, for M <= 16 and K >= 256
+cudaError_t launch_mex_colmax_wide(const MexGeo&, const float* x, float* mx, const int* flag, cudaStream_t);
+cudaError_t launch_mex_fwd_smallm(const MexGeo&, const float* x, const float* eot, const float* mo, float* y, const int* flag, cudaStream_t);
+cudaError_t launch_mex_dx_smallm(const MexGeo&, const float* x, const float* eo, const float* mo, const float* y, const float* dy,
+                                 float* dx, const int* flag, cudaStream_t);
+cudaError_t launch_mex_doff_smallm(const MexGeo&, const float* x, const float* mo, const float* mx, const float* y, const float* dy,
+                                   float* part, int splits, const int* flag, cudaStream_t);
 // forward on the library's fixed device scratch; returns a status code of simnets_b200.h
 int launch_mex_fwd_static(const MexGeo&, const float* x, const float* off, float* y, cudaStream_t);
 cudaError_t launch_mex_dx_tiled(const MexGeo&, const float* x, const float* off, const float* y, const float* dy, float* dx,

@@ -1,0 +1,119 @@
+// Shared by the MEX kernel files: workspace carve-up, tap decoding, per-position bookkeeping.
+#pragma once
+#include "kernels.cuh"
+#include "tile.cuh"
+
+namespace simnets {
+namespace {
+
+constexpr float kSafeSpread = 60.0f;
+
+struct MexWs {           // workspace carve-up, every part 256-byte aligned
+    int* flag;           // != 0: factorisation unsafe, take the exact kernels
+    float* mo;           // [R][M]
+    float* eo;           // [R][M][Kp]  Eo, offsets layout, rows padded to a multiple of 4 floats
+    float* eot;          // [R][K][Mp]  Eo transposed, rows padded likewise (16-byte aligned rows for async copies)
+    float* mx;           // [B][N]
+    float* part;         // [S][R][M][K] split-q partial sums of the offsets gradient
+    size_t bytes;
+    size_t fwd_bytes;    // bytes the forward pass touches (everything before `part`)
+};
+
+__host__ inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+__host__ __device__ inline int pad4(int v) { return (v + 3) & ~3; }
+
+// offsets-gradient tiling: 128 x 128 outputs (chunks of 16 positions) when both M and K fill it, else 64 x 64 (chunks of 32)
+__host__ inline bool doff_big(const MexGeo& g) { return g.M >= 96 && g.K >= 96; }
+
+// Few instances over long patches (a classifier head: M = 10, K = 8192): one CTA per position instead of GEMM tiles.
+__host__ inline bool smallm_shape(const MexGeo& g) { return g.M <= 16 && g.K >= 256; }
+
+__host__ inline int doff_splits(const MexGeo& g) {
+    if (smallm_shape(g)) {
+        const long long P = (long long)g.B * g.rs, ktiles = (g.K + 255) / 256;
+        long long s = (148 * 4 + ktiles * g.R - 1) / (ktiles * g.R);
+        if (s > (P + 15) / 16) s = (P + 15) / 16;
+        if (s < 1) s = 1;
+        if (s > 64) s = 64;
+        return int(s);
+    }
+    const int tile = doff_big(g) ? 128 : 64, kc = doff_big(g) ? 16 : 32;
+    const long long P = (long long)g.B * g.rs;
+    const long long chunks = (P + kc - 1) / kc;
+    const long long tiles = (long long)((g.M + tile - 1) / tile) * ((g.K + tile - 1) / tile) * g.R;
+    long long s = (148 * 2 + tiles - 1) / tiles;
+    if (s > chunks) s = chunks;
+    if (s < 1) s = 1;
+    if (s > 64) s = 64;
+    return int(s);
+}
+
+__host__ inline MexWs carve(const MexGeo& g, void* base) {
+    MexWs w;
+    char* p = static_cast<char*>(base);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { char* r = p ? p + off : nullptr; off += align256(bytes); return r; };
+    w.flag = reinterpret_cast<int*>(take(16));
+    w.mo = reinterpret_cast<float*>(take(sizeof(float) * g.R * g.M));
+    w.eo = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.M * pad4(g.K)));
+    w.eot = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.K * pad4(g.M)));
+    w.mx = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.B * g.N));
+    w.fwd_bytes = off;
+    w.part = reinterpret_cast<float*>(take(sizeof(float) * (size_t)doff_splits(g) * g.R * g.M * g.K));
+    w.bytes = off;
+    return w;
+}
+
+struct Tap { int c, h, w; };
+
+template <bool SPATIAL1>
+__device__ __forceinline__ Tap tap_of(const MexGeo& g, int k) {
+    Tap t;
+    if (SPATIAL1) { t.c = k; t.h = 0; t.w = 0; }
+    else { t.w = k % g.bw; const int q = k / g.bw; t.h = q % g.bh; t.c = q / g.bh; }
+    return t;
+}
+
+// value of tap k of the patch whose corner is (c0, h0, w0) in sample xs
+template <bool SPATIAL1>
+__device__ __forceinline__ float patch_value(const MexGeo& g, const float* __restrict__ xs, int c0, int h0, int w0, int k, float oob) {
+    const Tap t = tap_of<SPATIAL1>(g, k);
+    const int cc = c0 + t.c, hh = h0 + t.h, ww = w0 + t.w;
+    if (cc >= 0 && cc < g.C && hh >= 0 && hh < g.H && ww >= 0 && ww < g.W) return __ldg(xs + ((size_t)cc * g.H + hh) * g.W + ww);
+    return oob;
+}
+
+// Index of tap k of the patch at (c0, h0, w0) inside its sample, for geometries in which no patch leaves the input.
+template <bool SPATIAL1>
+__device__ __forceinline__ int interior_index(const MexGeo& g, int c0, int h0, int w0, int k) {
+    const Tap t = tap_of<SPATIAL1>(g, k);
+    return ((c0 + t.c) * g.H + h0 + t.h) * g.W + w0 + t.w;
+}
+
+// Per-column (= one output position of one sample) bookkeeping shared by the tile kernels.
+struct Column {
+    long long base;      // n*M*N + pos : offset of y[n, 0, pos]; -1 for a position outside the output grid
+    int n, c0, h0, w0;   // sample and patch corner in the input
+    float mx;
+};
+
+// j-th position (over the whole batch) of region r -> Column
+__device__ __forceinline__ Column column_of(const MexGeo& g, int r, long long jl, long long P, const float* __restrict__ mx) {
+    Column c;
+    c.base = -1; c.n = 0; c.c0 = c.h0 = c.w0 = 0; c.mx = 0.f;
+    if (jl >= P) return c;
+    int n, l;
+    if (P <= 0x7fffffffLL) { const unsigned j32 = unsigned(jl); n = int(j32 / unsigned(g.rs)); l = int(j32 - unsigned(n) * unsigned(g.rs)); }
+    else { n = int(jl / g.rs); l = int(jl % g.rs); }
+    const int pos = mex_region_position(g, r, l);
+    if (pos < 0) return c;
+    const int w = pos % g.Wo, h = (pos / g.Wo) % g.Ho, cc = pos / (g.Wo * g.Ho);
+    c.n = n; c.c0 = cc * g.sc - g.pc; c.h0 = h * g.sh - g.ph; c.w0 = w * g.sw - g.pw;
+    c.base = (long long)n * g.M * g.N + pos;
+    c.mx = mx ? mx[(long long)n * g.N + pos] : 0.f;
+    return c;
+}
+
+
+}  // namespace
+}  // namespace simnets

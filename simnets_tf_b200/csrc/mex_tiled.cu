@@ -25,55 +25,11 @@
 #include <mutex>
 #include "kernels.cuh"
 #include "tile.cuh"
+#include "mex_common.cuh"
 
 namespace simnets {
 
 namespace {
-
-constexpr float kSafeSpread = 60.0f;
-
-struct MexWs {           // workspace carve-up, every part 256-byte aligned
-    int* flag;           // != 0: factorisation unsafe, take the exact kernels
-    float* mo;           // [R][M]
-    float* eo;           // [R][M][Kp]  Eo, offsets layout, rows padded to a multiple of 4 floats
-    float* eot;          // [R][K][Mp]  Eo transposed, rows padded likewise (16-byte aligned rows for async copies)
-    float* mx;           // [B][N]
-    float* part;         // [S][R][M][K] split-q partial sums of the offsets gradient
-    size_t bytes;
-    size_t fwd_bytes;    // bytes the forward pass touches (everything before `part`)
-};
-
-__host__ inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
-__host__ __device__ inline int pad4(int v) { return (v + 3) & ~3; }
-
-constexpr int kDoffTile = 64, kDoffKC = 32;
-
-__host__ int doff_splits(const MexGeo& g) {
-    const long long P = (long long)g.B * g.rs;
-    const long long chunks = (P + kDoffKC - 1) / kDoffKC;
-    const long long tiles = (long long)((g.M + kDoffTile - 1) / kDoffTile) * ((g.K + kDoffTile - 1) / kDoffTile) * g.R;
-    long long s = (148 * 2 + tiles - 1) / tiles;
-    if (s > chunks) s = chunks;
-    if (s < 1) s = 1;
-    if (s > 64) s = 64;
-    return int(s);
-}
-
-__host__ MexWs carve(const MexGeo& g, void* base) {
-    MexWs w;
-    char* p = static_cast<char*>(base);
-    size_t off = 0;
-    auto take = [&](size_t bytes) { char* r = p ? p + off : nullptr; off += align256(bytes); return r; };
-    w.flag = reinterpret_cast<int*>(take(16));
-    w.mo = reinterpret_cast<float*>(take(sizeof(float) * g.R * g.M));
-    w.eo = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.M * pad4(g.K)));
-    w.eot = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.K * pad4(g.M)));
-    w.mx = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.B * g.N));
-    w.fwd_bytes = off;
-    w.part = reinterpret_cast<float*>(take(sizeof(float) * (size_t)doff_splits(g) * g.R * g.M * g.K));
-    w.bytes = off;
-    return w;
-}
 
 // ------------------------------------------------------------------ prepasses
 // One block per (region, instance): stabiliser mo, Eo in both layouts, and the safety flag.
@@ -114,32 +70,6 @@ __global__ void __launch_bounds__(128) mex_prep_offsets(MexGeo g, const float* _
     }
 }
 
-struct Tap { int c, h, w; };
-
-template <bool SPATIAL1>
-__device__ __forceinline__ Tap tap_of(const MexGeo& g, int k) {
-    Tap t;
-    if (SPATIAL1) { t.c = k; t.h = 0; t.w = 0; }
-    else { t.w = k % g.bw; const int q = k / g.bw; t.h = q % g.bh; t.c = q / g.bh; }
-    return t;
-}
-
-// value of tap k of the patch whose corner is (c0, h0, w0) in sample xs
-template <bool SPATIAL1>
-__device__ __forceinline__ float patch_value(const MexGeo& g, const float* __restrict__ xs, int c0, int h0, int w0, int k, float oob) {
-    const Tap t = tap_of<SPATIAL1>(g, k);
-    const int cc = c0 + t.c, hh = h0 + t.h, ww = w0 + t.w;
-    if (cc >= 0 && cc < g.C && hh >= 0 && hh < g.H && ww >= 0 && ww < g.W) return __ldg(xs + ((size_t)cc * g.H + hh) * g.W + ww);
-    return oob;
-}
-
-// Index of tap k of the patch at (c0, h0, w0) inside its sample, for geometries in which no patch leaves the input.
-template <bool SPATIAL1>
-__device__ __forceinline__ int interior_index(const MexGeo& g, int c0, int h0, int w0, int k) {
-    const Tap t = tap_of<SPATIAL1>(g, k);
-    return ((c0 + t.c) * g.H + h0 + t.h) * g.W + w0 + t.w;
-}
-
 // mx[n][pos] = max (eps > 0) or min (eps < 0) over the K taps of the patch at pos; NaN taps are ignored,
 // as the reference's max pass ignores them (std::max(acc, NaN) keeps acc).
 template <bool SPATIAL1>
@@ -160,28 +90,6 @@ __global__ void __launch_bounds__(256) mex_colmax(MexGeo g, const float* __restr
         }
         mx[idx] = v;
     }
-}
-
-// Per-column (= one output position of one sample) bookkeeping shared by the tile kernels.
-struct Column {
-    long long base;      // n*M*N + pos : offset of y[n, 0, pos]; -1 for a position outside the output grid
-    int n, c0, h0, w0;   // sample and patch corner in the input
-    float mx;
-};
-
-// j-th position (over the whole batch) of region r -> Column
-__device__ __forceinline__ Column column_of(const MexGeo& g, int r, long long jl, long long P, const float* __restrict__ mx) {
-    Column c;
-    c.base = -1; c.n = 0; c.c0 = c.h0 = c.w0 = 0; c.mx = 0.f;
-    if (jl >= P) return c;
-    const int n = int(jl / g.rs), l = int(jl % g.rs);
-    const int pos = mex_region_position(g, r, l);
-    if (pos < 0) return c;
-    const int w = pos % g.Wo, h = (pos / g.Wo) % g.Ho, cc = pos / (g.Wo * g.Ho);
-    c.n = n; c.c0 = cc * g.sc - g.pc; c.h0 = h * g.sh - g.ph; c.w0 = w * g.sw - g.pw;
-    c.base = (long long)n * g.M * g.N + pos;
-    c.mx = mx[(long long)n * g.N + pos];
-    return c;
 }
 
 // ------------------------------------------------------------------- forward
@@ -344,47 +252,48 @@ __global__ void __launch_bounds__(256) mex_dx_tiled(MexGeo g, const float* __res
 // ---------------------------------------------------------- offsets gradient
 // C[i = m, j = k] = sum_{q = positions of region r in this split} (dy*G)[m][q] * Ex[k][q]; both operands
 // are contiguous along q in memory, so they are stored transposed (swizzled stages).
-template <bool SPATIAL1>
+template <int TILE, int KC, bool SPATIAL1>
 __global__ void __launch_bounds__(256) mex_doff_tiled(MexGeo g, const float* __restrict__ x, const float* __restrict__ mo,
                                                       const float* __restrict__ mx, const float* __restrict__ y,
                                                       const float* __restrict__ dy, float* __restrict__ part, int splits,
                                                       const int* __restrict__ flag) {
-    using Cfg = TileCfg<kDoffTile, kDoffTile, kDoffKC, 4, 4, 1, 1>;
+    using Cfg = TileCfg<TILE, TILE, KC, TILE / 16, TILE / 16, 1, 1>;
     static_assert(Cfg::THREADS == 256, "256 threads");
+    constexpr int ROWS = 256 / KC;                                  // tile rows one staging pass covers
     if (*flag) return;
     __shared__ __align__(16) float smem[Cfg::SMEM_FLOATS];
     const long long P = (long long)g.B * g.rs;
-    const int mtiles = (g.M + kDoffTile - 1) / kDoffTile, ktiles = (g.K + kDoffTile - 1) / kDoffTile;
+    const int mtiles = (g.M + TILE - 1) / TILE, ktiles = (g.K + TILE - 1) / TILE;
     int bid = blockIdx.x;
     const int kt = bid % ktiles; bid /= ktiles;
     const int mt = bid % mtiles; bid /= mtiles;
     const int r = bid % g.R;
     const int split = bid / g.R;
-    const int i0 = mt * kDoffTile, jk0 = kt * kDoffTile;
-    const long long chunks = (P + kDoffKC - 1) / kDoffKC;
+    const int i0 = mt * TILE, jk0 = kt * TILE;
+    const long long chunks = (P + KC - 1) / KC;
     const long long c_begin = chunks * split / splits, c_end = chunks * (split + 1) / splits;
 
     const TileThread<Cfg> t;
     const float eps = float(g.eps), cst = float(g.cst), oob = float(g.oob);
-    const int qq = threadIdx.x % 32, e0 = threadIdx.x / 32;         // this thread stages q = qq, rows e0 + 8*s
+    const int qq = threadIdx.x % KC, e0 = threadIdx.x / KC;         // this thread stages q = qq, rows e0 + ROWS*s
     const float* mor = mo + r * g.M;
     float mom[Cfg::A_PER];
 #pragma unroll
-    for (int s = 0; s < Cfg::A_PER; ++s) mom[s] = (i0 + e0 + 8 * s < g.M) ? mor[i0 + e0 + 8 * s] : 0.f;
+    for (int s = 0; s < Cfg::A_PER; ++s) mom[s] = (i0 + e0 + ROWS * s < g.M) ? mor[i0 + e0 + ROWS * s] : 0.f;
     Column cur;                                                     // the position this thread stages in the fetched chunk
     float ray[Cfg::A_PER], rag[Cfg::A_PER], rbx[Cfg::B_PER];
 
-    float2 acc[4][2];
+    float2 acc[Cfg::RM][Cfg::RN / 2];
 #pragma unroll
-    for (int r_ = 0; r_ < 4; ++r_)
+    for (int r_ = 0; r_ < Cfg::RM; ++r_)
 #pragma unroll
-        for (int c_ = 0; c_ < 2; ++c_) acc[r_][c_] = make_float2(0.f, 0.f);
+        for (int c_ = 0; c_ < Cfg::RN / 2; ++c_) acc[r_][c_] = make_float2(0.f, 0.f);
 
     auto fetchA = [&](int chunk, float*) {
-        cur = column_of(g, r, (c_begin + chunk) * kDoffKC + qq, P, mx);
+        cur = column_of(g, r, (c_begin + chunk) * KC + qq, P, mx);
 #pragma unroll
         for (int s = 0; s < Cfg::A_PER; ++s) {
-            const int m = i0 + e0 + 8 * s;
+            const int m = i0 + e0 + ROWS * s;
             const bool ok = cur.base >= 0 && m < g.M;
             ray[s] = ok ? __ldcs(y + cur.base + (long long)m * g.N) : 0.f;
             rag[s] = ok ? __ldcs(dy + cur.base + (long long)m * g.N) : 0.f;
@@ -394,20 +303,20 @@ __global__ void __launch_bounds__(256) mex_doff_tiled(MexGeo g, const float* __r
         const float* xs = x + (size_t)cur.n * g.C * g.H * g.W;
 #pragma unroll
         for (int s = 0; s < Cfg::B_PER; ++s) {
-            const int k = jk0 + e0 + 8 * s;
+            const int k = jk0 + e0 + ROWS * s;
             rbx[s] = (cur.base >= 0 && k < g.K) ? patch_value<SPATIAL1>(g, xs, cur.c0, cur.h0, cur.w0, k, oob) : 0.f;
         }
     };
     auto commitA = [&](float* As) {
 #pragma unroll
         for (int s = 0; s < Cfg::A_PER; ++s)
-            As[stage_offset<kDoffTile, true>(qq, e0 + 8 * s)] = rag[s] * fast_exp(eps * (cur.mx + mom[s] - ray[s]) + cst);
+            As[stage_offset<TILE, true>(qq, e0 + ROWS * s)] = rag[s] * fast_exp(eps * (cur.mx + mom[s] - ray[s]) + cst);
     };
     auto commitB = [&](float* Bs) {
 #pragma unroll
         for (int s = 0; s < Cfg::B_PER; ++s) {
-            const int e = e0 + 8 * s;
-            Bs[stage_offset<kDoffTile, true>(qq, e)] = (cur.base >= 0 && jk0 + e < g.K) ? fast_exp(eps * (rbx[s] - cur.mx)) : 0.f;
+            const int e = e0 + ROWS * s;
+            Bs[stage_offset<TILE, true>(qq, e)] = (cur.base >= 0 && jk0 + e < g.K) ? fast_exp(eps * (rbx[s] - cur.mx)) : 0.f;
         }
     };
     auto comb = [&](int r_, int cp, const float2 (&a)[1], const float2 (&b)[1]) { acc[r_][cp] = fma2(a[0], b[0], acc[r_][cp]); };
@@ -415,11 +324,11 @@ __global__ void __launch_bounds__(256) mex_doff_tiled(MexGeo g, const float* __r
 
     float* dst = part + ((size_t)split * g.R + r) * g.M * g.K;
 #pragma unroll
-    for (int r_ = 0; r_ < 4; ++r_) {
+    for (int r_ = 0; r_ < Cfg::RM; ++r_) {
         const int m = i0 + t.row(r_);
         if (m >= g.M) continue;
 #pragma unroll
-        for (int c_ = 0; c_ < 4; ++c_) {
+        for (int c_ = 0; c_ < Cfg::RN; ++c_) {
             const int k = jk0 + t.col(c_);
             if (k < g.K) dst[(size_t)m * g.K + k] = (c_ & 1) ? acc[r_][c_ >> 1].y : acc[r_][c_ >> 1].x;
         }
@@ -451,10 +360,12 @@ bool blocks_cover_input(const MexGeo& g) {
     return full(g.C, g.bc, g.sc, g.pc) && full(g.H, g.bh, g.sh, g.ph) && full(g.W, g.bw, g.sw, g.pw);
 }
 
-cudaError_t run_prepasses(const MexGeo& g, const MexWs& w, const float* x, const float* off, cudaStream_t s) {
+cudaError_t run_prepasses(const MexGeo& g, const MexWs& w, const float* x, const float* off, cudaStream_t s, bool need_mx = true) {
     cudaError_t e = cudaMemsetAsync(w.flag, 0, 16, s);
     if (e != cudaSuccess) return e;
     mex_prep_offsets<<<g.R * g.M, 128, 0, s>>>(g, off, w.mo, w.eo, w.eot, w.flag);
+    if (!need_mx) { count_launch(); return cudaGetLastError(); }
+    if (g.K >= 256) { count_launch(); return launch_mex_colmax_wide(g, x, w.mx, w.flag, s); }
     const long long total = (long long)g.B * g.N;
     const int grid = int(std::min<long long>((total + 255) / 256, 148LL * 16));
     if (g.bh == 1 && g.bw == 1) mex_colmax<true><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
@@ -478,6 +389,13 @@ size_t mex_workspace_bytes(const MexGeo& g, bool f64, uint32_t flags) {
 
 cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* off, float* y, void* ws, uint32_t, cudaStream_t s) {
     const MexWs w = carve(g, ws);
+    if (smallm_shape(g)) {
+        cudaError_t e = run_prepasses(g, w, x, off, s, false);
+        if (e != cudaSuccess) return e;
+        e = launch_mex_fwd_smallm(g, x, w.eot, w.mo, y, w.flag, s);
+        if (e != cudaSuccess) return e;
+        return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);
+    }
     cudaError_t e = run_prepasses(g, w, x, off, s);
     if (e != cudaSuccess) return e;
     const long long P = (long long)g.B * g.rs;
@@ -539,11 +457,17 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
                                 void* ws, uint32_t, cudaStream_t s) {
     if (!blocks_disjoint(g)) return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, nullptr);
     const MexWs w = carve(g, ws);
-    cudaError_t e = run_prepasses(g, w, x, off, s);
+    const bool small = smallm_shape(g);
+    cudaError_t e = run_prepasses(g, w, x, off, s, !small);
     if (e != cudaSuccess) return e;
     if (!blocks_cover_input(g)) {
         e = cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)g.B * g.C * g.H * g.W, s);
         if (e != cudaSuccess) return e;
+    }
+    if (small) {
+        e = launch_mex_dx_smallm(g, x, w.eo, w.mo, y, dy, dx, w.flag, s);
+        if (e != cudaSuccess) return e;
+        return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
     }
     const long long P = (long long)g.B * g.rs;
     const bool sp1 = g.bh == 1 && g.bw == 1;
@@ -566,9 +490,23 @@ cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* 
     cudaError_t e = run_prepasses(g, w, x, off, s);
     if (e != cudaSuccess) return e;
     const int splits = doff_splits(g);
-    const long long blocks = (long long)((g.M + kDoffTile - 1) / kDoffTile) * ((g.K + kDoffTile - 1) / kDoffTile) * g.R * splits;
-    if (g.bh == 1 && g.bw == 1) mex_doff_tiled<true><<<int(blocks), 256, 0, s>>>(g, x, w.mo, w.mx, y, dy, w.part, splits, w.flag);
-    else mex_doff_tiled<false><<<int(blocks), 256, 0, s>>>(g, x, w.mo, w.mx, y, dy, w.part, splits, w.flag);
+    if (smallm_shape(g)) {
+        e = launch_mex_doff_smallm(g, x, w.mo, w.mx, y, dy, w.part, splits, w.flag, s);
+        if (e != cudaSuccess) return e;
+        const long long n = (long long)g.R * g.M * g.K;
+        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, g.K, splits, w.part, w.eo, doff, accumulate, w.flag);
+        count_launch();
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
+    }
+    const int tile = doff_big(g) ? 128 : 64;
+    const long long blocks = (long long)((g.M + tile - 1) / tile) * ((g.K + tile - 1) / tile) * g.R * splits;
+    const bool sp1 = g.bh == 1 && g.bw == 1;
+#define DOFF(T, KC, SP) mex_doff_tiled<T, KC, SP><<<int(blocks), 256, 0, s>>>(g, x, w.mo, w.mx, y, dy, w.part, splits, w.flag)
+    if (doff_big(g)) { if (sp1) DOFF(128, 16, true); else DOFF(128, 16, false); }
+    else { if (sp1) DOFF(64, 32, true); else DOFF(64, 32, false); }
+#undef DOFF
     const long long n = (long long)g.R * g.M * g.K;
     mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, g.K, splits, w.part, w.eo, doff, accumulate, w.flag);
     count_launch(2);

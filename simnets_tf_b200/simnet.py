@@ -83,6 +83,26 @@ def init_parameters(spec, seed):
     return out
 
 
+class _SumPool(torch.autograd.Function):
+    """k x k sum pooling (stride k).  The backward of a sum pool copies each output gradient to the k*k
+    inputs it summed, which is a nearest-neighbour upsampling."""
+
+    @staticmethod
+    def forward(ctx, x, k):
+        ctx.k = k
+        return F.avg_pool2d(x, k) * float(k * k)
+
+    @staticmethod
+    def backward(ctx, dy):
+        return F.interpolate(dy, scale_factor=ctx.k, mode="nearest"), None
+
+
+def sum_pool(x, k):
+    if x.shape[2] % k or x.shape[3] % k:
+        return F.avg_pool2d(x, k) * float(k * k)
+    return _SumPool.apply(x, k)
+
+
 class SimNet(torch.nn.Module):
     """A specification instantiated on the CUDA operators."""
 
@@ -111,7 +131,7 @@ class SimNet(torch.nn.Module):
             if mod is not None:
                 x = mod(x)
             elif entry[0] == "sumpool":
-                x = F.avg_pool2d(x, entry[1]) * float(entry[1] * entry[1])
+                x = sum_pool(x, entry[1])
             elif entry[0] == "flatten":
                 x = x.flatten(1)
         return x

@@ -152,6 +152,9 @@ def _mex_small():
     cases.append(mex_case("whole_image_stride", (2, 8, 4, 4), 10, (8, 4, 4), (-1, -1, -1), softmax=True, seed=310))
     cases.append(mex_case("wide_M_K", (2, 40, 6, 6), 70, (40, 1, 1), (40, 1, 1), softmax=True, unshared_region=(2,), seed=311, normalize=True))
     cases.append(mex_case("empty_batch", (0, 4, 6, 6), 3, (4, 1, 1), (4, 1, 1), softmax=True, seed=312))
+    # few instances over long patches (classifier-head shape): overlapping, padded blocks and disjoint blocks with a remainder
+    cases.append(mex_case("head_overlap", (3, 16, 9, 9), 5, (16, 5, 5), (16, 2, 2), (0, 1, 1), softmax=True, unshared_region=(2,), seed=313))
+    cases.append(mex_case("head_disjoint", (3, 16, 9, 9), 7, (16, 4, 4), (16, 4, 4), eps=2.0, unshared=False, shared_region=(1,), seed=314, normalize=True))
     return cases
 
 
