@@ -238,29 +238,34 @@ __global__ void __launch_bounds__(kThreads) mex_dx_direct(MexGeo g, const T* __r
     }
 }
 
-// One block per (region r, instance m, tap k): reduces over batch and the region's positions.
+// One block at a time per (region r, instance m, tap k): reduces over batch and the region's positions.
+// The grid is capped and strides over the (r, m, k) triples, so that a gated-off launch costs a few
+// hundred blocks, not one per parameter.
 template <typename T>
 __global__ void __launch_bounds__(kThreads) mex_doff_direct(MexGeo g, const T* __restrict__ x, const T* __restrict__ off,
                                                             const T* __restrict__ y, const T* __restrict__ dy,
                                                             T* __restrict__ doff, int accumulate, const int* __restrict__ gate) {
     __shared__ T smem[kThreads];
     if (gate && *gate == 0) return;
-    const int rmk = blockIdx.x;
-    const int k = rmk % g.K, m = (rmk / g.K) % g.M, r = rmk / (g.K * g.M);
-    const T o = off[rmk], oob = T(g.oob), eps = T(g.eps), cst = T(g.cst);
-    T sum = T(0);
-    const long long total = (long long)g.B * g.rs;
-    for (long long i = threadIdx.x; i < total; i += kThreads) {
-        const int l = int(i % g.rs), n = int(i / g.rs);
-        const int j = mex_region_position(g, r, l);
-        if (j < 0) continue;
-        const int w = j % g.Wo, h = (j / g.Wo) % g.Ho, c = j / (g.Wo * g.Ho);
-        const T v = mex_tap(g, x + (size_t)n * g.C * g.H * g.W, c, h, w, k, oob);
-        const size_t oi = ((size_t)n * g.M + m) * g.N + j;
-        sum += mex_weight(g, eps, cst, v, o, y[oi], dy[oi]);
+    const T oob = T(g.oob), eps = T(g.eps), cst = T(g.cst);
+    const long long triples = (long long)g.R * g.M * g.K;
+    for (long long rmk = blockIdx.x; rmk < triples; rmk += gridDim.x) {
+        const int k = int(rmk % g.K), m = int((rmk / g.K) % g.M), r = int(rmk / ((long long)g.K * g.M));
+        const T o = off[rmk];
+        T sum = T(0);
+        const long long total = (long long)g.B * g.rs;
+        for (long long i = threadIdx.x; i < total; i += kThreads) {
+            const int l = int(i % g.rs), n = int(i / g.rs);
+            const int j = mex_region_position(g, r, l);
+            if (j < 0) continue;
+            const int w = j % g.Wo, h = (j / g.Wo) % g.Ho, c = j / (g.Wo * g.Ho);
+            const T v = mex_tap(g, x + (size_t)n * g.C * g.H * g.W, c, h, w, k, oob);
+            const size_t oi = ((size_t)n * g.M + m) * g.N + j;
+            sum += mex_weight(g, eps, cst, v, o, y[oi], dy[oi]);
+        }
+        const T rsum = block_sum(sum, smem);
+        if (threadIdx.x == 0) doff[rmk] = accumulate ? doff[rmk] + rsum : rsum;
     }
-    const T rsum = block_sum(sum, smem);
-    if (threadIdx.x == 0) doff[rmk] = accumulate ? doff[rmk] + rsum : rsum;
 }
 
 inline int grid_for(long long total) {
@@ -325,7 +330,8 @@ cudaError_t launch_mex_dx_direct(const MexGeo& g, bool f64, const void* x, const
 
 cudaError_t launch_mex_doff_direct(const MexGeo& g, bool f64, const void* x, const void* off, const void* y, const void* dy,
                                    void* doff, bool accumulate, cudaStream_t s, const int* gate) {
-    const int blocks = g.R * g.M * g.K;
+    const long long triples = (long long)g.R * g.M * g.K;
+    const int blocks = int(triples < 148 * 16 ? triples : 148 * 16);
     SIMNETS_DTYPE_SWITCH(f64,
         (mex_doff_direct<float><<<blocks, kThreads, 0, s>>>(g, (const float*)x, (const float*)off, (const float*)y, (const float*)dy, (float*)doff, accumulate, gate)),
         (mex_doff_direct<double><<<blocks, kThreads, 0, s>>>(g, (const double*)x, (const double*)off, (const double*)y, (const double*)dy, (double*)doff, accumulate, gate)));

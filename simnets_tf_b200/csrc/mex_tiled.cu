@@ -365,7 +365,8 @@ cudaError_t run_prepasses(const MexGeo& g, const MexWs& w, const float* x, const
     if (e != cudaSuccess) return e;
     mex_prep_offsets<<<g.R * g.M, 128, 0, s>>>(g, off, w.mo, w.eo, w.eot, w.flag);
     if (!need_mx) { count_launch(); return cudaGetLastError(); }
-    if (g.K >= 256) { count_launch(); return launch_mex_colmax_wide(g, x, w.mx, w.flag, s); }
+    // long patches over few positions are contiguous per position: reduce them with one CTA each
+    if (g.K >= 256 && g.N <= 16) { count_launch(); return launch_mex_colmax_wide(g, x, w.mx, w.flag, s); }
     const long long total = (long long)g.B * g.N;
     const int grid = int(std::min<long long>((total + 255) / 256, 148LL * 16));
     if (g.bh == 1 && g.bw == 1) mex_colmax<true><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
