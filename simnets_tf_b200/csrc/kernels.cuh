@@ -41,6 +41,12 @@ cudaError_t launch_mex_dx_smallm(const MexGeo&, const float* x, const float* eo,
                                  float* dx, const int* flag, cudaStream_t);
 cudaError_t launch_mex_doff_smallm(const MexGeo&, const float* x, const float* mo, const float* mx, const float* y, const float* dy,
                                    float* part, int splits, const int* flag, cudaStream_t);
+// mex_smallk.cu -- one thread per position, for K <= 32 (HBM-bound streaming regime)
+cudaError_t launch_mex_fwd_smallk(const MexGeo&, const float* x, const float* eo, const float* mo, float* y, const int* flag, cudaStream_t);
+cudaError_t launch_mex_dx_smallk(const MexGeo&, const float* x, const float* eo, const float* mo, const float* y, const float* dy,
+                                 float* dx, const int* flag, cudaStream_t);
+cudaError_t launch_mex_doff_smallk(const MexGeo&, const float* x, const float* mo, const float* y, const float* dy,
+                                   float* part, int slabs, const int* flag, cudaStream_t);
 // forward on the library's fixed device scratch; returns a status code of simnets_b200.h
 int launch_mex_fwd_static(const MexGeo&, const float* x, const float* off, float* y, cudaStream_t);
 cudaError_t launch_mex_dx_tiled(const MexGeo&, const float* x, const float* off, const float* y, const float* dy, float* dx,

@@ -28,7 +28,18 @@ __host__ inline bool doff_big(const MexGeo& g) { return g.M >= 96 && g.K >= 96; 
 // Few instances over long patches (a classifier head: M = 10, K = 8192): one CTA per position instead of GEMM tiles.
 __host__ inline bool smallm_shape(const MexGeo& g) { return g.M <= 16 && g.K >= 256; }
 
+// Short patches (K <= 32): the streaming kernels of mex_smallk.cu.
+__host__ inline bool smallk_shape(const MexGeo& g) { return g.K <= 32; }
+
 __host__ inline int doff_splits(const MexGeo& g) {
+    if (smallk_shape(g)) {
+        const long long P = (long long)g.B * g.rs, tiles = (P + 31) / 32, ctas = (long long)((g.M + 255) / 256) * g.R;
+        long long s = (148 * 3 + ctas - 1) / ctas;
+        if (s > tiles) s = tiles;
+        if (s < 1) s = 1;
+        if (s > 512) s = 512;
+        return int(s);
+    }
     if (smallm_shape(g)) {
         const long long P = (long long)g.B * g.rs, ktiles = (g.K + 255) / 256;
         long long s = (148 * 4 + ktiles * g.R - 1) / (ktiles * g.R);

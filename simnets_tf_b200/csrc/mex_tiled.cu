@@ -390,6 +390,13 @@ size_t mex_workspace_bytes(const MexGeo& g, bool f64, uint32_t flags) {
 
 cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* off, float* y, void* ws, uint32_t, cudaStream_t s) {
     const MexWs w = carve(g, ws);
+    if (smallk_shape(g)) {
+        cudaError_t e = run_prepasses(g, w, x, off, s, false);
+        if (e != cudaSuccess) return e;
+        e = launch_mex_fwd_smallk(g, x, w.eo, w.mo, y, w.flag, s);
+        if (e != cudaSuccess) return e;
+        return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);
+    }
     if (smallm_shape(g)) {
         cudaError_t e = run_prepasses(g, w, x, off, s, false);
         if (e != cudaSuccess) return e;
@@ -458,12 +465,17 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
                                 void* ws, uint32_t, cudaStream_t s) {
     if (!blocks_disjoint(g)) return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, nullptr);
     const MexWs w = carve(g, ws);
-    const bool small = smallm_shape(g);
+    const bool small = smallm_shape(g) || smallk_shape(g);
     cudaError_t e = run_prepasses(g, w, x, off, s, !small);
     if (e != cudaSuccess) return e;
     if (!blocks_cover_input(g)) {
         e = cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)g.B * g.C * g.H * g.W, s);
         if (e != cudaSuccess) return e;
+    }
+    if (smallk_shape(g)) {
+        e = launch_mex_dx_smallk(g, x, w.eo, w.mo, y, dy, dx, w.flag, s);
+        if (e != cudaSuccess) return e;
+        return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
     }
     if (small) {
         e = launch_mex_dx_smallm(g, x, w.eo, w.mo, y, dy, dx, w.flag, s);
@@ -488,9 +500,19 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
 cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* doff,
                                   bool accumulate, void* ws, uint32_t, cudaStream_t s) {
     const MexWs w = carve(g, ws);
-    cudaError_t e = run_prepasses(g, w, x, off, s);
+    cudaError_t e = run_prepasses(g, w, x, off, s, !smallk_shape(g));
     if (e != cudaSuccess) return e;
     const int splits = doff_splits(g);
+    if (smallk_shape(g)) {
+        e = launch_mex_doff_smallk(g, x, w.mo, y, dy, w.part, splits, w.flag, s);
+        if (e != cudaSuccess) return e;
+        const long long n = (long long)g.R * g.M * g.K;
+        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, g.K, splits, w.part, w.eo, doff, accumulate, w.flag);
+        count_launch();
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
+    }
     if (smallm_shape(g)) {
         e = launch_mex_doff_smallm(g, x, w.mo, w.mx, y, dy, w.part, splits, w.flag, s);
         if (e != cudaSuccess) return e;

@@ -26,6 +26,7 @@ struct SimWs {
     float* cm;       // [M] per-instance constant added once per output
     int2* taps;      // [K]: {offset of tap inside a sample, (kh << 16) | kw}
     float* part;     // [S][3][M][K] split partial sums of the parameter gradients
+    float* dxp;      // [2][bh*bw*M][Cp]: t and s*w (s = 2 for plain L2, else 1), channel-contiguous, for the input gradient
     size_t bytes;
 };
 
@@ -52,13 +53,15 @@ __host__ SimWs carve(const SimGeo& g, void* base) {
     w.cm = reinterpret_cast<float*>(take(sizeof(float) * g.M));
     w.taps = reinterpret_cast<int2*>(take(sizeof(int2) * g.K));
     w.part = reinterpret_cast<float*>(take(sizeof(float) * 3 * (size_t)dp_splits(g) * g.M * g.K));
+    w.dxp = reinterpret_cast<float*>(take(sizeof(float) * 2 * (size_t)g.bh * g.bw * g.M * pad4(g.C)));
     w.bytes = off;
     return w;
 }
 
 // One block per instance m: tap-major parameter planes, the per-instance constant, and (block 0) the tap table.
 __global__ void __launch_bounds__(128) sim_prep(SimGeo g, const float* __restrict__ tm, const float* __restrict__ wt,
-                                                float* __restrict__ planes, float* __restrict__ cm, int2* __restrict__ taps) {
+                                                float* __restrict__ planes, float* __restrict__ cm, int2* __restrict__ taps,
+                                                float* __restrict__ dxp) {
     __shared__ float red[128];
     const int m = blockIdx.x;
     const float fudge = float(g.fudge);
@@ -73,10 +76,11 @@ __global__ void __launch_bounds__(128) sim_prep(SimGeo g, const float* __restric
         planes[(size_t)k * ldm + m] = t;
         planes[plane + (size_t)k * ldm + m] = scale;
         planes[2 * plane + (size_t)k * ldm + m] = c;
-        if (m == 0) {
-            const int kw = k % g.bw, kh = (k / g.bw) % g.bh, c_ = k / (g.bw * g.bh);
-            taps[k] = make_int2((c_ * g.H + kh) * g.W + kw, (kh << 16) | kw);
-        }
+        const int kw = k % g.bw, kh = (k / g.bw) % g.bh, c_ = k / (g.bw * g.bh);
+        if (m == 0) taps[k] = make_int2((c_ * g.H + kh) * g.W + kw, (kh << 16) | kw);
+        const size_t q = (size_t)(kh * g.bw + kw) * g.M + m, dplane = (size_t)g.bh * g.bw * g.M * pad4(g.C);
+        dxp[q * pad4(g.C) + c_] = t;
+        dxp[dplane + q * pad4(g.C) + c_] = (g.mode == SIM_L2 ? 2.f : 1.f) * w;
     }
     red[threadIdx.x] = csum;
     __syncthreads();
@@ -336,6 +340,129 @@ __global__ void __launch_bounds__(256) sim_dparams_tiled(SimGeo g, const float* 
     }
 }
 
+// -------------------------------------------------------------- input gradient
+// dx[n, c, h, w] = sum over the taps (kh, kw) whose patch covers the pixel and over m of  s*w * dy * (t - x)   (L1: sign(t - x))
+// as a generalized GEMM with i = c, j = pixel, q = (kh, kw, m): the reference's column gradient followed by col2im
+// (HUJI-Deep/simnets-tf src/kernels/similarity_grad_kernel_cpu.cpp:205-268) becomes one gather, nothing is scattered.
+// A = (t, s*w)[q][c] from the prepass, B[q][j] = dy at the output position that tap (kh, kw) maps the pixel to (0 if none),
+// and the pixel's own x value sits in registers.  NaN pixels give 0 in the ignore_nan_input modes (epilogue select).
+// Known deviation: a pixel holding +-inf whose coverage is partial (taps cut off by padding or stride) yields NaN where
+// the reference yields +-inf, because a cut-off tap contributes 0 * (t - inf).
+struct DxColumn { long long base; int n, h, w; };   // base = n*C*H*W + h*W + w, or -1 past the end
+
+template <int TM, int MODE>
+__global__ void __launch_bounds__(256) sim_dx_tiled(SimGeo g, const float* __restrict__ x, const float* __restrict__ dxp,
+                                                    const float* __restrict__ dy, float* __restrict__ dx) {
+    constexpr bool L1 = MODE == SIM_L1 || MODE == SIM_L1_SKIP;
+    constexpr bool SKIP_NAN = MODE == SIM_L2N_NAN || MODE == SIM_L1_SKIP;
+    using Cfg = TileCfg<TM, 128, 8, TM / 16, 8, 2, 1>;
+    static_assert(Cfg::THREADS == 256, "256 threads");
+    __shared__ __align__(16) float smem[Cfg::SMEM_FLOATS];
+    __shared__ long long col_base[Cfg::TN];
+    const long long P = (long long)g.B * g.H * g.W;
+    const int ctiles = (g.C + TM - 1) / TM;
+    const int ct = blockIdx.x % ctiles;
+    const long long jt = blockIdx.x / ctiles;
+    const int i0 = ct * TM;
+    const long long j0 = jt * Cfg::TN;
+    const int Q = g.bh * g.bw * g.M, ldc = pad4(g.C);
+    const size_t dplane = (size_t)Q * ldc;
+
+    const TileThread<Cfg> t;
+    const int s_lane = threadIdx.x % 128, s_k = threadIdx.x / 128;
+    DxColumn sc;
+    {
+        const long long j = j0 + s_lane;
+        sc.base = -1; sc.n = sc.h = sc.w = 0;
+        if (j < P) {
+            const int hw = g.H * g.W;
+            sc.n = int(j / hw);
+            const int p = int(j - (long long)sc.n * hw);
+            sc.h = p / g.W; sc.w = p % g.W;
+            sc.base = (long long)sc.n * g.C * hw + p;
+        }
+    }
+    if (s_k == 0) col_base[s_lane] = sc.base;
+    const float* dyn = dy + (size_t)sc.n * g.M * g.N;
+    // staging cursor over q = (tap, m): element s of a chunk is q = chunk*8 + s_k + 2*s
+    float rb[Cfg::B_PER];
+
+    float2 acc[Cfg::RM][Cfg::RN / 2];
+#pragma unroll
+    for (int r_ = 0; r_ < Cfg::RM; ++r_)
+#pragma unroll
+        for (int c_ = 0; c_ < Cfg::RN / 2; ++c_) acc[r_][c_] = make_float2(0.f, 0.f);
+
+    auto fetchA = [&](int chunk, float* As) {
+#pragma unroll
+        for (int p = 0; p < 2; ++p) stage_copy_async<Cfg, TM>(As + p * Cfg::KC * TM, dxp + p * dplane, ldc, chunk * Cfg::KC, Q, i0, g.C);
+    };
+    auto fetchB = [&](int chunk, float*) {
+#pragma unroll
+        for (int s = 0; s < Cfg::B_PER; ++s) {
+            const int q = chunk * Cfg::KC + s_k + s * 2;
+            float v = 0.f;
+            if (q < Q && sc.base >= 0) {
+                const int tap = q / g.M, m = q - tap * g.M;
+                const int kh = tap / g.bw, kw = tap - kh * g.bw;
+                const int hp = sc.h + g.ph - kh, wp = sc.w + g.pw - kw;
+                if (hp >= 0 && wp >= 0) {
+                    const int ho = hp / g.sh, wo = wp / g.sw;
+                    if (ho * g.sh == hp && wo * g.sw == wp && ho < g.oh && wo < g.ow) v = __ldg(dyn + (size_t)m * g.N + ho * g.ow + wo);
+                }
+            }
+            rb[s] = v;
+        }
+    };
+    auto commitA = [&](float*) { cp_async_wait_all(); };
+    auto commitB = [&](float* Bs) {
+#pragma unroll
+        for (int s = 0; s < Cfg::B_PER; ++s) Bs[(s_k + s * 2) * Cfg::TN + s_lane] = rb[s];
+    };
+
+    // wait for col_base, then this thread's own x values (one per output)
+    __syncthreads();
+    long long cb[Cfg::RN];
+#pragma unroll
+    for (int c_ = 0; c_ < Cfg::RN; ++c_) cb[c_] = col_base[t.col(c_)];
+    float2 xx[Cfg::RM][Cfg::RN / 2];
+    const size_t chw = (size_t)g.H * g.W;
+#pragma unroll
+    for (int r_ = 0; r_ < Cfg::RM; ++r_) {
+        const int c = i0 + t.row(r_);
+#pragma unroll
+        for (int c_ = 0; c_ < Cfg::RN; ++c_) {
+            const float v = (c < g.C && cb[c_] >= 0) ? __ldg(x + cb[c_] + (size_t)c * chw) : 0.f;
+            if (c_ & 1) xx[r_][c_ >> 1].y = v; else xx[r_][c_ >> 1].x = v;
+        }
+    }
+    auto comb = [&](int r_, int cp, const float2 (&a)[2], const float2 (&b)[1]) {
+        const float2 d = add2(a[0], neg2(xx[r_][cp]));
+        const float2 e = mul2(a[1], b[0]);
+        if (L1) {
+            const float2 sg = make_float2(float((0.f < d.x) - (d.x < 0.f)), float((0.f < d.y) - (d.y < 0.f)));
+            acc[r_][cp] = fma2(e, sg, acc[r_][cp]);
+        } else {
+            acc[r_][cp] = fma2(e, d, acc[r_][cp]);
+        }
+    };
+    tile_mainloop<Cfg, false, false>(smem, (Q + Cfg::KC - 1) / Cfg::KC, t, fetchA, fetchB, commitA, commitB, comb);
+
+#pragma unroll
+    for (int r_ = 0; r_ < Cfg::RM; ++r_) {
+        const int c = i0 + t.row(r_);
+        if (c >= g.C) continue;
+#pragma unroll
+        for (int c_ = 0; c_ < Cfg::RN; ++c_) {
+            if (cb[c_] < 0) continue;
+            float v = (c_ & 1) ? acc[r_][c_ >> 1].y : acc[r_][c_ >> 1].x;
+            const float xv = (c_ & 1) ? xx[r_][c_ >> 1].y : xx[r_][c_ >> 1].x;
+            if (SKIP_NAN && xv != xv) v = 0.f;
+            dx[cb[c_] + (size_t)c * chw] = v;
+        }
+    }
+}
+
 // Sums the split partials in split order and applies the per-parameter factors of the backward functors.
 __global__ void __launch_bounds__(256) sim_dparams_reduce(SimGeo g, int splits, const float* __restrict__ part,
                                                           const float* __restrict__ wt, float* __restrict__ dt, float* __restrict__ dw,
@@ -360,7 +487,7 @@ __global__ void __launch_bounds__(256) sim_dparams_reduce(SimGeo g, int splits, 
 }
 
 void launch_prep(const SimGeo& g, const SimWs& w, const float* t, const float* wt, cudaStream_t s) {
-    sim_prep<<<g.M, 128, 0, s>>>(g, t, wt, w.planes, w.cm, w.taps);
+    sim_prep<<<g.M, 128, 0, s>>>(g, t, wt, w.planes, w.cm, w.taps, w.dxp);
     count_launch();
 }
 
@@ -401,8 +528,38 @@ cudaError_t launch_sim_fwd_tiled(const SimGeo& g, const float* x, const float* t
     return cudaGetLastError();
 }
 
-cudaError_t launch_sim_dx_tiled(const SimGeo& g, const float* x, const float* t, const float* w, const float* dy, float* dx, void*, cudaStream_t s) {
-    return launch_sim_dx_direct(g, false, x, t, w, dy, dx, s);
+// every pixel is covered by at least one tap (otherwise an uncovered NaN pixel would have to come out as 0)
+static bool every_pixel_covered(const SimGeo& g) {
+    auto axis = [](int dim, int block, int stride, int pad, int out) {
+        if (stride > block) return false;                        // gaps between patches
+        return pad >= 0 && (out - 1) * stride + block - pad >= dim;   // last patch reaches the end; first starts at <= 0
+    };
+    return axis(g.H, g.bh, g.sh, g.ph, g.oh) && axis(g.W, g.bw, g.sw, g.pw, g.ow);
+}
+
+cudaError_t launch_sim_dx_tiled(const SimGeo& g, const float* x, const float* t, const float* w, const float* dy, float* dx, void* ws, cudaStream_t s) {
+    // few channels: the gather kernel is memory bound there and needs no staging; also when some pixel has no tap at all
+    if (g.C < 16 || !every_pixel_covered(g)) return launch_sim_dx_direct(g, false, x, t, w, dy, dx, s);
+    const SimWs W = carve(g, ws);
+    launch_prep(g, W, t, w, s);
+    const long long P = (long long)g.B * g.H * g.W;
+    const bool wide = g.C > 64;
+    const long long blocks = ((P + 127) / 128) * ((g.C + (wide ? 127 : 63)) / (wide ? 128 : 64));
+    if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+#define DX(TM, MODE) sim_dx_tiled<TM, MODE><<<int(blocks), 256, 0, s>>>(g, x, W.dxp, dy, dx)
+#define DX_MODES(TM)                                         \
+    switch (g.mode) {                                        \
+    case SIM_L1: DX(TM, SIM_L1); break;                      \
+    case SIM_L1_SKIP: DX(TM, SIM_L1_SKIP); break;            \
+    case SIM_L2: DX(TM, SIM_L2); break;                      \
+    case SIM_L2N: DX(TM, SIM_L2N); break;                    \
+    default: DX(TM, SIM_L2N_NAN); break;                     \
+    }
+    if (wide) { DX_MODES(128) } else { DX_MODES(64) }
+#undef DX_MODES
+#undef DX
+    count_launch();
+    return cudaGetLastError();
 }
 
 cudaError_t launch_sim_dparams_tiled(const SimGeo& g, const float* x, const float* t, const float* w, const float* dy,

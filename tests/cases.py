@@ -75,6 +75,10 @@ def _sim_small():
     cases.append(sim_case("stride_gt_block", (2, 2, 11, 11), 3, "L2", (2, 2), (3, 3), (0, 0), seed=157))
     cases.append(sim_case("wide_M_K", (2, 8, 9, 9), 70, "L2", (3, 3), (1, 1), (1, 1), norm=True, ignore_nan=True, nan_frac=0.1, seed=158))
     cases.append(sim_case("empty_batch", (0, 2, 6, 6), 3, "L2", (3, 3), (1, 1), (1, 1), seed=159))
+    # enough channels for the tiled input-gradient kernel (C >= 16), with NaNs, stride 2 and L1
+    cases.append(sim_case("dx_tiled_nan", (2, 20, 9, 10), 12, "L2", (3, 3), (1, 1), (1, 1), norm=True, ignore_nan=True, nan_frac=0.1, seed=160))
+    cases.append(sim_case("dx_tiled_l1_s2", (2, 17, 8, 8), 6, "L1", (3, 3), (2, 2), (1, 1), seed=161))
+    cases.append(sim_case("dx_tiled_l2", (3, 16, 7, 9), 70, "L2", (2, 3), (1, 2), (1, 1), oob=0.25, seed=162))
     return cases
 
 
@@ -152,6 +156,10 @@ def _mex_small():
     cases.append(mex_case("whole_image_stride", (2, 8, 4, 4), 10, (8, 4, 4), (-1, -1, -1), softmax=True, seed=310))
     cases.append(mex_case("wide_M_K", (2, 40, 6, 6), 70, (40, 1, 1), (40, 1, 1), softmax=True, unshared_region=(2,), seed=311, normalize=True))
     cases.append(mex_case("empty_batch", (0, 4, 6, 6), 3, (4, 1, 1), (4, 1, 1), softmax=True, seed=312))
+    # mid-size patches (32 < K < 256) with many instances: the GEMM-tiled kernels, with regions, padding and remainders
+    cases.append(mex_case("tiled_regions", (3, 48, 7, 7), 20, (48, 1, 1), (48, 1, 1), softmax=True, unshared_region=(1, 2, 3), seed=315, normalize=True))
+    cases.append(mex_case("tiled_spatial", (2, 6, 13, 12), 33, (6, 3, 3), (6, 3, 3), eps=0.75, unshared=False, shared_region=(2,), seed=316))
+    cases.append(mex_case("tiled_padded", (2, 5, 9, 9), 18, (5, 3, 3), (5, 3, 3), (0, 1, 1), eps=-1.25, oob=0.3, softmax=True, unshared_region=(2,), seed=317))
     # few instances over long patches (classifier-head shape): overlapping, padded blocks and disjoint blocks with a remainder
     cases.append(mex_case("head_overlap", (3, 16, 9, 9), 5, (16, 5, 5), (16, 2, 2), (0, 1, 1), softmax=True, unshared_region=(2,), seed=313))
     cases.append(mex_case("head_disjoint", (3, 16, 9, 9), 7, (16, 4, 4), (16, 4, 4), eps=2.0, unshared=False, shared_region=(1,), seed=314, normalize=True))
