@@ -62,6 +62,9 @@ enum { SIMNETS_SIM_L1 = 0, SIMNETS_SIM_L2 = 1 };
  * skipped (term contributes 0).  Requires similarity_function == L1. */
 #define SIMNETS_FLAG_SIM_L1_SKIP_NAN   (1u << 4)
 
+/* MEX only: keep the factorised GEMM on the CUDA cores (no tcgen05 tensor-core kernels). */
+#define SIMNETS_FLAG_MEX_NO_TENSORCORE (1u << 5)
+
 /* ---- Similarity ---------------------------------------------------------- */
 /* Mirrors the attrs of the Similarity op family (src/ops/similarity_op.cpp:61-75)
  * and the dimensions SimilarityKernelCommon::CalculateDimensions derives

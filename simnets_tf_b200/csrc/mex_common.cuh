@@ -15,6 +15,7 @@ struct MexWs {           // workspace carve-up, every part 256-byte aligned
     float* eot;          // [R][K][Mp]  Eo transposed, rows padded likewise (16-byte aligned rows for async copies)
     float* mx;           // [B][N]
     float* part;         // [S][R][M][K] split-q partial sums of the offsets gradient
+    float* tc_tiles;     // Eo split into TF32 hi / lo planes, tile by tile in the tensor-core operand layout
     size_t bytes;
     size_t fwd_bytes;    // bytes the forward pass touches (everything before `part`)
 };
@@ -30,6 +31,9 @@ __host__ inline bool smallm_shape(const MexGeo& g) { return g.M <= 16 && g.K >= 
 
 // Short patches (K <= 32): the streaming kernels of mex_smallk.cu.
 __host__ inline bool smallk_shape(const MexGeo& g) { return g.K <= 32; }
+
+// GEMM-sized layers (many instances, mid to long patches): the tensor-core forward of mex_tc.cu.
+__host__ inline bool tc_shape(const MexGeo& g) { return !smallk_shape(g) && !smallm_shape(g) && g.M >= 48 && g.K >= 48; }
 
 __host__ inline int doff_splits(const MexGeo& g) {
     if (smallk_shape(g)) {
@@ -71,6 +75,7 @@ __host__ inline MexWs carve(const MexGeo& g, void* base) {
     w.mx = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.B * g.N));
     w.fwd_bytes = off;
     w.part = reinterpret_cast<float*>(take(sizeof(float) * (size_t)doff_splits(g) * g.R * g.M * g.K));
+    w.tc_tiles = reinterpret_cast<float*>(take(tc_shape(g) ? sizeof(float) * mex_tc_tile_floats(g) : 0));
     w.bytes = off;
     return w;
 }

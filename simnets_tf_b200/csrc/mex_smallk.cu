@@ -46,7 +46,7 @@ __device__ __forceinline__ void load_offsets_chunk(const MexGeo& g, const float*
 
 // ------------------------------------------------------------------- forward
 template <int KP, int C, bool SPATIAL1>
-__global__ void __launch_bounds__(kT) mex_fwd_smallk(MexGeo g, const float* __restrict__ x, const float* __restrict__ eo,
+__global__ void __launch_bounds__(kT, 2) mex_fwd_smallk(MexGeo g, const float* __restrict__ x, const float* __restrict__ eo,
                                                      const float* __restrict__ mo, float* __restrict__ y, const int* __restrict__ flag) {
     __shared__ __align__(16) float eo_s[kMC * KP];
     __shared__ float mo_s[kMC];
@@ -57,7 +57,8 @@ __global__ void __launch_bounds__(kT) mex_fwd_smallk(MexGeo g, const float* __re
     const float eps = float(g.eps);
     float2 ex[C][KP / 2];
     float cadd[C];
-    float* yb[C];
+    float* yb[C];                             // walks down the instances: y[n, m, pos] for m = 0, 1, ...
+    bool live[C];
 #pragma unroll
     for (int c = 0; c < C; ++c) {
         const Column col = column_of(g, r, j0 + c * kT + threadIdx.x, P, nullptr);
@@ -66,7 +67,8 @@ __global__ void __launch_bounds__(kT) mex_fwd_smallk(MexGeo g, const float* __re
 #pragma unroll
         for (int k = 0; k < KP / 2; ++k) ex[c][k] = make_float2(fast_exp(eps * (v[2 * k] - mxv)), fast_exp(eps * (v[2 * k + 1] - mxv)));
         cadd[c] = mxv + float(g.cst) / eps;
-        yb[c] = col.base >= 0 ? y + col.base : nullptr;
+        live[c] = col.base >= 0;
+        yb[c] = y + (live[c] ? col.base : 0);
     }
     const float k_log = 0.69314718056f / eps;
     for (int m0 = 0; m0 < g.M; m0 += kMC) {
@@ -74,7 +76,7 @@ __global__ void __launch_bounds__(kT) mex_fwd_smallk(MexGeo g, const float* __re
         load_offsets_chunk<KP>(g, eo, mo, r, m0, eo_s, mo_s);
         __syncthreads();
         const int mend = min(kMC, g.M - m0);
-#pragma unroll 2
+#pragma unroll 4
         for (int mm = 0; mm < mend; ++mm) {
             float2 e[KP / 2];
 #pragma unroll
@@ -83,14 +85,17 @@ __global__ void __launch_bounds__(kT) mex_fwd_smallk(MexGeo g, const float* __re
                 e[2 * q] = make_float2(t.x, t.y); e[2 * q + 1] = make_float2(t.z, t.w);
             }
             const float mom = mo_s[mm];
-            const long long row = (long long)(m0 + mm) * g.N;
 #pragma unroll
             for (int c = 0; c < C; ++c) {
-                float2 s2 = mul2(e[0], ex[c][0]);
+                // two independent chains halve the dependent-FMA depth of one output
+                float2 s2 = mul2(e[0], ex[c][0]), s3 = mul2(e[1], ex[c][1]);
 #pragma unroll
-                for (int k = 1; k < KP / 2; ++k) s2 = fma2(e[k], ex[c][k], s2);
-                const float val = fmaf(__log2f(s2.x + s2.y), k_log, cadd[c] + mom);
-                if (yb[c]) __stcs(yb[c] + row, val);
+                for (int k = 2; k < KP / 2; k += 2) { s2 = fma2(e[k], ex[c][k], s2); s3 = fma2(e[k + 1], ex[c][k + 1], s3); }
+                s2 = add2(s2, s3);
+                float lg;                                  // S >= exp(-60): never denormal, the flush-to-zero form is exact enough
+                asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(lg) : "f"(s2.x + s2.y));
+                if (live[c]) __stcs(yb[c], fmaf(lg, k_log, cadd[c] + mom));
+                yb[c] += g.N;
             }
         }
     }

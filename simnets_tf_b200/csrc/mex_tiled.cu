@@ -388,7 +388,7 @@ size_t mex_workspace_bytes(const MexGeo& g, bool f64, uint32_t flags) {
     return carve(g, nullptr).bytes;
 }
 
-cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* off, float* y, void* ws, uint32_t, cudaStream_t s) {
+cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* off, float* y, void* ws, uint32_t flags, cudaStream_t s) {
     const MexWs w = carve(g, ws);
     if (smallk_shape(g)) {
         cudaError_t e = run_prepasses(g, w, x, off, s, false);
@@ -406,6 +406,13 @@ cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* o
     }
     cudaError_t e = run_prepasses(g, w, x, off, s);
     if (e != cudaSuccess) return e;
+    if (tc_shape(g) && !(flags & SIMNETS_FLAG_MEX_NO_TENSORCORE)) {
+        e = launch_mex_tc_prep(g, w.eo, w.tc_tiles, s);
+        if (e != cudaSuccess) return e;
+        e = launch_mex_fwd_tc(g, x, w.tc_tiles, w.mo, w.mx, y, w.flag, patches_inside_input(g), s);
+        if (e != cudaSuccess) return e;
+        return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);
+    }
     const long long P = (long long)g.B * g.rs;
     const bool sp1 = g.bh == 1 && g.bw == 1;
     const bool wide = g.M > 64;
@@ -457,7 +464,7 @@ int launch_mex_fwd_static(const MexGeo& g, const float* x, const float* off, flo
     }
     // launch_mex_fwd_tiled clears the one word that must start at zero (the safety flag) on every call;
     // everything else in the scratch is fully rewritten by the prepasses before it is read.
-    e = launch_mex_fwd_tiled(g, x, off, y, ptr, 0, s);
+    e = launch_mex_fwd_tiled(g, x, off, y, ptr, SIMNETS_FLAG_MEX_NO_TENSORCORE, s);   // the scratch bound covers the CUDA-core path
     return e == cudaSuccess ? SIMNETS_OK : int(e);
 }
 
