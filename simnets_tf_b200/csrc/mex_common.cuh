@@ -1,5 +1,6 @@
 // Shared by the MEX kernel files: workspace carve-up, tap decoding, per-position bookkeeping.
 #pragma once
+#include <algorithm>
 #include "kernels.cuh"
 #include "tile.cuh"
 
@@ -74,7 +75,8 @@ __host__ inline MexWs carve(const MexGeo& g, void* base) {
     w.eot = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.K * pad4(g.M)));
     w.mx = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.B * g.N));
     w.fwd_bytes = off;
-    w.part = reinterpret_cast<float*>(take(sizeof(float) * (size_t)doff_splits(g) * g.R * g.M * g.K));
+    const int max_splits = tc_shape(g) ? std::max(doff_splits(g), mex_tc_doff_splits(g)) : doff_splits(g);
+    w.part = reinterpret_cast<float*>(take(sizeof(float) * (size_t)max_splits * g.R * g.M * g.K));
     w.tc_tiles = reinterpret_cast<float*>(take(tc_shape(g) ? sizeof(float) * mex_tc_tile_floats(g) : 0));
     w.bytes = off;
     return w;

@@ -1,7 +1,10 @@
-// MEX forward on the 5th-generation tensor cores (tcgen05, accumulators in tensor memory).
+// MEX forward, input gradient and offsets gradient on the 5th-generation tensor cores (tcgen05, accumulators
+// in tensor memory).
 //
-// After the factorisation of mex_tiled.cu the forward pass is a plain GEMM  S[j, m] = sum_k Ex[j, k] * Eo[m, k]
-// with both operands in (0, 1].  FP32 accuracy is kept with the split-TF32 scheme: every operand is written to
+// After the factorisation of mex_tiled.cu all three passes are plain GEMMs over operands derived from x, y, dy
+// and the offsets:  forward  S[j, m] = sum_k Ex[j, k] * Eo[m, k];  input gradient  T[j, k] = sum_m Q[j, m] * Eo[m, k]
+// (dx = Ex * T);  offsets gradient  U[m, k] = sum_j Q[m, j] * Ex[k, j]  (dO = Eo * U), with Q = dy * G.
+// FP32 accuracy is kept with the split-TF32 scheme: every operand is written to
 // shared memory as hi = round-to-TF32(v) and lo = v - hi, and each k-step issues three MMAs
 // (hi*hi + hi*lo + lo*hi); the dropped lo*lo term and the truncation of lo are below 3 * 2^-21 of a product, and
 // all products are positive, so S keeps ~6 significant digits (tests compare y at 1e-5 of tensor scale).
@@ -80,27 +83,130 @@ __device__ __forceinline__ float tf32_hi(float v) {
     return __uint_as_float(r);
 }
 
-// byte offset of element (row, k) inside a [rows x 16] K-major core-matrix tile (lbo = 128, sbo = 512)
-__host__ __device__ constexpr int core_offset(int row, int k) { return (row >> 3) * 512 + (k >> 2) * 128 + (row & 7) * 16 + (k & 3) * 4; }
+// byte offset of element (row, k) inside a [rows x KT] K-major core-matrix tile with leading byte offset LBO
+// (distance between 16-byte chunks along k) and stride byte offset (KT / 4) * LBO (distance between 8-row groups)
+template <int KT, int LBO>
+__host__ __device__ constexpr int core_off(int row, int k) { return (row >> 3) * ((KT / 4) * LBO) + (k >> 2) * LBO + (row & 7) * 16 + (k & 3) * 4; }
+__host__ __device__ constexpr int core_offset(int row, int k) { return core_off<16, 128>(row, k); }
 
-// ---- prepass: Eo split into hi / lo, laid out tile by tile exactly as the MMA reads it -------------------------
-// tiles[r][mt][kc][plane][NT * 16 floats]; rows past M and taps past K are zero.
-__global__ void __launch_bounds__(256) mex_tc_prep(MexGeo g, int NT, const float* __restrict__ eo, float* __restrict__ tiles) {
-    const int kchunks = (g.K + kTcKT - 1) / kTcKT, mtiles = (g.M + NT - 1) / NT;
-    const int ldk = pad4(g.K);
-    const long long total = (long long)g.R * mtiles * kchunks * NT * kTcKT;
+// Shared state of one tensor-core tile computation.
+struct TcShared {
+    uint64_t bar_free[2];
+    uint64_t bar_done;
+    uint32_t tmem;
+    int failed;
+};
+
+// Set-up common to the three kernels: barriers, tensor-memory allocation of `cols` columns (power of two >= 32).
+__device__ __forceinline__ uint32_t tc_begin(TcShared& sh, uint32_t cols) {
+    if (threadIdx.x == 0) {
+        mbar_init(&sh.bar_free[0], 1); mbar_init(&sh.bar_free[1], 1); mbar_init(&sh.bar_done, 1);
+        sh.failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if ((threadIdx.x >> 5) == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem)), "r"(cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    return sh.tmem;
+}
+
+// Frees the tensor memory; every thread of the CTA must call it, after its last tensor-memory load.
+__device__ __forceinline__ void tc_end(uint32_t tmem, uint32_t cols) {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if ((threadIdx.x >> 5) == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(cols) : "memory");
+}
+
+// Main loop: D[128 x NT] = sum over nchunks chunks of KT reduction elements of A[128 x KT] * B[NT x KT]^T with split-TF32
+// operands, STAGES shared-memory stages.  Per chunk c every thread calls store(c, a_hi, a_lo, b_hi, b_lo), which writes
+// the stage from registers filled earlier (plain stores and / or cp.async), then load(c + 1), which only ISSUES the
+// global loads of the next chunk into registers: they are in flight across the fence, the barrier, the MMA issue
+// and the wait for the stage.  Returns true on every thread if all MMAs completed, false if a bounded wait expired.
+template <int NT, int KT, int LBO, int STAGES, class Load, class Store>
+__device__ __forceinline__ bool tc_mainloop(TcShared& sh, unsigned char* dsm, uint32_t tmem_d, int nchunks, Load load, Store store) {
+    constexpr int SBO = (KT / 4) * LBO;
+    constexpr int A_BYTES = (128 / 8) * SBO, B_BYTES = (NT / 8) * SBO;
+    constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+    constexpr uint32_t idesc = umma_idesc(NT);
+    bool ok = true;
+    if (nchunks > 0) load(0);
+    for (int c = 0; c < nchunks; ++c) {
+        const int stage = c % STAGES, use = c / STAGES;
+        unsigned char* sA = dsm + stage * STAGE_BYTES;
+        unsigned char* sB = sA + 2 * A_BYTES;
+        if (use >= 1 && ok) ok = mbar_wait(&sh.bar_free[stage], uint32_t(use - 1) & 1u);   // the MMAs that last read this stage are done
+        store(c, sA, sA + A_BYTES, sB, sB + B_BYTES);
+        if (c + 1 < nchunks) load(c + 1);
+        cp_async_wait_all();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA's async proxy
+        __syncthreads();
+        if (threadIdx.x == 0 && ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_hi = smem_u32(sA), a_lo = a_hi + A_BYTES, b_hi = smem_u32(sB), b_lo = b_hi + B_BYTES;
+#pragma unroll
+            for (int ks = 0; ks < KT / 8; ++ks) {                       // a k-step of 8 = two 16-byte chunks
+                const uint32_t o = ks * 2 * LBO;
+                const uint64_t dah = umma_desc(a_hi + o, LBO, SBO), dal = umma_desc(a_lo + o, LBO, SBO);
+                const uint64_t dbh = umma_desc(b_hi + o, LBO, SBO), dbl = umma_desc(b_lo + o, LBO, SBO);
+                umma_tf32(tmem_d, dal, dbh, idesc, (c | ks) != 0);
+                umma_tf32(tmem_d, dah, dbl, idesc, 1);
+                umma_tf32(tmem_d, dah, dbh, idesc, 1);
+            }
+            umma_commit(c + 1 < nchunks ? &sh.bar_free[stage] : &sh.bar_done);
+        }
+    }
+    if (ok && nchunks > 0) ok = mbar_wait(&sh.bar_done, 0);
+    if (!ok) sh.failed = 1;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    __syncthreads();
+    return sh.failed == 0;
+}
+
+template <int NT, int KT, int LBO, int STAGES>
+constexpr int tc_smem_bytes() { return STAGES * (2 * (128 / 8) * (KT / 4) * LBO + 2 * (NT / 8) * (KT / 4) * LBO); }
+
+// 32 consecutive tensor-memory columns of this thread's lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// split v into TF32 hi and the exact remainder
+// (the remainder is rounded to TF32 here, to nearest, rather than left to the tensor core's truncation)
+__device__ __forceinline__ void split_tf32(float v, float& hi, float& lo) { hi = tf32_hi(v); lo = tf32_hi(v - hi); }
+
+// ---- prepass: a [rows x red] matrix split into hi / lo, laid out tile by tile exactly as the MMA reads it -------
+// tiles[r][row tile of NT][chunk of 16 along red][plane][NT * 16 floats]; out-of-range entries are zero.
+// Forward: rows = instances, red = taps (source Eo[r][m][ld]); input gradient: rows = taps, red = instances (Eo^T).
+__global__ void __launch_bounds__(256) mex_tc_prep(int R, int rows, int red, int ld, int NT, const float* __restrict__ src, float* __restrict__ tiles) {
+    const int chunks = (red + kTcKT - 1) / kTcKT, rtiles = (rows + NT - 1) / NT;
+    const long long total = (long long)R * rtiles * chunks * NT * kTcKT;
     for (long long i = blockIdx.x * 256LL + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
         const int kk = int(i % kTcKT);
         long long q = i / kTcKT;
         const int row = int(q % NT); q /= NT;
-        const int kc = int(q % kchunks); q /= kchunks;
-        const int mt = int(q % mtiles), r = int(q / mtiles);
-        const int m = mt * NT + row, k = kc * kTcKT + kk;
-        const float v = (m < g.M && k < g.K) ? eo[((size_t)r * g.M + m) * ldk + k] : 0.f;
-        const float hi = tf32_hi(v);
-        float* tile = tiles + (((size_t)r * mtiles + mt) * kchunks + kc) * 2 * NT * kTcKT;
+        const int kc = int(q % chunks); q /= chunks;
+        const int rt = int(q % rtiles), r = int(q / rtiles);
+        const int gr = rt * NT + row, gk = kc * kTcKT + kk;
+        const float v = (gr < rows && gk < red) ? src[((size_t)r * rows + gr) * ld + gk] : 0.f;
+        float hi, lo;
+        split_tf32(v, hi, lo);
+        float* tile = tiles + (((size_t)r * rtiles + rt) * chunks + kc) * 2 * NT * kTcKT;
         tile[core_offset(row, kk) / 4] = hi;
-        tile[NT * kTcKT + core_offset(row, kk) / 4] = v - hi;
+        tile[NT * kTcKT + core_offset(row, kk) / 4] = lo;
     }
 }
 
@@ -109,15 +215,9 @@ template <int NT, bool SPATIAL1, bool INTERIOR>
 __global__ void __launch_bounds__(kTcThreads) mex_fwd_tc(MexGeo g, const float* __restrict__ x, const float* __restrict__ tiles,
                                                         const float* __restrict__ mo, const float* __restrict__ mx,
                                                         float* __restrict__ y, int* __restrict__ flag) {
-    constexpr int A_BYTES = kTcPos * kTcKT * 4;        // one plane of the position operand, one stage
-    constexpr int B_BYTES = NT * kTcKT * 4;            // one plane of the instance operand, one stage
-    constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
     extern __shared__ __align__(128) unsigned char dsm[];
-    __shared__ uint64_t bar_free[2];
-    __shared__ uint64_t bar_done;
-    __shared__ uint32_t tmem_holder;
+    __shared__ TcShared sh;
     __shared__ float mo_s[NT];
-    __shared__ int failed;
     if (flag[0]) return;                                // factorisation unsafe: the exact kernels run instead
 
     const long long P = (long long)g.B * g.rs;
@@ -127,21 +227,8 @@ __global__ void __launch_bounds__(kTcThreads) mex_fwd_tc(MexGeo g, const float* 
     const int mt = bid % mtiles;
     const long long jt = bid / mtiles;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    if (threadIdx.x == 0) {
-        mbar_init(&bar_free[0], 1); mbar_init(&bar_free[1], 1); mbar_init(&bar_done, 1);
-        failed = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_holder)), "r"(uint32_t(NT)) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
     for (int i = threadIdx.x; i < NT; i += kTcThreads) mo_s[i] = (mt * NT + i < g.M) ? mo[r * g.M + mt * NT + i] : 0.f;
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_d = tmem_holder;
+    const uint32_t tmem_d = tc_begin(sh, NT);
 
     // staging role: position row = tid % 128, taps (tid / 128) * 8 .. + 7 of every stage
     const int prow = threadIdx.x % kTcPos, khalf = threadIdx.x / kTcPos;
@@ -150,68 +237,37 @@ __global__ void __launch_bounds__(kTcThreads) mex_fwd_tc(MexGeo g, const float* 
     const float* xs = x + (size_t)sc.n * g.C * g.H * g.W;
     const float eps = float(g.eps), oob = float(g.oob);
     const float* btiles = tiles + ((size_t)r * mtiles + mt) * kchunks * 2 * NT * kTcKT;
-    constexpr uint32_t idesc = umma_idesc(NT);
-    bool ok = true;
 
-    for (int c = 0; c < kchunks; ++c) {
-        const int stage = c & 1;
-        unsigned char* sA = dsm + stage * STAGE_BYTES;           // [hi | lo] position operand
-        unsigned char* sB = sA + 2 * A_BYTES;                    // [hi | lo] instance operand
-        // the MMAs that last read this stage (chunk c - 2) must have completed
-        if (c >= 2 && ok) ok = mbar_wait(&bar_free[stage], uint32_t((c >> 1) - 1) & 1u);
+    float xv[8];                                             // raw taps of the chunk being prefetched
+    auto load = [&](int c) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int k = c * kTcKT + khalf * 8 + u;
+            xv[u] = 0.f;
+            if (live && k < g.K)
+                xv[u] = INTERIOR ? __ldg(xs + interior_index<SPATIAL1>(g, sc.c0, sc.h0, sc.w0, k))
+                                 : patch_value<SPATIAL1>(g, xs, sc.c0, sc.h0, sc.w0, k, oob);
+        }
+    };
+    auto store = [&](int c, unsigned char* a_hi, unsigned char* a_lo, unsigned char* b_hi, unsigned char*) {
         // instance operand: verbatim copy of the pre-split tile (hi plane then lo plane, contiguous)
-        {
-            const float* src = btiles + (size_t)c * 2 * NT * kTcKT;
-            for (int v = threadIdx.x; v < 2 * B_BYTES / 16; v += kTcThreads)
-                cp_async16(reinterpret_cast<float*>(sB) + v * 4, src + v * 4, 16);
-        }
+        const float* src = btiles + (size_t)c * 2 * NT * kTcKT;
+        for (int v = threadIdx.x; v < 2 * NT * kTcKT / 4; v += kTcThreads) cp_async16(reinterpret_cast<float*>(b_hi) + v * 4, src + v * 4, 16);
         // position operand: 8 taps of this thread's position
-        {
-            float e[8];
+        float e[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int k = c * kTcKT + khalf * 8 + u;
-                float v = 0.f;
-                if (live && k < g.K) {
-                    const float xv = INTERIOR ? __ldg(xs + interior_index<SPATIAL1>(g, sc.c0, sc.h0, sc.w0, k))
-                                              : patch_value<SPATIAL1>(g, xs, sc.c0, sc.h0, sc.w0, k, oob);
-                    v = fast_exp(eps * (xv - sc.mx));
-                }
-                e[u] = v;
-            }
+        for (int u = 0; u < 8; ++u) e[u] = (live && c * kTcKT + khalf * 8 + u < g.K) ? fast_exp(eps * (xv[u] - sc.mx)) : 0.f;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {                        // two 16-byte groups of 4 taps
-                float4 hi, lo;
-                hi.x = tf32_hi(e[4 * h]); hi.y = tf32_hi(e[4 * h + 1]); hi.z = tf32_hi(e[4 * h + 2]); hi.w = tf32_hi(e[4 * h + 3]);
-                lo.x = e[4 * h] - hi.x; lo.y = e[4 * h + 1] - hi.y; lo.z = e[4 * h + 2] - hi.z; lo.w = e[4 * h + 3] - hi.w;
-                const int off = core_offset(prow, khalf * 8 + 4 * h);
-                *reinterpret_cast<float4*>(sA + off) = hi;
-                *reinterpret_cast<float4*>(sA + A_BYTES + off) = lo;
-            }
+        for (int h = 0; h < 2; ++h) {                            // two 16-byte groups of 4 taps
+            float4 hi, lo;
+            split_tf32(e[4 * h], hi.x, lo.x); split_tf32(e[4 * h + 1], hi.y, lo.y);
+            split_tf32(e[4 * h + 2], hi.z, lo.z); split_tf32(e[4 * h + 3], hi.w, lo.w);
+            const int off = core_offset(prow, khalf * 8 + 4 * h);
+            *reinterpret_cast<float4*>(a_hi + off) = hi;
+            *reinterpret_cast<float4*>(a_lo + off) = lo;
         }
-        cp_async_wait_all();
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA's async proxy
-        __syncthreads();
-        if (threadIdx.x == 0 && ok) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_hi = smem_u32(sA), a_lo = a_hi + A_BYTES, b_hi = smem_u32(sB), b_lo = b_hi + B_BYTES;
-#pragma unroll
-            for (int ks = 0; ks < kTcKT / 8; ++ks) {                  // k-step of 8 = two 16-byte chunks = 256 bytes further
-                const uint32_t o = ks * 256;
-                const uint64_t dah = umma_desc(a_hi + o, 128, 512), dal = umma_desc(a_lo + o, 128, 512);
-                const uint64_t dbh = umma_desc(b_hi + o, 128, 512), dbl = umma_desc(b_lo + o, 128, 512);
-                umma_tf32(tmem_d, dal, dbh, idesc, (c | ks) != 0);
-                umma_tf32(tmem_d, dah, dbl, idesc, 1);
-                umma_tf32(tmem_d, dah, dbh, idesc, 1);
-            }
-            umma_commit(c + 1 < kchunks ? &bar_free[stage] : &bar_done);
-        }
-    }
-    if (ok) ok = mbar_wait(&bar_done, 0);
-    if (!ok) failed = 1;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    __syncthreads();
-    const bool good = failed == 0;
+    };
+    const bool good = tc_mainloop<NT, kTcKT, 128, 2>(sh, dsm, tmem_d, kchunks, load, store);
 
     // epilogue: lane = position, registers = instances.  Warps w and w + 4 share a lane quarter and split the columns.
     if (good) {
@@ -223,17 +279,7 @@ __global__ void __launch_bounds__(kTcThreads) mex_fwd_tc(MexGeo g, const float* 
 #pragma unroll 1
         for (int c0 = half * (NT / 2); c0 < (half + 1) * (NT / 2); c0 += 32) {
             uint32_t v[32];
-            const uint32_t taddr = tmem_d + (uint32_t(quarter * 32) << 16) + uint32_t(c0);
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                  "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                  "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                  "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                : "r"(taddr) : "memory");
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            tmem_ld32(tmem_d + (uint32_t(quarter * 32) << 16) + uint32_t(c0), v);
             if (col.base >= 0) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
@@ -245,49 +291,283 @@ __global__ void __launch_bounds__(kTcThreads) mex_fwd_tc(MexGeo g, const float* 
     } else if (threadIdx.x == 0) {
         atomicExch(&flag[1], 1);                                 // a wait expired: results of this launch are invalid
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 0)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(uint32_t(NT)) : "memory");
+    tc_end(tmem_d, NT);
 }
 
+// ---- input gradient ----------------------------------------------------------------------------------------------
+// T[j (position, lane), k (tap, column)] = sum_m Q[j, m] * Eo[m, k];  dx[tap k of position j] = Ex[j, k] * T[j, k].
+// A = Q computed from y, dy (reads coalesced along positions), B = pre-split Eo^T tiles.  Blocks must not overlap.
+template <int NT, bool SPATIAL1>
+__global__ void __launch_bounds__(kTcThreads) mex_dx_tc(MexGeo g, const float* __restrict__ x, const float* __restrict__ tiles,
+                                                       const float* __restrict__ mo, const float* __restrict__ mx,
+                                                       const float* __restrict__ y, const float* __restrict__ dy,
+                                                       float* __restrict__ dx, int* __restrict__ flag) {
+    extern __shared__ __align__(128) unsigned char dsm[];
+    __shared__ TcShared sh;
+    if (flag[0]) return;
+    const long long P = (long long)g.B * g.rs;
+    const int ktiles = (g.K + NT - 1) / NT, mchunks = (g.M + kTcKT - 1) / kTcKT;
+    int bid = blockIdx.x;
+    const int r = bid % g.R; bid /= g.R;
+    const int kt = bid % ktiles;
+    const long long jt = bid / ktiles;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tmem_d = tc_begin(sh, NT);
+
+    const int prow = threadIdx.x % kTcPos, mhalf = threadIdx.x / kTcPos;
+    const Column sc = column_of(g, r, jt * kTcPos + prow, P, mx);
+    const bool live = sc.base >= 0;
+    const float eps = float(g.eps), cst = float(g.cst);
+    const float* mor = mo + r * g.M;
+    const float* yb = y + (live ? sc.base : 0);
+    const float* gb = dy + (live ? sc.base : 0);
+    const float* btiles = tiles + ((size_t)r * ktiles + kt) * mchunks * 2 * NT * kTcKT;
+
+    float yv[8], gv[8], mv[8];
+    auto load = [&](int c) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int m = min(c * kTcKT + mhalf * 8 + u, g.M - 1);
+            yv[u] = __ldcs(yb + (long long)m * g.N);
+            gv[u] = __ldcs(gb + (long long)m * g.N);
+            mv[u] = __ldg(mor + m);
+        }
+    };
+    auto store = [&](int c, unsigned char* a_hi, unsigned char* a_lo, unsigned char* b_hi, unsigned char*) {
+        const float* src = btiles + (size_t)c * 2 * NT * kTcKT;
+        for (int v = threadIdx.x; v < 2 * NT * kTcKT / 4; v += kTcThreads) cp_async16(reinterpret_cast<float*>(b_hi) + v * 4, src + v * 4, 16);
+        float q[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const bool in = live && c * kTcKT + mhalf * 8 + u < g.M;
+            q[u] = in ? gv[u] * fast_exp(eps * (sc.mx + mv[u] - yv[u]) + cst) : 0.f;
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float4 hi, lo;
+            split_tf32(q[4 * h], hi.x, lo.x); split_tf32(q[4 * h + 1], hi.y, lo.y);
+            split_tf32(q[4 * h + 2], hi.z, lo.z); split_tf32(q[4 * h + 3], hi.w, lo.w);
+            const int off = core_offset(prow, mhalf * 8 + 4 * h);
+            *reinterpret_cast<float4*>(a_hi + off) = hi;
+            *reinterpret_cast<float4*>(a_lo + off) = lo;
+        }
+    };
+    const bool good = tc_mainloop<NT, kTcKT, 128, 2>(sh, dsm, tmem_d, mchunks, load, store);
+
+    if (good) {
+        const int quarter = warp & 3, half = warp >> 2;
+        const Column col = column_of(g, r, jt * kTcPos + quarter * 32 + lane, P, mx);
+        const size_t sample = (size_t)col.n * g.C * g.H * g.W;
+#pragma unroll 1
+        for (int c0 = half * (NT / 2); c0 < (half + 1) * (NT / 2); c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem_d + (uint32_t(quarter * 32) << 16) + uint32_t(c0), v);
+            if (col.base >= 0) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int k = kt * NT + c0 + i;
+                    if (k >= g.K) continue;
+                    const Tap tp = tap_of<SPATIAL1>(g, k);
+                    const int cc = col.c0 + tp.c, hh = col.h0 + tp.h, ww = col.w0 + tp.w;
+                    if (cc < 0 || cc >= g.C || hh < 0 || hh >= g.H || ww < 0 || ww >= g.W) continue;
+                    const size_t a = sample + ((size_t)cc * g.H + hh) * g.W + ww;
+                    dx[a] = fast_exp(eps * (__ldg(x + a) - col.mx)) * __uint_as_float(v[i]);
+                }
+            }
+        }
+    } else if (threadIdx.x == 0) {
+        atomicExch(&flag[1], 1);
+    }
+    tc_end(tmem_d, NT);
+}
+
+// ---- offsets gradient --------------------------------------------------------------------------------------------
+// U[m (instance, lane), k (tap, column)] = sum over this split's positions j of Q[m, j] * Ex[k, j]; both operands are
+// computed on the fly with lanes running along positions (coalesced reads of y, dy, x) and stored one float at a
+// time; a leading byte offset of 144 spreads the eight 16-byte chunks of a row over all banks.
+constexpr int kDoKT = 32, kDoLBO = 144;
+
+template <int NT, bool SPATIAL1>
+__global__ void __launch_bounds__(kTcThreads) mex_doff_tc(MexGeo g, const float* __restrict__ x, const float* __restrict__ mo,
+                                                         const float* __restrict__ mx, const float* __restrict__ y,
+                                                         const float* __restrict__ dy, float* __restrict__ part, int splits,
+                                                         int* __restrict__ flag) {
+    extern __shared__ __align__(128) unsigned char dsm[];
+    __shared__ TcShared sh;
+    __shared__ float mo_s[128];
+    if (flag[0]) return;
+    const long long P = (long long)g.B * g.rs;
+    const int mtiles = (g.M + 127) / 128, ktiles = (g.K + NT - 1) / NT;
+    int bid = blockIdx.x;
+    const int kt = bid % ktiles; bid /= ktiles;
+    const int mt = bid % mtiles; bid /= mtiles;
+    const int r = bid % g.R;
+    const int split = bid / g.R;
+    const long long chunks = (P + kDoKT - 1) / kDoKT;
+    const long long c_begin = chunks * split / splits, c_end = chunks * (split + 1) / splits;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x < 128) mo_s[threadIdx.x] = (mt * 128 + threadIdx.x < g.M) ? mo[r * g.M + mt * 128 + threadIdx.x] : 0.f;
+    const uint32_t tmem_d = tc_begin(sh, NT);
+    const float eps = float(g.eps), cst = float(g.cst), oob = float(g.oob);
+
+    // registers of the chunk being prefetched: lane = position of the chunk, this warp's 16 instances and NT / 8 taps
+    Column col;
+    float yv[16], gv[16], xv[NT / 8];
+    auto load = [&](int c) {
+        col = column_of(g, r, (c_begin + c) * kDoKT + lane, P, mx);
+        const bool live = col.base >= 0;
+        const float* yb = y + (live ? col.base : 0);
+        const float* gb = dy + (live ? col.base : 0);
+        const float* xs = x + (size_t)col.n * g.C * g.H * g.W;
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            const int m = min(mt * 128 + warp * 16 + u, g.M - 1);
+            yv[u] = __ldcs(yb + (long long)m * g.N);
+            gv[u] = __ldcs(gb + (long long)m * g.N);
+        }
+#pragma unroll
+        for (int u = 0; u < NT / 8; ++u) {
+            const int k = kt * NT + warp * (NT / 8) + u;
+            xv[u] = (live && k < g.K) ? patch_value<SPATIAL1>(g, xs, col.c0, col.h0, col.w0, k, oob) : 0.f;
+        }
+    };
+    auto store = [&](int, unsigned char* a_hi, unsigned char* a_lo, unsigned char* b_hi, unsigned char* b_lo) {
+        const bool live = col.base >= 0;
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {                           // A: Q[m, j]
+            const int row = warp * 16 + u;
+            const bool in = live && mt * 128 + row < g.M;
+            float hi, lo;
+            split_tf32(in ? gv[u] * fast_exp(eps * (col.mx + mo_s[row] - yv[u]) + cst) : 0.f, hi, lo);
+            const int off = core_off<kDoKT, kDoLBO>(row, lane);
+            *reinterpret_cast<float*>(a_hi + off) = hi;
+            *reinterpret_cast<float*>(a_lo + off) = lo;
+        }
+#pragma unroll
+        for (int u = 0; u < NT / 8; ++u) {                       // B: Ex[k, j]
+            const int row = warp * (NT / 8) + u;
+            const bool in = live && kt * NT + row < g.K;
+            float hi, lo;
+            split_tf32(in ? fast_exp(eps * (xv[u] - col.mx)) : 0.f, hi, lo);
+            const int off = core_off<kDoKT, kDoLBO>(row, lane);
+            *reinterpret_cast<float*>(b_hi + off) = hi;
+            *reinterpret_cast<float*>(b_lo + off) = lo;
+        }
+    };
+    const bool good = tc_mainloop<NT, kDoKT, kDoLBO, 1>(sh, dsm, tmem_d, int(c_end - c_begin), load, store);
+
+    if (good) {
+        const int quarter = warp & 3, half = warp >> 2;
+        const int m = mt * 128 + quarter * 32 + lane;
+        float* dst = part + (((size_t)split * g.R + r) * g.M + (m < g.M ? m : 0)) * g.K;
+#pragma unroll 1
+        for (int c0 = half * (NT / 2); c0 < (half + 1) * (NT / 2); c0 += 32) {
+            uint32_t v[32];
+            if (c_end > c_begin) tmem_ld32(tmem_d + (uint32_t(quarter * 32) << 16) + uint32_t(c0), v);
+            if (m < g.M) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int k = kt * NT + c0 + i;
+                    if (k < g.K) dst[k] = c_end > c_begin ? __uint_as_float(v[i]) : 0.f;
+                }
+            }
+        }
+    } else if (threadIdx.x == 0) {
+        atomicExch(&flag[1], 1);
+    }
+    tc_end(tmem_d, NT);
+}
+
+template <class Kernel>
+cudaError_t set_smem_once(Kernel kernel, int smem, bool& done) {
+    if (done) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) done = true;
+    return e;
+}
+
+#define TC_RUN(KERNEL, SMEM, GRID, ...)                                        \
+    do {                                                                       \
+        static bool attr_done = false;                                         \
+        const cudaError_t e_ = set_smem_once(KERNEL, SMEM, attr_done);          \
+        if (e_ != cudaSuccess) return e_;                                      \
+        KERNEL<<<GRID, kTcThreads, SMEM, s>>>(__VA_ARGS__);                     \
+    } while (0)
+
 template <int NT>
-cudaError_t launch_nt(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, float* y, int* flag,
-                      bool sp1, bool interior, cudaStream_t s) {
+cudaError_t launch_fwd_nt(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, float* y, int* flag,
+                          bool sp1, bool interior, cudaStream_t s) {
     const long long P = (long long)g.B * g.rs;
     const long long blocks = ((P + kTcPos - 1) / kTcPos) * ((g.M + NT - 1) / NT) * g.R;
     if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    constexpr int smem = 2 * (2 * kTcPos * kTcKT * 4 + 2 * NT * kTcKT * 4);
-#define TC_LAUNCH(SP, IN)                                                                                               \
-    do {                                                                                                                \
-        static bool attr_set = false;                                                                                   \
-        if (!attr_set) {                                                                                                \
-            cudaError_t e = cudaFuncSetAttribute(mex_fwd_tc<NT, SP, IN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
-            if (e != cudaSuccess) return e;                                                                             \
-            attr_set = true;                                                                                            \
-        }                                                                                                               \
-        mex_fwd_tc<NT, SP, IN><<<int(blocks), kTcThreads, smem, s>>>(g, x, tiles, mo, mx, y, flag);                      \
-    } while (0)
-    if (sp1) { if (interior) TC_LAUNCH(true, true); else TC_LAUNCH(true, false); }
-    else { if (interior) TC_LAUNCH(false, true); else TC_LAUNCH(false, false); }
-#undef TC_LAUNCH
+    constexpr int smem = tc_smem_bytes<NT, kTcKT, 128, 2>();
+    if (sp1) {
+        if (interior) TC_RUN((mex_fwd_tc<NT, true, true>), smem, int(blocks), g, x, tiles, mo, mx, y, flag);
+        else TC_RUN((mex_fwd_tc<NT, true, false>), smem, int(blocks), g, x, tiles, mo, mx, y, flag);
+    } else {
+        if (interior) TC_RUN((mex_fwd_tc<NT, false, true>), smem, int(blocks), g, x, tiles, mo, mx, y, flag);
+        else TC_RUN((mex_fwd_tc<NT, false, false>), smem, int(blocks), g, x, tiles, mo, mx, y, flag);
+    }
     count_launch();
     return cudaGetLastError();
 }
 
-}  // namespace
-
-int mex_tc_nt(const MexGeo& g) { return g.M > 128 ? 256 : (g.M > 64 ? 128 : 64); }
-
-size_t mex_tc_tile_floats(const MexGeo& g) {
-    const int NT = mex_tc_nt(g);
-    return (size_t)g.R * ((g.M + NT - 1) / NT) * ((g.K + kTcKT - 1) / kTcKT) * 2 * NT * kTcKT;
+template <int NT>
+cudaError_t launch_dx_nt(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, const float* y,
+                         const float* dy, float* dx, int* flag, cudaStream_t s) {
+    const long long P = (long long)g.B * g.rs;
+    const long long blocks = ((P + kTcPos - 1) / kTcPos) * ((g.K + NT - 1) / NT) * g.R;
+    if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    constexpr int smem = tc_smem_bytes<NT, kTcKT, 128, 2>();
+    if (g.bh == 1 && g.bw == 1) TC_RUN((mex_dx_tc<NT, true>), smem, int(blocks), g, x, tiles, mo, mx, y, dy, dx, flag);
+    else TC_RUN((mex_dx_tc<NT, false>), smem, int(blocks), g, x, tiles, mo, mx, y, dy, dx, flag);
+    count_launch();
+    return cudaGetLastError();
 }
 
-cudaError_t launch_mex_tc_prep(const MexGeo& g, const float* eo, float* tiles, cudaStream_t s) {
-    const int NT = mex_tc_nt(g);
-    const long long total = (long long)mex_tc_tile_floats(g) / 2;
-    mex_tc_prep<<<int(std::min<long long>((total + 255) / 256, 148LL * 8)), 256, 0, s>>>(g, NT, eo, tiles);
+template <int NT>
+cudaError_t launch_doff_nt(const MexGeo& g, const float* x, const float* mo, const float* mx, const float* y, const float* dy,
+                           float* part, int splits, int* flag, cudaStream_t s) {
+    const long long blocks = (long long)((g.M + 127) / 128) * ((g.K + NT - 1) / NT) * g.R * splits;
+    if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    constexpr int smem = tc_smem_bytes<NT, kDoKT, kDoLBO, 1>();
+    if (g.bh == 1 && g.bw == 1) TC_RUN((mex_doff_tc<NT, true>), smem, int(blocks), g, x, mo, mx, y, dy, part, splits, flag);
+    else TC_RUN((mex_doff_tc<NT, false>), smem, int(blocks), g, x, mo, mx, y, dy, part, splits, flag);
+    count_launch();
+    return cudaGetLastError();
+}
+
+inline int pick_nt(int n) { return n > 128 ? 256 : (n > 64 ? 128 : 64); }
+
+}  // namespace
+
+int mex_tc_nt(const MexGeo& g) { return pick_nt(g.M); }
+
+// floats of the pre-split tiles: forward (rows = instances) and input gradient (rows = taps) side by side
+size_t mex_tc_tile_floats(const MexGeo& g) {
+    const int ntf = pick_nt(g.M), ntd = pick_nt(g.K);
+    const size_t fwd = (size_t)g.R * ((g.M + ntf - 1) / ntf) * ((g.K + kTcKT - 1) / kTcKT) * 2 * ntf * kTcKT;
+    const size_t dxf = (size_t)g.R * ((g.K + ntd - 1) / ntd) * ((g.M + kTcKT - 1) / kTcKT) * 2 * ntd * kTcKT;
+    return fwd > dxf ? fwd : dxf;
+}
+
+// number of position splits of the tensor-core offsets gradient (each CTA: 128 instances x NT taps)
+int mex_tc_doff_splits(const MexGeo& g) {
+    const int nt = pick_nt(g.K);
+    const long long P = (long long)g.B * g.rs, chunks = (P + kDoKT - 1) / kDoKT;
+    const long long tiles = (long long)((g.M + 127) / 128) * ((g.K + nt - 1) / nt) * g.R;
+    const int per_sm = nt == 256 ? 2 : (nt == 128 ? 3 : 4);      // CTAs per SM that shared and tensor memory allow
+    long long s = (148LL * per_sm * 2) / tiles;                  // about two full waves
+    if (s > chunks) s = chunks;
+    if (s < 1) s = 1;
+    if (s > 512) s = 512;
+    return int(s);
+}
+
+cudaError_t launch_mex_tc_prep(const MexGeo& g, bool transposed, const float* src, float* tiles, cudaStream_t s) {
+    const int rows = transposed ? g.K : g.M, red = transposed ? g.M : g.K, NT = pick_nt(rows);
+    const long long total = (long long)g.R * ((rows + NT - 1) / NT) * ((red + kTcKT - 1) / kTcKT) * NT * kTcKT;
+    mex_tc_prep<<<int(std::min<long long>((total + 255) / 256, 148LL * 8)), 256, 0, s>>>(g.R, rows, red, pad4(red), NT, src, tiles);
     count_launch();
     return cudaGetLastError();
 }
@@ -295,10 +575,28 @@ cudaError_t launch_mex_tc_prep(const MexGeo& g, const float* eo, float* tiles, c
 cudaError_t launch_mex_fwd_tc(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, float* y,
                               int* flag, bool interior, cudaStream_t s) {
     const bool sp1 = g.bh == 1 && g.bw == 1;
-    switch (mex_tc_nt(g)) {
-    case 256: return launch_nt<256>(g, x, tiles, mo, mx, y, flag, sp1, interior, s);
-    case 128: return launch_nt<128>(g, x, tiles, mo, mx, y, flag, sp1, interior, s);
-    default: return launch_nt<64>(g, x, tiles, mo, mx, y, flag, sp1, interior, s);
+    switch (pick_nt(g.M)) {
+    case 256: return launch_fwd_nt<256>(g, x, tiles, mo, mx, y, flag, sp1, interior, s);
+    case 128: return launch_fwd_nt<128>(g, x, tiles, mo, mx, y, flag, sp1, interior, s);
+    default: return launch_fwd_nt<64>(g, x, tiles, mo, mx, y, flag, sp1, interior, s);
+    }
+}
+
+cudaError_t launch_mex_dx_tc(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, const float* y,
+                             const float* dy, float* dx, int* flag, cudaStream_t s) {
+    switch (pick_nt(g.K)) {
+    case 256: return launch_dx_nt<256>(g, x, tiles, mo, mx, y, dy, dx, flag, s);
+    case 128: return launch_dx_nt<128>(g, x, tiles, mo, mx, y, dy, dx, flag, s);
+    default: return launch_dx_nt<64>(g, x, tiles, mo, mx, y, dy, dx, flag, s);
+    }
+}
+
+cudaError_t launch_mex_doff_tc(const MexGeo& g, const float* x, const float* mo, const float* mx, const float* y, const float* dy,
+                               float* part, int splits, int* flag, cudaStream_t s) {
+    switch (pick_nt(g.K)) {
+    case 256: return launch_doff_nt<256>(g, x, mo, mx, y, dy, part, splits, flag, s);
+    case 128: return launch_doff_nt<128>(g, x, mo, mx, y, dy, part, splits, flag, s);
+    default: return launch_doff_nt<64>(g, x, mo, mx, y, dy, part, splits, flag, s);
     }
 }
 

@@ -407,7 +407,7 @@ cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* o
     cudaError_t e = run_prepasses(g, w, x, off, s);
     if (e != cudaSuccess) return e;
     if (tc_shape(g) && !(flags & SIMNETS_FLAG_MEX_NO_TENSORCORE)) {
-        e = launch_mex_tc_prep(g, w.eo, w.tc_tiles, s);
+        e = launch_mex_tc_prep(g, false, w.eo, w.tc_tiles, s);
         if (e != cudaSuccess) return e;
         e = launch_mex_fwd_tc(g, x, w.tc_tiles, w.mo, w.mx, y, w.flag, patches_inside_input(g), s);
         if (e != cudaSuccess) return e;
@@ -469,7 +469,7 @@ int launch_mex_fwd_static(const MexGeo& g, const float* x, const float* off, flo
 }
 
 cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* dx,
-                                void* ws, uint32_t, cudaStream_t s) {
+                                void* ws, uint32_t flags, cudaStream_t s) {
     if (!blocks_disjoint(g)) return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, nullptr);
     const MexWs w = carve(g, ws);
     const bool small = smallm_shape(g) || smallk_shape(g);
@@ -481,6 +481,13 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
     }
     if (smallk_shape(g)) {
         e = launch_mex_dx_smallk(g, x, w.eo, w.mo, y, dy, dx, w.flag, s);
+        if (e != cudaSuccess) return e;
+        return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
+    }
+    if (tc_shape(g) && !(flags & SIMNETS_FLAG_MEX_NO_TENSORCORE)) {
+        e = launch_mex_tc_prep(g, true, w.eot, w.tc_tiles, s);
+        if (e != cudaSuccess) return e;
+        e = launch_mex_dx_tc(g, x, w.tc_tiles, w.mo, w.mx, y, dy, dx, w.flag, s);
         if (e != cudaSuccess) return e;
         return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
     }
@@ -505,10 +512,21 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
 }
 
 cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* doff,
-                                  bool accumulate, void* ws, uint32_t, cudaStream_t s) {
+                                  bool accumulate, void* ws, uint32_t flags, cudaStream_t s) {
     const MexWs w = carve(g, ws);
     cudaError_t e = run_prepasses(g, w, x, off, s, !smallk_shape(g));
     if (e != cudaSuccess) return e;
+    if (tc_shape(g) && !(flags & SIMNETS_FLAG_MEX_NO_TENSORCORE)) {
+        const int tsplits = mex_tc_doff_splits(g);
+        e = launch_mex_doff_tc(g, x, w.mo, w.mx, y, dy, w.part, tsplits, w.flag, s);
+        if (e != cudaSuccess) return e;
+        const long long n = (long long)g.R * g.M * g.K;
+        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, g.K, tsplits, w.part, w.eo, doff, accumulate, w.flag);
+        count_launch();
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
+    }
     const int splits = doff_splits(g);
     if (smallk_shape(g)) {
         e = launch_mex_doff_smallk(g, x, w.mo, y, dy, w.part, splits, w.flag, s);
