@@ -33,10 +33,13 @@ struct SimWs {
 __host__ inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 __host__ __device__ inline int pad4(int v) { return (v + 3) & ~3; }
 
+// taps per parameter-gradient tile: 32 when the patch is that short (cfg5: K = 27), else 64
+__host__ inline int dp_tn(const SimGeo& g) { return g.K <= 32 ? 32 : 64; }
+
 __host__ int dp_splits(const SimGeo& g) {
     const long long P = (long long)g.B * g.N;
     const long long chunks = (P + kDpKC - 1) / kDpKC;
-    const long long tiles = (long long)((g.M + kDpTile - 1) / kDpTile) * ((g.K + kDpTile - 1) / kDpTile);
+    const long long tiles = (long long)((g.M + kDpTile - 1) / kDpTile) * ((g.K + dp_tn(g) - 1) / dp_tn(g));
     long long s = (148 * 2 + tiles - 1) / tiles;
     if (s > chunks) s = chunks;
     if (s < 1) s = 1;
@@ -222,24 +225,25 @@ __global__ void __launch_bounds__(256) sim_fwd_tiled(SimGeo g, const float* __re
 // -------------------------------------------------------- parameter gradients
 // Accumulators per output (m, k): sT = sum a*d, sW = sum a*d*d (L1: a*sign(d), a*|d|), sN = sum a*mask,
 // with a = dy and d = mask*(x - t).  Both operands are contiguous along q (positions) in memory.
-template <int MODE>
-__global__ void __launch_bounds__(256) sim_dparams_tiled(SimGeo g, const float* __restrict__ x, const float* __restrict__ tm,
+template <int MODE, int TN>
+__global__ void __launch_bounds__(TN * 4) sim_dparams_tiled(SimGeo g, const float* __restrict__ x, const float* __restrict__ tm,
                                                          const float* __restrict__ dy, const int2* __restrict__ taps,
                                                          float* __restrict__ part, int splits) {
     constexpr bool MASKED = MODE == SIM_L2N_NAN || MODE == SIM_L1_SKIP;
     constexpr bool NORM = MODE == SIM_L2N || MODE == SIM_L2N_NAN;
     constexpr bool L1 = MODE == SIM_L1 || MODE == SIM_L1_SKIP;
     constexpr int NB = MASKED ? 2 : 1;
-    using Cfg = TileCfg<kDpTile, kDpTile, kDpKC, 4, 4, 1, NB>;
-    static_assert(Cfg::THREADS == 256, "256 threads");
+    using Cfg = TileCfg<kDpTile, TN, kDpKC, 4, 4, 1, NB>;
+    static_assert(Cfg::THREADS == TN * 4, "64 x TN outputs, 4 x 4 per thread");
+    constexpr int ROWS = Cfg::THREADS / 32;          // tile rows one staging pass covers
     __shared__ __align__(16) float smem[Cfg::SMEM_FLOATS];
     const long long P = (long long)g.B * g.N;
-    const int ktiles = (g.K + kDpTile - 1) / kDpTile, mtiles = (g.M + kDpTile - 1) / kDpTile;
+    const int ktiles = (g.K + TN - 1) / TN, mtiles = (g.M + kDpTile - 1) / kDpTile;
     int bid = blockIdx.x;
     const int kt = bid % ktiles; bid /= ktiles;
     const int mt = bid % mtiles;
     const int split = bid / mtiles;
-    const int i0 = mt * kDpTile, jk0 = kt * kDpTile;
+    const int i0 = mt * kDpTile, jk0 = kt * TN;
     const long long chunks = (P + kDpKC - 1) / kDpKC;
     const long long c_begin = chunks * split / splits, c_end = chunks * (split + 1) / splits;
 
@@ -251,7 +255,7 @@ __global__ void __launch_bounds__(256) sim_dparams_tiled(SimGeo g, const float* 
     int2 mytaps[Cfg::B_PER];
 #pragma unroll
     for (int s = 0; s < Cfg::B_PER; ++s) {
-        const int k = jk0 + e0 + 8 * s;
+        const int k = jk0 + e0 + ROWS * s;
         mytaps[s] = k < g.K ? taps[k] : make_int2(0, 0);
     }
     float2 tt[4][2];
@@ -273,7 +277,7 @@ __global__ void __launch_bounds__(256) sim_dparams_tiled(SimGeo g, const float* 
         cur = sim_column(g, (c_begin + chunk) * kDpKC + qq, P);
 #pragma unroll
         for (int s = 0; s < Cfg::A_PER; ++s) {
-            const int m = i0 + e0 + 8 * s;
+            const int m = i0 + e0 + ROWS * s;
             ra[s] = (cur.base >= 0 && m < g.M) ? __ldcs(dy + cur.base + (long long)m * g.N) : 0.f;
         }
     };
@@ -283,7 +287,7 @@ __global__ void __launch_bounds__(256) sim_dparams_tiled(SimGeo g, const float* 
         const float* xc = xs + cur.h0 * g.W + cur.w0;
 #pragma unroll
         for (int s = 0; s < Cfg::B_PER; ++s) {
-            const int k = jk0 + e0 + 8 * s;
+            const int k = jk0 + e0 + ROWS * s;
             // dead positions carry dy = 0 and a finite value, so every term they touch is exactly 0
             if (cur.base < 0 || k >= g.K) rb[s] = 0.f;
             else if (inside) rb[s] = __ldg(xc + mytaps[s].x);
@@ -292,12 +296,12 @@ __global__ void __launch_bounds__(256) sim_dparams_tiled(SimGeo g, const float* 
     };
     auto commitA = [&](float* As) {
 #pragma unroll
-        for (int s = 0; s < Cfg::A_PER; ++s) As[stage_offset<kDpTile, true>(qq, e0 + 8 * s)] = ra[s];
+        for (int s = 0; s < Cfg::A_PER; ++s) As[stage_offset<kDpTile, true>(qq, e0 + ROWS * s)] = ra[s];
     };
     auto commitB = [&](float* Bs) {
 #pragma unroll
         for (int s = 0; s < Cfg::B_PER; ++s) {
-            const int o = stage_offset<kDpTile, true>(qq, e0 + 8 * s);
+            const int o = stage_offset<TN, true>(qq, e0 + ROWS * s);
             if (MASKED) {
                 const bool nan = rb[s] != rb[s];
                 Bs[o] = nan ? 0.f : rb[s];
@@ -567,8 +571,13 @@ cudaError_t launch_sim_dparams_tiled(const SimGeo& g, const float* x, const floa
     const SimWs W = carve(g, ws);
     launch_prep(g, W, t, w, s);
     const int splits = dp_splits(g);
-    const int blocks = ((g.M + kDpTile - 1) / kDpTile) * ((g.K + kDpTile - 1) / kDpTile) * splits;
-#define DP(MODE) sim_dparams_tiled<MODE><<<blocks, 256, 0, s>>>(g, x, t, dy, W.taps, W.part, splits)
+    const int tn = dp_tn(g);
+    const int blocks = ((g.M + kDpTile - 1) / kDpTile) * ((g.K + tn - 1) / tn) * splits;
+#define DP(MODE)                                                                                              \
+    do {                                                                                                      \
+        if (tn == 32) sim_dparams_tiled<MODE, 32><<<blocks, 128, 0, s>>>(g, x, t, dy, W.taps, W.part, splits); \
+        else sim_dparams_tiled<MODE, 64><<<blocks, 256, 0, s>>>(g, x, t, dy, W.taps, W.part, splits);          \
+    } while (0)
     switch (g.mode) {
     case SIM_L1: DP(SIM_L1); break;
     case SIM_L1_SKIP: DP(SIM_L1_SKIP); break;
