@@ -218,6 +218,13 @@ SIMNETS_API int simnets_mex_offsets_grad(const simnets_mex_desc* d,
                                          const void* x, const void* offsets, const void* y, const void* dy,
                                          void* doffsets, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Both MEX gradients in one call (same results as the two calls above; the work they share -- offset
+ * exponentials, per-position maxima -- is done once).  Stands in for running MexInputGrad and MexOffsetsGrad
+ * back to back, which is what the reference's gradient function always does (python/simnets/ops/mex.py:47-81). */
+SIMNETS_API int simnets_mex_backward(const simnets_mex_desc* d,
+                                     const void* x, const void* offsets, const void* y, const void* dy,
+                                     void* dx, void* doffsets, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- misc ----------------------------------------------------------------- */
 SIMNETS_API const char* simnets_status_string(int status);
 /* Number of kernels this library has launched in this process (all devices). */

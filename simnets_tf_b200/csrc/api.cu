@@ -197,4 +197,22 @@ int simnets_mex_offsets_grad(const simnets_mex_desc* d, const void* x, const voi
     return from_cuda(launch_mex_doff_direct(g, f64, x, off, y, dy, doff, acc, as_stream(stream)));
 }
 
+int simnets_mex_backward(const simnets_mex_desc* d, const void* x, const void* off, const void* y, const void* dy,
+                         void* dx, void* doff, void* ws, size_t ws_bytes, void* stream) {
+    MexGeo g;
+    const int rc = mex_geometry(d, nullptr, &g);
+    if (rc) return rc;
+    if (!off || !doff || (g.B > 0 && (!x || !y || !dy || !dx))) return SIMNETS_E_NULL;
+    const bool f64 = d->dtype == SIMNETS_F64;
+    const bool acc = (d->flags & SIMNETS_FLAG_ACCUMULATE) != 0;
+    if (mex_use_tiled(g, f64, d->flags)) {
+        if (!ws || ws_bytes < mex_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;
+        return from_cuda(launch_mex_backward_tiled(g, (const float*)x, (const float*)off, (const float*)y, (const float*)dy,
+                                                   (float*)dx, (float*)doff, acc, ws, d->flags, as_stream(stream)));
+    }
+    const int r1 = from_cuda(launch_mex_dx_direct(g, f64, x, off, y, dy, dx, as_stream(stream)));
+    if (r1) return r1;
+    return from_cuda(launch_mex_doff_direct(g, f64, x, off, y, dy, doff, acc, as_stream(stream)));
+}
+
 }  // extern "C"

@@ -60,7 +60,9 @@ cudaError_t launch_mex_doff_tc(const MexGeo&, const float* x, const float* mo, c
 // forward on the library's fixed device scratch; returns a status code of simnets_b200.h
 int launch_mex_fwd_static(const MexGeo&, const float* x, const float* off, float* y, cudaStream_t);
 cudaError_t launch_mex_dx_tiled(const MexGeo&, const float* x, const float* off, const float* y, const float* dy, float* dx,
-                                void* ws, uint32_t flags, cudaStream_t);
+                                void* ws, uint32_t flags, cudaStream_t, bool prepped = false);
+cudaError_t launch_mex_backward_tiled(const MexGeo&, const float* x, const float* off, const float* y, const float* dy, float* dx,
+                                      float* doff, bool accumulate, void* ws, uint32_t flags, cudaStream_t);
 cudaError_t launch_mex_doff_tiled(const MexGeo&, const float* x, const float* off, const float* y, const float* dy, float* doff,
-                                  bool accumulate, void* ws, uint32_t flags, cudaStream_t);
+                                  bool accumulate, void* ws, uint32_t flags, cudaStream_t, bool prepped = false);
 }  // namespace simnets

@@ -469,11 +469,11 @@ int launch_mex_fwd_static(const MexGeo& g, const float* x, const float* off, flo
 }
 
 cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* dx,
-                                void* ws, uint32_t flags, cudaStream_t s) {
+                                void* ws, uint32_t flags, cudaStream_t s, bool prepped) {
     if (!blocks_disjoint(g)) return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, nullptr);
     const MexWs w = carve(g, ws);
     const bool small = smallm_shape(g) || smallk_shape(g);
-    cudaError_t e = run_prepasses(g, w, x, off, s, !small);
+    cudaError_t e = prepped ? cudaSuccess : run_prepasses(g, w, x, off, s, !small);
     if (e != cudaSuccess) return e;
     if (!blocks_cover_input(g)) {
         e = cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)g.B * g.C * g.H * g.W, s);
@@ -512,9 +512,9 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
 }
 
 cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* doff,
-                                  bool accumulate, void* ws, uint32_t flags, cudaStream_t s) {
+                                  bool accumulate, void* ws, uint32_t flags, cudaStream_t s, bool prepped) {
     const MexWs w = carve(g, ws);
-    cudaError_t e = run_prepasses(g, w, x, off, s, !smallk_shape(g));
+    cudaError_t e = prepped ? cudaSuccess : run_prepasses(g, w, x, off, s, !smallk_shape(g));
     if (e != cudaSuccess) return e;
     if (tc_shape(g) && !(flags & SIMNETS_FLAG_MEX_NO_TENSORCORE)) {
         const int tsplits = mex_tc_doff_splits(g);
@@ -561,6 +561,17 @@ cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* 
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
+}
+
+// Both gradients of one layer in one call: the offsets prepass and the per-position maxima are computed once.
+cudaError_t launch_mex_backward_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* dx,
+                                      float* doff, bool accumulate, void* ws, uint32_t flags, cudaStream_t s) {
+    const MexWs w = carve(g, ws);
+    cudaError_t e = run_prepasses(g, w, x, off, s, !smallk_shape(g));
+    if (e != cudaSuccess) return e;
+    e = launch_mex_dx_tiled(g, x, off, y, dy, dx, ws, flags, s, true);
+    if (e != cudaSuccess) return e;
+    return launch_mex_doff_tiled(g, x, off, y, dy, doff, accumulate, ws, flags, s, true);
 }
 
 }  // namespace simnets

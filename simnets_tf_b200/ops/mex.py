@@ -85,7 +85,7 @@ def _cost(d, g, kind):
     """(signature, algorithmic bytes, terms) of one call: bytes = every input read once + every output written once."""
     x, o, y = d.batch * d.channels * d.height * d.width, g.num_regions * g.M * g.K, d.batch * g.M * g.N
     e = 4 if d.dtype == abi.F32 else 8
-    nbytes = {"fwd": x + o + y, "dx": 2 * x + o + 2 * y, "doff": x + 2 * o + 2 * y}[kind] * e
+    nbytes = {"fwd": x + o + y, "dx": 2 * x + o + 2 * y, "doff": x + 2 * o + 2 * y, "bwd": 2 * x + 2 * o + 2 * y}[kind] * e
     sig = "B%d C%d %dx%d M%d K%d N%d R%d" % (d.batch, d.channels, d.height, d.width, g.M, g.K, g.N, g.num_regions)
     return sig, nbytes, y * g.K
 
@@ -150,6 +150,24 @@ def mex_offsets_grad(input, offsets, orig_output, output_grad, num_instances, fl
     return doff
 
 
+def mex_backward(input, offsets, orig_output, output_grad, num_instances, flags=0, **attrs):
+    """`MexInputGrad` and `MexOffsetsGrad` in one library call: (input_grad, offsets_grad)."""
+    attrs = _attrs(**attrs)
+    dev = require_cuda(input, offsets, orig_output, output_grad)
+    input, offsets, y, dy = input.contiguous(), offsets.contiguous(), orig_output.contiguous(), output_grad.contiguous()
+    d = _desc(input, num_instances, attrs, flags)
+    g = _geometry(d)
+    _check_offsets(offsets, g, num_instances)
+    dx, doff = torch.empty_like(input), torch.empty_like(offsets)
+    with torch.cuda.device(dev):
+        ws, n = _ws(d, dev)
+        sig, nbytes, terms = _cost(d, g, "bwd")     # fused: x, offsets, y, dy read once, dx and doffsets written
+        with timed("mex_backward", sig, nbytes, 2 * terms):
+            _lib.check(_lib.lib().simnets_mex_backward(C.byref(d), input.data_ptr(), offsets.data_ptr(), y.data_ptr(), dy.data_ptr(),
+                                                       dx.data_ptr(), doff.data_ptr(), ws, n, stream_ptr(dev)))
+    return dx, doff
+
+
 class _Mex(torch.autograd.Function):
     @staticmethod
     def forward(ctx, input, offsets, num_instances, attrs):
@@ -162,9 +180,11 @@ class _Mex(torch.autograd.Function):
     def backward(ctx, grad):
         input, offsets, y = ctx.saved_tensors
         gi = go = None
-        if ctx.needs_input_grad[0]:
+        if ctx.needs_input_grad[0] and ctx.needs_input_grad[1]:
+            gi, go = mex_backward(input, offsets, y, grad, ctx.num_instances, **ctx.attrs)
+        elif ctx.needs_input_grad[0]:
             gi = mex_input_grad(input, offsets, y, grad, ctx.num_instances, **ctx.attrs)
-        if ctx.needs_input_grad[1]:
+        elif ctx.needs_input_grad[1]:
             go = mex_offsets_grad(input, offsets, y, grad, ctx.num_instances, **ctx.attrs)
         return gi, go, None, None
 

@@ -68,6 +68,20 @@ def test_autograd_wiring_matches_grad_ops(port):
     cases.assert_parity(od.grad.cpu().numpy(), port.mex_offsets_grad(d, x, off, ry, dy), tol=2e-5, what="doff")
 
 
+@pytest.mark.parametrize("name", ["blocks_bug", "eps_half", "tiled_regions", "head_disjoint", "wide_M_K", "eps_pinf"])
+def test_fused_backward_equals_the_two_gradient_ops(port, name):
+    """simnets_mex_backward shares the prepasses between the two gradients; results must not change."""
+    c = next(c for c in cases.MEX_SMALL if c["name"] == name)
+    d = cases.mex_desc(c)
+    x, off, dy = cases.mex_inputs(c, port.mex_offsets_shape(d), port.mex_out_shape(d))
+    xd, od, dyd = (gpu_util.dev(a) for a in (x, off, dy))
+    yd = gpu_util.dev(port.mex_forward(d, x, off))
+    attrs = cases.mex_attrs(c)
+    dx, doff = mex_ops.mex_backward(xd, od, yd, dyd, c["M"], **attrs)
+    assert torch.equal(dx, mex_ops.mex_input_grad(xd, od, yd, dyd, c["M"], **attrs))
+    assert torch.equal(doff, mex_ops.mex_offsets_grad(xd, od, yd, dyd, c["M"], **attrs))
+
+
 def test_wide_dynamic_range_takes_the_exact_route(port):
     """Offsets and inputs spanning hundreds of units (and -inf entries) would underflow a factorised
     evaluation; results must still match the oracle, whichever route the library picks."""
