@@ -65,6 +65,13 @@ enum { SIMNETS_SIM_L1 = 0, SIMNETS_SIM_L2 = 1 };
 /* MEX only: keep the factorised GEMM on the CUDA cores (no tcgen05 tensor-core kernels). */
 #define SIMNETS_FLAG_MEX_NO_TENSORCORE (1u << 5)
 
+/* MEX gradient entry points only: dy is given at half resolution, dy[batch, M * channels_out, height_out / 2,
+ * width_out / 2], each value standing for the 2x2 window of output positions that a 2x2 / stride-2 sum pooling
+ * added up (the gradient of such a pooling copies its dy to the four inputs; with this flag the copy is never
+ * materialised).  height_out and width_out must be even, else SIMNETS_E_UNSUPPORTED.  No counterpart in the
+ * reference, whose graphs run the pooling gradient as a separate TensorFlow op. */
+#define SIMNETS_FLAG_MEX_DY_POOLED2    (1u << 6)
+
 /* ---- Similarity ---------------------------------------------------------- */
 /* Mirrors the attrs of the Similarity op family (src/ops/similarity_op.cpp:61-75)
  * and the dimensions SimilarityKernelCommon::CalculateDimensions derives

@@ -212,7 +212,6 @@ __global__ void __launch_bounds__(kThreads) mex_dx_direct(MexGeo g, const T* __r
         const int c0 = int(q % g.C), n = int(q / g.C);
         const T v = x[idx];
         const T* y_n = y + (size_t)n * g.M * g.N;
-        const T* g_n = dy + (size_t)n * g.M * g.N;
         T total_sum = T(0);
         for (int kc = 0; kc < g.bc; ++kc) {
             const int cp = c0 + g.pc - kc;
@@ -227,9 +226,10 @@ __global__ void __launch_bounds__(kThreads) mex_dx_direct(MexGeo g, const T* __r
                     const int k = (kc * g.bh + kh) * g.bw + kw;
                     const int j = (c * g.Ho + h) * g.Wo + w;
                     const T* o = off + (size_t)mex_region_of(g, c, h, w) * g.M * g.K + k;
+                    const T* g_j = dy + mex_dy_base(g, n, j);
                     T sum = T(0);
                     for (int m = 0; m < g.M; ++m)
-                        sum += mex_weight(g, eps, cst, v, o[(size_t)m * g.K], y_n[(size_t)m * g.N + j], g_n[(size_t)m * g.N + j]);
+                        sum += mex_weight(g, eps, cst, v, o[(size_t)m * g.K], y_n[(size_t)m * g.N + j], g_j[(size_t)m * g.Ng]);
                     total_sum += sum;
                 }
             }
@@ -261,7 +261,7 @@ __global__ void __launch_bounds__(kThreads) mex_doff_direct(MexGeo g, const T* _
             const int w = j % g.Wo, h = (j / g.Wo) % g.Ho, c = j / (g.Wo * g.Ho);
             const T v = mex_tap(g, x + (size_t)n * g.C * g.H * g.W, c, h, w, k, oob);
             const size_t oi = ((size_t)n * g.M + m) * g.N + j;
-            sum += mex_weight(g, eps, cst, v, o, y[oi], dy[oi]);
+            sum += mex_weight(g, eps, cst, v, o, y[oi], dy[mex_dy_base(g, n, j) + (long long)m * g.Ng]);
         }
         const T rsum = block_sum(sum, smem);
         if (threadIdx.x == 0) doff[rmk] = accumulate ? doff[rmk] + rsum : rsum;

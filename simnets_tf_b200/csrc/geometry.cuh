@@ -28,6 +28,7 @@ struct MexGeo {
     int oc, oh, ow;        // number of regions along each axis
     int R, rs;             // num_regions, region_size
     int K, N;              // K = bc*bh*bw, N = Co*Ho*Wo
+    int gp, Ng;            // dy is given pooled gp x gp over (h, w) (1 = full resolution); Ng = positions per instance in dy
     int unshared;
     int finite;            // epsilon is finite
     int softmax;
@@ -39,6 +40,15 @@ __host__ __device__ __forceinline__ int mex_region_of(const MexGeo& g, int c, in
     const int rh = g.unshared ? h % g.oh : h / g.rh;
     const int rw = g.unshared ? w % g.ow : w / g.rw;
     return (rc * g.oh + rh) * g.ow + rw;
+}
+
+// Offset of dy[n, instance 0, output position pos]; consecutive instances are g.Ng apart.  With gp > 1 the
+// caller's dy holds one value per gp x gp window of output positions (the gradient of a sum pooling that
+// consumed the output), and every position of a window reads that value.
+__host__ __device__ __forceinline__ long long mex_dy_base(const MexGeo& g, int n, int pos) {
+    if (g.gp == 1) return (long long)n * g.M * g.N + pos;
+    const int w = pos % g.Wo, h = (pos / g.Wo) % g.Ho, c = pos / (g.Wo * g.Ho);
+    return (long long)n * g.M * g.Ng + (c * (g.Ho / g.gp) + h / g.gp) * (g.Wo / g.gp) + w / g.gp;
 }
 
 // Position l (0 <= l < region_size) of region r -> flat output position (c*Ho + h)*Wo + w, or -1

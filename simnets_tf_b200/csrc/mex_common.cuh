@@ -27,11 +27,12 @@ __host__ __device__ inline int pad4(int v) { return (v + 3) & ~3; }
 // offsets-gradient tiling: 128 x 128 outputs (chunks of 16 positions) when both M and K fill it, else 64 x 64 (chunks of 32)
 __host__ inline bool doff_big(const MexGeo& g) { return g.M >= 96 && g.K >= 96; }
 
+// (The two specialised families below read dy at full resolution only; a pooled dy takes the general tiles.)
 // Few instances over long patches (a classifier head: M = 10, K = 8192): one CTA per position instead of GEMM tiles.
-__host__ inline bool smallm_shape(const MexGeo& g) { return g.M <= 16 && g.K >= 256; }
+__host__ inline bool smallm_shape(const MexGeo& g) { return g.gp == 1 && g.M <= 16 && g.K >= 256; }
 
 // Short patches (K <= 32): the streaming kernels of mex_smallk.cu.
-__host__ inline bool smallk_shape(const MexGeo& g) { return g.K <= 32; }
+__host__ inline bool smallk_shape(const MexGeo& g) { return g.gp == 1 && g.K <= 32; }
 
 // GEMM-sized layers (many instances, mid to long patches): the tensor-core forward of mex_tc.cu.
 __host__ inline bool tc_shape(const MexGeo& g) { return !smallk_shape(g) && !smallm_shape(g) && g.M >= 48 && g.K >= 48; }
@@ -111,6 +112,7 @@ __device__ __forceinline__ int interior_index(const MexGeo& g, int c0, int h0, i
 // Per-column (= one output position of one sample) bookkeeping shared by the tile kernels.
 struct Column {
     long long base;      // n*M*N + pos : offset of y[n, 0, pos]; -1 for a position outside the output grid
+    long long gbase;     // offset of dy[n, 0, pos] (instances g.Ng apart): equals base unless dy is given pooled
     int n, c0, h0, w0;   // sample and patch corner in the input
     float mx;
 };
@@ -118,7 +120,7 @@ struct Column {
 // j-th position (over the whole batch) of region r -> Column
 __device__ __forceinline__ Column column_of(const MexGeo& g, int r, long long jl, long long P, const float* __restrict__ mx) {
     Column c;
-    c.base = -1; c.n = 0; c.c0 = c.h0 = c.w0 = 0; c.mx = 0.f;
+    c.base = -1; c.gbase = 0; c.n = 0; c.c0 = c.h0 = c.w0 = 0; c.mx = 0.f;
     if (jl >= P) return c;
     int n, l;
     if (P <= 0x7fffffffLL) { const unsigned j32 = unsigned(jl); n = int(j32 / unsigned(g.rs)); l = int(j32 - unsigned(n) * unsigned(g.rs)); }
@@ -128,6 +130,7 @@ __device__ __forceinline__ Column column_of(const MexGeo& g, int r, long long jl
     const int w = pos % g.Wo, h = (pos / g.Wo) % g.Ho, cc = pos / (g.Wo * g.Ho);
     c.n = n; c.c0 = cc * g.sc - g.pc; c.h0 = h * g.sh - g.ph; c.w0 = w * g.sw - g.pw;
     c.base = (long long)n * g.M * g.N + pos;
+    c.gbase = g.gp == 1 ? c.base : (long long)n * g.M * g.Ng + (cc * (g.Ho / g.gp) + h / g.gp) * (g.Wo / g.gp) + w / g.gp;
     c.mx = mx ? mx[(long long)n * g.N + pos] : 0.f;
     return c;
 }

@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(kTcThreads) mex_dx_tc(MexGeo g, const float* _
     const float eps = float(g.eps), cst = float(g.cst);
     const float* mor = mo + r * g.M;
     const float* yb = y + (live ? sc.base : 0);
-    const float* gb = dy + (live ? sc.base : 0);
+    const float* gb = dy + (live ? sc.gbase : 0);
     const float* btiles = tiles + ((size_t)r * ktiles + kt) * mchunks * 2 * NT * kTcKT;
 
     float yv[8], gv[8], mv[8];
@@ -329,7 +329,7 @@ __global__ void __launch_bounds__(kTcThreads) mex_dx_tc(MexGeo g, const float* _
         for (int u = 0; u < 8; ++u) {
             const int m = min(c * kTcKT + mhalf * 8 + u, g.M - 1);
             yv[u] = __ldcs(yb + (long long)m * g.N);
-            gv[u] = __ldcs(gb + (long long)m * g.N);
+            gv[u] = __ldcs(gb + (long long)m * g.Ng);
             mv[u] = __ldg(mor + m);
         }
     };
@@ -417,13 +417,13 @@ __global__ void __launch_bounds__(kTcThreads) mex_doff_tc(MexGeo g, const float*
         col = column_of(g, r, (c_begin + c) * kDoKT + lane, P, mx);
         const bool live = col.base >= 0;
         const float* yb = y + (live ? col.base : 0);
-        const float* gb = dy + (live ? col.base : 0);
+        const float* gb = dy + (live ? col.gbase : 0);
         const float* xs = x + (size_t)col.n * g.C * g.H * g.W;
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
             const int m = min(mt * 128 + warp * 16 + u, g.M - 1);
             yv[u] = __ldcs(yb + (long long)m * g.N);
-            gv[u] = __ldcs(gb + (long long)m * g.N);
+            gv[u] = __ldcs(gb + (long long)m * g.Ng);
         }
 #pragma unroll
         for (int u = 0; u < NT / 8; ++u) {

@@ -217,7 +217,7 @@ __global__ void __launch_bounds__(256) mex_dx_tiled(MexGeo g, const float* __res
             const int m = chunk * Cfg::KC + s_k + s * 2;
             const bool ok = m < g.M && live;
             rby[s] = ok ? __ldcs(y + sc.base + (long long)m * g.N) : 0.f;
-            rbg[s] = ok ? __ldcs(dy + sc.base + (long long)m * g.N) : 0.f;
+            rbg[s] = ok ? __ldcs(dy + sc.gbase + (long long)m * g.Ng) : 0.f;
             rbm[s] = ok ? __ldg(mor + m) : 0.f;
         }
     };
@@ -296,7 +296,7 @@ __global__ void __launch_bounds__(256) mex_doff_tiled(MexGeo g, const float* __r
             const int m = i0 + e0 + ROWS * s;
             const bool ok = cur.base >= 0 && m < g.M;
             ray[s] = ok ? __ldcs(y + cur.base + (long long)m * g.N) : 0.f;
-            rag[s] = ok ? __ldcs(dy + cur.base + (long long)m * g.N) : 0.f;
+            rag[s] = ok ? __ldcs(dy + cur.gbase + (long long)m * g.Ng) : 0.f;
         }
     };
     auto fetchB = [&](int, float*) {

@@ -13,6 +13,7 @@ import torch
 
 from .ops.mex import _expand_dim_specification, _mex_dims_helper
 from .ops.mex import mex as _mex
+from .ops.mex import mex_sum_pool2 as _mex_sum_pool2
 from .ops.similarity import similarity as _similarity
 
 
@@ -161,12 +162,15 @@ class Mex(torch.nn.Module):
         flat = self.offsets.reshape(self.offsets.shape[0] * self.offsets.shape[1], -1)
         return (flat - torch.logsumexp(flat, dim=1, keepdim=True)).reshape(self.offsets.shape)
 
-    def forward(self, x):
+    def forward(self, x, sum_pool2=False):
+        """sum_pool2=True returns the 2x2 sum pooling of the layer's output (pooling gradient fused into the
+        MEX gradient kernels)."""
         if self.offsets is None:
             self.build(tuple(x.shape), x.device, x.dtype)
         if self.channels_last:
             x = x.permute(0, 3, 1, 2)
-        y = _mex(x, self.effective_offsets(), self.num_instances, blocks=self.blocks, padding=self.padding,
+        op = _mex_sum_pool2 if sum_pool2 else _mex
+        y = op(x, self.effective_offsets(), self.num_instances, blocks=self.blocks, padding=self.padding,
                  strides=self.strides, use_unshared_regions=self.use_unshared_regions,
                  shared_offset_region=self.shared_offset_region,
                  blocks_out_of_bounds_value=self.blocks_out_of_bounds_value,

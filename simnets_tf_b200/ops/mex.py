@@ -75,6 +75,14 @@ def _geometry(d):
     return g
 
 
+def _check_dy(dy, input, g, pooled):
+    """dy has the op's output shape, or half its height and width when it is given pooled."""
+    k = 2 if pooled else 1
+    want = (input.shape[0], g.channels_out_total, g.height_out // k, g.width_out // k)
+    if tuple(dy.shape) != want:
+        raise ValueError("output_grad must have shape %s, got %s" % (want, tuple(dy.shape)))
+
+
 def _check_offsets(offsets, g, num_instances):
     want = (g.num_regions, num_instances, g.block_c, g.block_h, g.block_w)
     if tuple(offsets.shape) != want:
@@ -112,14 +120,17 @@ def mex_forward(input, offsets, num_instances, flags=0, **attrs):
     return y
 
 
-def mex_input_grad(input, offsets, orig_output, output_grad, num_instances, flags=0, **attrs):
-    """The `MexInputGrad` op."""
+def mex_input_grad(input, offsets, orig_output, output_grad, num_instances, flags=0, pooled=False, **attrs):
+    """The `MexInputGrad` op.  pooled=True: `output_grad` is the gradient of a 2x2 sum pooling of the output
+    (half height and width); the library reads it in place of its 2x upsampling."""
     attrs = _attrs(**attrs)
+    flags |= abi.FLAG_MEX_DY_POOLED2 if pooled else 0
     dev = require_cuda(input, offsets, orig_output, output_grad)
     input, offsets, y, dy = input.contiguous(), offsets.contiguous(), orig_output.contiguous(), output_grad.contiguous()
     d = _desc(input, num_instances, attrs, flags)
     g = _geometry(d)
     _check_offsets(offsets, g, num_instances)
+    _check_dy(dy, input, g, pooled)
     dx = torch.empty_like(input)
     with torch.cuda.device(dev):
         ws, n = _ws(d, dev)
@@ -129,14 +140,17 @@ def mex_input_grad(input, offsets, orig_output, output_grad, num_instances, flag
     return dx
 
 
-def mex_offsets_grad(input, offsets, orig_output, output_grad, num_instances, flags=0, out=None, **attrs):
-    """The `MexOffsetsGrad` op.  `out` / FLAG_ACCUMULATE as in `similarity_parameters_grad`."""
+def mex_offsets_grad(input, offsets, orig_output, output_grad, num_instances, flags=0, out=None, pooled=False, **attrs):
+    """The `MexOffsetsGrad` op.  `out` / FLAG_ACCUMULATE as in `similarity_parameters_grad`; `pooled` as in
+    `mex_input_grad`."""
     attrs = _attrs(**attrs)
+    flags |= abi.FLAG_MEX_DY_POOLED2 if pooled else 0
     dev = require_cuda(input, offsets, orig_output, output_grad)
     input, offsets, y, dy = input.contiguous(), offsets.contiguous(), orig_output.contiguous(), output_grad.contiguous()
     d = _desc(input, num_instances, attrs, flags)
     g = _geometry(d)
     _check_offsets(offsets, g, num_instances)
+    _check_dy(dy, input, g, pooled)
     if out is None:
         doff = torch.empty_like(offsets)
     else:
@@ -150,22 +164,39 @@ def mex_offsets_grad(input, offsets, orig_output, output_grad, num_instances, fl
     return doff
 
 
-def mex_backward(input, offsets, orig_output, output_grad, num_instances, flags=0, **attrs):
-    """`MexInputGrad` and `MexOffsetsGrad` in one library call: (input_grad, offsets_grad)."""
+def mex_backward(input, offsets, orig_output, output_grad, num_instances, flags=0, pooled=False, **attrs):
+    """`MexInputGrad` and `MexOffsetsGrad` in one library call: (input_grad, offsets_grad).  `pooled` as in
+    `mex_input_grad`."""
     attrs = _attrs(**attrs)
+    flags |= abi.FLAG_MEX_DY_POOLED2 if pooled else 0
     dev = require_cuda(input, offsets, orig_output, output_grad)
     input, offsets, y, dy = input.contiguous(), offsets.contiguous(), orig_output.contiguous(), output_grad.contiguous()
     d = _desc(input, num_instances, attrs, flags)
     g = _geometry(d)
     _check_offsets(offsets, g, num_instances)
+    _check_dy(dy, input, g, pooled)
     dx, doff = torch.empty_like(input), torch.empty_like(offsets)
     with torch.cuda.device(dev):
         ws, n = _ws(d, dev)
         sig, nbytes, terms = _cost(d, g, "bwd")     # fused: x, offsets, y, dy read once, dx and doffsets written
+        if pooled:
+            sig, nbytes = sig + " dy/4", nbytes - 3 * dy.numel() * dy.element_size()
         with timed("mex_backward", sig, nbytes, 2 * terms):
             _lib.check(_lib.lib().simnets_mex_backward(C.byref(d), input.data_ptr(), offsets.data_ptr(), y.data_ptr(), dy.data_ptr(),
                                                        dx.data_ptr(), doff.data_ptr(), ws, n, stream_ptr(dev)))
     return dx, doff
+
+
+def _gradients(ctx, grad, pooled):
+    input, offsets, y = ctx.saved_tensors
+    gi = go = None
+    if ctx.needs_input_grad[0] and ctx.needs_input_grad[1]:
+        gi, go = mex_backward(input, offsets, y, grad, ctx.num_instances, pooled=pooled, **ctx.attrs)
+    elif ctx.needs_input_grad[0]:
+        gi = mex_input_grad(input, offsets, y, grad, ctx.num_instances, pooled=pooled, **ctx.attrs)
+    elif ctx.needs_input_grad[1]:
+        go = mex_offsets_grad(input, offsets, y, grad, ctx.num_instances, pooled=pooled, **ctx.attrs)
+    return gi, go, None, None
 
 
 class _Mex(torch.autograd.Function):
@@ -178,15 +209,23 @@ class _Mex(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad):
-        input, offsets, y = ctx.saved_tensors
-        gi = go = None
-        if ctx.needs_input_grad[0] and ctx.needs_input_grad[1]:
-            gi, go = mex_backward(input, offsets, y, grad, ctx.num_instances, **ctx.attrs)
-        elif ctx.needs_input_grad[0]:
-            gi = mex_input_grad(input, offsets, y, grad, ctx.num_instances, **ctx.attrs)
-        elif ctx.needs_input_grad[1]:
-            go = mex_offsets_grad(input, offsets, y, grad, ctx.num_instances, **ctx.attrs)
-        return gi, go, None, None
+        return _gradients(ctx, grad, False)
+
+
+class _MexSumPool2(torch.autograd.Function):
+    """MEX followed by a 2x2 / stride-2 sum pooling.  The pooling's gradient (every dy value copied to the four
+    positions it summed) is never written out: the MEX gradient kernels read the pooled dy directly."""
+
+    @staticmethod
+    def forward(ctx, input, offsets, num_instances, attrs):
+        y = mex_forward(input, offsets, num_instances, **attrs)
+        ctx.attrs, ctx.num_instances = attrs, num_instances
+        ctx.save_for_backward(input, offsets, y)
+        return torch.nn.functional.avg_pool2d(y, 2) * 4.0
+
+    @staticmethod
+    def backward(ctx, grad):
+        return _gradients(ctx, grad, True)
 
 
 def mex(input, offsets, num_instances, softmax_mode=None, padding=None, strides=None, blocks=None, epsilon=None,
@@ -203,3 +242,15 @@ def mex(input, offsets, num_instances, softmax_mode=None, padding=None, strides=
                    use_unshared_regions=use_unshared_regions, shared_offset_region=shared_offset_region,
                    unshared_offset_region=unshared_offset_region)
     return _Mex.apply(input, offsets, num_instances, attrs)
+
+
+def mex_sum_pool2(input, offsets, num_instances, **kwargs):
+    """`mex(...)` followed by a 2x2 sum pooling (the MEX + pooling pair of the reference's example networks,
+    README.md:114-131, where the pooling is `4 * AveragePooling2D(2)`), with the pooling's backward folded into
+    the MEX gradient kernels.  Same keyword arguments as `mex`.  Falls back to the two separate ops when the
+    MEX output height or width is odd."""
+    attrs = _attrs(**{k: v for k, v in kwargs.items() if k != "name"})
+    g = _geometry(_desc(input, num_instances, attrs))
+    if g.height_out % 2 or g.width_out % 2:
+        return torch.nn.functional.avg_pool2d(_Mex.apply(input, offsets, num_instances, attrs), 2) * 4.0
+    return _MexSumPool2.apply(input, offsets, num_instances, attrs)

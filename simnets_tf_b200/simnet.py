@@ -124,16 +124,24 @@ class SimNet(torch.nn.Module):
             else:
                 mods.append(None)
         self.stages = torch.nn.ModuleList([m for m in mods if m is not None])
+        self.fuse_pooling = True
         self._plan = [(e, m) for e, m in zip(spec["layers"], mods)]
 
     def forward(self, x):
-        for entry, mod in self._plan:
+        plan, i = self._plan, 0
+        while i < len(plan):
+            entry, mod = plan[i]
+            if entry[0] == "mex" and self.fuse_pooling and i + 1 < len(plan) and plan[i + 1][0] == ("sumpool", 2):
+                x = mod(x, sum_pool2=True)          # MEX + 2x2 sum pooling, pooling gradient inside the MEX gradient kernels
+                i += 2
+                continue
             if mod is not None:
                 x = mod(x)
             elif entry[0] == "sumpool":
                 x = sum_pool(x, entry[1])
             elif entry[0] == "flatten":
                 x = x.flatten(1)
+            i += 1
         return x
 
     def loss(self, x, labels, global_batch=None):

@@ -64,3 +64,34 @@ def check_mex(port, c, flags=0, f64_tiebreak=False, tol=1e-5, dtype=abi.F32):
     for name, ours, ref, ref64 in (("y", y, ry, r64[0]), ("dx", dx, rdx, r64[1]), ("doff", doff, rdoff, r64[2])):
         errs[name] = cases.assert_parity(ours, ref, ref64, tol=tol, what="%s %s" % (c["name"], name))
     return errs
+
+
+def check_mex_pooled_dy(port, c, flags=0, tol=1e-5, dtype=abi.F32):
+    """Gradients taken from a dy given at half resolution (the gradient of a 2x2 sum pooling of the output) must
+    equal the oracle's gradients for the explicitly upsampled dy.  Returns None for odd output sizes."""
+    npdt, tdt = (np.float32, torch.float32) if dtype == abi.F32 else (np.float64, torch.float64)
+    d = cases.mex_desc(c, dtype=dtype)
+    oshape = port.mex_out_shape(d)
+    if oshape[2] % 2 or oshape[3] % 2 or oshape[0] == 0:
+        return None
+    x, off, _ = cases.mex_inputs(c, port.mex_offsets_shape(d), oshape, npdt)
+    dyp = np.random.default_rng(c["seed"] + 5).standard_normal((oshape[0], oshape[1], oshape[2] // 2, oshape[3] // 2)).astype(npdt)
+    dy = np.repeat(np.repeat(dyp, 2, axis=2), 2, axis=3)
+    attrs = cases.mex_attrs(c)
+    fl = c["flags"] | flags
+    ry = port.mex_forward(d, x, off)
+    xd, od, dypd, ryd = (dev(a, tdt) for a in (x, off, dyp, ry))
+    dx = mex_ops.mex_input_grad(xd, od, ryd, dypd, c["M"], flags=fl, pooled=True, **attrs)
+    doff = mex_ops.mex_offsets_grad(xd, od, ryd, dypd, c["M"], flags=fl, pooled=True, **attrs)
+    dx2, doff2 = mex_ops.mex_backward(xd, od, ryd, dypd, c["M"], flags=fl, pooled=True, **attrs)
+    assert torch.equal(dx, dx2) and torch.equal(doff, doff2)
+    rdx = port.mex_input_grad(d, x, off, ry, dy)
+    rdoff = port.mex_offsets_grad(d, x, off, ry, dy)
+    r64 = [None, None]
+    if dtype == abi.F32:
+        d64 = cases.mex_desc(c, dtype=abi.F64)
+        x64, o64, dy64 = (a.astype(np.float64) for a in (x, off, dy))
+        y64 = port.mex_forward(d64, x64, o64)
+        r64 = [port.mex_input_grad(d64, x64, o64, y64, dy64), port.mex_offsets_grad(d64, x64, o64, y64, dy64)]
+    return {"dx": cases.assert_parity(dx.cpu().numpy(), rdx, r64[0], tol=tol, what=c["name"] + " pooled dx"),
+            "doff": cases.assert_parity(doff.cpu().numpy(), rdoff, r64[1], tol=tol, what=c["name"] + " pooled doff")}

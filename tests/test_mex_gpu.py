@@ -82,6 +82,49 @@ def test_fused_backward_equals_the_two_gradient_ops(port, name):
     assert torch.equal(doff, mex_ops.mex_offsets_grad(xd, od, yd, dyd, c["M"], **attrs))
 
 
+@pytest.mark.parametrize("c", cases.MEX_SMALL + cases.MEX_CONFIGS, ids=lambda c: c["name"])
+def test_pooled_output_gradient(port, c):
+    """SIMNETS_FLAG_MEX_DY_POOLED2: dy at half resolution stands for its 2x nearest upsampling."""
+    if gpu_util.check_mex_pooled_dy(port, c) is None:
+        pytest.skip("odd output size")
+
+
+@pytest.mark.parametrize("c", cases.MEX_SMALL[::2], ids=lambda c: c["name"])
+def test_pooled_output_gradient_direct_and_f64(port, c):
+    if gpu_util.check_mex_pooled_dy(port, c, flags=abi.FLAG_FORCE_DIRECT) is None:
+        pytest.skip("odd output size")
+    gpu_util.check_mex_pooled_dy(port, c, dtype=abi.F64, tol=1e-12)
+
+
+def test_pooled_gradient_rejects_odd_output():
+    x = torch.randn(2, 4, 5, 5, device="cuda")
+    off = torch.zeros(1, 3, 4, 1, 1, device="cuda")
+    attrs = dict(blocks=[4, 1, 1], strides=[4, 1, 1], use_unshared_regions=False, shared_offset_region=[-1])
+    y = mex_ops.mex_forward(x, off, 3, **attrs)
+    with pytest.raises(RuntimeError):
+        mex_ops.mex_input_grad(x, off, y, torch.zeros(2, 3, 2, 2, device="cuda"), 3, pooled=True, **attrs)
+
+
+def test_mex_sum_pool2_equals_mex_then_pooling():
+    """The fused MEX + 2x2 sum pooling op: same forward bits, same gradients as the two ops chained."""
+    torch.manual_seed(3)
+    x = torch.randn(6, 64, 8, 8, device="cuda")
+    off = (0.3 * torch.randn(4, 96, 64, 1, 1, device="cuda"))
+    kw = dict(blocks=[64, 1, 1], strides=[64, 1, 1], softmax_mode=True, use_unshared_regions=True, unshared_offset_region=[2])
+    outs = []
+    for fused in (True, False):
+        xa, oa = x.clone().requires_grad_(True), off.clone().requires_grad_(True)
+        if fused:
+            z = mex_ops.mex_sum_pool2(xa, oa, 96, **kw)
+        else:
+            z = torch.nn.functional.avg_pool2d(mex_ops.mex(xa, oa, 96, **kw), 2) * 4.0
+        (z * torch.linspace(-1, 1, z.numel(), device="cuda").reshape(z.shape)).sum().backward()
+        outs.append((z.detach(), xa.grad, oa.grad))
+    assert torch.equal(outs[0][0], outs[1][0])
+    assert cases.rel_err(outs[0][1].cpu().numpy(), outs[1][1].cpu().numpy()) < 1e-6
+    assert cases.rel_err(outs[0][2].cpu().numpy(), outs[1][2].cpu().numpy()) < 1e-6
+
+
 def test_wide_dynamic_range_takes_the_exact_route(port):
     """Offsets and inputs spanning hundreds of units (and -inf entries) would underflow a factorised
     evaluation; results must still match the oracle, whichever route the library picks."""
