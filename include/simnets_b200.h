@@ -65,6 +65,10 @@ enum { SIMNETS_SIM_L1 = 0, SIMNETS_SIM_L2 = 1 };
 /* MEX only: keep the factorised GEMM on the CUDA cores (no tcgen05 tensor-core kernels). */
 #define SIMNETS_FLAG_MEX_NO_TENSORCORE (1u << 5)
 
+/* MEX only: run the tensor-core kernels that compute one tile per CTA instead of the persistent,
+ * warp-specialised ones (same results; kept for comparison measurements). */
+#define SIMNETS_FLAG_MEX_TC_ONE_TILE   (1u << 7)
+
 /* MEX gradient entry points only: dy is given at half resolution, dy[batch, M * channels_out, height_out / 2,
  * width_out / 2], each value standing for the 2x2 window of output positions that a 2x2 / stride-2 sum pooling
  * added up (the gradient of such a pooling copies its dy to the four inputs; with this flag the copy is never

@@ -20,6 +20,20 @@ struct SimGeo {
     double fudge, oob;
 };
 
+// Division of 0 <= n < 2^31 by a positive constant known on the host: n / d = (n * mul) >> shift, exactly
+// (mul = ceil(2^shift / d), shift = 31 + ceil(log2 d)).  One wide multiply and a shift instead of a division loop.
+struct FastDiv { uint32_t d, mul, shift; };
+__host__ inline FastDiv make_fastdiv(int d) {
+    FastDiv f;
+    f.d = uint32_t(d < 1 ? 1 : d);
+    uint32_t l = 0;
+    while ((1ull << l) < f.d) ++l;
+    f.shift = 31 + l;
+    f.mul = uint32_t(((1ull << f.shift) + f.d - 1) / f.d);
+    return f;
+}
+__host__ __device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv& f) { return uint32_t(((unsigned long long)n * f.mul) >> f.shift); }
+
 struct MexGeo {
     int B, C, H, W, M;
     int bc, bh, bw, sc, sh, sw, pc, ph, pw;
@@ -28,6 +42,7 @@ struct MexGeo {
     int oc, oh, ow;        // number of regions along each axis
     int R, rs;             // num_regions, region_size
     int K, N;              // K = bc*bh*bw, N = Co*Ho*Wo
+    FastDiv f_rs, f_rw, f_rh, f_ow, f_oh;   // dividers for region_size, rw, rh, ow, oh
     int gp, Ng;            // dy is given pooled gp x gp over (h, w) (1 = full resolution); Ng = positions per instance in dy
     int unshared;
     int finite;            // epsilon is finite
@@ -48,7 +63,20 @@ __host__ __device__ __forceinline__ int mex_region_of(const MexGeo& g, int c, in
 __host__ __device__ __forceinline__ long long mex_dy_base(const MexGeo& g, int n, int pos) {
     if (g.gp == 1) return (long long)n * g.M * g.N + pos;
     const int w = pos % g.Wo, h = (pos / g.Wo) % g.Ho, c = pos / (g.Wo * g.Ho);
-    return (long long)n * g.M * g.Ng + (c * (g.Ho / g.gp) + h / g.gp) * (g.Wo / g.gp) + w / g.gp;
+    return (long long)n * g.M * g.Ng + (c * (g.Ho >> 1) + (h >> 1)) * (g.Wo >> 1) + (w >> 1);     // gp is 1 or 2
+}
+
+// Position l (0 <= l < region_size) of region r -> output coordinates; false when the region's footprint hangs
+// over the edge of the output grid there.
+__host__ __device__ __forceinline__ bool mex_region_chw(const MexGeo& g, int r, int l, int& c, int& h, int& w) {
+    const uint32_t q0 = fast_div(uint32_t(r), g.f_ow), rw = uint32_t(r) - q0 * g.ow;
+    const uint32_t rc = fast_div(q0, g.f_oh), rh = q0 - rc * g.oh;
+    const uint32_t q1 = fast_div(uint32_t(l), g.f_rw), lw = uint32_t(l) - q1 * g.rw;
+    const uint32_t lc = fast_div(q1, g.f_rh), lh = q1 - lc * g.rh;
+    c = g.unshared ? int(lc) * g.oc + int(rc) : int(rc) * g.rc + int(lc);
+    h = g.unshared ? int(lh) * g.oh + int(rh) : int(rh) * g.rh + int(lh);
+    w = g.unshared ? int(lw) * g.ow + int(rw) : int(rw) * g.rw + int(lw);
+    return c < g.Co && h < g.Ho && w < g.Wo;
 }
 
 // Position l (0 <= l < region_size) of region r -> flat output position (c*Ho + h)*Wo + w, or -1

@@ -112,6 +112,8 @@ int mex_geometry(const simnets_mex_desc* d, simnets_mex_geometry* o, MexGeo* g) 
         g->oc = count[0]; g->oh = count[1]; g->ow = count[2];
         g->R = int(R); g->rs = extent[0] * extent[1] * extent[2];
         g->K = int(K); g->N = int(N);
+        g->f_rs = make_fastdiv(g->rs); g->f_rw = make_fastdiv(g->rw); g->f_rh = make_fastdiv(g->rh);
+        g->f_ow = make_fastdiv(g->ow); g->f_oh = make_fastdiv(g->oh);
         g->gp = (d->flags & SIMNETS_FLAG_MEX_DY_POOLED2) ? 2 : 1;
         if (out[1] % g->gp || out[2] % g->gp) return SIMNETS_E_UNSUPPORTED;
         g->Ng = out[0] * (out[1] / g->gp) * (out[2] / g->gp);

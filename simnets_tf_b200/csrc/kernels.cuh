@@ -48,6 +48,7 @@ cudaError_t launch_mex_dx_smallk(const MexGeo&, const float* x, const float* eo,
 cudaError_t launch_mex_doff_smallk(const MexGeo&, const float* x, const float* mo, const float* y, const float* dy,
                                    float* part, int slabs, const int* flag, cudaStream_t);
 // mex_tc.cu -- the three MEX GEMMs on tcgen05 tensor cores (split-TF32), for GEMM-sized layers
+int mex_tc_nt(const MexGeo&);
 size_t mex_tc_tile_floats(const MexGeo&);
 int mex_tc_doff_splits(const MexGeo&);
 cudaError_t launch_mex_tc_prep(const MexGeo&, bool transposed, const float* src, float* tiles, cudaStream_t);
@@ -57,6 +58,9 @@ cudaError_t launch_mex_dx_tc(const MexGeo&, const float* x, const float* tiles, 
                              const float* dy, float* dx, int* flag, cudaStream_t);
 cudaError_t launch_mex_doff_tc(const MexGeo&, const float* x, const float* mo, const float* mx, const float* y, const float* dy,
                                float* part, int splits, int* flag, cudaStream_t);
+// mex_tc_ws.cu -- persistent, warp-specialised versions (producer / MMA / epilogue roles, double-buffered accumulator)
+cudaError_t launch_mex_fwd_ws(const MexGeo&, const float* x, const float* tiles, const float* mo, const float* mx, float* y,
+                              int* flag, bool interior, cudaStream_t);
 // forward on the library's fixed device scratch; returns a status code of simnets_b200.h
 int launch_mex_fwd_static(const MexGeo&, const float* x, const float* off, float* y, cudaStream_t);
 cudaError_t launch_mex_dx_tiled(const MexGeo&, const float* x, const float* off, const float* y, const float* dy, float* dx,

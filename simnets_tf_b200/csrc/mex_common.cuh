@@ -32,10 +32,18 @@ __host__ inline bool doff_big(const MexGeo& g) { return g.M >= 96 && g.K >= 96; 
 __host__ inline bool smallm_shape(const MexGeo& g) { return g.gp == 1 && g.M <= 16 && g.K >= 256; }
 
 // Short patches (K <= 32): the streaming kernels of mex_smallk.cu.
+#ifdef SMALLK_TC
+__host__ inline bool smallk_shape(const MexGeo& g) { return g.gp == 1 && g.K <= 32 && !(g.M >= 48 && g.K >= 8); }
+#else
 __host__ inline bool smallk_shape(const MexGeo& g) { return g.gp == 1 && g.K <= 32; }
+#endif
 
 // GEMM-sized layers (many instances, mid to long patches): the tensor-core forward of mex_tc.cu.
+#ifdef SMALLK_TC
+__host__ inline bool tc_shape(const MexGeo& g) { return !smallk_shape(g) && !smallm_shape(g) && g.M >= 48 && (g.K >= 48 || (g.gp == 1 && g.K >= 8 && g.K <= 32)); }
+#else
 __host__ inline bool tc_shape(const MexGeo& g) { return !smallk_shape(g) && !smallm_shape(g) && g.M >= 48 && g.K >= 48; }
+#endif
 
 __host__ inline int doff_splits(const MexGeo& g) {
     if (smallk_shape(g)) {
@@ -123,14 +131,15 @@ __device__ __forceinline__ Column column_of(const MexGeo& g, int r, long long jl
     c.base = -1; c.gbase = 0; c.n = 0; c.c0 = c.h0 = c.w0 = 0; c.mx = 0.f;
     if (jl >= P) return c;
     int n, l;
-    if (P <= 0x7fffffffLL) { const unsigned j32 = unsigned(jl); n = int(j32 / unsigned(g.rs)); l = int(j32 - unsigned(n) * unsigned(g.rs)); }
+    if (P <= 0x7fffffffLL) { const uint32_t j32 = uint32_t(jl); n = int(fast_div(j32, g.f_rs)); l = int(j32 - uint32_t(n) * uint32_t(g.rs)); }
     else { n = int(jl / g.rs); l = int(jl % g.rs); }
-    const int pos = mex_region_position(g, r, l);
-    if (pos < 0) return c;
-    const int w = pos % g.Wo, h = (pos / g.Wo) % g.Ho, cc = pos / (g.Wo * g.Ho);
+    int cc, h, w;
+    if (!mex_region_chw(g, r, l, cc, h, w)) return c;
+    const int pos = (cc * g.Ho + h) * g.Wo + w;
     c.n = n; c.c0 = cc * g.sc - g.pc; c.h0 = h * g.sh - g.ph; c.w0 = w * g.sw - g.pw;
     c.base = (long long)n * g.M * g.N + pos;
-    c.gbase = g.gp == 1 ? c.base : (long long)n * g.M * g.Ng + (cc * (g.Ho / g.gp) + h / g.gp) * (g.Wo / g.gp) + w / g.gp;
+    c.gbase = c.base;
+    if (g.gp == 2) c.gbase = (long long)n * g.M * g.Ng + (cc * (g.Ho >> 1) + (h >> 1)) * (g.Wo >> 1) + (w >> 1);     // gp is 1 or 2
     c.mx = mx ? mx[(long long)n * g.N + pos] : 0.f;
     return c;
 }

@@ -409,7 +409,8 @@ cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* o
     if (tc_shape(g) && !(flags & SIMNETS_FLAG_MEX_NO_TENSORCORE)) {
         e = launch_mex_tc_prep(g, false, w.eo, w.tc_tiles, s);
         if (e != cudaSuccess) return e;
-        e = launch_mex_fwd_tc(g, x, w.tc_tiles, w.mo, w.mx, y, w.flag, patches_inside_input(g), s);
+        e = (flags & SIMNETS_FLAG_MEX_TC_ONE_TILE) ? launch_mex_fwd_tc(g, x, w.tc_tiles, w.mo, w.mx, y, w.flag, patches_inside_input(g), s)
+                                                   : launch_mex_fwd_ws(g, x, w.tc_tiles, w.mo, w.mx, y, w.flag, patches_inside_input(g), s);
         if (e != cudaSuccess) return e;
         return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);
     }

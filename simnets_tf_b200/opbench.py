@@ -62,7 +62,11 @@ def run(layer, op, batch, iters, warmup, flags=0, seed=0):
         dy = torch.randn(y.shape, generator=gen).to(dev)
         calls = {"forward": lambda: mex_ops.mex_forward(x, off, inst, flags=flags, **attrs),
                  "input_grad": lambda: mex_ops.mex_input_grad(x, off, y, dy, inst, flags=flags, **attrs),
-                 "offsets_grad": lambda: mex_ops.mex_offsets_grad(x, off, y, dy, inst, flags=flags, **attrs)}
+                 "offsets_grad": lambda: mex_ops.mex_offsets_grad(x, off, y, dy, inst, flags=flags, **attrs),
+                 "backward": lambda: mex_ops.mex_backward(x, off, y, dy, inst, flags=flags, **attrs)}
+        if g.height_out % 2 == 0 and g.width_out % 2 == 0:
+            dyp = torch.randn(y.shape[:2] + (y.shape[2] // 2, y.shape[3] // 2), generator=gen).to(dev)
+            calls["backward_pooled"] = lambda: mex_ops.mex_backward(x, off, y, dyp, inst, flags=flags, pooled=True, **attrs)
     fn = calls[op]
     for _ in range(warmup):
         fn()
@@ -83,7 +87,7 @@ def run(layer, op, batch, iters, warmup, flags=0, seed=0):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--layer", choices=sorted(LAYERS), required=True)
-    ap.add_argument("--op", default="forward", choices=["forward", "input_grad", "params_grad", "offsets_grad"])
+    ap.add_argument("--op", default="forward", choices=["forward", "input_grad", "params_grad", "offsets_grad", "backward", "backward_pooled"])
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
