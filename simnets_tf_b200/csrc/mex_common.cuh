@@ -45,6 +45,12 @@ __host__ inline bool tc_shape(const MexGeo& g) { return !smallk_shape(g) && !sma
 __host__ inline bool tc_shape(const MexGeo& g) { return !smallk_shape(g) && !smallm_shape(g) && g.M >= 48 && g.K >= 48; }
 #endif
 
+// no patch reaches outside the input: no padding, and the last patch along each axis ends inside
+__host__ inline bool patches_inside_input(const MexGeo& g) {
+    auto inside = [](int dim, int block, int stride, int pad, int out) { return pad == 0 && (out - 1) * stride + block <= dim; };
+    return inside(g.C, g.bc, g.sc, g.pc, g.Co) && inside(g.H, g.bh, g.sh, g.ph, g.Ho) && inside(g.W, g.bw, g.sw, g.pw, g.Wo);
+}
+
 __host__ inline int doff_splits(const MexGeo& g) {
     if (smallk_shape(g)) {
         const long long P = (long long)g.B * g.rs, tiles = (P + 31) / 32, ctas = (long long)((g.M + 255) / 256) * g.R;

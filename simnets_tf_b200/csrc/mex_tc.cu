@@ -129,11 +129,19 @@ __global__ void __launch_bounds__(kTcThreads) mex_fwd_tc(MexGeo g, const float* 
     tc_end(tmem_d, NT);
 }
 
+// Read-only global load that the compiler keeps in program order with the other loads of this kind: the epilogue
+// below wants eight of them in flight per batch, not all thirty-two hoisted to the top (which spills).
+__device__ __forceinline__ float ld_nc_ordered(const float* p) {
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
 // ---- input gradient ----------------------------------------------------------------------------------------------
 // T[j (position, lane), k (tap, column)] = sum_m Q[j, m] * Eo[m, k];  dx[tap k of position j] = Ex[j, k] * T[j, k].
 // A = Q computed from y, dy (reads coalesced along positions), B = pre-split Eo^T tiles.  Blocks must not overlap.
-template <int NT, bool SPATIAL1>
-__global__ void __launch_bounds__(kTcThreads) mex_dx_tc(MexGeo g, const float* __restrict__ x, const float* __restrict__ tiles,
+template <int NT, bool SPATIAL1, bool INTERIOR>
+__global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4)) mex_dx_tc(MexGeo g, const float* __restrict__ x, const float* __restrict__ tiles,
                                                        const float* __restrict__ mo, const float* __restrict__ mx,
                                                        const float* __restrict__ y, const float* __restrict__ dy,
                                                        float* __restrict__ dx, int* __restrict__ flag) {
@@ -149,39 +157,53 @@ __global__ void __launch_bounds__(kTcThreads) mex_dx_tc(MexGeo g, const float* _
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t tmem_d = tc_begin(sh, NT);
 
+    // Q[j, m] = dy * exp(eps * (mx_j + mo_m - y) + c) = dy * 2^(a * mx_j + (a * mo_m + c') - a * y),  a = eps * log2(e)
     const int prow = threadIdx.x % kTcPos, mhalf = threadIdx.x / kTcPos;
     const Column sc = column_of(g, r, jt * kTcPos + prow, P, mx);
     const bool live = sc.base >= 0;
-    const float eps = float(g.eps), cst = float(g.cst);
+    const float a = float(g.eps) * 1.4426950408889634f, c2 = float(g.cst) * 1.4426950408889634f;
+    const float amx = a * sc.mx + c2;
     const float* mor = mo + r * g.M;
-    const float* yb = y + (live ? sc.base : 0);
-    const float* gb = dy + (live ? sc.gbase : 0);
+    const size_t ystep = (size_t)g.N * sizeof(float), gstep = (size_t)g.Ng * sizeof(float);
+    // running pointers to (row of the next chunk to load, this thread's first instance of it)
+    const char* yp = reinterpret_cast<const char*>(y + (live ? sc.base : 0)) + (size_t)(mhalf * 8) * ystep;
+    const char* gp = reinterpret_cast<const char*>(dy + (live ? sc.gbase : 0)) + (size_t)(mhalf * 8) * gstep;
     const float* btiles = tiles + ((size_t)r * ktiles + kt) * mchunks * 2 * NT * kTcKT;
+    const int M = g.M;
 
     float yv[8], gv[8], mv[8];
     auto load = [&](int c) {
+        const int m0 = c * kTcKT + mhalf * 8;
+        if (m0 + 8 <= M) {
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int m = min(c * kTcKT + mhalf * 8 + u, g.M - 1);
-            yv[u] = __ldcs(yb + (long long)m * g.N);
-            gv[u] = __ldcs(gb + (long long)m * g.Ng);
-            mv[u] = __ldg(mor + m);
+            for (int u = 0; u < 8; ++u) {
+                yv[u] = __ldcs(reinterpret_cast<const float*>(yp + u * ystep));
+                gv[u] = live ? __ldcs(reinterpret_cast<const float*>(gp + u * gstep)) : 0.f;
+                mv[u] = __ldg(mor + m0 + u);
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const bool in = m0 + u < M;
+                yv[u] = in ? __ldcs(reinterpret_cast<const float*>(yp + u * ystep)) : 0.f;
+                gv[u] = (in && live) ? __ldcs(reinterpret_cast<const float*>(gp + u * gstep)) : 0.f;      // dy = 0: no contribution
+                mv[u] = in ? __ldg(mor + m0 + u) : 0.f;
+            }
         }
+        yp += kTcKT * ystep;
+        gp += kTcKT * gstep;
     };
     auto store = [&](int c, unsigned char* a_hi, unsigned char* a_lo, unsigned char* b_hi, unsigned char*) {
         const float* src = btiles + (size_t)c * 2 * NT * kTcKT;
         for (int v = threadIdx.x; v < 2 * NT * kTcKT / 4; v += kTcThreads) cp_async16(reinterpret_cast<float*>(b_hi) + v * 4, src + v * 4, 16);
         float q[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const bool in = live && c * kTcKT + mhalf * 8 + u < g.M;
-            q[u] = in ? gv[u] * fast_exp(eps * (sc.mx + mv[u] - yv[u]) + cst) : 0.f;
-        }
+        for (int u = 0; u < 8; ++u) q[u] = gv[u] * ex2_ftz(fmaf(-a, yv[u], fmaf(a, mv[u], amx)));
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             float4 hi, lo;
-            split_tf32(q[4 * h], hi.x, lo.x); split_tf32(q[4 * h + 1], hi.y, lo.y);
-            split_tf32(q[4 * h + 2], hi.z, lo.z); split_tf32(q[4 * h + 3], hi.w, lo.w);
+            split_tf32_trunc(q[4 * h], hi.x, lo.x); split_tf32_trunc(q[4 * h + 1], hi.y, lo.y);
+            split_tf32_trunc(q[4 * h + 2], hi.z, lo.z); split_tf32_trunc(q[4 * h + 3], hi.w, lo.w);
             const int off = core_offset(prow, mhalf * 8 + 4 * h);
             *reinterpret_cast<float4*>(a_hi + off) = hi;
             *reinterpret_cast<float4*>(a_lo + off) = lo;
@@ -192,21 +214,49 @@ __global__ void __launch_bounds__(kTcThreads) mex_dx_tc(MexGeo g, const float* _
     if (good) {
         const int quarter = warp & 3, half = warp >> 2;
         const Column col = column_of(g, r, jt * kTcPos + quarter * 32 + lane, P, mx);
-        const size_t sample = (size_t)col.n * g.C * g.H * g.W;
+        const float b = -a * col.mx;                                   // Ex = 2^(a * x - a * mx)
+        if (SPATIAL1 && INTERIOR) {
+            // tap k of a 1x1 block that never leaves the input: channel c0 + k of one pixel, planes H * W floats apart
+            const unsigned hw = unsigned(g.H) * unsigned(g.W);           // the launcher takes this path only if NT * H * W < 2^31
+            const size_t first = (((size_t)col.n * g.C + col.c0 + kt * NT) * g.H + col.h0) * g.W + col.w0;
+            const float* xb = x + first;
+            float* db = dx + first;
 #pragma unroll 1
-        for (int c0 = half * (NT / 2); c0 < (half + 1) * (NT / 2); c0 += 32) {
-            uint32_t v[32];
-            tmem_ld32(tmem_d + (uint32_t(quarter * 32) << 16) + uint32_t(c0), v);
-            if (col.base >= 0) {
+            for (int c0 = half * (NT / 2); c0 < (half + 1) * (NT / 2); c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_d + (uint32_t(quarter * 32) << 16) + uint32_t(c0), v);
+                if (col.base >= 0) {
+                    const int kleft = g.K - kt * NT - c0;
+                    unsigned off = unsigned(c0) * hw;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int k = kt * NT + c0 + i;
-                    if (k >= g.K) continue;
-                    const Tap tp = tap_of<SPATIAL1>(g, k);
-                    const int cc = col.c0 + tp.c, hh = col.h0 + tp.h, ww = col.w0 + tp.w;
-                    if (cc < 0 || cc >= g.C || hh < 0 || hh >= g.H || ww < 0 || ww >= g.W) continue;
-                    const size_t a = sample + ((size_t)cc * g.H + hh) * g.W + ww;
-                    dx[a] = fast_exp(eps * (__ldg(x + a) - col.mx)) * __uint_as_float(v[i]);
+                    for (int i0 = 0; i0 < 32; i0 += 8) {                 // eight loads in flight, then their eight stores
+                        float xr[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) xr[i] = (i0 + i < kleft) ? ld_nc_ordered(xb + (off + i * hw)) : 0.f;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            if (i0 + i < kleft) db[off + i * hw] = ex2_ftz(fmaf(xr[i], a, b)) * __uint_as_float(v[i0 + i]);
+                        off += 8 * hw;
+                    }
+                }
+            }
+        } else {
+            const size_t sample = (size_t)col.n * g.C * g.H * g.W;
+#pragma unroll 1
+            for (int c0 = half * (NT / 2); c0 < (half + 1) * (NT / 2); c0 += 32) {
+                uint32_t v[32];
+                tmem_ld32(tmem_d + (uint32_t(quarter * 32) << 16) + uint32_t(c0), v);
+                if (col.base >= 0) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int k = kt * NT + c0 + i;
+                        if (k >= g.K) continue;
+                        const Tap tp = tap_of<SPATIAL1>(g, k);
+                        const int cc = col.c0 + tp.c, hh = col.h0 + tp.h, ww = col.w0 + tp.w;
+                        if (cc < 0 || cc >= g.C || hh < 0 || hh >= g.H || ww < 0 || ww >= g.W) continue;
+                        const size_t ad = sample + ((size_t)cc * g.H + hh) * g.W + ww;
+                        dx[ad] = ex2_ftz(fmaf(__ldg(x + ad), a, b)) * __uint_as_float(v[i]);
+                    }
                 }
             }
         }
@@ -222,14 +272,14 @@ __global__ void __launch_bounds__(kTcThreads) mex_dx_tc(MexGeo g, const float* _
 // time; a leading byte offset of 144 spreads the eight 16-byte chunks of a row over all banks.
 constexpr int kDoKT = 32, kDoLBO = 144;
 
-template <int NT, bool SPATIAL1>
-__global__ void __launch_bounds__(kTcThreads) mex_doff_tc(MexGeo g, const float* __restrict__ x, const float* __restrict__ mo,
+template <int NT, bool SPATIAL1, bool INTERIOR>
+__global__ void __launch_bounds__(kTcThreads, 2) mex_doff_tc(MexGeo g, const float* __restrict__ x, const float* __restrict__ mo,
                                                          const float* __restrict__ mx, const float* __restrict__ y,
                                                          const float* __restrict__ dy, float* __restrict__ part, int splits,
                                                          int* __restrict__ flag) {
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ TcShared sh;
-    __shared__ float mo_s[128];
+    __shared__ float amo_s[128];                        // a * mo + c' of this CTA's instances
     if (flag[0]) return;
     const long long P = (long long)g.B * g.rs;
     const int mtiles = (g.M + 127) / 128, ktiles = (g.K + NT - 1) / NT;
@@ -241,9 +291,17 @@ __global__ void __launch_bounds__(kTcThreads) mex_doff_tc(MexGeo g, const float*
     const long long chunks = (P + kDoKT - 1) / kDoKT;
     const long long c_begin = chunks * split / splits, c_end = chunks * (split + 1) / splits;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x < 128) mo_s[threadIdx.x] = (mt * 128 + threadIdx.x < g.M) ? mo[r * g.M + mt * 128 + threadIdx.x] : 0.f;
+    // Q = dy * 2^(a * mx + (a * mo + c') - a * y),  Ex = 2^(a * x - a * mx),  a = eps * log2(e)
+    const float a = float(g.eps) * 1.4426950408889634f, c2 = float(g.cst) * 1.4426950408889634f, oob = float(g.oob);
+    if (threadIdx.x < 128) amo_s[threadIdx.x] = (mt * 128 + threadIdx.x < g.M) ? fmaf(a, mo[r * g.M + mt * 128 + threadIdx.x], c2) : 0.f;
     const uint32_t tmem_d = tc_begin(sh, NT);
-    const float eps = float(g.eps), cst = float(g.cst), oob = float(g.oob);
+
+    const int M = g.M, K = g.K;
+    const int m0 = mt * 128 + warp * 16;                 // this warp's 16 instances
+    const int k0 = kt * NT + warp * (NT / 8);            // and its NT / 8 taps
+    const size_t ystep = (size_t)g.N * sizeof(float), gstep = (size_t)g.Ng * sizeof(float);
+    const unsigned hw = unsigned(g.H) * unsigned(g.W);
+    const bool m_full = m0 + 16 <= M, k_full = k0 + NT / 8 <= K;
 
     // registers of the chunk being prefetched: lane = position of the chunk, this warp's 16 instances and NT / 8 taps
     Column col;
@@ -251,29 +309,42 @@ __global__ void __launch_bounds__(kTcThreads) mex_doff_tc(MexGeo g, const float*
     auto load = [&](int c) {
         col = column_of(g, r, (c_begin + c) * kDoKT + lane, P, mx);
         const bool live = col.base >= 0;
-        const float* yb = y + (live ? col.base : 0);
-        const float* gb = dy + (live ? col.gbase : 0);
-        const float* xs = x + (size_t)col.n * g.C * g.H * g.W;
+        const char* yp = reinterpret_cast<const char*>(y + (live ? col.base : 0)) + (size_t)m0 * ystep;
+        const char* gp = reinterpret_cast<const char*>(dy + (live ? col.gbase : 0)) + (size_t)m0 * gstep;
+        if (m_full) {
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-            const int m = min(mt * 128 + warp * 16 + u, g.M - 1);
-            yv[u] = __ldcs(yb + (long long)m * g.N);
-            gv[u] = __ldcs(gb + (long long)m * g.Ng);
+            for (int u = 0; u < 16; ++u) {
+                yv[u] = __ldcs(reinterpret_cast<const float*>(yp + u * ystep));
+                gv[u] = live ? __ldcs(reinterpret_cast<const float*>(gp + u * gstep)) : 0.f;     // dy = 0: no contribution
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const bool in = m0 + u < M;
+                yv[u] = in ? __ldcs(reinterpret_cast<const float*>(yp + u * ystep)) : 0.f;
+                gv[u] = (in && live) ? __ldcs(reinterpret_cast<const float*>(gp + u * gstep)) : 0.f;
+            }
         }
+        if (SPATIAL1 && INTERIOR) {
+            const float* xp = x + (((size_t)col.n * g.C + col.c0 + k0) * g.H + col.h0) * g.W + col.w0;
 #pragma unroll
-        for (int u = 0; u < NT / 8; ++u) {
-            const int k = kt * NT + warp * (NT / 8) + u;
-            xv[u] = (live && k < g.K) ? patch_value<SPATIAL1>(g, xs, col.c0, col.h0, col.w0, k, oob) : 0.f;
+            for (int u = 0; u < NT / 8; ++u) xv[u] = (live && (k_full || k0 + u < K)) ? __ldg(xp + (size_t)u * hw) : 0.f;
+        } else {
+            const float* xs = x + (size_t)col.n * g.C * g.H * g.W;
+#pragma unroll
+            for (int u = 0; u < NT / 8; ++u)
+                xv[u] = (live && k0 + u < K) ? patch_value<SPATIAL1>(g, xs, col.c0, col.h0, col.w0, k0 + u, oob) : 0.f;
         }
     };
     auto store = [&](int, unsigned char* a_hi, unsigned char* a_lo, unsigned char* b_hi, unsigned char* b_lo) {
         const bool live = col.base >= 0;
+        const float amx = a * col.mx;
+        const float bx = live ? -amx : -INFINITY;                // dead column: every Ex becomes 2^-inf = 0
 #pragma unroll
         for (int u = 0; u < 16; ++u) {                           // A: Q[m, j]
             const int row = warp * 16 + u;
-            const bool in = live && mt * 128 + row < g.M;
             float hi, lo;
-            split_tf32(in ? gv[u] * fast_exp(eps * (col.mx + mo_s[row] - yv[u]) + cst) : 0.f, hi, lo);
+            split_tf32_trunc(gv[u] * ex2_ftz(fmaf(-a, yv[u], amx + amo_s[row])), hi, lo);
             const int off = core_off<kDoKT, kDoLBO>(row, lane);
             *reinterpret_cast<float*>(a_hi + off) = hi;
             *reinterpret_cast<float*>(a_lo + off) = lo;
@@ -281,9 +352,8 @@ __global__ void __launch_bounds__(kTcThreads) mex_doff_tc(MexGeo g, const float*
 #pragma unroll
         for (int u = 0; u < NT / 8; ++u) {                       // B: Ex[k, j]
             const int row = warp * (NT / 8) + u;
-            const bool in = live && kt * NT + row < g.K;
             float hi, lo;
-            split_tf32(in ? fast_exp(eps * (xv[u] - col.mx)) : 0.f, hi, lo);
+            split_tf32_trunc((k_full || k0 + u < K) ? ex2_ftz(fmaf(xv[u], a, bx)) : 0.f, hi, lo);
             const int off = core_off<kDoKT, kDoLBO>(row, lane);
             *reinterpret_cast<float*>(b_hi + off) = hi;
             *reinterpret_cast<float*>(b_lo + off) = lo;
@@ -354,8 +424,12 @@ cudaError_t launch_dx_nt(const MexGeo& g, const float* x, const float* tiles, co
     const long long blocks = ((P + kTcPos - 1) / kTcPos) * ((g.K + NT - 1) / NT) * g.R;
     if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     constexpr int smem = tc_smem_bytes<NT, kTcKT, 128, 2>();
-    if (g.bh == 1 && g.bw == 1) TC_RUN((mex_dx_tc<NT, true>), smem, int(blocks), g, x, tiles, mo, mx, y, dy, dx, flag);
-    else TC_RUN((mex_dx_tc<NT, false>), smem, int(blocks), g, x, tiles, mo, mx, y, dy, dx, flag);
+    if (g.bh == 1 && g.bw == 1) {
+        if (patches_inside_input(g) && (long long)NT * g.H * g.W < 0x7fffffffLL) TC_RUN((mex_dx_tc<NT, true, true>), smem, int(blocks), g, x, tiles, mo, mx, y, dy, dx, flag);
+        else TC_RUN((mex_dx_tc<NT, true, false>), smem, int(blocks), g, x, tiles, mo, mx, y, dy, dx, flag);
+    } else {
+        TC_RUN((mex_dx_tc<NT, false, false>), smem, int(blocks), g, x, tiles, mo, mx, y, dy, dx, flag);
+    }
     count_launch();
     return cudaGetLastError();
 }
@@ -366,8 +440,12 @@ cudaError_t launch_doff_nt(const MexGeo& g, const float* x, const float* mo, con
     const long long blocks = (long long)((g.M + 127) / 128) * ((g.K + NT - 1) / NT) * g.R * splits;
     if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     constexpr int smem = tc_smem_bytes<NT, kDoKT, kDoLBO, 1>();
-    if (g.bh == 1 && g.bw == 1) TC_RUN((mex_doff_tc<NT, true>), smem, int(blocks), g, x, mo, mx, y, dy, part, splits, flag);
-    else TC_RUN((mex_doff_tc<NT, false>), smem, int(blocks), g, x, mo, mx, y, dy, part, splits, flag);
+    if (g.bh == 1 && g.bw == 1) {
+        if (patches_inside_input(g)) TC_RUN((mex_doff_tc<NT, true, true>), smem, int(blocks), g, x, mo, mx, y, dy, part, splits, flag);
+        else TC_RUN((mex_doff_tc<NT, true, false>), smem, int(blocks), g, x, mo, mx, y, dy, part, splits, flag);
+    } else {
+        TC_RUN((mex_doff_tc<NT, false, false>), smem, int(blocks), g, x, mo, mx, y, dy, part, splits, flag);
+    }
     count_launch();
     return cudaGetLastError();
 }
@@ -391,7 +469,7 @@ int mex_tc_doff_splits(const MexGeo& g) {
     const int nt = pick_nt(g.K);
     const long long P = (long long)g.B * g.rs, chunks = (P + kDoKT - 1) / kDoKT;
     const long long tiles = (long long)((g.M + 127) / 128) * ((g.K + nt - 1) / nt) * g.R;
-    const int per_sm = nt == 256 ? 2 : (nt == 128 ? 3 : 4);      // CTAs per SM that shared and tensor memory allow
+    const int per_sm = 2;                                        // CTAs per SM (128 registers per thread)
     long long s = (148LL * per_sm * 2) / tiles;                  // about two full waves
     if (s > chunks) s = chunks;
     if (s < 1) s = 1;

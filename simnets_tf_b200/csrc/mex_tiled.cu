@@ -347,12 +347,6 @@ __global__ void __launch_bounds__(256) mex_doff_reduce(long long n, int K, int s
     }
 }
 
-// no patch reaches outside the input: no padding, and the last patch along each axis ends inside
-bool patches_inside_input(const MexGeo& g) {
-    auto inside = [](int dim, int block, int stride, int pad, int out) { return pad == 0 && (out - 1) * stride + block <= dim; };
-    return inside(g.C, g.bc, g.sc, g.pc, g.Co) && inside(g.H, g.bh, g.sh, g.ph, g.Ho) && inside(g.W, g.bw, g.sw, g.pw, g.Wo);
-}
-
 bool blocks_disjoint(const MexGeo& g) { return g.sc >= g.bc && g.sh >= g.bh && g.sw >= g.bw; }
 
 bool blocks_cover_input(const MexGeo& g) {
