@@ -61,6 +61,8 @@ cudaError_t launch_mex_doff_tc(const MexGeo&, const float* x, const float* mo, c
 // mex_tc_ws.cu -- persistent, warp-specialised versions (producer / MMA / epilogue roles, double-buffered accumulator)
 cudaError_t launch_mex_fwd_ws(const MexGeo&, const float* x, const float* tiles, const float* mo, const float* mx, float* y,
                               int* flag, bool interior, cudaStream_t);
+cudaError_t launch_mex_dx_ws(const MexGeo&, const float* x, const float* tiles, const float* mo, const float* mx, const float* y,
+                             const float* dy, float* dx, int* flag, cudaStream_t);
 // forward on the library's fixed device scratch; returns a status code of simnets_b200.h
 int launch_mex_fwd_static(const MexGeo&, const float* x, const float* off, float* y, cudaStream_t);
 cudaError_t launch_mex_dx_tiled(const MexGeo&, const float* x, const float* off, const float* y, const float* dy, float* dx,

@@ -32,18 +32,15 @@ __host__ inline bool doff_big(const MexGeo& g) { return g.M >= 96 && g.K >= 96; 
 __host__ inline bool smallm_shape(const MexGeo& g) { return g.gp == 1 && g.M <= 16 && g.K >= 256; }
 
 // Short patches (K <= 32): the streaming kernels of mex_smallk.cu.
-#ifdef SMALLK_TC
-__host__ inline bool smallk_shape(const MexGeo& g) { return g.gp == 1 && g.K <= 32 && !(g.M >= 48 && g.K >= 8); }
-#else
 __host__ inline bool smallk_shape(const MexGeo& g) { return g.gp == 1 && g.K <= 32; }
-#endif
 
 // GEMM-sized layers (many instances, mid to long patches): the tensor-core forward of mex_tc.cu.
-#ifdef SMALLK_TC
-__host__ inline bool tc_shape(const MexGeo& g) { return !smallk_shape(g) && !smallm_shape(g) && g.M >= 48 && (g.K >= 48 || (g.gp == 1 && g.K >= 8 && g.K <= 32)); }
-#else
-__host__ inline bool tc_shape(const MexGeo& g) { return !smallk_shape(g) && !smallm_shape(g) && g.M >= 48 && g.K >= 48; }
-#endif
+// (M and N bounds: the kernels keep one value per instance in shared memory and address the instances of a chunk
+// with 32-bit offsets of up to 16 N elements; the same for 32 H W input elements.)
+__host__ inline bool tc_shape(const MexGeo& g) {
+    return !smallk_shape(g) && !smallm_shape(g) && g.M >= 48 && g.K >= 48 && g.M <= 2048 && g.N < (1 << 26) &&
+           (long long)g.H * g.W < (1 << 25);
+}
 
 // no patch reaches outside the input: no padding, and the last patch along each axis ends inside
 __host__ inline bool patches_inside_input(const MexGeo& g) {

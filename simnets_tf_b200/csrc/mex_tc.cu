@@ -129,17 +129,11 @@ __global__ void __launch_bounds__(kTcThreads) mex_fwd_tc(MexGeo g, const float* 
     tc_end(tmem_d, NT);
 }
 
-// Read-only global load that the compiler keeps in program order with the other loads of this kind: the epilogue
-// below wants eight of them in flight per batch, not all thirty-two hoisted to the top (which spills).
-__device__ __forceinline__ float ld_nc_ordered(const float* p) {
-    float v;
-    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
-    return v;
-}
-
 // ---- input gradient ----------------------------------------------------------------------------------------------
 // T[j (position, lane), k (tap, column)] = sum_m Q[j, m] * Eo[m, k];  dx[tap k of position j] = Ex[j, k] * T[j, k].
 // A = Q computed from y, dy (reads coalesced along positions), B = pre-split Eo^T tiles.  Blocks must not overlap.
+constexpr int kDxMaxM = 2048;      // instances whose a * mo + c' fit the kernel's shared-memory table (larger M: CUDA-core kernels)
+
 template <int NT, bool SPATIAL1, bool INTERIOR>
 __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4)) mex_dx_tc(MexGeo g, const float* __restrict__ x, const float* __restrict__ tiles,
                                                        const float* __restrict__ mo, const float* __restrict__ mx,
@@ -147,6 +141,7 @@ __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4
                                                        float* __restrict__ dx, int* __restrict__ flag) {
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ TcShared sh;
+    __shared__ __align__(16) float amo_s[kDxMaxM];        // a * mo + c' of every instance (rounded up to a whole chunk)
     if (flag[0]) return;
     const long long P = (long long)g.B * g.rs;
     const int ktiles = (g.K + NT - 1) / NT, mchunks = (g.M + kTcKT - 1) / kTcKT;
@@ -155,19 +150,20 @@ __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4
     const int kt = bid % ktiles;
     const long long jt = bid / ktiles;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t tmem_d = tc_begin(sh, NT);
-
     // Q[j, m] = dy * exp(eps * (mx_j + mo_m - y) + c) = dy * 2^(a * mx_j + (a * mo_m + c') - a * y),  a = eps * log2(e)
+    const float a = float(g.eps) * 1.4426950408889634f, c2 = float(g.cst) * 1.4426950408889634f;
+    for (int i = threadIdx.x; i < mchunks * kTcKT; i += kTcThreads) amo_s[i] = i < g.M ? fmaf(a, mo[r * g.M + i], c2) : 0.f;
+    const uint32_t tmem_d = tc_begin(sh, NT);             // (its barrier also publishes amo_s)
+
     const int prow = threadIdx.x % kTcPos, mhalf = threadIdx.x / kTcPos;
     const Column sc = column_of(g, r, jt * kTcPos + prow, P, mx);
     const bool live = sc.base >= 0;
-    const float a = float(g.eps) * 1.4426950408889634f, c2 = float(g.cst) * 1.4426950408889634f;
-    const float amx = a * sc.mx + c2;
-    const float* mor = mo + r * g.M;
-    const size_t ystep = (size_t)g.N * sizeof(float), gstep = (size_t)g.Ng * sizeof(float);
-    // running pointers to (row of the next chunk to load, this thread's first instance of it)
-    const char* yp = reinterpret_cast<const char*>(y + (live ? sc.base : 0)) + (size_t)(mhalf * 8) * ystep;
-    const char* gp = reinterpret_cast<const char*>(dy + (live ? sc.gbase : 0)) + (size_t)(mhalf * 8) * gstep;
+    const float amx = a * sc.mx;
+    // Running pointers to (this thread's first instance of the next chunk to load, its position); the eight instances
+    // of a chunk are addressed with 32-bit element offsets u * N from them (the launcher checks 16 * N < 2^31).
+    const unsigned Nu = unsigned(g.N), Ngu = unsigned(g.Ng);
+    const float* yp = y + (live ? sc.base : 0) + (size_t)(mhalf * 8) * Nu;
+    const float* gp = dy + (live ? sc.gbase : 0) + (size_t)(mhalf * 8) * Ngu;
     const float* btiles = tiles + ((size_t)r * ktiles + kt) * mchunks * 2 * NT * kTcKT;
     const int M = g.M;
 
@@ -177,28 +173,30 @@ __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4
         if (m0 + 8 <= M) {
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                yv[u] = __ldcs(reinterpret_cast<const float*>(yp + u * ystep));
-                gv[u] = live ? __ldcs(reinterpret_cast<const float*>(gp + u * gstep)) : 0.f;
-                mv[u] = __ldg(mor + m0 + u);
+                yv[u] = __ldcs(yp + u * Nu);
+                gv[u] = live ? __ldcs(gp + u * Ngu) : 0.f;
             }
+            const float4 m0123 = *reinterpret_cast<const float4*>(amo_s + m0), m4567 = *reinterpret_cast<const float4*>(amo_s + m0 + 4);
+            mv[0] = m0123.x; mv[1] = m0123.y; mv[2] = m0123.z; mv[3] = m0123.w;
+            mv[4] = m4567.x; mv[5] = m4567.y; mv[6] = m4567.z; mv[7] = m4567.w;
         } else {
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const bool in = m0 + u < M;
-                yv[u] = in ? __ldcs(reinterpret_cast<const float*>(yp + u * ystep)) : 0.f;
-                gv[u] = (in && live) ? __ldcs(reinterpret_cast<const float*>(gp + u * gstep)) : 0.f;      // dy = 0: no contribution
-                mv[u] = in ? __ldg(mor + m0 + u) : 0.f;
+                yv[u] = in ? __ldcs(yp + u * Nu) : 0.f;
+                gv[u] = (in && live) ? __ldcs(gp + u * Ngu) : 0.f;      // dy = 0: no contribution
+                mv[u] = amo_s[m0 + u];
             }
         }
-        yp += kTcKT * ystep;
-        gp += kTcKT * gstep;
+        yp += (size_t)kTcKT * Nu;
+        gp += (size_t)kTcKT * Ngu;
     };
     auto store = [&](int c, unsigned char* a_hi, unsigned char* a_lo, unsigned char* b_hi, unsigned char*) {
         const float* src = btiles + (size_t)c * 2 * NT * kTcKT;
         for (int v = threadIdx.x; v < 2 * NT * kTcKT / 4; v += kTcThreads) cp_async16(reinterpret_cast<float*>(b_hi) + v * 4, src + v * 4, 16);
         float q[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) q[u] = gv[u] * ex2_ftz(fmaf(-a, yv[u], fmaf(a, mv[u], amx)));
+        for (int u = 0; u < 8; ++u) q[u] = gv[u] * ex2_ftz(fmaf(-a, yv[u], mv[u] + amx));
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             float4 hi, lo;
@@ -273,7 +271,7 @@ __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4
 constexpr int kDoKT = 32, kDoLBO = 144;
 
 template <int NT, bool SPATIAL1, bool INTERIOR>
-__global__ void __launch_bounds__(kTcThreads, 2) mex_doff_tc(MexGeo g, const float* __restrict__ x, const float* __restrict__ mo,
+__global__ void __launch_bounds__(kTcThreads, NT == 64 ? 3 : 2) mex_doff_tc(MexGeo g, const float* __restrict__ x, const float* __restrict__ mo,
                                                          const float* __restrict__ mx, const float* __restrict__ y,
                                                          const float* __restrict__ dy, float* __restrict__ part, int splits,
                                                          int* __restrict__ flag) {
@@ -299,7 +297,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) mex_doff_tc(MexGeo g, const flo
     const int M = g.M, K = g.K;
     const int m0 = mt * 128 + warp * 16;                 // this warp's 16 instances
     const int k0 = kt * NT + warp * (NT / 8);            // and its NT / 8 taps
-    const size_t ystep = (size_t)g.N * sizeof(float), gstep = (size_t)g.Ng * sizeof(float);
+    const unsigned Nu = unsigned(g.N), Ngu = unsigned(g.Ng);        // 32-bit element offsets u * N below: 16 * N < 2^31
     const unsigned hw = unsigned(g.H) * unsigned(g.W);
     const bool m_full = m0 + 16 <= M, k_full = k0 + NT / 8 <= K;
 
@@ -309,26 +307,26 @@ __global__ void __launch_bounds__(kTcThreads, 2) mex_doff_tc(MexGeo g, const flo
     auto load = [&](int c) {
         col = column_of(g, r, (c_begin + c) * kDoKT + lane, P, mx);
         const bool live = col.base >= 0;
-        const char* yp = reinterpret_cast<const char*>(y + (live ? col.base : 0)) + (size_t)m0 * ystep;
-        const char* gp = reinterpret_cast<const char*>(dy + (live ? col.gbase : 0)) + (size_t)m0 * gstep;
+        const float* yp = y + (live ? col.base : 0) + (size_t)m0 * Nu;
+        const float* gp = dy + (live ? col.gbase : 0) + (size_t)m0 * Ngu;
         if (m_full) {
 #pragma unroll
             for (int u = 0; u < 16; ++u) {
-                yv[u] = __ldcs(reinterpret_cast<const float*>(yp + u * ystep));
-                gv[u] = live ? __ldcs(reinterpret_cast<const float*>(gp + u * gstep)) : 0.f;     // dy = 0: no contribution
+                yv[u] = __ldcs(yp + u * Nu);
+                gv[u] = live ? __ldcs(gp + u * Ngu) : 0.f;               // dy = 0: no contribution
             }
         } else {
 #pragma unroll
             for (int u = 0; u < 16; ++u) {
                 const bool in = m0 + u < M;
-                yv[u] = in ? __ldcs(reinterpret_cast<const float*>(yp + u * ystep)) : 0.f;
-                gv[u] = (in && live) ? __ldcs(reinterpret_cast<const float*>(gp + u * gstep)) : 0.f;
+                yv[u] = in ? __ldcs(yp + u * Nu) : 0.f;
+                gv[u] = (in && live) ? __ldcs(gp + u * Ngu) : 0.f;
             }
         }
         if (SPATIAL1 && INTERIOR) {
             const float* xp = x + (((size_t)col.n * g.C + col.c0 + k0) * g.H + col.h0) * g.W + col.w0;
 #pragma unroll
-            for (int u = 0; u < NT / 8; ++u) xv[u] = (live && (k_full || k0 + u < K)) ? __ldg(xp + (size_t)u * hw) : 0.f;
+            for (int u = 0; u < NT / 8; ++u) xv[u] = (live && (k_full || k0 + u < K)) ? __ldg(xp + u * hw) : 0.f;
         } else {
             const float* xs = x + (size_t)col.n * g.C * g.H * g.W;
 #pragma unroll
@@ -469,7 +467,7 @@ int mex_tc_doff_splits(const MexGeo& g) {
     const int nt = pick_nt(g.K);
     const long long P = (long long)g.B * g.rs, chunks = (P + kDoKT - 1) / kDoKT;
     const long long tiles = (long long)((g.M + 127) / 128) * ((g.K + nt - 1) / nt) * g.R;
-    const int per_sm = 2;                                        // CTAs per SM (128 registers per thread)
+    const int per_sm = nt == 64 ? 3 : 2;                         // CTAs per SM that the register budget allows
     long long s = (148LL * per_sm * 2) / tiles;                  // about two full waves
     if (s > chunks) s = chunks;
     if (s < 1) s = 1;

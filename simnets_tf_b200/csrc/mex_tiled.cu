@@ -482,7 +482,10 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
     if (tc_shape(g) && !(flags & SIMNETS_FLAG_MEX_NO_TENSORCORE)) {
         e = launch_mex_tc_prep(g, true, w.eot, w.tc_tiles, s);
         if (e != cudaSuccess) return e;
-        e = launch_mex_dx_tc(g, x, w.tc_tiles, w.mo, w.mx, y, dy, dx, w.flag, s);
+        // long patches (wide tap tiles, heavy epilogue): the persistent kernel; otherwise several one-tile CTAs per SM,
+        // all of whose warps evaluate the exponentials, are faster (measured on the three MEX layers of the 3x32x32 net)
+        e = ((flags & SIMNETS_FLAG_MEX_TC_ONE_TILE) || g.K <= 128) ? launch_mex_dx_tc(g, x, w.tc_tiles, w.mo, w.mx, y, dy, dx, w.flag, s)
+                                                                   : launch_mex_dx_ws(g, x, w.tc_tiles, w.mo, w.mx, y, dy, dx, w.flag, s);
         if (e != cudaSuccess) return e;
         return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
     }

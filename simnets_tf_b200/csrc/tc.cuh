@@ -174,6 +174,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Read-only global load that the compiler keeps in program order with the other loads of this kind: the epilogue
+// below wants eight of them in flight per batch, not all thirty-two hoisted to the top (which spills).
+__device__ __forceinline__ float ld_nc_ordered(const float* p) {
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
 // 2^v and log2(v) on the special-function unit, denormals flushed (operands here are sums and ratios of
 // exponentials that stay far above the denormal range)
 __device__ __forceinline__ float ex2_ftz(float v) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v)); return r; }
