@@ -42,6 +42,12 @@ __host__ inline bool tc_shape(const MexGeo& g) {
            (long long)g.H * g.W < (1 << 25);
 }
 
+// Short patches under many instances: the FORWARD is then dominated by writing y, one log per output; on the tensor
+// cores the K multiply-adds per output disappear from the instruction stream, which the streaming kernel cannot match.
+__host__ inline bool tc_fwd_smallk_shape(const MexGeo& g) {
+    return smallk_shape(g) && g.K >= 8 && g.M >= 48 && g.M <= 2048 && g.N < (1 << 26) && (long long)g.H * g.W < (1 << 25);
+}
+
 // no patch reaches outside the input: no padding, and the last patch along each axis ends inside
 __host__ inline bool patches_inside_input(const MexGeo& g) {
     auto inside = [](int dim, int block, int stride, int pad, int out) { return pad == 0 && (out - 1) * stride + block <= dim; };
@@ -89,7 +95,7 @@ __host__ inline MexWs carve(const MexGeo& g, void* base) {
     w.fwd_bytes = off;
     const int max_splits = tc_shape(g) ? std::max(doff_splits(g), mex_tc_doff_splits(g)) : doff_splits(g);
     w.part = reinterpret_cast<float*>(take(sizeof(float) * (size_t)max_splits * g.R * g.M * g.K));
-    w.tc_tiles = reinterpret_cast<float*>(take(tc_shape(g) ? sizeof(float) * mex_tc_tile_floats(g) : 0));
+    w.tc_tiles = reinterpret_cast<float*>(take((tc_shape(g) || tc_fwd_smallk_shape(g)) ? sizeof(float) * mex_tc_tile_floats(g) : 0));
     w.bytes = off;
     return w;
 }

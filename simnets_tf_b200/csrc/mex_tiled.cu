@@ -384,7 +384,8 @@ size_t mex_workspace_bytes(const MexGeo& g, bool f64, uint32_t flags) {
 
 cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* off, float* y, void* ws, uint32_t flags, cudaStream_t s) {
     const MexWs w = carve(g, ws);
-    if (smallk_shape(g)) {
+    const bool tc_ok = !(flags & SIMNETS_FLAG_MEX_NO_TENSORCORE);
+    if (smallk_shape(g) && !(tc_ok && tc_fwd_smallk_shape(g) && !(flags & SIMNETS_FLAG_MEX_TC_ONE_TILE))) {
         cudaError_t e = run_prepasses(g, w, x, off, s, false);
         if (e != cudaSuccess) return e;
         e = launch_mex_fwd_smallk(g, x, w.eo, w.mo, y, w.flag, s);
@@ -400,7 +401,7 @@ cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* o
     }
     cudaError_t e = run_prepasses(g, w, x, off, s);
     if (e != cudaSuccess) return e;
-    if (tc_shape(g) && !(flags & SIMNETS_FLAG_MEX_NO_TENSORCORE)) {
+    if ((tc_shape(g) || tc_fwd_smallk_shape(g)) && tc_ok) {
         e = launch_mex_tc_prep(g, false, w.eo, w.tc_tiles, s);
         if (e != cudaSuccess) return e;
         e = (flags & SIMNETS_FLAG_MEX_TC_ONE_TILE) ? launch_mex_fwd_tc(g, x, w.tc_tiles, w.mo, w.mx, y, w.flag, patches_inside_input(g), s)

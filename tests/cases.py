@@ -166,6 +166,7 @@ def _mex_small():
     cases.append(mex_case("tc_spatial_padded", (2, 32, 9, 9), 50, (16, 2, 2), (16, 2, 2), (0, 1, 1), eps=-1.25, oob=0.3, softmax=True,
                           unshared_region=(2,), seed=320))
     cases.append(mex_case("tc_long_patches", (2, 128, 6, 6), 100, (128, 1, 1), (128, 1, 1), softmax=True, unshared_region=(2,), seed=321, normalize=True))
+    cases.append(mex_case("tc_longer_patches", (3, 160, 4, 4), 56, (160, 1, 1), (160, 1, 1), softmax=True, eps=0.7, unshared_region=(2,), seed=322, normalize=True))
     # few instances over long patches (classifier-head shape): overlapping, padded blocks and disjoint blocks with a remainder
     cases.append(mex_case("head_overlap", (3, 16, 9, 9), 5, (16, 5, 5), (16, 2, 2), (0, 1, 1), softmax=True, unshared_region=(2,), seed=313))
     cases.append(mex_case("head_disjoint", (3, 16, 9, 9), 7, (16, 4, 4), (16, 4, 4), eps=2.0, unshared=False, shared_region=(1,), seed=314, normalize=True))
@@ -179,6 +180,7 @@ MEX_CONFIGS = [
     mex_case("cfg4_mex_sub", (2, 256, 32, 32), 256, (4, 2, 2), (4, 2, 2), eps=0.5, softmax=True, unshared=False, shared_region=(-1,), seed=3),
     mex_case("cfg5_mex2_sub", (4, 128, 16, 16), 256, (128, 1, 1), (128, 1, 1), softmax=True, unshared_region=(2,), seed=4, normalize=True),
     mex_case("cfg5_mex1_sub", (4, 64, 32, 32), 128, (64, 1, 1), (64, 1, 1), softmax=True, unshared_region=(2,), seed=5, normalize=True),
+    mex_case("cfg5_mex3_sub", (4, 256, 8, 8), 512, (256, 1, 1), (256, 1, 1), softmax=True, unshared_region=(2,), seed=7, normalize=True),
     mex_case("tc_many_tiles", (8, 48, 50, 50), 48, (48, 1, 1), (48, 1, 1), softmax=True, unshared=False, shared_region=(-1,), seed=6, normalize=True),
     mex_case("cfg5_head_sub", (4, 512, 4, 4), 10, (512, 4, 4), (1, 1, 1), softmax=True, seed=4, normalize=True),
 ]

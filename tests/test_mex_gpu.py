@@ -30,6 +30,13 @@ def test_small_grid_exact_evaluation(port, c):
     gpu_util.check_mex(port, c, flags=abi.FLAG_MEX_EXACT, f64_tiebreak=True)
 
 
+@pytest.mark.parametrize("c", [c for c in cases.MEX_SMALL + cases.MEX_CONFIGS if c["name"].startswith(("tc_", "cfg5_mex"))],
+                         ids=lambda c: c["name"])
+def test_tensor_core_shapes_one_tile_kernels(port, c):
+    """The one-tile-per-CTA tensor-core kernels (SIMNETS_FLAG_MEX_TC_ONE_TILE) must agree with the oracle as well."""
+    gpu_util.check_mex(port, c, flags=abi.FLAG_MEX_TC_ONE_TILE, f64_tiebreak=True)
+
+
 @pytest.mark.parametrize("c", cases.MEX_SMALL[::3], ids=lambda c: c["name"])
 def test_small_grid_float64(port, c):
     gpu_util.check_mex(port, c, dtype=abi.F64, tol=1e-12)
