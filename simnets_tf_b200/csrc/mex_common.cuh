@@ -42,9 +42,10 @@ __host__ inline bool tc_shape(const MexGeo& g) {
            (long long)g.H * g.W < (1 << 25);
 }
 
-// Short patches under many instances: the FORWARD is then dominated by writing y, one log per output; on the tensor
-// cores the K multiply-adds per output disappear from the instruction stream, which the streaming kernel cannot match.
-__host__ inline bool tc_fwd_smallk_shape(const MexGeo& g) {
+// Short patches under many instances: the passes are dominated by writing y or reading y and dy, one exp or log per
+// element; on the tensor cores the K multiply-adds per element disappear from the instruction stream, which the
+// streaming kernels of mex_smallk.cu cannot match (measured on a 4x2x2-block, 256-instance layer).
+__host__ inline bool tc_smallk_shape(const MexGeo& g) {
     return smallk_shape(g) && g.K >= 8 && g.M >= 48 && g.M <= 2048 && g.N < (1 << 26) && (long long)g.H * g.W < (1 << 25);
 }
 
@@ -82,6 +83,12 @@ __host__ inline int doff_splits(const MexGeo& g) {
     return int(s);
 }
 
+// which family a launch takes
+__host__ inline bool use_tc_kernels(const MexGeo& g, uint32_t flags) {
+    return !(flags & SIMNETS_FLAG_MEX_NO_TENSORCORE) && (tc_shape(g) || tc_smallk_shape(g));
+}
+__host__ inline bool use_smallk_kernels(const MexGeo& g, uint32_t flags) { return smallk_shape(g) && !use_tc_kernels(g, flags); }
+
 __host__ inline MexWs carve(const MexGeo& g, void* base) {
     MexWs w;
     char* p = static_cast<char*>(base);
@@ -93,9 +100,9 @@ __host__ inline MexWs carve(const MexGeo& g, void* base) {
     w.eot = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.K * pad4(g.M)));
     w.mx = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.B * g.N));
     w.fwd_bytes = off;
-    const int max_splits = tc_shape(g) ? std::max(doff_splits(g), mex_tc_doff_splits(g)) : doff_splits(g);
+    const int max_splits = (tc_shape(g) || tc_smallk_shape(g)) ? std::max(doff_splits(g), mex_tc_doff_splits(g)) : doff_splits(g);
     w.part = reinterpret_cast<float*>(take(sizeof(float) * (size_t)max_splits * g.R * g.M * g.K));
-    w.tc_tiles = reinterpret_cast<float*>(take((tc_shape(g) || tc_fwd_smallk_shape(g)) ? sizeof(float) * mex_tc_tile_floats(g) : 0));
+    w.tc_tiles = reinterpret_cast<float*>(take((tc_shape(g) || tc_smallk_shape(g)) ? sizeof(float) * mex_tc_tile_floats(g) : 0));
     w.bytes = off;
     return w;
 }

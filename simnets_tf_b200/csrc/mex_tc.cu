@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4
         if (m0 + 8 <= M) {
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                yv[u] = __ldcs(yp + u * Nu);
+                yv[u] = live ? __ldcs(yp + u * Nu) : 0.f;               // a dead row must not read a stranger's y: 0 * 2^(big) = NaN
                 gv[u] = live ? __ldcs(gp + u * Ngu) : 0.f;
             }
             const float4 m0123 = *reinterpret_cast<const float4*>(amo_s + m0), m4567 = *reinterpret_cast<const float4*>(amo_s + m0 + 4);
@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const bool in = m0 + u < M;
-                yv[u] = in ? __ldcs(yp + u * Nu) : 0.f;
+                yv[u] = (in && live) ? __ldcs(yp + u * Nu) : 0.f;
                 gv[u] = (in && live) ? __ldcs(gp + u * Ngu) : 0.f;      // dy = 0: no contribution
                 mv[u] = amo_s[m0 + u];
             }
@@ -312,14 +312,14 @@ __global__ void __launch_bounds__(kTcThreads, NT == 64 ? 3 : 2) mex_doff_tc(MexG
         if (m_full) {
 #pragma unroll
             for (int u = 0; u < 16; ++u) {
-                yv[u] = __ldcs(yp + u * Nu);
+                yv[u] = live ? __ldcs(yp + u * Nu) : 0.f;               // a dead row must not read a stranger's y: 0 * 2^(big) = NaN
                 gv[u] = live ? __ldcs(gp + u * Ngu) : 0.f;               // dy = 0: no contribution
             }
         } else {
 #pragma unroll
             for (int u = 0; u < 16; ++u) {
                 const bool in = m0 + u < M;
-                yv[u] = in ? __ldcs(yp + u * Nu) : 0.f;
+                yv[u] = (in && live) ? __ldcs(yp + u * Nu) : 0.f;
                 gv[u] = (in && live) ? __ldcs(gp + u * Ngu) : 0.f;
             }
         }

@@ -372,14 +372,14 @@ __global__ void __launch_bounds__(kWsThreads, 1) mex_dx_ws(MexGeo g, const float
             if (m0 + kTcKT <= M) {
 #pragma unroll
                 for (int u = 0; u < kTcKT; ++u) {
-                    yv[u] = __ldcs(yp + u * Nu);
+                    yv[u] = live ? __ldcs(yp + u * Nu) : 0.f;               // a dead row must not read a stranger's y: 0 * 2^(big) = NaN
                     gv[u] = live ? __ldcs(gp + u * Ngu) : 0.f;                // dy = 0: no contribution
                 }
             } else {
 #pragma unroll
                 for (int u = 0; u < kTcKT; ++u) {
                     const bool in = m0 + u < M;
-                    yv[u] = in ? __ldcs(yp + u * Nu) : 0.f;
+                    yv[u] = (in && live) ? __ldcs(yp + u * Nu) : 0.f;
                     gv[u] = (in && live) ? __ldcs(gp + u * Ngu) : 0.f;
                 }
             }

@@ -384,8 +384,7 @@ size_t mex_workspace_bytes(const MexGeo& g, bool f64, uint32_t flags) {
 
 cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* off, float* y, void* ws, uint32_t flags, cudaStream_t s) {
     const MexWs w = carve(g, ws);
-    const bool tc_ok = !(flags & SIMNETS_FLAG_MEX_NO_TENSORCORE);
-    if (smallk_shape(g) && !(tc_ok && tc_fwd_smallk_shape(g) && !(flags & SIMNETS_FLAG_MEX_TC_ONE_TILE))) {
+    if (use_smallk_kernels(g, flags)) {
         cudaError_t e = run_prepasses(g, w, x, off, s, false);
         if (e != cudaSuccess) return e;
         e = launch_mex_fwd_smallk(g, x, w.eo, w.mo, y, w.flag, s);
@@ -401,7 +400,7 @@ cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* o
     }
     cudaError_t e = run_prepasses(g, w, x, off, s);
     if (e != cudaSuccess) return e;
-    if ((tc_shape(g) || tc_fwd_smallk_shape(g)) && tc_ok) {
+    if (use_tc_kernels(g, flags)) {
         e = launch_mex_tc_prep(g, false, w.eo, w.tc_tiles, s);
         if (e != cudaSuccess) return e;
         e = (flags & SIMNETS_FLAG_MEX_TC_ONE_TILE) ? launch_mex_fwd_tc(g, x, w.tc_tiles, w.mo, w.mx, y, w.flag, patches_inside_input(g), s)
@@ -468,19 +467,19 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
                                 void* ws, uint32_t flags, cudaStream_t s, bool prepped) {
     if (!blocks_disjoint(g)) return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, nullptr);
     const MexWs w = carve(g, ws);
-    const bool small = smallm_shape(g) || smallk_shape(g);
+    const bool small = smallm_shape(g) || use_smallk_kernels(g, flags);
     cudaError_t e = prepped ? cudaSuccess : run_prepasses(g, w, x, off, s, !small);
     if (e != cudaSuccess) return e;
     if (!blocks_cover_input(g)) {
         e = cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)g.B * g.C * g.H * g.W, s);
         if (e != cudaSuccess) return e;
     }
-    if (smallk_shape(g)) {
+    if (use_smallk_kernels(g, flags)) {
         e = launch_mex_dx_smallk(g, x, w.eo, w.mo, y, dy, dx, w.flag, s);
         if (e != cudaSuccess) return e;
         return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
     }
-    if (tc_shape(g) && !(flags & SIMNETS_FLAG_MEX_NO_TENSORCORE)) {
+    if (use_tc_kernels(g, flags)) {
         e = launch_mex_tc_prep(g, true, w.eot, w.tc_tiles, s);
         if (e != cudaSuccess) return e;
         // long patches (wide tap tiles, heavy epilogue): the persistent kernel; otherwise several one-tile CTAs per SM,
@@ -513,9 +512,9 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
 cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* doff,
                                   bool accumulate, void* ws, uint32_t flags, cudaStream_t s, bool prepped) {
     const MexWs w = carve(g, ws);
-    cudaError_t e = prepped ? cudaSuccess : run_prepasses(g, w, x, off, s, !smallk_shape(g));
+    cudaError_t e = prepped ? cudaSuccess : run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags));
     if (e != cudaSuccess) return e;
-    if (tc_shape(g) && !(flags & SIMNETS_FLAG_MEX_NO_TENSORCORE)) {
+    if (use_tc_kernels(g, flags)) {
         const int tsplits = mex_tc_doff_splits(g);
         e = launch_mex_doff_tc(g, x, w.mo, w.mx, y, dy, w.part, tsplits, w.flag, s);
         if (e != cudaSuccess) return e;
@@ -527,7 +526,7 @@ cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* 
         return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
     }
     const int splits = doff_splits(g);
-    if (smallk_shape(g)) {
+    if (use_smallk_kernels(g, flags)) {
         e = launch_mex_doff_smallk(g, x, w.mo, y, dy, w.part, splits, w.flag, s);
         if (e != cudaSuccess) return e;
         const long long n = (long long)g.R * g.M * g.K;
@@ -566,7 +565,7 @@ cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* 
 cudaError_t launch_mex_backward_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* dx,
                                       float* doff, bool accumulate, void* ws, uint32_t flags, cudaStream_t s) {
     const MexWs w = carve(g, ws);
-    cudaError_t e = run_prepasses(g, w, x, off, s, !smallk_shape(g));
+    cudaError_t e = run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags));
     if (e != cudaSuccess) return e;
     e = launch_mex_dx_tiled(g, x, off, y, dy, dx, ws, flags, s, true);
     if (e != cudaSuccess) return e;

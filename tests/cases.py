@@ -181,6 +181,7 @@ MEX_CONFIGS = [
     mex_case("cfg5_mex2_sub", (4, 128, 16, 16), 256, (128, 1, 1), (128, 1, 1), softmax=True, unshared_region=(2,), seed=4, normalize=True),
     mex_case("cfg5_mex1_sub", (4, 64, 32, 32), 128, (64, 1, 1), (64, 1, 1), softmax=True, unshared_region=(2,), seed=5, normalize=True),
     mex_case("cfg5_mex3_sub", (4, 256, 8, 8), 512, (256, 1, 1), (256, 1, 1), softmax=True, unshared_region=(2,), seed=7, normalize=True),
+    mex_case("cfg3_mex4_sub", (6, 256, 2, 2), 512, (256, 1, 1), (256, 1, 1), softmax=True, unshared_region=(2,), seed=8, normalize=True),
     mex_case("tc_many_tiles", (8, 48, 50, 50), 48, (48, 1, 1), (48, 1, 1), softmax=True, unshared=False, shared_region=(-1,), seed=6, normalize=True),
     mex_case("cfg5_head_sub", (4, 512, 4, 4), 10, (512, 4, 4), (1, 1, 1), softmax=True, seed=4, normalize=True),
 ]

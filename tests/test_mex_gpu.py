@@ -132,6 +132,25 @@ def test_mex_sum_pool2_equals_mex_then_pooling():
     assert cases.rel_err(outs[0][2].cpu().numpy(), outs[1][2].cpu().numpy()) < 1e-6
 
 
+def test_rows_past_the_last_position_do_not_leak(port):
+    """A region with fewer positions than a tile leaves tile rows without a position.  Such a row once read the y of
+    an unrelated position while its dy was forced to 0; with outputs around -400 that is 0 * 2^(+577) = NaN in the
+    offsets gradient.  Inputs shifted far from zero make the leak visible."""
+    c = next(c for c in cases.MEX_CONFIGS if c["name"] == "cfg3_mex4_sub")
+    d = cases.mex_desc(c)
+    x, off, dy = cases.mex_inputs(c, port.mex_offsets_shape(d), port.mex_out_shape(d))
+    x = (x - 400.0).astype(np.float32)
+    ry = port.mex_forward(d, x, off)
+    assert ry.max() < -300
+    xd, od, dyd, ryd = (gpu_util.dev(a) for a in (x, off, dy, ry))
+    attrs = cases.mex_attrs(c)
+    for flags in (0, abi.FLAG_MEX_TC_ONE_TILE):
+        dx, doff = mex_ops.mex_backward(xd, od, ryd, dyd, c["M"], flags=flags, **attrs)
+        cases.assert_parity(dx.cpu().numpy(), port.mex_input_grad(d, x, off, ry, dy), tol=2e-5, what="dx")
+        cases.assert_parity(doff.cpu().numpy(), port.mex_offsets_grad(d, x, off, ry, dy), tol=2e-5, what="doff")
+        cases.assert_parity(mex_ops.mex_forward(xd, od, c["M"], flags=flags, **attrs).cpu().numpy(), ry, what="y")
+
+
 def test_wide_dynamic_range_takes_the_exact_route(port):
     """Offsets and inputs spanning hundreds of units (and -inf entries) would underflow a factorised
     evaluation; results must still match the oracle, whichever route the library picks."""
