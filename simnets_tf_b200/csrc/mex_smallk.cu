@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(kT, 2) mex_dx_smallk(MexGeo g, const float* __
                 const long long row = (long long)(m0 + mb + u) * g.N;
 #pragma unroll
                 for (int c = 0; c < C; ++c) {
-                    yv[u][c] = ok ? __ldcs(y + sbase[c] + row) : 0.f;
+                    yv[u][c] = (ok && livef[c] != 0.f) ? __ldcs(y + sbase[c] + row) : 0.f;     // a dead position must not read a stranger's y (0 * exp(big) = NaN)
                     gv[u][c] = ok ? __ldcs(dy + sbase[c] + row) : 0.f;
                 }
             }
