@@ -14,6 +14,7 @@ restatement) on the host cores, on a bounded sample of the same workload per ste
 import argparse
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -29,6 +30,9 @@ GLOBAL_BATCH = {"cfg5": 2048, "cfg3": 256}
 DATA_SEED = {"cfg5": 4, "cfg3": 2}
 FALLBACK_HBM_GBS = 6650.0          # earlier measurement on this pool, used only without MEASURED_PEAKS.json
 NOMINAL_FP32_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
+# dram__bytes_read.sum + dram__bytes_write.sum of one whole library call, per sample, from ncu at batch 512
+# (kernel by kernel in profiles/mex_backward_cfg5_mex1.md); key = operator signature without its batch
+NCU_DRAM_BYTES_PER_SAMPLE = {"mex_backward[C64 32x32 M128 K64 N1024 R4 dy/4]": 1249.5e6 / 512}
 
 
 def make_data(workload, spec):
@@ -300,8 +304,13 @@ def run_ours(args):
                       "Gterms_per_s": round(r["terms"] / r["calls"] / (avg_ms * 1e-3) / 1e9, 2)})
     table.sort(key=lambda r: -r["ms_total"])
     top = table[0]
+    # DRAM traffic of the dominant call from one ncu capture at a smaller batch, scaled to this batch (every byte these
+    # kernels touch belongs to one sample); null for an op that has no capture
+    m = re.match(r"(\w+)\[B(\d+) (.*)\]$", top["op"])
+    per_sample = NCU_DRAM_BYTES_PER_SAMPLE.get("%s[%s]" % (m.group(1), m.group(3))) if m else None
+    traffic = int(per_sample * int(m.group(2))) if per_sample else None
     roofline = {"kernel": top["op"], "bound": "hbm", "achieved": top["GBps"], "peak": hbm_peak, "unit": "GB/s",
-                "frac": round(top["GBps"] / hbm_peak, 4), "peak_source": "of " + peak_src, "traffic": None,
+                "frac": round(top["GBps"] / hbm_peak, 4), "peak_source": "of " + peak_src, "traffic": traffic,
                 "share_of_step": round(top["ms_total"] / ms, 4),
                 "fp32": {"Gterms_per_s": top["Gterms_per_s"], "nominal_fp32_tflops": round(NOMINAL_FP32_TFLOPS, 2)}}
 
