@@ -345,7 +345,11 @@ def main():
     ap.add_argument("--ref-sample", type=int, default=0, help="samples per reference step (default: one per host core, at least 8)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying one CUDA graph")
+    ap.add_argument("--global-batch", type=int, default=0,
+                    help="diagnostics only: another global batch than the configuration's (e.g. 256 on one GPU = the per-GPU share of 8)")
     args = ap.parse_args()
+    if args.global_batch:
+        GLOBAL_BATCH[args.workload] = args.global_batch
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":

@@ -236,6 +236,16 @@ SIMNETS_API int simnets_mex_backward(const simnets_mex_desc* d,
                                      const void* x, const void* offsets, const void* y, const void* dy,
                                      void* dx, void* doffsets, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- sum pooling ----------------------------------------------------------- */
+/* y[p, h, w] = x[p, 2h, 2w] + x[p, 2h, 2w+1] + x[p, 2h+1, 2w] + x[p, 2h+1, 2w+1] over a dense float32 tensor
+ * [planes, height, width] (planes = batch * channels); height and width even, else SIMNETS_E_UNSUPPORTED.
+ * The 2x2 sum pooling the reference's example networks put behind every MEX layer (README.md:114-131, there
+ * `4 * AveragePooling2D(2)`).  No counterpart in the reference's own sources: its graphs use TensorFlow's pooling
+ * op.  Its gradient is not an entry point: the MEX gradient entry points take the pooled dy directly
+ * (SIMNETS_FLAG_MEX_DY_POOLED2). */
+SIMNETS_API int simnets_sum_pool2x2_forward(int64_t planes, int32_t height, int32_t width,
+                                            const void* x, void* y, void* stream);
+
 /* ---- misc ----------------------------------------------------------------- */
 SIMNETS_API const char* simnets_status_string(int status);
 /* Number of kernels this library has launched in this process (all devices). */

