@@ -246,6 +246,15 @@ SIMNETS_API int simnets_mex_backward(const simnets_mex_desc* d,
 SIMNETS_API int simnets_sum_pool2x2_forward(int64_t planes, int32_t height, int32_t width,
                                             const void* x, void* y, void* stream);
 
+/* ---- normalize_offsets ------------------------------------------------------ */
+/* The `normalize_offsets` option of the reference's Keras Mex layer (python/simnets/keras.py:155-160): each of the
+ * `rows` = num_regions * num_instances rows of `k` = block_c * block_h * block_w float32 offsets minus its log-sum-exp;
+ * and the gradient of that map, doffsets = dout - softmax(offsets) * sum(dout) per row.  In the reference this is a
+ * chain of TensorFlow ops around the Mex op, so there is no counterpart in its C++ sources. */
+SIMNETS_API int simnets_normalize_offsets_forward(int64_t rows, int32_t k, const void* offsets, void* out, void* stream);
+SIMNETS_API int simnets_normalize_offsets_backward(int64_t rows, int32_t k, const void* offsets, const void* dout,
+                                                   void* doffsets, void* stream);
+
 /* ---- misc ----------------------------------------------------------------- */
 SIMNETS_API const char* simnets_status_string(int status);
 /* Number of kernels this library has launched in this process (all devices). */

@@ -47,6 +47,8 @@ def lib():
         l.simnets_mex_input_grad.argtypes = [md, _P, _P, _P, _P, _P, _P, C.c_size_t, _P]
         l.simnets_mex_offsets_grad.argtypes = [md, _P, _P, _P, _P, _P, _P, C.c_size_t, _P]
         l.simnets_mex_backward.argtypes = [md, _P, _P, _P, _P, _P, _P, _P, C.c_size_t, _P]
+        l.simnets_normalize_offsets_forward.argtypes = [C.c_int64, C.c_int32, _P, _P, _P]
+        l.simnets_normalize_offsets_backward.argtypes = [C.c_int64, C.c_int32, _P, _P, _P, _P]
         l.simnets_sum_pool2x2_forward.argtypes = [C.c_int64, C.c_int32, C.c_int32, _P, _P, _P]
         l.get_mex_offsets_nregions.restype = C.c_int
         _lib = l

@@ -215,6 +215,18 @@ int simnets_mex_backward(const simnets_mex_desc* d, const void* x, const void* o
     return from_cuda(launch_mex_doff_direct(g, f64, x, off, y, dy, doff, acc, as_stream(stream)));
 }
 
+int simnets_normalize_offsets_forward(int64_t rows, int32_t k, const void* off, void* out, void* stream) {
+    if (rows < 0 || k < 0) return SIMNETS_E_DESC;
+    if (rows > 0 && k > 0 && (!off || !out)) return SIMNETS_E_NULL;
+    return from_cuda(launch_normalize_offsets_fwd(rows, k, (const float*)off, (float*)out, as_stream(stream)));
+}
+
+int simnets_normalize_offsets_backward(int64_t rows, int32_t k, const void* off, const void* dout, void* doff, void* stream) {
+    if (rows < 0 || k < 0) return SIMNETS_E_DESC;
+    if (rows > 0 && k > 0 && (!off || !dout || !doff)) return SIMNETS_E_NULL;
+    return from_cuda(launch_normalize_offsets_bwd(rows, k, (const float*)off, (const float*)dout, (float*)doff, as_stream(stream)));
+}
+
 int simnets_sum_pool2x2_forward(int64_t planes, int32_t height, int32_t width, const void* x, void* y, void* stream) {
     if (planes < 0 || height < 0 || width < 0) return SIMNETS_E_DESC;
     if (height % 2 || width % 2) return SIMNETS_E_UNSUPPORTED;

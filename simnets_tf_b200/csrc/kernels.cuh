@@ -9,6 +9,10 @@ namespace simnets {
 
 void count_launch(int n = 1);
 
+// offsets_norm.cu
+cudaError_t launch_normalize_offsets_fwd(long long rows, int K, const float* off, float* out, cudaStream_t);
+cudaError_t launch_normalize_offsets_bwd(long long rows, int K, const float* off, const float* dout, float* doff, cudaStream_t);
+
 // pool.cu
 cudaError_t launch_sum_pool2(long long planes, int H, int W, const float* x, float* y, cudaStream_t);
 

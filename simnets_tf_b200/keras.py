@@ -109,6 +109,35 @@ class DirichletInit(object):
 dirichlet_init = DirichletInit
 
 
+class _NormalizeOffsets(torch.autograd.Function):
+    """offsets[r, m, ...] minus the log-sum-exp over the block (the `normalize_offsets` option)."""
+
+    @staticmethod
+    def forward(ctx, offsets):
+        from . import _lib
+        from ._torch_glue import stream_ptr
+        off = offsets.contiguous()
+        rows, k = off.shape[0] * off.shape[1], off[0, 0].numel()
+        out = torch.empty_like(off)
+        with torch.cuda.device(off.device):
+            _lib.check(_lib.lib().simnets_normalize_offsets_forward(rows, k, off.data_ptr(), out.data_ptr(), stream_ptr(off.device)))
+        ctx.save_for_backward(off)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        from . import _lib
+        from ._torch_glue import stream_ptr
+        off, = ctx.saved_tensors
+        grad = grad.contiguous()
+        rows, k = off.shape[0] * off.shape[1], off[0, 0].numel()
+        doff = torch.empty_like(off)
+        with torch.cuda.device(off.device):
+            _lib.check(_lib.lib().simnets_normalize_offsets_backward(rows, k, off.data_ptr(), grad.data_ptr(), doff.data_ptr(),
+                                                                     stream_ptr(off.device)))
+        return doff
+
+
 class Mex(torch.nn.Module):
     """MEX layer; `normalize_offsets` subtracts a per-(region, instance) logsumexp from the offsets variable."""
 
@@ -159,6 +188,8 @@ class Mex(torch.nn.Module):
     def effective_offsets(self):
         if not self.normalize_offsets:
             return self.offsets
+        if self.offsets.is_cuda and self.offsets.dtype == torch.float32:
+            return _NormalizeOffsets.apply(self.offsets)             # one library kernel each way
         flat = self.offsets.reshape(self.offsets.shape[0] * self.offsets.shape[1], -1)
         return (flat - torch.logsumexp(flat, dim=1, keepdim=True)).reshape(self.offsets.shape)
 

@@ -127,6 +127,30 @@ def test_sum_pool2x2_kernel(shape):
         assert torch.allclose(mex_ops.sum_pool2x2(flat), torch.nn.functional.avg_pool2d(flat, 2) * 4.0, rtol=1e-6, atol=1e-6)
 
 
+@pytest.mark.parametrize("shape", [(4, 5, 3, 2, 2), (1, 1, 1, 1, 1), (2, 10, 8192, 1, 1), (3, 7, 33, 1, 1), (0, 4, 2, 1, 1)])
+def test_normalize_offsets_kernels(shape):
+    """The library's normalize_offsets (forward and gradient) against the composed torch expression, in float64."""
+    from simnets_tf_b200 import keras as layers
+    torch.manual_seed(2)
+    off = torch.randn(*shape, device="cuda") * 3
+    if off.numel() > 8:
+        off.view(-1)[3] = float("-inf")                    # a log-space zero probability
+    a = off.clone().requires_grad_(True)
+    out = layers._NormalizeOffsets.apply(a)
+    b = off.double().clone().requires_grad_(True)
+    flat = b.reshape(shape[0] * shape[1], -1)
+    want = (flat - torch.logsumexp(flat, dim=1, keepdim=True)).reshape(shape)
+    assert out.shape == want.shape
+    fin = torch.isfinite(want)
+    assert torch.equal(torch.isfinite(out), fin)
+    assert torch.allclose(out[fin].double(), want[fin], rtol=1e-6, atol=1e-6)
+    g = torch.randn(*shape, device="cuda")
+    out.backward(g)
+    want.backward(g.double())
+    if off.numel():
+        assert torch.allclose(a.grad.double(), b.grad, rtol=1e-5, atol=1e-6)
+
+
 def test_mex_sum_pool2_equals_mex_then_pooling():
     """The fused MEX + 2x2 sum pooling op: same forward bits, same gradients as the two ops chained."""
     torch.manual_seed(3)
