@@ -117,7 +117,7 @@ class _NormalizeOffsets(torch.autograd.Function):
         from . import _lib
         from ._torch_glue import stream_ptr
         off = offsets.contiguous()
-        rows, k = off.shape[0] * off.shape[1], off[0, 0].numel()
+        rows, k = off.shape[0] * off.shape[1], int(math.prod(off.shape[2:]))
         out = torch.empty_like(off)
         with torch.cuda.device(off.device):
             _lib.check(_lib.lib().simnets_normalize_offsets_forward(rows, k, off.data_ptr(), out.data_ptr(), stream_ptr(off.device)))
@@ -130,7 +130,7 @@ class _NormalizeOffsets(torch.autograd.Function):
         from ._torch_glue import stream_ptr
         off, = ctx.saved_tensors
         grad = grad.contiguous()
-        rows, k = off.shape[0] * off.shape[1], off[0, 0].numel()
+        rows, k = off.shape[0] * off.shape[1], int(math.prod(off.shape[2:]))
         doff = torch.empty_like(off)
         with torch.cuda.device(off.device):
             _lib.check(_lib.lib().simnets_normalize_offsets_backward(rows, k, off.data_ptr(), grad.data_ptr(), doff.data_ptr(),
