@@ -138,7 +138,7 @@ def test_normalize_offsets_kernels(shape):
     a = off.clone().requires_grad_(True)
     out = layers._NormalizeOffsets.apply(a)
     b = off.double().clone().requires_grad_(True)
-    flat = b.reshape(shape[0] * shape[1], -1)
+    flat = b.reshape(shape[0] * shape[1], shape[2] * shape[3] * shape[4])
     want = (flat - torch.logsumexp(flat, dim=1, keepdim=True)).reshape(shape)
     assert out.shape == want.shape
     fin = torch.isfinite(want)
