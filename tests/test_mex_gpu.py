@@ -183,11 +183,17 @@ def test_rows_past_the_last_position_do_not_leak(port):
     assert ry.max() < -300
     xd, od, dyd, ryd = (gpu_util.dev(a) for a in (x, off, dy, ry))
     attrs = cases.mex_attrs(c)
+    # inputs near -400 carry 3e-5 of float32 spacing, so the float32 oracle is itself that far from exact arithmetic:
+    # judge against the float64 oracle as the acceptance rule allows
+    d64 = cases.mex_desc(c, dtype=abi.F64)
+    x64, o64, dy64 = (a.astype(np.float64) for a in (x, off, dy))
+    y64 = port.mex_forward(d64, x64, o64)
+    dx64, doff64 = port.mex_input_grad(d64, x64, o64, y64, dy64), port.mex_offsets_grad(d64, x64, o64, y64, dy64)
     for flags in (0, abi.FLAG_MEX_TC_ONE_TILE):
         dx, doff = mex_ops.mex_backward(xd, od, ryd, dyd, c["M"], flags=flags, **attrs)
-        cases.assert_parity(dx.cpu().numpy(), port.mex_input_grad(d, x, off, ry, dy), tol=2e-5, what="dx")
-        cases.assert_parity(doff.cpu().numpy(), port.mex_offsets_grad(d, x, off, ry, dy), tol=2e-5, what="doff")
-        cases.assert_parity(mex_ops.mex_forward(xd, od, c["M"], flags=flags, **attrs).cpu().numpy(), ry, what="y")
+        cases.assert_parity(dx.cpu().numpy(), port.mex_input_grad(d, x, off, ry, dy), dx64, tol=2e-5, what="dx")
+        cases.assert_parity(doff.cpu().numpy(), port.mex_offsets_grad(d, x, off, ry, dy), doff64, tol=2e-5, what="doff")
+        cases.assert_parity(mex_ops.mex_forward(xd, od, c["M"], flags=flags, **attrs).cpu().numpy(), ry, y64, what="y")
 
 
 def test_wide_dynamic_range_takes_the_exact_route(port):
