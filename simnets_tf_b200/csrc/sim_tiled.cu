@@ -41,7 +41,7 @@ __host__ int dp_splits(const SimGeo& g) {
     const long long chunks = (P + kDpKC - 1) / kDpKC;
     const long long tiles = (long long)((g.M + kDpTile - 1) / kDpTile) * ((g.K + dp_tn(g) - 1) / dp_tn(g));
     // the narrow tile runs four CTAs of 128 threads per SM (128 registers per thread): two waves of those
-    const int ctas = dp_tn(g) == 32 ? 148 * 8 : 148 * 2;
+    const int ctas = dp_tn(g) == 32 ? 148 * 8 : 148 * 4;                  // (the wide tile: two CTAs of 256 threads per SM)
     long long s = (ctas + tiles - 1) / tiles;
     if (s > chunks) s = chunks;
     if (s < 1) s = 1;
@@ -228,7 +228,7 @@ __global__ void __launch_bounds__(256, TM == 128 ? 2 : 1) sim_fwd_tiled(SimGeo g
 // Accumulators per output (m, k): sT = sum a*d, sW = sum a*d*d (L1: a*sign(d), a*|d|), sN = sum a*mask,
 // with a = dy and d = mask*(x - t).  Both operands are contiguous along q (positions) in memory.
 template <int MODE, int TN>
-__global__ void __launch_bounds__(TN * 4, TN == 32 ? 4 : 1) sim_dparams_tiled(SimGeo g, const float* __restrict__ x, const float* __restrict__ tm,
+__global__ void __launch_bounds__(TN * 4, TN == 32 ? 4 : 2) sim_dparams_tiled(SimGeo g, const float* __restrict__ x, const float* __restrict__ tm,
                                                          const float* __restrict__ dy, const int2* __restrict__ taps,
                                                          float* __restrict__ part, int splits) {
     constexpr bool MASKED = MODE == SIM_L2N_NAN || MODE == SIM_L1_SKIP;
