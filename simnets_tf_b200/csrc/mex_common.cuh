@@ -133,6 +133,32 @@ __device__ __forceinline__ int interior_index(const MexGeo& g, int c0, int h0, i
     return ((c0 + t.c) * g.H + h0 + t.h) * g.W + w0 + t.w;
 }
 
+// Decoded taps of a block in shared memory: decoding tap k of a c x h x w block costs two divisions and two modulos,
+// which at short patches (4x2x2 blocks) was most of the instructions of the kernels that gather x tap by tap.
+// Entry = (c << 16) | (h << 8) | w; usable when tap_table_ok(g), filled once per CTA before its first barrier.
+constexpr int kTapTable = 1024;
+__device__ __forceinline__ bool tap_table_ok(const MexGeo& g) { return g.K <= kTapTable && g.bh <= 256 && g.bw <= 256 && g.bc <= 32768; }
+__device__ __forceinline__ void fill_tap_table(const MexGeo& g, int* tab) {
+    if (!tap_table_ok(g)) return;
+    for (int k = threadIdx.x; k < g.K; k += blockDim.x) {
+        const Tap t = tap_of<false>(g, k);
+        tab[k] = (t.c << 16) | (t.h << 8) | t.w;
+    }
+}
+template <bool SPATIAL1>
+__device__ __forceinline__ Tap tap_get(const MexGeo& g, const int* tab, bool tab_ok, int k) {
+    if (SPATIAL1 || !tab_ok) return tap_of<SPATIAL1>(g, k);
+    const int v = tab[k];
+    Tap t; t.c = v >> 16; t.h = (v >> 8) & 255; t.w = v & 255;
+    return t;
+}
+// value of a decoded tap of the patch whose corner is (c0, h0, w0) in sample xs
+__device__ __forceinline__ float patch_value_at(const MexGeo& g, const float* __restrict__ xs, int c0, int h0, int w0, Tap t, float oob) {
+    const int cc = c0 + t.c, hh = h0 + t.h, ww = w0 + t.w;
+    if (cc >= 0 && cc < g.C && hh >= 0 && hh < g.H && ww >= 0 && ww < g.W) return __ldg(xs + ((size_t)cc * g.H + hh) * g.W + ww);
+    return oob;
+}
+
 // Per-column (= one output position of one sample) bookkeeping shared by the tile kernels.
 struct Column {
     long long base;      // n*M*N + pos : offset of y[n, 0, pos]; -1 for a position outside the output grid

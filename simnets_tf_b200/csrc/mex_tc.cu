@@ -141,8 +141,11 @@ __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4
                                                        float* __restrict__ dx, int* __restrict__ flag) {
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ TcShared sh;
-    __shared__ __align__(16) float amo_s[kDxMaxM];        // a * mo + c' of every instance (rounded up to a whole chunk)
+    __shared__ __align__(16) float amo_s[kDxMaxM];        // mo of every instance of the region (rounded up to a whole chunk)
+    __shared__ int tap_tab[SPATIAL1 ? 1 : kTapTable];
     if (flag[0]) return;
+    if (!SPATIAL1) fill_tap_table(g, tap_tab);            // (published by the barrier inside tc_begin)
+    const bool tab_ok = tap_table_ok(g);
     const long long P = (long long)g.B * g.rs;
     const int ktiles = (g.K + NT - 1) / NT, mchunks = (g.M + kTcKT - 1) / kTcKT;
     int bid = blockIdx.x;
@@ -150,15 +153,16 @@ __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4
     const int kt = bid % ktiles;
     const long long jt = bid / ktiles;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Q[j, m] = dy * exp(eps * (mx_j + mo_m - y) + c) = dy * 2^(a * mx_j + (a * mo_m + c') - a * y),  a = eps * log2(e)
+    // Q[j, m] = dy * exp(eps * (mx_j + mo_m - y) + c) = dy * 2^(a * ((mx_j - y) + mo_m) + c'),  a = eps * log2(e).  The
+    // difference mx - y is taken first: both can be hundreds of units from zero while their difference is small.
     const float a = float(g.eps) * 1.4426950408889634f, c2 = float(g.cst) * 1.4426950408889634f;
-    for (int i = threadIdx.x; i < mchunks * kTcKT; i += kTcThreads) amo_s[i] = i < g.M ? fmaf(a, mo[r * g.M + i], c2) : 0.f;
+    for (int i = threadIdx.x; i < mchunks * kTcKT; i += kTcThreads) amo_s[i] = i < g.M ? mo[r * g.M + i] : 0.f;
     const uint32_t tmem_d = tc_begin(sh, NT);             // (its barrier also publishes amo_s)
 
     const int prow = threadIdx.x % kTcPos, mhalf = threadIdx.x / kTcPos;
     const Column sc = column_of(g, r, jt * kTcPos + prow, P, mx);
     const bool live = sc.base >= 0;
-    const float amx = a * sc.mx;
+    const float mxv = sc.mx;
     // Running pointers to (this thread's first instance of the next chunk to load, its position); the eight instances
     // of a chunk are addressed with 32-bit element offsets u * N from them (the launcher checks 16 * N < 2^31).
     const unsigned Nu = unsigned(g.N), Ngu = unsigned(g.Ng);
@@ -196,7 +200,7 @@ __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4
         for (int v = threadIdx.x; v < 2 * NT * kTcKT / 4; v += kTcThreads) cp_async16(reinterpret_cast<float*>(b_hi) + v * 4, src + v * 4, 16);
         float q[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) q[u] = gv[u] * ex2_ftz(fmaf(-a, yv[u], mv[u] + amx));
+        for (int u = 0; u < 8; ++u) q[u] = gv[u] * ex2_ftz(fmaf(a, (mxv - yv[u]) + mv[u], c2));
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             float4 hi, lo;
@@ -212,7 +216,7 @@ __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4
     if (good) {
         const int quarter = warp & 3, half = warp >> 2;
         const Column col = column_of(g, r, jt * kTcPos + quarter * 32 + lane, P, mx);
-        const float b = -a * col.mx;                                   // Ex = 2^(a * x - a * mx)
+        const float emx = col.mx;                                      // Ex = 2^(a * (x - mx))
         if (SPATIAL1 && INTERIOR) {
             // tap k of a 1x1 block that never leaves the input: channel c0 + k of one pixel, planes H * W floats apart
             const unsigned hw = unsigned(g.H) * unsigned(g.W);           // the launcher takes this path only if NT * H * W < 2^31
@@ -233,7 +237,7 @@ __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4
                         for (int i = 0; i < 8; ++i) xr[i] = (i0 + i < kleft) ? ld_nc_ordered(xb + (off + i * hw)) : 0.f;
 #pragma unroll
                         for (int i = 0; i < 8; ++i)
-                            if (i0 + i < kleft) db[off + i * hw] = ex2_ftz(fmaf(xr[i], a, b)) * __uint_as_float(v[i0 + i]);
+                            if (i0 + i < kleft) db[off + i * hw] = ex2_ftz(a * (xr[i] - emx)) * __uint_as_float(v[i0 + i]);
                         off += 8 * hw;
                     }
                 }
@@ -249,11 +253,11 @@ __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4
                     for (int i = 0; i < 32; ++i) {
                         const int k = kt * NT + c0 + i;
                         if (k >= g.K) continue;
-                        const Tap tp = tap_of<SPATIAL1>(g, k);
+                        const Tap tp = tap_get<SPATIAL1>(g, tap_tab, tab_ok, k);
                         const int cc = col.c0 + tp.c, hh = col.h0 + tp.h, ww = col.w0 + tp.w;
                         if (cc < 0 || cc >= g.C || hh < 0 || hh >= g.H || ww < 0 || ww >= g.W) continue;
                         const size_t ad = sample + ((size_t)cc * g.H + hh) * g.W + ww;
-                        dx[ad] = ex2_ftz(fmaf(__ldg(x + ad), a, b)) * __uint_as_float(v[i]);
+                        dx[ad] = ex2_ftz(a * (__ldg(x + ad) - emx)) * __uint_as_float(v[i]);
                     }
                 }
             }
@@ -277,8 +281,11 @@ __global__ void __launch_bounds__(kTcThreads, NT == 64 ? 3 : 2) mex_doff_tc(MexG
                                                          int* __restrict__ flag) {
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ TcShared sh;
-    __shared__ float amo_s[128];                        // a * mo + c' of this CTA's instances
+    __shared__ float amo_s[128];                        // mo of this CTA's instances
+    __shared__ int tap_tab[SPATIAL1 ? 1 : kTapTable];
     if (flag[0]) return;
+    if (!SPATIAL1) fill_tap_table(g, tap_tab);          // (published by the barrier inside tc_begin)
+    const bool tab_ok = tap_table_ok(g);
     const long long P = (long long)g.B * g.rs;
     const int mtiles = (g.M + 127) / 128, ktiles = (g.K + NT - 1) / NT;
     int bid = blockIdx.x;
@@ -289,9 +296,9 @@ __global__ void __launch_bounds__(kTcThreads, NT == 64 ? 3 : 2) mex_doff_tc(MexG
     const long long chunks = (P + kDoKT - 1) / kDoKT;
     const long long c_begin = chunks * split / splits, c_end = chunks * (split + 1) / splits;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Q = dy * 2^(a * mx + (a * mo + c') - a * y),  Ex = 2^(a * x - a * mx),  a = eps * log2(e)
+    // Q = dy * 2^(a * ((mx - y) + mo) + c'),  Ex = 2^(a * (x - mx)),  a = eps * log2(e); differences first (see mex_dx_tc)
     const float a = float(g.eps) * 1.4426950408889634f, c2 = float(g.cst) * 1.4426950408889634f, oob = float(g.oob);
-    if (threadIdx.x < 128) amo_s[threadIdx.x] = (mt * 128 + threadIdx.x < g.M) ? fmaf(a, mo[r * g.M + mt * 128 + threadIdx.x], c2) : 0.f;
+    if (threadIdx.x < 128) amo_s[threadIdx.x] = (mt * 128 + threadIdx.x < g.M) ? mo[r * g.M + mt * 128 + threadIdx.x] : 0.f;
     const uint32_t tmem_d = tc_begin(sh, NT);
 
     const int M = g.M, K = g.K;
@@ -331,18 +338,18 @@ __global__ void __launch_bounds__(kTcThreads, NT == 64 ? 3 : 2) mex_doff_tc(MexG
             const float* xs = x + (size_t)col.n * g.C * g.H * g.W;
 #pragma unroll
             for (int u = 0; u < NT / 8; ++u)
-                xv[u] = (live && k0 + u < K) ? patch_value<SPATIAL1>(g, xs, col.c0, col.h0, col.w0, k0 + u, oob) : 0.f;
+                xv[u] = (live && k0 + u < K) ? patch_value_at(g, xs, col.c0, col.h0, col.w0, tap_get<SPATIAL1>(g, tap_tab, tab_ok, k0 + u), oob) : 0.f;
         }
     };
     auto store = [&](int, unsigned char* a_hi, unsigned char* a_lo, unsigned char* b_hi, unsigned char* b_lo) {
         const bool live = col.base >= 0;
-        const float amx = a * col.mx;
-        const float bx = live ? -amx : -INFINITY;                // dead column: every Ex becomes 2^-inf = 0
+        const float mxv = col.mx;
+        const float mxd = live ? mxv : (a > 0.f ? INFINITY : -INFINITY);     // dead column: x = 0, so a * (x - mxd) = -inf and Ex = 0
 #pragma unroll
         for (int u = 0; u < 16; ++u) {                           // A: Q[m, j]
             const int row = warp * 16 + u;
             float hi, lo;
-            split_tf32_trunc(gv[u] * ex2_ftz(fmaf(-a, yv[u], amx + amo_s[row])), hi, lo);
+            split_tf32_trunc(gv[u] * ex2_ftz(fmaf(a, (mxv - yv[u]) + amo_s[row], c2)), hi, lo);
             const int off = core_off<kDoKT, kDoLBO>(row, lane);
             *reinterpret_cast<float*>(a_hi + off) = hi;
             *reinterpret_cast<float*>(a_lo + off) = lo;
@@ -351,7 +358,7 @@ __global__ void __launch_bounds__(kTcThreads, NT == 64 ? 3 : 2) mex_doff_tc(MexG
         for (int u = 0; u < NT / 8; ++u) {                       // B: Ex[k, j]
             const int row = warp * (NT / 8) + u;
             float hi, lo;
-            split_tf32_trunc((k_full || k0 + u < K) ? ex2_ftz(fmaf(xv[u], a, bx)) : 0.f, hi, lo);
+            split_tf32_trunc((k_full || k0 + u < K) ? ex2_ftz(a * (xv[u] - mxd)) : 0.f, hi, lo);
             const int off = core_off<kDoKT, kDoLBO>(row, lane);
             *reinterpret_cast<float*>(b_hi + off) = hi;
             *reinterpret_cast<float*>(b_lo + off) = lo;

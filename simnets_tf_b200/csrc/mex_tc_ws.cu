@@ -193,7 +193,10 @@ __global__ void __launch_bounds__(kWsThreads, 1) mex_fwd_ws(MexGeo g, const floa
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ WsShared<STAGES> sh;
     __shared__ __align__(16) float mo_w[kWsEpilogueWarps][NT / 2];
+    __shared__ int tap_tab[SPATIAL1 ? 1 : kTapTable];
     if (flag[0]) return;                                // factorisation unsafe: the exact kernels run instead
+    if (!SPATIAL1) fill_tap_table(g, tap_tab);          // (published by the barrier inside ws_setup)
+    const bool tab_ok = tap_table_ok(g);
 
     const long long P = (long long)g.B * g.rs;
     const int mtiles = (g.M + NT - 1) / NT, kchunks = (g.K + kTcKT - 1) / kTcKT;
@@ -233,8 +236,11 @@ __global__ void __launch_bounds__(kWsThreads, 1) mex_fwd_ws(MexGeo g, const floa
                     const int k = c * kTcKT + u;
                     xv[u] = 0.f;
                     if (live && k < K)
-                        xv[u] = INTERIOR ? __ldg(xs + interior_index<SPATIAL1>(g, col.c0, col.h0, col.w0, k))
-                                         : patch_value<SPATIAL1>(g, xs, col.c0, col.h0, col.w0, k, oob);
+                    {
+                        const Tap tp = tap_get<SPATIAL1>(g, tap_tab, tab_ok, k);
+                        xv[u] = INTERIOR ? __ldg(xs + ((col.c0 + tp.c) * g.H + col.h0 + tp.h) * g.W + col.w0 + tp.w)
+                                         : patch_value_at(g, xs, col.c0, col.h0, col.w0, tp, oob);
+                    }
                 }
             }
         };
@@ -245,9 +251,11 @@ __global__ void __launch_bounds__(kWsThreads, 1) mex_fwd_ws(MexGeo g, const floa
             if (sh.failed) break;
             float e[kTcKT];
             {
-                const float b = col.base >= 0 ? -a * col.mx : -INFINITY;     // a dead row holds x = 0: every tap becomes 2^-inf = 0
+                // x - mx first: both may be far from zero while their difference is small.  A dead row holds x = 0 and
+                // gets an infinite maximum of the sign that makes a * (x - mx) = -inf, i.e. every tap 0
+                const float mxd = col.base >= 0 ? col.mx : (a > 0.f ? INFINITY : -INFINITY);
 #pragma unroll
-                for (int u = 0; u < kTcKT; ++u) e[u] = ex2_ftz(fmaf(xv[u], a, b));
+                for (int u = 0; u < kTcKT; ++u) e[u] = ex2_ftz(a * (xv[u] - mxd));
                 if ((c + 1) * kTcKT > K) {
 #pragma unroll
                     for (int u = 0; u < kTcKT; ++u) if (c * kTcKT + u >= K) e[u] = 0.f;
@@ -345,7 +353,10 @@ __global__ void __launch_bounds__(kWsThreads, 1) mex_dx_ws(MexGeo g, const float
     constexpr uint32_t TMEM_COLS = 2 * NT < 32 ? 32 : 2 * NT;
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ WsShared<STAGES> sh;
+    __shared__ int tap_tab[SPATIAL1 ? 1 : kTapTable];
     if (flag[0]) return;
+    if (!SPATIAL1) fill_tap_table(g, tap_tab);          // (published by the barrier inside ws_setup)
+    const bool tab_ok = tap_table_ok(g);
 
     const long long P = (long long)g.B * g.rs;
     const int ktiles = (g.K + NT - 1) / NT, mchunks = (g.M + kTcKT - 1) / kTcKT;
@@ -391,12 +402,12 @@ __global__ void __launch_bounds__(kWsThreads, 1) mex_dx_ws(MexGeo g, const float
             if (sh.failed) break;
             float q[kTcKT];
             {
-                const float amx = fmaf(a, col.mx, c2);
+                const float mxv = col.mx;
                 const float* mor = mo + it.r * M + c * kTcKT;               // offset maxima of this chunk's instances (cached, same for all lanes)
 #pragma unroll
                 for (int u = 0; u < kTcKT; ++u) {
                     const float mv = c * kTcKT + u < M ? __ldg(mor + u) : 0.f;
-                    q[u] = gv[u] * ex2_ftz(fmaf(-a, yv[u], fmaf(a, mv, amx)));
+                    q[u] = gv[u] * ex2_ftz(fmaf(a, (mxv - yv[u]) + mv, c2));
                 }
             }
             c += kWsGroups;
@@ -435,7 +446,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) mex_dx_ws(MexGeo g, const float
             if (sh.failed) break;
             const WsItem it = ws_item(plan, int(blockIdx.x) + li * int(gridDim.x));        // it.mt = tap tile
             const Column col = column_of(g, it.r, (long long)it.jt * kTcPos + quarter * 32 + lane, P, mx);
-            const float b = -a * col.mx;                                     // Ex = 2^(a x - a mx)
+            const float emx = col.mx;                                        // Ex = 2^(a (x - mx))
             const int k_first = it.mt * NT + half * (NT / 2);
             if (!mbar_wait(&sh.acc_full[buf], (uint32_t(li) >> 1) & 1u)) { sh.failed = 1; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -457,7 +468,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) mex_dx_ws(MexGeo g, const float
                             for (int i = 0; i < 8; ++i) xr[i] = (i0 + i < kleft) ? ld_nc_ordered(xb + (i0 + i) * hw) : 0.f;
 #pragma unroll
                             for (int i = 0; i < 8; ++i)
-                                if (i0 + i < kleft) db[(i0 + i) * hw] = ex2_ftz(fmaf(xr[i], a, b)) * __uint_as_float(v[i0 + i]);
+                                if (i0 + i < kleft) db[(i0 + i) * hw] = ex2_ftz(a * (xr[i] - emx)) * __uint_as_float(v[i0 + i]);
                         }
                     }
                 }
@@ -472,11 +483,11 @@ __global__ void __launch_bounds__(kWsThreads, 1) mex_dx_ws(MexGeo g, const float
                         for (int i = 0; i < 32; ++i) {
                             const int k = k_first + c0 + i;
                             if (k >= g.K) continue;
-                            const Tap tp = tap_of<SPATIAL1>(g, k);
+                            const Tap tp = tap_get<SPATIAL1>(g, tap_tab, tab_ok, k);
                             const int cc = col.c0 + tp.c, hh = col.h0 + tp.h, ww = col.w0 + tp.w;
                             if (cc < 0 || cc >= g.C || hh < 0 || hh >= g.H || ww < 0 || ww >= g.W) continue;
                             const size_t ad = sample + ((size_t)cc * g.H + hh) * g.W + ww;
-                            dx[ad] = ex2_ftz(fmaf(__ldg(x + ad), a, b)) * __uint_as_float(v[i]);
+                            dx[ad] = ex2_ftz(a * (__ldg(x + ad) - emx)) * __uint_as_float(v[i]);
                         }
                     }
                 }

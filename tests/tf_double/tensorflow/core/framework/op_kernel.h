@@ -115,7 +115,7 @@ public:
     const Tensor& input(int i) const { return inputs[size_t(i)]; }
     Status allocate_output(int i, const TensorShape& shape, Tensor** out) {
         if (i < 0 || size_t(i) >= output_buffers.size()) return Status("no buffer for this output");
-        if (outputs.size() <= size_t(i)) outputs.resize(size_t(i) + 1);
+        if (outputs.size() < output_buffers.size()) outputs.resize(output_buffers.size());   // once: later calls must not move earlier outputs
         outputs[size_t(i)] = Tensor(inputs.empty() ? DT_FLOAT : inputs[0].dtype(), shape, output_buffers[size_t(i)]);
         *out = &outputs[size_t(i)];
         return Status::OK();
