@@ -28,13 +28,24 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// A block that spans whole rows and whole planes (the head over a complete 512 x 4 x 4 sample) is one contiguous run of
+// K floats: tap k sits at c0 * H * W + k, no decoding (two divisions and two modulos per tap otherwise) and no bounds test.
+__device__ __forceinline__ bool patches_contiguous(const MexGeo& g) {
+    return g.bw == g.W && g.pw == 0 && g.bh == g.H && g.ph == 0 && g.pc == 0 && (g.Co - 1) * g.sc + g.bc <= g.C;
+}
+template <bool SPATIAL1>
+__device__ __forceinline__ float tap_value(const MexGeo& g, const float* __restrict__ xs, const Column& col, int k, float oob, bool contig) {
+    if (contig) return __ldg(xs + (size_t)col.c0 * g.H * g.W + k);
+    return patch_value<SPATIAL1>(g, xs, col.c0, col.h0, col.w0, k, oob);
+}
+
 // max (eps > 0) or min over the K taps of one patch, over the whole block; NaN taps are ignored
 template <bool SPATIAL1>
 __device__ __forceinline__ float block_patch_extreme(const MexGeo& g, const float* __restrict__ xs, const Column& col, float oob, float* red) {
-    const bool up = g.eps > 0;
+    const bool up = g.eps > 0, contig = patches_contiguous(g);
     float v = up ? -CUDART_INF_F : CUDART_INF_F;
     for (int k = threadIdx.x; k < g.K; k += kT) {
-        const float t = patch_value<SPATIAL1>(g, xs, col.c0, col.h0, col.w0, k, oob);
+        const float t = tap_value<SPATIAL1>(g, xs, col, k, oob, contig);
         v = up ? fmaxf(v, t) : fminf(v, t);
     }
     v = up ? warp_max(v) : warp_min(v);
@@ -75,11 +86,12 @@ __global__ void __launch_bounds__(kT) mex_fwd_smallm(MexGeo g, const float* __re
     const float eps = float(g.eps), oob = float(g.oob);
     const float mxv = block_patch_extreme<SPATIAL1>(g, xs, col, oob, red);
     const int ldm = pad4(g.M);
+    const bool contig = patches_contiguous(g);
     float acc[kMaxM];
 #pragma unroll
     for (int m = 0; m < kMaxM; ++m) acc[m] = 0.f;
     for (int k = threadIdx.x; k < g.K; k += kT) {
-        const float e = fast_exp(eps * (patch_value<SPATIAL1>(g, xs, col.c0, col.h0, col.w0, k, oob) - mxv));
+        const float e = fast_exp(eps * (tap_value<SPATIAL1>(g, xs, col, k, oob, contig) - mxv));
         const float4* row = reinterpret_cast<const float4*>(eot + ((size_t)r * g.K + k) * ldm);
 #pragma unroll
         for (int q = 0; q < kMaxM / 4; ++q)
@@ -124,13 +136,19 @@ __global__ void __launch_bounds__(kT) mex_dx_smallm(MexGeo g, const float* __res
     __syncthreads();
     const int ldk = pad4(g.K);
     const float* eor = eo + (size_t)r * g.M * ldk;
+    const bool contig = patches_contiguous(g);
     for (int k = threadIdx.x; k < g.K; k += kT) {
-        const Tap tp = tap_of<SPATIAL1>(g, k);
-        const int cc = col.c0 + tp.c, hh = col.h0 + tp.h, ww = col.w0 + tp.w;
-        if (cc < 0 || cc >= g.C || hh < 0 || hh >= g.H || ww < 0 || ww >= g.W) continue;
+        size_t a;
+        if (contig) {
+            a = sample + (size_t)col.c0 * g.H * g.W + k;
+        } else {
+            const Tap tp = tap_of<SPATIAL1>(g, k);
+            const int cc = col.c0 + tp.c, hh = col.h0 + tp.h, ww = col.w0 + tp.w;
+            if (cc < 0 || cc >= g.C || hh < 0 || hh >= g.H || ww < 0 || ww >= g.W) continue;
+            a = sample + ((size_t)cc * g.H + hh) * g.W + ww;
+        }
         float s = 0.f;
         for (int m = 0; m < g.M; ++m) s = fmaf(__ldg(eor + (size_t)m * ldk + k), Q[m], s);
-        const size_t a = sample + ((size_t)cc * g.H + hh) * g.W + ww;
         dx[a] = fast_exp(eps * (x[a] - mxv)) * s;
     }
 }
@@ -154,6 +172,7 @@ __global__ void __launch_bounds__(kT) mex_doff_smallm(MexGeo g, const float* __r
     const long long groups = (P + kGroup - 1) / kGroup;
     const long long g_begin = groups * split / splits, g_end = groups * (split + 1) / splits;
     const float eps = float(g.eps), oob = float(g.oob), cst = float(g.cst);
+    const bool contig = patches_contiguous(g);
     float acc[kMaxM];
 #pragma unroll
     for (int m = 0; m < kMaxM; ++m) acc[m] = 0.f;
@@ -174,7 +193,7 @@ __global__ void __launch_bounds__(kT) mex_doff_smallm(MexGeo g, const float* __r
             for (int p = 0; p < kGroup; ++p) {
                 const Column& c = cols[p];
                 if (c.base < 0) continue;
-                const float v = patch_value<SPATIAL1>(g, x + (size_t)c.n * g.C * g.H * g.W, c.c0, c.h0, c.w0, k, oob);
+                const float v = tap_value<SPATIAL1>(g, x + (size_t)c.n * g.C * g.H * g.W, c, k, oob, contig);
                 const float e = fast_exp(eps * (v - c.mx));
 #pragma unroll
                 for (int m = 0; m < kMaxM; ++m) acc[m] = fmaf(Qs[p][m], e, acc[m]);
