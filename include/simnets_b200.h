@@ -76,6 +76,14 @@ enum { SIMNETS_SIM_L1 = 0, SIMNETS_SIM_L2 = 1 };
  * reference, whose graphs run the pooling gradient as a separate TensorFlow op. */
 #define SIMNETS_FLAG_MEX_DY_POOLED2    (1u << 6)
 
+/* MEX gradient entry points only: the workspace is the one the last simnets_mex_forward call was given for the
+ * same input, offsets, descriptor and flags (SIMNETS_FLAG_MEX_DY_POOLED2 aside) and nothing has written to it
+ * since, other gradient calls of that layer excepted.  The per-position maxima and the offsets tables that the
+ * forward pass left there are then used as they are instead of being computed again (same values, fewer
+ * launches).  Ignored where the forward pass of the shape does not leave them.  The caller owns the promise: a
+ * workspace that was reused in between gives wrong gradients, not an error. */
+#define SIMNETS_FLAG_MEX_WORKSPACE_PRIMED (1u << 8)
+
 /* ---- Similarity ---------------------------------------------------------- */
 /* Mirrors the attrs of the Similarity op family (src/ops/similarity_op.cpp:61-75)
  * and the dimensions SimilarityKernelCommon::CalculateDimensions derives

@@ -17,6 +17,7 @@ FLAG_SIM_L1_SKIP_NAN = 1 << 4
 FLAG_MEX_NO_TENSORCORE = 1 << 5
 FLAG_MEX_DY_POOLED2 = 1 << 6
 FLAG_MEX_TC_ONE_TILE = 1 << 7
+FLAG_MEX_WORKSPACE_PRIMED = 1 << 8
 
 OK = 0
 E_NULL, E_DESC, E_DTYPE, E_WORKSPACE, E_UNSUPPORTED, E_TOO_LARGE = -1, -2, -3, -4, -5, -6

@@ -369,6 +369,14 @@ cudaError_t run_prepasses(const MexGeo& g, const MexWs& w, const float* x, const
     return cudaGetLastError();
 }
 
+// The forward pass of this layer leaves in the workspace everything run_prepasses() would write for the gradients
+// (the short-patch and few-instance forward kernels skip the per-position maxima, which their gradients need).
+bool forward_primes_workspace(MexGeo g, uint32_t flags) {
+    if (!(flags & SIMNETS_FLAG_MEX_WORKSPACE_PRIMED)) return false;
+    g.gp = 1; g.Ng = g.N;        // the forward pass never sees a pooled dy
+    return !smallm_shape(g) && !use_smallk_kernels(g, flags);
+}
+
 }  // namespace
 
 bool mex_use_tiled(const MexGeo& g, bool f64, uint32_t flags) {
@@ -468,7 +476,7 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
     if (!blocks_disjoint(g)) return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, nullptr);
     const MexWs w = carve(g, ws);
     const bool small = smallm_shape(g) || use_smallk_kernels(g, flags);
-    cudaError_t e = prepped ? cudaSuccess : run_prepasses(g, w, x, off, s, !small);
+    cudaError_t e = (prepped || forward_primes_workspace(g, flags)) ? cudaSuccess : run_prepasses(g, w, x, off, s, !small);
     if (e != cudaSuccess) return e;
     if (!blocks_cover_input(g)) {
         e = cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)g.B * g.C * g.H * g.W, s);
@@ -512,7 +520,7 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
 cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* doff,
                                   bool accumulate, void* ws, uint32_t flags, cudaStream_t s, bool prepped) {
     const MexWs w = carve(g, ws);
-    cudaError_t e = prepped ? cudaSuccess : run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags));
+    cudaError_t e = (prepped || forward_primes_workspace(g, flags)) ? cudaSuccess : run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags));
     if (e != cudaSuccess) return e;
     if (use_tc_kernels(g, flags)) {
         const int tsplits = mex_tc_doff_splits(g);
@@ -565,7 +573,7 @@ cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* 
 cudaError_t launch_mex_backward_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* dx,
                                       float* doff, bool accumulate, void* ws, uint32_t flags, cudaStream_t s) {
     const MexWs w = carve(g, ws);
-    cudaError_t e = run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags));
+    cudaError_t e = forward_primes_workspace(g, flags) ? cudaSuccess : run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags));
     if (e != cudaSuccess) return e;
     e = launch_mex_dx_tiled(g, x, off, y, dy, dx, ws, flags, s, true);
     if (e != cudaSuccess) return e;

@@ -98,14 +98,36 @@ def _cost(d, g, kind):
     return sig, nbytes, y * g.K
 
 
-def _ws(d, dev):
+def _ws(d, dev, own=None):
     n = _lib.lib().simnets_mex_workspace_bytes(C.byref(d))
+    if own is not None:
+        if own.dtype != torch.uint8 or own.device != dev or not own.is_contiguous() or own.numel() < n:
+            raise ValueError("workspace: need a contiguous uint8 tensor of at least %d bytes on %s" % (n, dev))
+        return own.data_ptr(), own.numel()
     buf = workspace(dev, n)
     return buf.data_ptr(), buf.numel()
 
 
-def mex_forward(input, offsets, num_instances, flags=0, **attrs):
-    """The `Mex` op: [batch, num_instances * channels_out, height_out, width_out]."""
+def mex_layer_workspace(input, num_instances, pooled=False, flags=0, **attrs):
+    """A workspace of one layer's own, large enough for its forward and gradient calls: give it to `mex_forward`
+    as `workspace=` and to the gradient ops as `primed_workspace=`, and they reuse the per-position maxima and
+    the offsets tables of the forward pass instead of computing them again."""
+    attrs = _attrs(**attrs)
+    dev = require_cuda(input)
+    n = 256
+    for f in (flags, flags | (abi.FLAG_MEX_DY_POOLED2 if pooled else 0)):
+        d = _desc(input, num_instances, attrs, f)
+        n = max(n, int(_lib.lib().simnets_mex_workspace_bytes(C.byref(d))))
+    return torch.empty(n, dtype=torch.uint8, device=dev)
+
+
+def _primed(flags, primed_workspace):
+    return flags | (abi.FLAG_MEX_WORKSPACE_PRIMED if primed_workspace is not None else 0)
+
+
+def mex_forward(input, offsets, num_instances, flags=0, workspace=None, **attrs):
+    """The `Mex` op: [batch, num_instances * channels_out, height_out, width_out].  `workspace`: a buffer from
+    `mex_layer_workspace` to run in instead of the stream's shared scratch."""
     attrs = _attrs(**attrs)
     dev = require_cuda(input, offsets)
     input, offsets = input.contiguous(), offsets.contiguous()
@@ -114,17 +136,17 @@ def mex_forward(input, offsets, num_instances, flags=0, **attrs):
     _check_offsets(offsets, g, num_instances)
     y = torch.empty((input.shape[0], g.channels_out_total, g.height_out, g.width_out), dtype=input.dtype, device=dev)
     with torch.cuda.device(dev):
-        ws, n = _ws(d, dev)
+        ws, n = _ws(d, dev, workspace)
         with timed("mex_forward", *_cost(d, g, "fwd")):
             _lib.check(_lib.lib().simnets_mex_forward(C.byref(d), input.data_ptr(), offsets.data_ptr(), y.data_ptr(), ws, n, stream_ptr(dev)))
     return y
 
 
-def mex_input_grad(input, offsets, orig_output, output_grad, num_instances, flags=0, pooled=False, **attrs):
+def mex_input_grad(input, offsets, orig_output, output_grad, num_instances, flags=0, primed_workspace=None, pooled=False, **attrs):
     """The `MexInputGrad` op.  pooled=True: `output_grad` is the gradient of a 2x2 sum pooling of the output
     (half height and width); the library reads it in place of its 2x upsampling."""
     attrs = _attrs(**attrs)
-    flags |= abi.FLAG_MEX_DY_POOLED2 if pooled else 0
+    flags = _primed(flags | (abi.FLAG_MEX_DY_POOLED2 if pooled else 0), primed_workspace)
     dev = require_cuda(input, offsets, orig_output, output_grad)
     input, offsets, y, dy = input.contiguous(), offsets.contiguous(), orig_output.contiguous(), output_grad.contiguous()
     d = _desc(input, num_instances, attrs, flags)
@@ -133,18 +155,18 @@ def mex_input_grad(input, offsets, orig_output, output_grad, num_instances, flag
     _check_dy(dy, input, g, pooled)
     dx = torch.empty_like(input)
     with torch.cuda.device(dev):
-        ws, n = _ws(d, dev)
+        ws, n = _ws(d, dev, primed_workspace)
         with timed("mex_input_grad", *_cost(d, g, "dx")):
             _lib.check(_lib.lib().simnets_mex_input_grad(C.byref(d), input.data_ptr(), offsets.data_ptr(), y.data_ptr(), dy.data_ptr(),
                                                          dx.data_ptr(), ws, n, stream_ptr(dev)))
     return dx
 
 
-def mex_offsets_grad(input, offsets, orig_output, output_grad, num_instances, flags=0, out=None, pooled=False, **attrs):
+def mex_offsets_grad(input, offsets, orig_output, output_grad, num_instances, flags=0, primed_workspace=None, out=None, pooled=False, **attrs):
     """The `MexOffsetsGrad` op.  `out` / FLAG_ACCUMULATE as in `similarity_parameters_grad`; `pooled` as in
     `mex_input_grad`."""
     attrs = _attrs(**attrs)
-    flags |= abi.FLAG_MEX_DY_POOLED2 if pooled else 0
+    flags = _primed(flags | (abi.FLAG_MEX_DY_POOLED2 if pooled else 0), primed_workspace)
     dev = require_cuda(input, offsets, orig_output, output_grad)
     input, offsets, y, dy = input.contiguous(), offsets.contiguous(), orig_output.contiguous(), output_grad.contiguous()
     d = _desc(input, num_instances, attrs, flags)
@@ -157,18 +179,19 @@ def mex_offsets_grad(input, offsets, orig_output, output_grad, num_instances, fl
         doff = out
         assert doff.is_contiguous() and doff.numel() == offsets.numel()
     with torch.cuda.device(dev):
-        ws, n = _ws(d, dev)
+        ws, n = _ws(d, dev, primed_workspace)
         with timed("mex_offsets_grad", *_cost(d, g, "doff")):
             _lib.check(_lib.lib().simnets_mex_offsets_grad(C.byref(d), input.data_ptr(), offsets.data_ptr(), y.data_ptr(), dy.data_ptr(),
                                                            doff.data_ptr(), ws, n, stream_ptr(dev)))
     return doff
 
 
-def mex_backward(input, offsets, orig_output, output_grad, num_instances, flags=0, pooled=False, **attrs):
+def mex_backward(input, offsets, orig_output, output_grad, num_instances, flags=0, primed_workspace=None, pooled=False, **attrs):
     """`MexInputGrad` and `MexOffsetsGrad` in one library call: (input_grad, offsets_grad).  `pooled` as in
-    `mex_input_grad`."""
+    `mex_input_grad`.  `primed_workspace` (all three gradient ops): the buffer that `mex_forward` ran in for the same
+    input and offsets, untouched since."""
     attrs = _attrs(**attrs)
-    flags |= abi.FLAG_MEX_DY_POOLED2 if pooled else 0
+    flags = _primed(flags | (abi.FLAG_MEX_DY_POOLED2 if pooled else 0), primed_workspace)
     dev = require_cuda(input, offsets, orig_output, output_grad)
     input, offsets, y, dy = input.contiguous(), offsets.contiguous(), orig_output.contiguous(), output_grad.contiguous()
     d = _desc(input, num_instances, attrs, flags)
@@ -177,7 +200,7 @@ def mex_backward(input, offsets, orig_output, output_grad, num_instances, flags=
     _check_dy(dy, input, g, pooled)
     dx, doff = torch.empty_like(input), torch.empty_like(offsets)
     with torch.cuda.device(dev):
-        ws, n = _ws(d, dev)
+        ws, n = _ws(d, dev, primed_workspace)
         sig, nbytes, terms = _cost(d, g, "bwd")     # fused: x, offsets, y, dy read once, dx and doffsets written
         if pooled:
             sig, nbytes = sig + " dy/4", nbytes - 3 * dy.numel() * dy.element_size()
@@ -190,22 +213,31 @@ def mex_backward(input, offsets, orig_output, output_grad, num_instances, flags=
 def _gradients(ctx, grad, pooled):
     input, offsets, y = ctx.saved_tensors
     gi = go = None
+    kw = dict(pooled=pooled, primed_workspace=ctx.layer_ws, **ctx.attrs)
     if ctx.needs_input_grad[0] and ctx.needs_input_grad[1]:
-        gi, go = mex_backward(input, offsets, y, grad, ctx.num_instances, pooled=pooled, **ctx.attrs)
+        gi, go = mex_backward(input, offsets, y, grad, ctx.num_instances, **kw)
     elif ctx.needs_input_grad[0]:
-        gi = mex_input_grad(input, offsets, y, grad, ctx.num_instances, pooled=pooled, **ctx.attrs)
+        gi = mex_input_grad(input, offsets, y, grad, ctx.num_instances, **kw)
     elif ctx.needs_input_grad[1]:
-        go = mex_offsets_grad(input, offsets, y, grad, ctx.num_instances, pooled=pooled, **ctx.attrs)
+        go = mex_offsets_grad(input, offsets, y, grad, ctx.num_instances, **kw)
     return gi, go, None, None
+
+
+def _forward_for_autograd(ctx, input, offsets, num_instances, attrs, pooled):
+    # a differentiated layer runs in a workspace of its own, which its gradient pass then finds primed
+    ctx.layer_ws = None
+    if (ctx.needs_input_grad[0] or ctx.needs_input_grad[1]) and input.is_cuda and input.shape[0] > 0:
+        ctx.layer_ws = mex_layer_workspace(input, num_instances, pooled=pooled, **attrs)
+    y = mex_forward(input, offsets, num_instances, workspace=ctx.layer_ws, **attrs)
+    ctx.attrs, ctx.num_instances = attrs, num_instances
+    ctx.save_for_backward(input, offsets, y)
+    return y
 
 
 class _Mex(torch.autograd.Function):
     @staticmethod
     def forward(ctx, input, offsets, num_instances, attrs):
-        y = mex_forward(input, offsets, num_instances, **attrs)
-        ctx.attrs, ctx.num_instances = attrs, num_instances
-        ctx.save_for_backward(input, offsets, y)
-        return y
+        return _forward_for_autograd(ctx, input, offsets, num_instances, attrs, False)
 
     @staticmethod
     def backward(ctx, grad):
@@ -229,9 +261,7 @@ class _MexSumPool2(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, input, offsets, num_instances, attrs):
-        y = mex_forward(input, offsets, num_instances, **attrs)
-        ctx.attrs, ctx.num_instances = attrs, num_instances
-        ctx.save_for_backward(input, offsets, y)
+        y = _forward_for_autograd(ctx, input, offsets, num_instances, attrs, True)
         return sum_pool2x2(y) if y.dtype == torch.float32 else torch.nn.functional.avg_pool2d(y, 2) * 4.0
 
     @staticmethod

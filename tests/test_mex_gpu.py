@@ -90,6 +90,34 @@ def test_fused_backward_equals_the_two_gradient_ops(port, name):
 
 
 @pytest.mark.parametrize("c", cases.MEX_SMALL + cases.MEX_CONFIGS, ids=lambda c: c["name"])
+def test_gradients_from_the_forward_pass_workspace(port, c):
+    """SIMNETS_FLAG_MEX_WORKSPACE_PRIMED: gradients that reuse what the forward pass left in the layer's own
+    workspace are the gradients computed from scratch (full and pooled dy, all three entry points)."""
+    d = cases.mex_desc(c)
+    oshape = port.mex_out_shape(d)
+    x, off, dy = cases.mex_inputs(c, port.mex_offsets_shape(d), oshape)
+    xd, od, dyd = (gpu_util.dev(a) for a in (x, off, dy))
+    attrs, fl = cases.mex_attrs(c), c["flags"]
+    pooled_ok = oshape[0] > 0 and oshape[2] % 2 == 0 and oshape[3] % 2 == 0
+    for pooled in ([False, True] if pooled_ok else [False]):
+        g = dyd[:, :, ::2, ::2].contiguous() if pooled else dyd
+        ws = mex_ops.mex_layer_workspace(xd, c["M"], pooled=pooled, flags=fl, **attrs)
+        yd = mex_ops.mex_forward(xd, od, c["M"], flags=fl, workspace=ws, **attrs)
+        y2 = mex_ops.mex_forward(xd, od, c["M"], flags=fl, **attrs)
+        assert torch.equal(torch.nan_to_num(yd, nan=7.0), torch.nan_to_num(y2, nan=7.0))
+        kw = dict(flags=fl, pooled=pooled, **attrs)
+        want_dx = mex_ops.mex_input_grad(xd, od, yd, g, c["M"], **kw)
+        want_doff = mex_ops.mex_offsets_grad(xd, od, yd, g, c["M"], **kw)
+        # (equal bit for bit except where overlapping blocks take the kernels that add with atomics)
+        same = lambda a, b: torch.allclose(a, b, rtol=1e-5, atol=1e-7, equal_nan=True)
+        for _ in range(2):      # the gradient calls leave the workspace primed for one another
+            dx, doff = mex_ops.mex_backward(xd, od, yd, g, c["M"], primed_workspace=ws, **kw)
+            assert same(dx, want_dx) and same(doff, want_doff), c["name"]
+            assert same(mex_ops.mex_input_grad(xd, od, yd, g, c["M"], primed_workspace=ws, **kw), want_dx), c["name"]
+            assert same(mex_ops.mex_offsets_grad(xd, od, yd, g, c["M"], primed_workspace=ws, **kw), want_doff), c["name"]
+
+
+@pytest.mark.parametrize("c", cases.MEX_SMALL + cases.MEX_CONFIGS, ids=lambda c: c["name"])
 def test_pooled_output_gradient(port, c):
     """SIMNETS_FLAG_MEX_DY_POOLED2: dy at half resolution stands for its 2x nearest upsampling."""
     if gpu_util.check_mex_pooled_dy(port, c) is None:
