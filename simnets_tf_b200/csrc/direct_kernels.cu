@@ -268,9 +268,11 @@ __global__ void __launch_bounds__(kThreads) mex_doff_direct(MexGeo g, const T* _
     }
 }
 
-inline int grid_for(long long total) {
+// gated: the launch follows a factorised kernel and does work only if that one raised the safety flag; a grid that
+// just fills the GPU keeps the usual case (every CTA reads the flag and returns) at a few microseconds
+inline int grid_for(long long total, bool gated = false) {
     const long long blocks = (total + kThreads - 1) / kThreads;
-    const long long cap = 148LL * 32;
+    const long long cap = gated ? 148LL * 8 : 148LL * 32;
     return int(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 
@@ -312,7 +314,7 @@ cudaError_t launch_mex_fwd_direct(const MexGeo& g, bool f64, const void* x, cons
     const long long total = (long long)g.B * g.M * g.N;
     if (total == 0) return cudaSuccess;
     SIMNETS_DTYPE_SWITCH(f64,
-        (mex_fwd_direct<float><<<grid_for(total), kThreads, 0, s>>>(g, (const float*)x, (const float*)off, (float*)y, gate)),
+        (mex_fwd_direct<float><<<grid_for(total, gate != nullptr), kThreads, 0, s>>>(g, (const float*)x, (const float*)off, (float*)y, gate)),
         (mex_fwd_direct<double><<<grid_for(total), kThreads, 0, s>>>(g, (const double*)x, (const double*)off, (double*)y, gate)));
     count_launch();
     return cudaGetLastError();
@@ -322,7 +324,7 @@ cudaError_t launch_mex_dx_direct(const MexGeo& g, bool f64, const void* x, const
     const long long total = (long long)g.B * g.C * g.H * g.W;
     if (total == 0) return cudaSuccess;
     SIMNETS_DTYPE_SWITCH(f64,
-        (mex_dx_direct<float><<<grid_for(total), kThreads, 0, s>>>(g, (const float*)x, (const float*)off, (const float*)y, (const float*)dy, (float*)dx, gate)),
+        (mex_dx_direct<float><<<grid_for(total, gate != nullptr), kThreads, 0, s>>>(g, (const float*)x, (const float*)off, (const float*)y, (const float*)dy, (float*)dx, gate)),
         (mex_dx_direct<double><<<grid_for(total), kThreads, 0, s>>>(g, (const double*)x, (const double*)off, (const double*)y, (const double*)dy, (double*)dx, gate)));
     count_launch();
     return cudaGetLastError();

@@ -92,6 +92,42 @@ __global__ void __launch_bounds__(256) mex_colmax(MexGeo g, const float* __restr
     }
 }
 
+// The same maxima with eight threads per position (warp w of a CTA takes taps w, w + 8, ...): layers with few
+// positions and long patches (8x8 maps under 256 channels) otherwise leave most of the GPU idle while each
+// thread walks its patch alone.  max and min are associative and NaN taps are skipped either way: same values.
+template <bool SPATIAL1>
+__global__ void __launch_bounds__(256) mex_colmax_sliced(MexGeo g, const float* __restrict__ x, float* __restrict__ mx, const int* __restrict__ flag) {
+    __shared__ float part[8][32];
+    if (*flag) return;
+    const long long total = (long long)g.B * g.N;
+    const bool up = g.eps > 0;
+    const float oob = float(g.oob);
+    const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+    for (long long first = blockIdx.x * 32LL; first < total; first += (long long)gridDim.x * 32) {
+        const long long idx = first + lane;
+        float v = up ? -CUDART_INF_F : CUDART_INF_F;
+        if (idx < total) {
+            const int pos = int(idx % g.N), n = int(idx / g.N);
+            const int w = pos % g.Wo, h = (pos / g.Wo) % g.Ho, c = pos / (g.Wo * g.Ho);
+            const float* xs = x + (size_t)n * g.C * g.H * g.W;
+            const int c0 = c * g.sc - g.pc, h0 = h * g.sh - g.ph, w0 = w * g.sw - g.pw;
+#pragma unroll 4
+            for (int k = slice; k < g.K; k += 8) {
+                const float t = patch_value<SPATIAL1>(g, xs, c0, h0, w0, k, oob);
+                v = up ? fmaxf(v, t) : fminf(v, t);
+            }
+        }
+        part[slice][lane] = v;
+        __syncthreads();
+        if (slice == 0 && idx < total) {
+#pragma unroll
+            for (int q = 1; q < 8; ++q) v = up ? fmaxf(v, part[q][lane]) : fminf(v, part[q][lane]);
+            mx[idx] = v;
+        }
+        __syncthreads();
+    }
+}
+
 // ------------------------------------------------------------------- forward
 // C[i = m, j = position] = sum_{q = k} EoT[k][m] * Ex[k][j]
 // INTERIOR: no patch of this geometry leaves the input, so taps need no bounds test.
@@ -362,9 +398,17 @@ cudaError_t run_prepasses(const MexGeo& g, const MexWs& w, const float* x, const
     // long patches over few positions are contiguous per position: reduce them with one CTA each
     if (g.K >= 256 && g.N <= 16) { count_launch(); return launch_mex_colmax_wide(g, x, w.mx, w.flag, s); }
     const long long total = (long long)g.B * g.N;
-    const int grid = int(std::min<long long>((total + 255) / 256, 148LL * 16));
-    if (g.bh == 1 && g.bw == 1) mex_colmax<true><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
-    else mex_colmax<false><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
+    // (measured on 32x32x64, 16x16x128 and 8x8x256 maps at batches 256 and 2048: eight threads per position win for
+    // long patches while one thread per position would not fill the GPU's 148 x 2048 thread slots)
+    if (g.K >= 128 && total < 148LL * 2048) {
+        const int grid = int(std::min<long long>((total + 31) / 32, 148LL * 32));
+        if (g.bh == 1 && g.bw == 1) mex_colmax_sliced<true><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
+        else mex_colmax_sliced<false><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
+    } else {
+        const int grid = int(std::min<long long>((total + 255) / 256, 148LL * 16));
+        if (g.bh == 1 && g.bw == 1) mex_colmax<true><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
+        else mex_colmax<false><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
+    }
     count_launch(2);
     return cudaGetLastError();
 }

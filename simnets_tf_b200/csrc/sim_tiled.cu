@@ -470,25 +470,40 @@ __global__ void __launch_bounds__(256) sim_dx_tiled(SimGeo g, const float* __res
 }
 
 // Sums the split partials in split order and applies the per-parameter factors of the backward functors.
-__global__ void __launch_bounds__(256) sim_dparams_reduce(SimGeo g, int splits, const float* __restrict__ part,
+// 32 outputs x 16 slices of the splits per CTA; the slices are added in a fixed order (same sums on every run)
+__global__ void __launch_bounds__(512) sim_dparams_reduce(SimGeo g, int splits, const float* __restrict__ part,
                                                           const float* __restrict__ wt, float* __restrict__ dt, float* __restrict__ dw,
                                                           int accumulate) {
+    __shared__ float red[3][16][32];
     const int mk = g.M * g.K;
     const float fudge = float(g.fudge);
-    for (int i = blockIdx.x * 256 + threadIdx.x; i < mk; i += gridDim.x * 256) {
+    const bool third = g.mode == SIM_L2N || g.mode == SIM_L2N_NAN;
+    const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+    for (int first = blockIdx.x * 32; first < mk; first += gridDim.x * 32) {
+        const int i = first + lane;
         float a = 0.f, b = 0.f, c = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float* p = part + (size_t)s * 3 * mk;
-            a += p[i]; b += p[mk + i];
-            if (g.mode == SIM_L2N || g.mode == SIM_L2N_NAN) c += p[2 * mk + i];
+        if (i < mk) {
+#pragma unroll 4
+            for (int s = slice; s < splits; s += 16) {
+                const float* p = part + (size_t)s * 3 * mk;
+                a += p[i]; b += p[mk + i];
+                if (third) c += p[2 * mk + i];
+            }
         }
-        const float w = wt[i];
-        float gt, gw;
-        if (g.mode == SIM_L1 || g.mode == SIM_L1_SKIP) { gt = w * a; gw = -b; }
-        else if (g.mode == SIM_L2) { gt = 2.f * w * a; gw = -b; }
-        else { gt = w * a; gw = 0.5f * (c / (w + fudge) - b); }
-        dt[i] = accumulate ? dt[i] + gt : gt;
-        dw[i] = accumulate ? dw[i] + gw : gw;
+        red[0][slice][lane] = a; red[1][slice][lane] = b; red[2][slice][lane] = c;
+        __syncthreads();
+        if (slice == 0 && i < mk) {
+#pragma unroll
+            for (int q = 1; q < 16; ++q) { a += red[0][q][lane]; b += red[1][q][lane]; c += red[2][q][lane]; }
+            const float w = wt[i];
+            float gt, gw;
+            if (g.mode == SIM_L1 || g.mode == SIM_L1_SKIP) { gt = w * a; gw = -b; }
+            else if (g.mode == SIM_L2) { gt = 2.f * w * a; gw = -b; }
+            else { gt = w * a; gw = 0.5f * (c / (w + fudge) - b); }
+            dt[i] = accumulate ? dt[i] + gt : gt;
+            dw[i] = accumulate ? dw[i] + gw : gw;
+        }
+        __syncthreads();
     }
 }
 
@@ -589,7 +604,7 @@ cudaError_t launch_sim_dparams_tiled(const SimGeo& g, const float* x, const floa
     }
 #undef DP
     const int mk = g.M * g.K;
-    sim_dparams_reduce<<<std::min((mk + 255) / 256, 148 * 8), 256, 0, s>>>(g, splits, W.part, w, dt, dw, accumulate);
+    sim_dparams_reduce<<<std::min((mk + 31) / 32, 148 * 8), 512, 0, s>>>(g, splits, W.part, w, dt, dw, accumulate);
     count_launch(2);
     return cudaGetLastError();
 }
