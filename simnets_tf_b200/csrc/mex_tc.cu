@@ -475,7 +475,7 @@ int mex_tc_doff_splits(const MexGeo& g) {
     const long long P = (long long)g.B * g.rs, chunks = (P + kDoKT - 1) / kDoKT;
     const long long tiles = (long long)((g.M + 127) / 128) * ((g.K + nt - 1) / nt) * g.R;
     const int per_sm = nt == 64 ? 3 : 2;                         // CTAs per SM that the register budget allows
-    long long s = (148LL * per_sm * 2) / tiles;                  // about two full waves
+    long long s = (148LL * per_sm) / tiles;                      // one full wave: measured against a half, two and four (the partial sums are 128 x NT floats per CTA)
     if (s > chunks) s = chunks;
     if (s < 1) s = 1;
     if (s > 512) s = 512;
