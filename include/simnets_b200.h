@@ -69,6 +69,16 @@ enum { SIMNETS_SIM_L1 = 0, SIMNETS_SIM_L2 = 1 };
  * warp-specialised ones (same results; kept for comparison measurements). */
 #define SIMNETS_FLAG_MEX_TC_ONE_TILE   (1u << 7)
 
+/* MEX only: never pair the tiles of sibling regions (layers whose unshared regions alternate along the width
+ * otherwise run on kernels that read and write pixel pairs); same results, kept for comparison measurements. */
+#define SIMNETS_FLAG_MEX_NO_PAIR_TILES (1u << 9)
+
+/* Test hook, simnets_mex_forward on a pair-tile shape only: the kernel's MMA role withholds the completion signal of
+ * its first accumulator and every bounded wait is shortened to a fraction of a millisecond, so that one wait runs out.
+ * Nothing hangs or faults: the roles leave their loops, tensor memory is freed, word 1 of the workspace status is set
+ * (simnets_mex_workspace_status) and the exact kernels launched behind the tensor-core kernel redo the work. */
+#define SIMNETS_FLAG_MEX_TEST_EXPIRE_WAIT (1u << 10)
+
 /* MEX gradient entry points only: dy is given at half resolution, dy[batch, M * channels_out, height_out / 2,
  * width_out / 2], each value standing for the 2x2 window of output positions that a 2x2 / stride-2 sum pooling
  * added up (the gradient of such a pooling copies its dy to the four inputs; with this flag the copy is never
@@ -198,6 +208,18 @@ SIMNETS_API size_t simnets_mex_workspace_bytes(const simnets_mex_desc* d);
 SIMNETS_API int simnets_mex_forward(const simnets_mex_desc* d,
                                     const void* x, const void* offsets, void* y,
                                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* Status words of a MEX workspace after the calls that used it, copied to host_out[0..1] by one 8-byte asynchronous
+ * device-to-host copy on `stream` (synchronise the stream before reading; pinned host memory keeps the copy
+ * asynchronous).  No counterpart in the reference, whose kernels have nothing to report.
+ *   host_out[0] != 0: the offsets of the call made the factorised evaluation unsafe (a non-finite offset, or
+ *                     |epsilon| * (max - min) of a row above 60); the exact per-term kernels computed the results.
+ *   host_out[1] != 0: a tensor-core kernel gave up on a bounded wait between its roles (about two seconds) and left
+ *                     early; the exact kernels launched behind it recomputed the outputs of that call, so they are
+ *                     valid, only slow.  Not expected outside SIMNETS_FLAG_MEX_TEST_EXPIRE_WAIT.
+ * The words are cleared by the next call that runs the prepasses on this workspace (every call without
+ * SIMNETS_FLAG_MEX_WORKSPACE_PRIMED). */
+SIMNETS_API int simnets_mex_workspace_status(const void* workspace, void* stream, int32_t* host_out);
 
 /* MEX forward for callers that have no scratch to give.  No counterpart in the reference: its
  * OpKernels always obtain temporaries from TensorFlow's allocator (context->allocate_temp).

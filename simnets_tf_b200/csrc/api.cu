@@ -10,6 +10,17 @@
 namespace simnets {
 static std::atomic<uint64_t> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(uint64_t(n), std::memory_order_relaxed); }
+int device_sm_count() {
+    static std::atomic<int> sms[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    int n = sms[dev].load(std::memory_order_relaxed);
+    if (!n) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        sms[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
 }  // namespace simnets
 
 using namespace simnets;
@@ -153,6 +164,11 @@ int simnets_mex_forward(const simnets_mex_desc* d, const void* x, const void* of
         return from_cuda(launch_mex_fwd_tiled(g, (const float*)x, (const float*)off, (float*)y, ws, d->flags, as_stream(stream)));
     }
     return from_cuda(launch_mex_fwd_direct(g, f64, x, off, y, as_stream(stream)));
+}
+
+int simnets_mex_workspace_status(const void* ws, void* stream, int32_t* host_out) {
+    if (!ws || !host_out) return SIMNETS_E_NULL;
+    return from_cuda(cudaMemcpyAsync(host_out, ws, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, as_stream(stream)));
 }
 
 int simnets_mex_forward_static_scratch(const simnets_mex_desc* d, const void* x, const void* off, void* y, void* stream) {

@@ -167,7 +167,7 @@ __device__ __forceinline__ T mex_tap(const MexGeo& g, const T* __restrict__ xs, 
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads) mex_fwd_direct(MexGeo g, const T* __restrict__ x, const T* __restrict__ off, T* __restrict__ y, const int* __restrict__ gate) {
-    if (gate && *gate == 0) return;
+    if (gate && (gate[0] | gate[1]) == 0) return;
     const long long total = (long long)g.B * g.M * g.N;
     const T oob = T(g.oob), eps = T(g.eps), cst = T(g.cst);
     for (long long idx = blockIdx.x * (long long)kThreads + threadIdx.x; idx < total; idx += (long long)gridDim.x * kThreads) {
@@ -202,7 +202,7 @@ __device__ __forceinline__ T mex_weight(const MexGeo& g, T eps, T cst, T data, T
 template <typename T>
 __global__ void __launch_bounds__(kThreads) mex_dx_direct(MexGeo g, const T* __restrict__ x, const T* __restrict__ off,
                                                           const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx, const int* __restrict__ gate) {
-    if (gate && *gate == 0) return;
+    if (gate && (gate[0] | gate[1]) == 0) return;
     const long long total = (long long)g.B * g.C * g.H * g.W;
     const T eps = T(g.eps), cst = T(g.cst);
     for (long long idx = blockIdx.x * (long long)kThreads + threadIdx.x; idx < total; idx += (long long)gridDim.x * kThreads) {
@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(kThreads) mex_doff_direct(MexGeo g, const T* _
                                                             const T* __restrict__ y, const T* __restrict__ dy,
                                                             T* __restrict__ doff, int accumulate, const int* __restrict__ gate) {
     __shared__ T smem[kThreads];
-    if (gate && *gate == 0) return;
+    if (gate && (gate[0] | gate[1]) == 0) return;
     const T oob = T(g.oob), eps = T(g.eps), cst = T(g.cst);
     const long long triples = (long long)g.R * g.M * g.K;
     for (long long rmk = blockIdx.x; rmk < triples; rmk += gridDim.x) {

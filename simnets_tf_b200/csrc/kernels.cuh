@@ -58,7 +58,8 @@ cudaError_t launch_mex_doff_smallk(const MexGeo&, const float* x, const float* m
 int mex_tc_nt(const MexGeo&);
 size_t mex_tc_tile_floats(const MexGeo&);
 int mex_tc_doff_splits(const MexGeo&);
-cudaError_t launch_mex_tc_prep(const MexGeo&, bool transposed, const float* src, float* tiles, cudaStream_t);
+// nt: tile width along the rows (0: the width the one-region kernels use for this shape)
+cudaError_t launch_mex_tc_prep(const MexGeo&, bool transposed, const float* src, float* tiles, cudaStream_t, int nt = 0);
 cudaError_t launch_mex_fwd_tc(const MexGeo&, const float* x, const float* tiles, const float* mo, const float* mx, float* y,
                               int* flag, bool interior, cudaStream_t);
 cudaError_t launch_mex_dx_tc(const MexGeo&, const float* x, const float* tiles, const float* mo, const float* mx, const float* y,
@@ -70,6 +71,20 @@ cudaError_t launch_mex_fwd_ws(const MexGeo&, const float* x, const float* tiles,
                               int* flag, bool interior, cudaStream_t);
 cudaError_t launch_mex_dx_ws(const MexGeo&, const float* x, const float* tiles, const float* mo, const float* mx, const float* y,
                              const float* dy, float* dx, int* flag, cudaStream_t);
+// mex_tc_pair.cu -- the same three passes on PAIRS of tiles of sibling regions (8-byte accesses of pixel pairs)
+bool mex_pair_shape(const MexGeo&);
+bool mex_pair_aligned(const void*, const void*, const void*, const void*);
+int mex_pair_nt_fwd(const MexGeo&);
+int mex_pair_nt_dx(const MexGeo&);
+int mex_pair_doff_splits(const MexGeo&);
+cudaError_t launch_mex_fwd_pair(const MexGeo&, const float* x, const float* tiles, const float* mo, const float* mx, float* y,
+                                int* flag, int test_expire, cudaStream_t);
+cudaError_t launch_mex_dx_pair(const MexGeo&, const float* x, const float* tiles, const float* mo, const float* mx, const float* y,
+                               const float* dy, float* dx, int* flag, cudaStream_t);
+cudaError_t launch_mex_doff_pair(const MexGeo&, const float* x, const float* mo, const float* mx, const float* y, const float* dy,
+                                 float* part, int* splits_out, int* flag, cudaStream_t);
+// number of multiprocessors of the current device (148 when no device answers)
+int device_sm_count();
 // forward on the library's fixed device scratch; returns a status code of simnets_b200.h
 int launch_mex_fwd_static(const MexGeo&, const float* x, const float* off, float* y, cudaStream_t);
 cudaError_t launch_mex_dx_tiled(const MexGeo&, const float* x, const float* off, const float* y, const float* dy, float* dx,

@@ -482,8 +482,8 @@ int mex_tc_doff_splits(const MexGeo& g) {
     return int(s);
 }
 
-cudaError_t launch_mex_tc_prep(const MexGeo& g, bool transposed, const float* src, float* tiles, cudaStream_t s) {
-    const int rows = transposed ? g.K : g.M, red = transposed ? g.M : g.K, NT = pick_nt(rows);
+cudaError_t launch_mex_tc_prep(const MexGeo& g, bool transposed, const float* src, float* tiles, cudaStream_t s, int nt) {
+    const int rows = transposed ? g.K : g.M, red = transposed ? g.M : g.K, NT = nt > 0 ? nt : pick_nt(rows);
     const long long total = (long long)g.R * ((rows + NT - 1) / NT) * ((red + kTcKT - 1) / kTcKT) * NT * kTcKT;
     mex_tc_prep<<<int(std::min<long long>((total + 255) / 256, 148LL * 8)), 256, 0, s>>>(g.R, rows, red, pad4(red), NT, src, tiles);
     count_launch();

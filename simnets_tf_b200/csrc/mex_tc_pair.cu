@@ -1,0 +1,911 @@
+// Pair-tile tensor-core MEX kernels: forward, input gradient and offsets gradient for layers whose offsets alternate
+// between two unshared regions along the width (unshared_offset_region = [.., 2] with 1x1 spatial blocks, unit stride,
+// no padding).
+//
+// In such a layer the horizontally adjacent output positions (w, w + 1), w even, belong to the sibling regions 2p and
+// 2p + 1 and read adjacent input pixels.  The kernels of mex_tc_ws.cu give a CTA the positions of ONE region, so every
+// thread reads every other float: half of each 32-byte sector is fetched for nothing, and a thread has 4 bytes in
+// flight per load.  Here a work item is a PAIR of tiles, 128 positions of region 2p and their right-hand neighbours in
+// region 2p + 1: each thread owns one pixel pair, every global access is an aligned 8-byte load or store of both
+// pixels, whole sectors are used once, and the bytes in flight per thread double.  The two tiles of a pair are two
+// independent GEMMs (different offsets operand, separate accumulators in tensor memory) that share their loads.
+//
+// Same GEMM formulation, operand layouts, split-TF32 scheme and role structure as mex_tc_ws.cu (producers -> MMA ->
+// epilogue over mbarrier rings, accumulators double buffered in tensor memory); what differs:
+//   * all eight producer warps fill every stage (a thread converts half of the stage's 16 reduction elements for its
+//     pixel pair) and keep the raw loads of the next DEPTH stages in flight in registers;
+//   * the offsets gradient is persistent too: a CTA owns (region pair, instance tiles, tap tile), walks its share of
+//     the positions in chunks of 16 pixel pairs and keeps its accumulators in tensor memory until the end, so that the
+//     per-CTA partial sums are written once.
+// Every mbarrier wait is bounded and also gives up as soon as another role has failed: a wait that runs out raises the
+// CTA's failure flag, every role leaves its loop, copies in flight are waited for, tensor memory is freed and word 1
+// of the workspace flags reports it (the exact kernels launched behind then redo the work).
+#include "ws.cuh"
+
+namespace simnets {
+
+namespace {
+
+constexpr int kPairProducerWarps = 8;
+constexpr int kPairProducers = kPairProducerWarps * 32;       // 256: thread % 128 = pixel-pair row, thread / 128 = half of the chunk
+constexpr int kPairEpilogueWarps = 8;
+constexpr int kPairMmaWarp = kPairProducerWarps + kPairEpilogueWarps;
+constexpr int kPairLoaderWarp = kPairMmaWarp + 1;
+constexpr int kPairThreads = (kPairLoaderWarp + 1) * 32;      // 576
+
+template <int STAGES>
+struct PairShared {
+    uint64_t full[STAGES];       // producers -> MMA (256 arrivals)
+    uint64_t bfull[STAGES];      // loader -> MMA (1 arrival + bytes)
+    uint64_t empty[STAGES];      // MMA -> producers, loader
+    uint64_t acc_full[2];        // MMA -> epilogue
+    uint64_t acc_empty[2];       // epilogue -> MMA (256 arrivals)
+    uint64_t drain;              // MMA warp: every MMA it issued has completed
+    uint32_t tmem;
+    volatile int failed;
+};
+
+// Bounded wait that also ends when another role of the CTA has given up.
+__device__ __forceinline__ bool pair_wait(volatile int& failed, uint64_t* bar, uint32_t parity, uint32_t tries) {
+    const uint32_t addr = smem_u32(bar);
+    if (mbar_try(addr, parity)) return true;
+    for (uint32_t it = 0; it < tries; ++it) {
+        if (failed) return false;
+        __nanosleep(64);
+        if (mbar_try(addr, parity)) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void bulk_expect(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_raw(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// 16 consecutive tensor-memory columns of this thread's lane (no wait: pair it with tmem_ld_wait)
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Asynchronous global -> shared copy of 8 (or 4) bytes by this thread, zero fill when `valid` is false; copies are
+// grouped with pair_async_commit and awaited with pair_async_wait<N> (at most N groups still pending).
+__device__ __forceinline__ void pair_async8(uint32_t sdst, const void* gsrc, bool valid) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(sdst), "l"(gsrc), "r"(valid ? 8u : 0u) : "memory");
+}
+__device__ __forceinline__ void pair_async4(uint32_t sdst, const void* gsrc, bool valid) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(sdst), "l"(gsrc), "r"(valid ? 4u : 0u) : "memory");
+}
+__device__ __forceinline__ void pair_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void pair_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ float2 ldg2(const float* p) { return __ldg(reinterpret_cast<const float2*>(p)); }
+__device__ __forceinline__ float2 ldcs2(const float* p) { return __ldcs(reinterpret_cast<const float2*>(p)); }
+
+// A pixel pair: the position jl of region 2 * pair and its right-hand neighbour in region 2 * pair + 1.
+struct PairColumn {
+    long long base;     // offset of y[n, 0, pos] for the left pixel (the right one is base + 1); -1: outside the output grid
+    long long gbase;    // offset of dy[n, 0, .] for the left pixel
+    size_t xbase;       // offset of x[n, c0, h0, w0] for the left pixel
+    float mx0, mx1;
+};
+
+__device__ __forceinline__ PairColumn pair_column_of(const MexGeo& g, int pair, long long jl, long long P, const float* __restrict__ mx) {
+    PairColumn p;
+    const Column c = column_of(g, 2 * pair, jl, P, nullptr);
+    p.base = c.base; p.gbase = c.gbase; p.xbase = 0; p.mx0 = p.mx1 = 0.f;
+    if (c.base >= 0) {
+        p.xbase = (((size_t)c.n * g.C + c.c0) * g.H + c.h0) * g.W + c.w0;
+        const float2 m = ldg2(mx + (c.base - (long long)c.n * (g.M - 1) * g.N));      // n * N + pos
+        p.mx0 = m.x; p.mx1 = m.y;
+    }
+    return p;
+}
+
+template <int STAGES>
+__device__ __forceinline__ uint32_t pair_setup(PairShared<STAGES>& sh, uint32_t tmem_cols) {
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sh.full[s], kPairProducers); mbar_init(&sh.bfull[s], 1); mbar_init(&sh.empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&sh.acc_full[b], 1); mbar_init(&sh.acc_empty[b], kPairEpilogueWarps * 32); }
+        mbar_init(&sh.drain, 1);
+        sh.failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if ((threadIdx.x >> 5) == kPairMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem)), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    return sh.tmem;
+}
+
+template <int STAGES>
+__device__ __forceinline__ void pair_teardown(PairShared<STAGES>& sh, uint32_t tmem, uint32_t tmem_cols, int* __restrict__ flag) {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if ((threadIdx.x >> 5) == kPairMmaWarp)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
+    if (threadIdx.x == 0 && sh.failed) atomicExch(&flag[1], 1);
+}
+
+// Stage of the forward and input-gradient kernels: [tile 0: A hi, A lo][tile 1: A hi, A lo][tile 0: B hi, B lo][tile 1: B hi, B lo]
+constexpr int kPairA = kTcPos * kTcKT * 4;                     // one plane of the position operand
+template <int NT> __host__ __device__ constexpr int pair_b_bytes() { return NT * kTcKT * 4; }
+template <int NT> __host__ __device__ constexpr int pair_stage_bytes() { return 4 * kPairA + 4 * pair_b_bytes<NT>(); }
+template <int NT> __host__ __device__ constexpr int pair_stages() { return NT == 128 ? 2 : 3; }
+// bytes of the producers' raw slot ring: DEPTH steps of SLOTS float2 per producer thread
+template <int DEPTH, int SLOTS> __host__ __device__ constexpr int pair_raw_bytes() { return DEPTH * SLOTS * kPairProducers * 8; }
+
+// Loader role: per stage the pre-split offsets tiles of both regions of the pair (two bulk copies on one barrier).
+// `tiles`: [region][row tile][chunk][2 planes][NT x 16].
+template <int NT, int STAGES>
+__device__ __forceinline__ void pair_loader_role(PairShared<STAGES>& sh, unsigned char* dsm, const float* __restrict__ tiles, const WsPlan& plan,
+                                                 int my_items, int row_tiles, int chunks, uint32_t tries) {
+    constexpr int B2 = 2 * pair_b_bytes<NT>(), STAGE_BYTES = pair_stage_bytes<NT>();
+    if ((threadIdx.x & 31) == 0) {
+        WsRing<STAGES> ring = {0, 0u};
+        int issued = 0;
+        for (int li = 0; li < my_items && !sh.failed; ++li) {
+            const WsItem it = ws_item(plan, int(blockIdx.x) + li * int(gridDim.x));       // it.r = region pair
+            const size_t per_region = (size_t)row_tiles * chunks * 2 * NT * kTcKT;
+            const float* src0 = tiles + (size_t)(2 * it.r) * per_region + (size_t)it.mt * chunks * 2 * NT * kTcKT;
+            const float* src1 = src0 + per_region;
+            bool ok = true;
+            for (int c = 0; c < chunks; ++c, src0 += 2 * NT * kTcKT, src1 += 2 * NT * kTcKT) {
+                if (ring.fill >= 1 && !pair_wait(sh.failed, &sh.empty[ring.stage], (ring.fill - 1) & 1u, tries)) { ok = false; break; }
+                unsigned char* dst = dsm + ring.stage * STAGE_BYTES + 4 * kPairA;
+                bulk_expect(&sh.bfull[ring.stage], 2 * B2);
+                bulk_copy_raw(dst, src0, B2, &sh.bfull[ring.stage]);
+                bulk_copy_raw(dst + B2, src1, B2, &sh.bfull[ring.stage]);
+                ring.advance(1);
+                if (issued < STAGES) ++issued;
+            }
+            if (!ok) { sh.failed = 1; break; }
+        }
+        // copies still in flight must land before the CTA may exit: walk back over the last `issued` stages
+        // (plain bounded waits: the failure flag must not cut these short)
+        for (int d = 0; d < issued; ++d) {
+            if (ring.stage == 0) { ring.stage = STAGES; --ring.fill; }
+            --ring.stage;
+            if (!mbar_wait(&sh.bfull[ring.stage], ring.fill & 1u)) sh.failed = 1;
+        }
+    }
+    __syncwarp();
+}
+
+// MMA role: both tiles of the pair per stage; accumulators of item li at columns (li % 2) * 2 NT + tile * NT.
+// skip_commit >= 0 (test hook): the accumulator of that local item is never published.
+template <int NT, int STAGES>
+__device__ __forceinline__ void pair_mma_role(PairShared<STAGES>& sh, unsigned char* dsm, uint32_t tmem, int my_items, int chunks,
+                                              uint32_t tries, int skip_commit) {
+    constexpr int B_BYTES = pair_b_bytes<NT>(), STAGE_BYTES = pair_stage_bytes<NT>();
+    constexpr uint32_t idesc = umma_idesc(NT);
+    constexpr int SBO = (kTcKT / 4) * 128;
+    const int lane = threadIdx.x & 31;
+    WsRing<STAGES> ring = {0, 0u};
+    for (int li = 0; li < my_items; ++li) {
+        const int buf = li & 1;
+        const uint32_t round = uint32_t(li) >> 1;
+        if (sh.failed) break;
+        if (round >= 1 && !pair_wait(sh.failed, &sh.acc_empty[buf], (round - 1) & 1u, tries)) { sh.failed = 1; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        bool ok = true;
+        for (int c = 0; c < chunks; ++c) {
+            const int stage = ring.stage;
+            if (!pair_wait(sh.failed, &sh.full[stage], ring.fill & 1u, tries) || !pair_wait(sh.failed, &sh.bfull[stage], ring.fill & 1u, tries)) { ok = false; break; }
+            ring.advance(1);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (lane == 0) {
+                const uint32_t base = smem_u32(dsm + stage * STAGE_BYTES);
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    const uint32_t a_hi = base + t * 2 * kPairA, a_lo = a_hi + kPairA;
+                    const uint32_t b_hi = base + 4 * kPairA + t * 2 * B_BYTES, b_lo = b_hi + B_BYTES;
+                    const uint32_t tmem_d = tmem + uint32_t((buf * 2 + t) * NT);
+#pragma unroll
+                    for (int ks = 0; ks < kTcKT / 8; ++ks) {
+                        const uint32_t o = ks * 2 * 128;
+                        const uint64_t dah = umma_desc(a_hi + o, 128, SBO), dal = umma_desc(a_lo + o, 128, SBO);
+                        const uint64_t dbh = umma_desc(b_hi + o, 128, SBO), dbl = umma_desc(b_lo + o, 128, SBO);
+                        umma_tf32(tmem_d, dal, dbh, idesc, (c | ks) != 0);
+                        umma_tf32(tmem_d, dah, dbl, idesc, 1);
+                        umma_tf32(tmem_d, dah, dbh, idesc, 1);
+                    }
+                }
+                umma_commit(&sh.empty[stage]);
+            }
+            __syncwarp();
+        }
+        if (!ok) { sh.failed = 1; break; }
+        if (lane == 0 && li != skip_commit) umma_commit(&sh.acc_full[buf]);
+        __syncwarp();
+    }
+    // whatever ended the loop, the tensor memory may be freed only after the MMAs in flight have completed
+    if (lane == 0) umma_commit(&sh.drain);
+    __syncwarp();
+    if (!mbar_wait(&sh.drain, 0)) sh.failed = 1;
+}
+
+// split 8 values into TF32 hi / lo and store them as the two 16-byte groups (k0, k0 + 4) of row `row`
+__device__ __forceinline__ void store_split8(unsigned char* a_hi, unsigned char* a_lo, int row, int k0, const float (&e)[8]) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float4 hi, lo;
+        split_tf32_trunc(e[4 * h], hi.x, lo.x); split_tf32_trunc(e[4 * h + 1], hi.y, lo.y);
+        split_tf32_trunc(e[4 * h + 2], hi.z, lo.z); split_tf32_trunc(e[4 * h + 3], hi.w, lo.w);
+        const int off = core_offset(row, k0 + 4 * h);
+        *reinterpret_cast<float4*>(a_hi + off) = hi;
+        *reinterpret_cast<float4*>(a_lo + off) = lo;
+    }
+}
+
+// Walks a CTA's sequence of (item, chunk) steps for the producers' prefetch cursor.
+struct StepCursor {
+    int li, c;
+    __device__ __forceinline__ bool advance(int chunks) { if (++c == chunks) { c = 0; ++li; return true; } return false; }
+};
+
+// ---- forward ---------------------------------------------------------------------------------------------------
+// item = (region pair, instance tile of NT, tile of 128 pixel pairs); a stage holds 16 taps.
+template <int NT, int DEPTH>
+__global__ void __launch_bounds__(kPairThreads, 1) mex_fwd_pair(MexGeo g, const float* __restrict__ x, const float* __restrict__ tiles,
+                                                               const float* __restrict__ mo, const float* __restrict__ mx,
+                                                               float* __restrict__ y, WsPlan plan, int* __restrict__ flag, int test_expire) {
+    constexpr int STAGES = pair_stages<NT>();
+    constexpr int STAGE_BYTES = pair_stage_bytes<NT>();
+    constexpr uint32_t TMEM_COLS = 4 * NT;
+    extern __shared__ __align__(128) unsigned char dsm[];
+    __shared__ PairShared<STAGES> sh;
+    __shared__ __align__(16) float mo_w[kPairEpilogueWarps][2][NT / 2];
+    if (flag[0]) return;                                // factorisation unsafe: the exact kernels run instead
+
+    const long long P = (long long)g.B * g.rs;
+    const int mtiles = (g.M + NT - 1) / NT, kchunks = (g.K + kTcKT - 1) / kTcKT;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int my_items = plan.items > int(blockIdx.x) ? (plan.items - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x) : 0;
+    const uint32_t tries = test_expire ? 256u : kWaitTries;
+    const uint32_t tmem = pair_setup(sh, TMEM_COLS);
+
+    if (warp < kPairProducerWarps) {
+        // ---------------- producers: thread % 128 = pixel-pair row, thread / 128 = which 8 of the stage's 16 taps
+        const int prow = threadIdx.x % kTcPos, khalf = threadIdx.x / kTcPos;
+        const float a = float(g.eps) * 1.4426950408889634f;
+        const unsigned hw = unsigned(g.H) * unsigned(g.W);
+        const int K = g.K, total = my_items * kchunks;
+        // Raw pixel pairs travel global -> shared by per-thread asynchronous copies, DEPTH stages ahead, into a private
+        // slot ring behind the operand stages ([DEPTH][8 taps][256 threads] float2): no registers are held by loads in
+        // flight, and a thread only ever reads back what it copied itself.
+        float2* raw = reinterpret_cast<float2*>(dsm + STAGES * STAGE_BYTES) + threadIdx.x;
+        struct Meta { float mx0, mx1; int kleft; };          // kleft: taps of this thread's eight that exist (<= 0: dead row)
+        Meta meta[DEPTH];
+        StepCursor cur = {0, 0};
+        PairColumn col;
+        if (my_items > 0) {
+            const WsItem it = ws_item(plan, int(blockIdx.x));
+            col = pair_column_of(g, it.r, (long long)it.jt * kTcPos + prow, P, mx);
+        }
+        auto issue = [&](Meta& m, int d) {       // the chunk under the cursor, then move the cursor
+            const int k0 = cur.c * kTcKT + khalf * 8;
+            m.kleft = col.base >= 0 ? K - k0 : 0;
+            m.mx0 = col.mx0; m.mx1 = col.mx1;
+            const float* xp = x + col.xbase + (size_t)k0 * hw;
+            const uint32_t dst = smem_u32(raw + d * 8 * kPairProducers);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const bool in = u < m.kleft;
+                pair_async8(dst + u * kPairProducers * 8, in ? xp + u * hw : x, in);
+            }
+            if (cur.advance(kchunks) && cur.li < my_items) {
+                const WsItem it = ws_item(plan, int(blockIdx.x) + cur.li * int(gridDim.x));
+                col = pair_column_of(g, it.r, (long long)it.jt * kTcPos + prow, P, mx);
+            }
+        };
+#pragma unroll
+        for (int d = 0; d < DEPTH; ++d) { if (d < total) issue(meta[d], d); pair_async_commit(); }
+        WsRing<STAGES> ring = {0, 0u};
+        bool alive = true;
+        for (int s0 = 0; s0 < total && alive; s0 += DEPTH) {
+#pragma unroll
+            for (int d = 0; d < DEPTH; ++d) {
+                const int step = s0 + d;
+                if (step >= total || !alive) break;
+                pair_async_wait<DEPTH - 1>();                        // this step's copies have landed
+                const Meta m = meta[d];
+                float e0[8], e1[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    // x - mx first: both may be far from zero while their difference is small
+                    const float2 v = raw[(d * 8 + u) * kPairProducers];
+                    e0[u] = u < m.kleft ? ex2_ftz(a * (v.x - m.mx0)) : 0.f;
+                    e1[u] = u < m.kleft ? ex2_ftz(a * (v.y - m.mx1)) : 0.f;
+                }
+                if (step + DEPTH < total) issue(meta[d], d);          // reuses the slot just read; lands DEPTH stages later
+                pair_async_commit();
+                const int stage = ring.stage;
+                if (sh.failed || (ring.fill >= 1 && !pair_wait(sh.failed, &sh.empty[stage], (ring.fill - 1) & 1u, tries))) { sh.failed = 1; alive = false; break; }
+                unsigned char* sA = dsm + stage * STAGE_BYTES;
+                store_split8(sA, sA + kPairA, prow, khalf * 8, e0);
+                store_split8(sA + 2 * kPairA, sA + 3 * kPairA, prow, khalf * 8, e1);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&sh.full[stage]);
+                ring.advance(1);
+            }
+        }
+        pair_async_wait<0>();
+    } else if (warp == kPairLoaderWarp) {
+        pair_loader_role<NT, STAGES>(sh, dsm, tiles, plan, my_items, mtiles, kchunks, tries);
+    } else if (warp == kPairMmaWarp) {
+        pair_mma_role<NT, STAGES>(sh, dsm, tmem, my_items, kchunks, tries, test_expire ? 0 : -1);
+    } else {
+        // ---------------- epilogue: lane = pixel pair, registers = instances of both tiles
+        const int ew = warp - kPairProducerWarps, quarter = warp & 3, half = ew >> 2;
+        float* mow0 = mo_w[ew][0];
+        float* mow1 = mo_w[ew][1];
+        const float inv_eps = 1.f / float(g.eps), k_log = 0.69314718056f * inv_eps, c_add = float(g.cst) * inv_eps;
+        const unsigned Nu = unsigned(g.N);
+        for (int li = 0; li < my_items; ++li) {
+            const int buf = li & 1;
+            if (sh.failed) break;
+            const WsItem it = ws_item(plan, int(blockIdx.x) + li * int(gridDim.x));
+            const int m0 = it.mt * NT + half * (NT / 2);
+            for (int i = lane; i < NT / 2; i += 32) {
+                const bool in = m0 + i < g.M;
+                mow0[i] = in ? __ldg(mo + (2 * it.r) * g.M + m0 + i) : 0.f;
+                mow1[i] = in ? __ldg(mo + (2 * it.r + 1) * g.M + m0 + i) : 0.f;
+            }
+            __syncwarp();
+            const PairColumn col = pair_column_of(g, it.r, (long long)it.jt * kTcPos + quarter * 32 + lane, P, mx);
+            const float cadd0 = col.mx0 + c_add, cadd1 = col.mx1 + c_add;
+            float* yb = y + (col.base >= 0 ? col.base : 0) + (long long)m0 * g.N;
+            if (!pair_wait(sh.failed, &sh.acc_full[buf], (uint32_t(li) >> 1) & 1u, tries)) { sh.failed = 1; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+            for (int c0 = 0; c0 < NT / 2; c0 += 16) {
+                uint32_t v0[16], v1[16];
+                const uint32_t taddr = tmem + uint32_t(buf * 2 * NT + half * (NT / 2) + c0) + (uint32_t(quarter * 32) << 16);
+                tmem_ld16_issue(taddr, v0);
+                tmem_ld16_issue(taddr + NT, v1);
+                tmem_ld_wait();
+                if (col.base >= 0) {
+                    float* yp = yb + (size_t)c0 * Nu;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        if (m0 + c0 + i < g.M) {
+                            float2 o;
+                            o.x = fmaf(lg2_ftz(__uint_as_float(v0[i])), k_log, cadd0 + mow0[c0 + i]);
+                            o.y = fmaf(lg2_ftz(__uint_as_float(v1[i])), k_log, cadd1 + mow1[c0 + i]);
+                            __stcs(reinterpret_cast<float2*>(yp + i * Nu), o);
+                        }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&sh.acc_empty[buf]);
+            __syncwarp();
+        }
+    }
+    pair_teardown(sh, tmem, TMEM_COLS, flag);
+}
+
+// ---- input gradient ----------------------------------------------------------------------------------------------
+// item = (region pair, tap tile of NT, tile of 128 pixel pairs); a stage holds 16 instances.  Q[j, m] = dy * 2^(a ((mx_j
+// - y) + mo_m) + c'); T = Q Eo; dx = Ex * T.  dy may be given pooled 2x2: both pixels of a pair then read one value.
+template <int NT, int DEPTH>
+__global__ void __launch_bounds__(kPairThreads, 1) mex_dx_pair(MexGeo g, const float* __restrict__ x, const float* __restrict__ tiles,
+                                                              const float* __restrict__ mo, const float* __restrict__ mx,
+                                                              const float* __restrict__ y, const float* __restrict__ dy,
+                                                              float* __restrict__ dx, WsPlan plan, int* __restrict__ flag) {
+    constexpr int STAGES = pair_stages<NT>();
+    constexpr int STAGE_BYTES = pair_stage_bytes<NT>();
+    constexpr uint32_t TMEM_COLS = 4 * NT;
+    extern __shared__ __align__(128) unsigned char dsm[];
+    __shared__ PairShared<STAGES> sh;
+    if (flag[0]) return;
+
+    const long long P = (long long)g.B * g.rs;
+    const int ktiles = (g.K + NT - 1) / NT, mchunks = (g.M + kTcKT - 1) / kTcKT;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int my_items = plan.items > int(blockIdx.x) ? (plan.items - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x) : 0;
+    const uint32_t tries = kWaitTries;
+    const uint32_t tmem = pair_setup(sh, TMEM_COLS);
+    const float a = float(g.eps) * 1.4426950408889634f, c2 = float(g.cst) * 1.4426950408889634f;
+
+    if (warp < kPairProducerWarps) {
+        // ---------------- producers: thread % 128 = pixel-pair row, thread / 128 = which 8 of the stage's 16 instances
+        const int prow = threadIdx.x % kTcPos, mhalf = threadIdx.x / kTcPos;
+        const int M = g.M, total = my_items * mchunks;
+        const unsigned Nu = unsigned(g.N), Ngu = unsigned(g.Ng);
+        const bool pooled = g.gp == 2;
+        // raw y and dy pairs: per-thread asynchronous copies DEPTH stages ahead into [DEPTH][2][8 instances][256 threads] float2
+        float2* raw = reinterpret_cast<float2*>(dsm + STAGES * STAGE_BYTES) + threadIdx.x;
+        struct Meta { float mx0, mx1; int mleft, m0, pair; };
+        Meta meta[DEPTH];
+        StepCursor cur = {0, 0};
+        PairColumn col;
+        int pair = 0;
+        if (my_items > 0) {
+            const WsItem it = ws_item(plan, int(blockIdx.x));
+            pair = it.r;
+            col = pair_column_of(g, it.r, (long long)it.jt * kTcPos + prow, P, mx);
+        }
+        auto issue = [&](Meta& m, int d) {
+            const int m0 = cur.c * kTcKT + mhalf * 8;
+            m.m0 = m0; m.pair = pair;
+            m.mleft = col.base >= 0 ? M - m0 : 0;          // a dead row must not read a stranger's y: 0 * 2^(big) = NaN
+            m.mx0 = col.mx0; m.mx1 = col.mx1;
+            const float* yp = y + (col.base >= 0 ? col.base : 0) + (size_t)m0 * Nu;
+            const float* gp = dy + (col.base >= 0 ? col.gbase : 0) + (size_t)m0 * Ngu;
+            const uint32_t dsty = smem_u32(raw + d * 16 * kPairProducers), dstg = dsty + 8 * kPairProducers * 8;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const bool in = u < m.mleft;
+                pair_async8(dsty + u * kPairProducers * 8, in ? yp + u * Nu : y, in);
+                if (pooled) pair_async4(dstg + u * kPairProducers * 8, in ? gp + u * Ngu : dy, in);
+                else pair_async8(dstg + u * kPairProducers * 8, in ? gp + u * Ngu : dy, in);
+            }
+            if (cur.advance(mchunks) && cur.li < my_items) {
+                const WsItem it = ws_item(plan, int(blockIdx.x) + cur.li * int(gridDim.x));
+                pair = it.r;
+                col = pair_column_of(g, it.r, (long long)it.jt * kTcPos + prow, P, mx);
+            }
+        };
+#pragma unroll
+        for (int d = 0; d < DEPTH; ++d) { if (d < total) issue(meta[d], d); pair_async_commit(); }
+        WsRing<STAGES> ring = {0, 0u};
+        bool alive = true;
+        for (int s0 = 0; s0 < total && alive; s0 += DEPTH) {
+#pragma unroll
+            for (int d = 0; d < DEPTH; ++d) {
+                const int step = s0 + d;
+                if (step >= total || !alive) break;
+                pair_async_wait<DEPTH - 1>();
+                const Meta m = meta[d];
+                float q0[8], q1[8];
+                {
+                    const float* mor0 = mo + (2 * m.pair) * M + m.m0;       // offset maxima of these instances (same address in every lane)
+                    const float* mor1 = mor0 + M;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const bool in = u < m.mleft;
+                        const float2 yv = raw[(d * 16 + u) * kPairProducers];
+                        float2 gv = raw[(d * 16 + 8 + u) * kPairProducers];
+                        if (pooled) gv.y = gv.x;
+                        const float m0v = in ? __ldg(mor0 + u) : 0.f, m1v = in ? __ldg(mor1 + u) : 0.f;
+                        q0[u] = in ? gv.x * ex2_ftz(fmaf(a, (m.mx0 - yv.x) + m0v, c2)) : 0.f;
+                        q1[u] = in ? gv.y * ex2_ftz(fmaf(a, (m.mx1 - yv.y) + m1v, c2)) : 0.f;
+                    }
+                }
+                if (step + DEPTH < total) issue(meta[d], d);
+                pair_async_commit();
+                const int stage = ring.stage;
+                if (sh.failed || (ring.fill >= 1 && !pair_wait(sh.failed, &sh.empty[stage], (ring.fill - 1) & 1u, tries))) { sh.failed = 1; alive = false; break; }
+                unsigned char* sA = dsm + stage * STAGE_BYTES;
+                store_split8(sA, sA + kPairA, prow, mhalf * 8, q0);
+                store_split8(sA + 2 * kPairA, sA + 3 * kPairA, prow, mhalf * 8, q1);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&sh.full[stage]);
+                ring.advance(1);
+            }
+        }
+        pair_async_wait<0>();
+    } else if (warp == kPairLoaderWarp) {
+        pair_loader_role<NT, STAGES>(sh, dsm, tiles, plan, my_items, ktiles, mchunks, tries);
+    } else if (warp == kPairMmaWarp) {
+        pair_mma_role<NT, STAGES>(sh, dsm, tmem, my_items, mchunks, tries, -1);
+    } else {
+        // ---------------- epilogue: lane = pixel pair, registers = taps of both tiles
+        const int ew = warp - kPairProducerWarps, quarter = warp & 3, half = ew >> 2;
+        const unsigned hw = unsigned(g.H) * unsigned(g.W);
+        for (int li = 0; li < my_items; ++li) {
+            const int buf = li & 1;
+            if (sh.failed) break;
+            const WsItem it = ws_item(plan, int(blockIdx.x) + li * int(gridDim.x));        // it.mt = tap tile
+            const PairColumn col = pair_column_of(g, it.r, (long long)it.jt * kTcPos + quarter * 32 + lane, P, mx);
+            const int k_first = it.mt * NT + half * (NT / 2);
+            const float* xb = x + col.xbase + (size_t)k_first * hw;
+            float* db = dx + col.xbase + (size_t)k_first * hw;
+            if (!pair_wait(sh.failed, &sh.acc_full[buf], (uint32_t(li) >> 1) & 1u, tries)) { sh.failed = 1; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+            for (int c0 = 0; c0 < NT / 2; c0 += 16) {
+                uint32_t v0[16], v1[16];
+                const uint32_t taddr = tmem + uint32_t(buf * 2 * NT + half * (NT / 2) + c0) + (uint32_t(quarter * 32) << 16);
+                tmem_ld16_issue(taddr, v0);
+                tmem_ld16_issue(taddr + NT, v1);
+                const int kleft = col.base >= 0 ? g.K - k_first - c0 : 0;
+                float2 xr[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) xr[i] = i < kleft ? ldg2(xb + (size_t)(c0 + i) * hw) : make_float2(0.f, 0.f);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    if (i < kleft) {
+                        float2 o;
+                        o.x = ex2_ftz(a * (xr[i].x - col.mx0)) * __uint_as_float(v0[i]);
+                        o.y = ex2_ftz(a * (xr[i].y - col.mx1)) * __uint_as_float(v1[i]);
+                        *reinterpret_cast<float2*>(db + (size_t)(c0 + i) * hw) = o;
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&sh.acc_empty[buf]);
+        }
+    }
+    pair_teardown(sh, tmem, TMEM_COLS, flag);
+}
+
+// ---- offsets gradient --------------------------------------------------------------------------------------------
+// U[m, k] = sum over positions j of Q[m, j] * Ex[k, j] per region.  A CTA owns (region pair, MT instance tiles of 128, one
+// tap tile of NT) and a contiguous share of the pair's positions, walked in chunks of 16 pixel pairs (two MMA k-steps);
+// its 2 x MT accumulators (128 lanes x NT columns each) stay in tensor memory until the last chunk.  Both operands are
+// computed: A = Q^T (rows = instances), B = Ex^T (rows = taps), reduction along positions, stored one float at a time in
+// the K-major core-matrix layout with a leading byte offset of 144, which spreads the 16 positions of a row and the
+// rows m, m + 4 of a warp's two half-warps over all 32 banks.
+constexpr int kDoPairKT = 16, kDoPairLBO = 144, kDoPairSBO = (kDoPairKT / 4) * kDoPairLBO;      // 576
+constexpr int kDoPairThreads = (kPairProducerWarps + 1) * 32;                                    // 288: producers + the MMA warp
+constexpr int kDoPairAPlane = (128 / 8) * kDoPairSBO;                                            // 9216
+template <int NT> __host__ __device__ constexpr int dopair_b_plane() { return (NT / 8) * kDoPairSBO; }
+template <int NT, int MT> __host__ __device__ constexpr int dopair_tile_bytes() { return 2 * MT * kDoPairAPlane + 2 * dopair_b_plane<NT>(); }
+template <int NT, int MT> __host__ __device__ constexpr int dopair_stage_bytes() { return 2 * dopair_tile_bytes<NT, MT>(); }
+template <int NT, int MT> __host__ __device__ constexpr int dopair_stages() { return 2; }
+// the producers' raw slot ring: DEPTH chunks of (2 * QROWS + XROWS) float2 per producer thread
+template <int NT, int MT, int DEPTH> __host__ __device__ constexpr int dopair_raw_bytes() { return DEPTH * (2 * (MT * 128 / 16) + NT / 16) * kPairProducers * 8; }
+
+template <int STAGES>
+struct DoPairShared {
+    uint64_t full[STAGES];       // producers -> MMA (256 arrivals)
+    uint64_t empty[STAGES];      // MMA -> producers
+    uint64_t acc_full;           // MMA -> epilogue (the producers, after their last chunk)
+    uint32_t tmem;
+    volatile int failed;
+};
+
+struct DoPairPlan { int units, mgroups, ktiles, splits; };
+
+template <int NT, int MT, int DEPTH>
+__global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, const float* __restrict__ x, const float* __restrict__ mo,
+                                                                  const float* __restrict__ mx, const float* __restrict__ y,
+                                                                  const float* __restrict__ dy, float* __restrict__ part,
+                                                                  DoPairPlan plan, int* __restrict__ flag) {
+    constexpr int STAGES = dopair_stages<NT, MT>();
+    constexpr int STAGE_BYTES = dopair_stage_bytes<NT, MT>(), TILE_BYTES = dopair_tile_bytes<NT, MT>();
+    constexpr int B_PLANE = dopair_b_plane<NT>();
+    constexpr uint32_t TMEM_COLS = (2 * MT * NT) < 32 ? 32 : 2 * MT * NT;
+    constexpr int QROWS = MT * 128 / 16, XROWS = NT / 16;         // rows of Q / of Ex a producer thread converts per chunk
+    extern __shared__ __align__(128) unsigned char dsm[];
+    __shared__ DoPairShared<STAGES> sh;
+    if (flag[0]) return;
+
+    const long long P = (long long)g.B * g.rs;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int unit = int(blockIdx.x) % plan.units, split = int(blockIdx.x) / plan.units;
+    const int kt = unit % plan.ktiles, mg = (unit / plan.ktiles) % plan.mgroups, pair = unit / (plan.ktiles * plan.mgroups);
+    const long long chunks = (P + kDoPairKT - 1) / kDoPairKT;
+    const long long c_begin = chunks * split / plan.splits, c_end = chunks * (split + 1) / plan.splits;
+    const int nchunks = int(c_end - c_begin);
+    const uint32_t tries = kWaitTries;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sh.full[s], kPairProducers); mbar_init(&sh.empty[s], 1); }
+        mbar_init(&sh.acc_full, 1);
+        sh.failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kPairProducerWarps) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sh.tmem;
+
+    const int M = g.M, K = g.K;
+    const int m_first = mg * MT * 128, k_first = kt * NT;
+
+    if (warp < kPairProducerWarps) {
+        // ---------------- producers: lane % 16 = pixel pair of the chunk; the two half-warps take rows rb and rb + 4
+        const int j = lane & 15;
+        const int rb = (warp & 3) + 4 * (lane >> 4) + 8 * (warp >> 2);         // 0..15: row inside every block of 16 rows
+        const float a = float(g.eps) * 1.4426950408889634f, c2 = float(g.cst) * 1.4426950408889634f;
+        const unsigned Nu = unsigned(g.N), Ngu = unsigned(g.Ng), hw = unsigned(g.H) * unsigned(g.W);
+        const bool pooled = g.gp == 2;
+        // offset maxima of this thread's instances, both regions
+        float mo0[QROWS], mo1[QROWS];
+#pragma unroll
+        for (int i = 0; i < QROWS; ++i) {
+            const int m = m_first + 16 * i + rb;
+            mo0[i] = m < M ? __ldg(mo + (2 * pair) * M + m) : 0.f;
+            mo1[i] = m < M ? __ldg(mo + (2 * pair + 1) * M + m) : 0.f;
+        }
+        // Raw y, dy and x pairs of a chunk travel global -> shared by per-thread asynchronous copies, DEPTH chunks ahead,
+        // into a private slot ring behind the operand stages ([DEPTH][RROWS][256 threads] float2); a thread reads back
+        // only what it copied itself, right before it reuses the slot for a later chunk.
+        constexpr int RROWS = 2 * QROWS + XROWS;
+        float2* raw = reinterpret_cast<float2*>(dsm + STAGES * STAGE_BYTES) + threadIdx.x;
+        struct Meta { float mx0, mx1; bool live; };
+        Meta meta[DEPTH];
+        int lc = 0;                                                     // chunk under the load cursor
+        auto issue = [&](Meta& m, int d) {
+            const PairColumn col = pair_column_of(g, pair, (c_begin + lc) * kDoPairKT + j, P, mx);
+            ++lc;
+            m.live = col.base >= 0; m.mx0 = col.mx0; m.mx1 = col.mx1;
+            const float* yp = y + (m.live ? col.base : 0) + (size_t)(m_first + rb) * Nu;
+            const float* gp = dy + (m.live ? col.gbase : 0) + (size_t)(m_first + rb) * Ngu;
+            const float* xp = x + col.xbase + (size_t)(k_first + rb) * hw;
+            const uint32_t dst = smem_u32(raw + d * RROWS * kPairProducers);
+#pragma unroll
+            for (int i = 0; i < QROWS; ++i) {
+                const bool in = m.live && m_first + 16 * i + rb < M;        // else zero fill: dy = 0 and y = 0, no contribution, no NaN
+                pair_async8(dst + i * kPairProducers * 8, in ? yp + (size_t)(16 * i) * Nu : y, in);
+                if (pooled) pair_async4(dst + (QROWS + i) * kPairProducers * 8, in ? gp + (size_t)(16 * i) * Ngu : dy, in);
+                else pair_async8(dst + (QROWS + i) * kPairProducers * 8, in ? gp + (size_t)(16 * i) * Ngu : dy, in);
+            }
+#pragma unroll
+            for (int i = 0; i < XROWS; ++i) {
+                const bool in = m.live && k_first + 16 * i + rb < K;
+                pair_async8(dst + (2 * QROWS + i) * kPairProducers * 8, in ? xp + (size_t)(16 * i) * hw : x, in);
+            }
+        };
+#pragma unroll
+        for (int d = 0; d < DEPTH; ++d) { if (d < nchunks) issue(meta[d], d); pair_async_commit(); }
+        WsRing<STAGES> ring = {0, 0u};
+        bool alive = true;
+        for (int s0 = 0; s0 < nchunks && alive; s0 += DEPTH) {
+#pragma unroll
+            for (int d = 0; d < DEPTH; ++d) {
+                const int step = s0 + d;
+                if (step >= nchunks || !alive) break;
+                pair_async_wait<DEPTH - 1>();                        // this chunk's copies have landed
+                const Meta m = meta[d];
+                float2 yv[QROWS], gv[QROWS], xv[XROWS];
+#pragma unroll
+                for (int i = 0; i < QROWS; ++i) {
+                    yv[i] = raw[(d * RROWS + i) * kPairProducers];
+                    gv[i] = raw[(d * RROWS + QROWS + i) * kPairProducers];
+                    if (pooled) gv[i].y = gv[i].x;
+                }
+#pragma unroll
+                for (int i = 0; i < XROWS; ++i) xv[i] = raw[(d * RROWS + 2 * QROWS + i) * kPairProducers];
+                if (step + DEPTH < nchunks) issue(meta[d], d);       // reuses the slot just read
+                pair_async_commit();
+                const int stage = ring.stage;
+                if (sh.failed || (ring.fill >= 1 && !pair_wait(sh.failed, &sh.empty[stage], (ring.fill - 1) & 1u, tries))) { sh.failed = 1; alive = false; break; }
+                unsigned char* t0 = dsm + stage * STAGE_BYTES;
+                unsigned char* t1 = t0 + TILE_BYTES;
+                // A: Q^T, MT tiles of 128 rows; plane order per tile of the pair: [MT x (hi, lo)] then B (hi, lo)
+#pragma unroll
+                for (int i = 0; i < QROWS; ++i) {
+                    const int row = 16 * i + rb;                               // row inside the CTA's MT * 128 instances
+                    const int mt = row >> 7, r7 = row & 127;
+                    const int off = mt * 2 * kDoPairAPlane + core_off<kDoPairKT, kDoPairLBO>(r7, j);
+                    const bool in = m.live && m_first + row < M;
+                    float hi, lo;
+                    split_tf32_trunc(in ? gv[i].x * ex2_ftz(fmaf(a, (m.mx0 - yv[i].x) + mo0[i], c2)) : 0.f, hi, lo);
+                    *reinterpret_cast<float*>(t0 + off) = hi;
+                    *reinterpret_cast<float*>(t0 + off + kDoPairAPlane) = lo;
+                    split_tf32_trunc(in ? gv[i].y * ex2_ftz(fmaf(a, (m.mx1 - yv[i].y) + mo1[i], c2)) : 0.f, hi, lo);
+                    *reinterpret_cast<float*>(t1 + off) = hi;
+                    *reinterpret_cast<float*>(t1 + off + kDoPairAPlane) = lo;
+                }
+                // B: Ex^T (zero for a dead column or a tap past K)
+#pragma unroll
+                for (int i = 0; i < XROWS; ++i) {
+                    const int row = 16 * i + rb;
+                    const bool in = m.live && k_first + row < K;
+                    const int off = MT * 2 * kDoPairAPlane + core_off<kDoPairKT, kDoPairLBO>(row, j);
+                    float hi, lo;
+                    split_tf32_trunc(in ? ex2_ftz(a * (xv[i].x - m.mx0)) : 0.f, hi, lo);
+                    *reinterpret_cast<float*>(t0 + off) = hi;
+                    *reinterpret_cast<float*>(t0 + off + B_PLANE) = lo;
+                    split_tf32_trunc(in ? ex2_ftz(a * (xv[i].y - m.mx1)) : 0.f, hi, lo);
+                    *reinterpret_cast<float*>(t1 + off) = hi;
+                    *reinterpret_cast<float*>(t1 + off + B_PLANE) = lo;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&sh.full[stage]);
+                ring.advance(1);
+            }
+        }
+        pair_async_wait<0>();
+        // ---------------- epilogue by the same warps: lane = instance row, registers = taps
+        bool good = alive && !sh.failed;
+        if (good && nchunks > 0) good = pair_wait(sh.failed, &sh.acc_full, 0, tries);
+        if (!good) sh.failed = 1;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (good) {
+            const int quarter = warp & 3, half = warp >> 2;           // lanes of tensor memory this warp may read; half of the 2 * MT accumulators
+#pragma unroll 1
+            for (int acc = half * MT; acc < (half + 1) * MT; ++acc) {            // acc = tile-of-pair * MT + instance tile; half = tile of the pair
+                const int t = acc / MT, mt = acc % MT;
+                const int m = m_first + mt * 128 + quarter * 32 + lane;
+                float* dst = part + (((size_t)split * g.R + (2 * pair + t)) * M + (m < M ? m : 0)) * K + k_first;
+#pragma unroll 1
+                for (int c0 = 0; c0 < NT; c0 += 16) {
+                    uint32_t v[16];
+                    if (nchunks > 0) {
+                        tmem_ld16_issue(tmem + uint32_t(acc * NT + c0) + (uint32_t(quarter * 32) << 16), v);
+                        tmem_ld_wait();
+                    }
+                    if (m < M) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (k_first + c0 + i < K) dst[c0 + i] = nchunks > 0 ? __uint_as_float(v[i]) : 0.f;
+                    }
+                }
+            }
+        }
+    } else {
+        // ---------------- MMA warp
+        constexpr uint32_t idesc = umma_idesc(NT);
+        WsRing<STAGES> ring = {0, 0u};
+        bool ok = true;
+        for (int c = 0; c < nchunks; ++c) {
+            const int stage = ring.stage;
+            if (sh.failed || !pair_wait(sh.failed, &sh.full[stage], ring.fill & 1u, tries)) { ok = false; break; }
+            ring.advance(1);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (lane == 0) {
+                const uint32_t base = smem_u32(dsm + stage * STAGE_BYTES);
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    const uint32_t tb = base + t * TILE_BYTES;
+                    const uint32_t b_hi = tb + MT * 2 * kDoPairAPlane, b_lo = b_hi + B_PLANE;
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const uint32_t a_hi = tb + mt * 2 * kDoPairAPlane, a_lo = a_hi + kDoPairAPlane;
+                        const uint32_t tmem_d = tmem + uint32_t((t * MT + mt) * NT);
+#pragma unroll
+                        for (int ks = 0; ks < kDoPairKT / 8; ++ks) {
+                            const uint32_t o = ks * 2 * kDoPairLBO;
+                            const uint64_t dah = umma_desc(a_hi + o, kDoPairLBO, kDoPairSBO), dal = umma_desc(a_lo + o, kDoPairLBO, kDoPairSBO);
+                            const uint64_t dbh = umma_desc(b_hi + o, kDoPairLBO, kDoPairSBO), dbl = umma_desc(b_lo + o, kDoPairLBO, kDoPairSBO);
+                            umma_tf32(tmem_d, dal, dbh, idesc, (c | ks) != 0);
+                            umma_tf32(tmem_d, dah, dbl, idesc, 1);
+                            umma_tf32(tmem_d, dah, dbh, idesc, 1);
+                        }
+                    }
+                }
+                umma_commit(&sh.empty[stage]);
+            }
+            __syncwarp();
+        }
+        if (!ok) sh.failed = 1;
+        // published even after a failure: the tensor memory may be freed only after the MMAs in flight have completed
+        if (lane == 0 && nchunks > 0) umma_commit(&sh.acc_full);
+        __syncwarp();
+        if (nchunks > 0 && !mbar_wait(&sh.acc_full, 0)) sh.failed = 1;
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == kPairProducerWarps)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    if (threadIdx.x == 0 && sh.failed) atomicExch(&flag[1], 1);
+}
+
+#define PAIR_RUN(KERNEL, THREADS, SMEM, GRID, ...)                               \
+    do {                                                                        \
+        static bool attr_done = false;                                          \
+        const cudaError_t e_ = ws_set_smem(KERNEL, SMEM, attr_done);            \
+        if (e_ != cudaSuccess) return e_;                                       \
+        KERNEL<<<GRID, THREADS, SMEM, s>>>(__VA_ARGS__);                         \
+    } while (0)
+
+inline int pair_nt(int n) { return n > 64 ? 128 : 64; }
+
+template <int NT>
+cudaError_t launch_fwd_pair_nt(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, float* y, int* flag,
+                               int test_expire, cudaStream_t s) {
+    const long long P = (long long)g.B * g.rs;
+    const int mtiles = (g.M + NT - 1) / NT, pairs = g.R / 2;
+    const long long items = ((P + kTcPos - 1) / kTcPos) * mtiles * pairs;
+    if (items >= 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    const WsPlan plan = {int(items), make_fastdiv(pairs), make_fastdiv(mtiles)};
+    const int grid = int(std::min<long long>(items, ws_sm_count()));
+    constexpr int smem = pair_stages<NT>() * pair_stage_bytes<NT>() + pair_raw_bytes<3, 8>();
+    PAIR_RUN((mex_fwd_pair<NT, 3>), kPairThreads, smem, grid, g, x, tiles, mo, mx, y, plan, flag, test_expire);
+    count_launch();
+    return cudaGetLastError();
+}
+
+template <int NT>
+cudaError_t launch_dx_pair_nt(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, const float* y,
+                              const float* dy, float* dx, int* flag, cudaStream_t s) {
+    const long long P = (long long)g.B * g.rs;
+    const int ktiles = (g.K + NT - 1) / NT, pairs = g.R / 2;
+    const long long items = ((P + kTcPos - 1) / kTcPos) * ktiles * pairs;
+    if (items >= 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    const WsPlan plan = {int(items), make_fastdiv(pairs), make_fastdiv(ktiles)};
+    const int grid = int(std::min<long long>(items, ws_sm_count()));
+    constexpr int smem = pair_stages<NT>() * pair_stage_bytes<NT>() + pair_raw_bytes<2, 16>();
+    PAIR_RUN((mex_dx_pair<NT, 2>), kPairThreads, smem, grid, g, x, tiles, mo, mx, y, dy, dx, plan, flag);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// tiling of the offsets gradient: tap tile width and instance tiles per CTA (2 * MT * NT <= 512 columns of tensor memory,
+// and two operand stages plus the raw slot ring within one CTA's shared memory)
+inline void dopair_tiling(const MexGeo& g, int& nt, int& mt) {
+    nt = g.K > 64 ? 128 : 64;       // wider tap tiles or two instance tiles per CTA leave no room for the raw slot ring
+    mt = 1;
+}
+
+inline DoPairPlan dopair_plan(const MexGeo& g) {
+    int nt, mt;
+    dopair_tiling(g, nt, mt);
+    DoPairPlan p;
+    p.mgroups = ((g.M + 127) / 128 + mt - 1) / mt;
+    p.ktiles = (g.K + nt - 1) / nt;
+    p.units = (g.R / 2) * p.mgroups * p.ktiles;
+    const long long chunks = ((long long)g.B * g.rs + kDoPairKT - 1) / kDoPairKT;
+    long long s = ws_sm_count() / p.units;
+    if (s > chunks) s = chunks;
+    if (s < 1) s = 1;
+    p.splits = int(s);
+    return p;
+}
+
+template <int NT, int MT, int DEPTH>
+cudaError_t launch_doff_pair_t(const MexGeo& g, const DoPairPlan& plan, const float* x, const float* mo, const float* mx, const float* y,
+                               const float* dy, float* part, int* flag, cudaStream_t s) {
+    constexpr int smem = dopair_stages<NT, MT>() * dopair_stage_bytes<NT, MT>() + dopair_raw_bytes<NT, MT, DEPTH>();
+    static_assert(smem <= 227 * 1024, "stages and raw ring must fit the shared memory of one CTA");
+    const long long grid = (long long)plan.units * plan.splits;
+    if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    PAIR_RUN((mex_doff_pair<NT, MT, DEPTH>), kDoPairThreads, smem, int(grid), g, x, mo, mx, y, dy, part, plan, flag);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+// Pair tiles serve a layer whose sibling regions alternate along the width (see the head of this file); pointers must
+// allow 8-byte accesses of pixel pairs.
+bool mex_pair_shape(const MexGeo& g) {
+    return g.bh == 1 && g.bw == 1 && g.sh == 1 && g.sw == 1 && g.ph == 0 && g.pw == 0 && g.pc == 0 &&
+           (g.Co - 1) * g.sc + g.bc <= g.C && g.Ho == g.H && g.Wo == g.W && g.unshared && g.ow == 2 && g.W % 2 == 0 &&
+           g.R % 2 == 0 && g.rw * 2 == g.Wo && (g.gp == 1 || g.gp == 2);
+}
+
+bool mex_pair_aligned(const void* a, const void* b, const void* c, const void* d) {
+    return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) | reinterpret_cast<uintptr_t>(d)) & 7u) == 0;
+}
+
+int mex_pair_nt_fwd(const MexGeo& g) { return pair_nt(g.M); }
+int mex_pair_nt_dx(const MexGeo& g) { return pair_nt(g.K); }
+int mex_pair_doff_splits(const MexGeo& g) { return dopair_plan(g).splits; }
+
+cudaError_t launch_mex_fwd_pair(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, float* y,
+                                int* flag, int test_expire, cudaStream_t s) {
+    if (pair_nt(g.M) == 128) return launch_fwd_pair_nt<128>(g, x, tiles, mo, mx, y, flag, test_expire, s);
+    return launch_fwd_pair_nt<64>(g, x, tiles, mo, mx, y, flag, test_expire, s);
+}
+
+cudaError_t launch_mex_dx_pair(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, const float* y,
+                               const float* dy, float* dx, int* flag, cudaStream_t s) {
+    if (pair_nt(g.K) == 128) return launch_dx_pair_nt<128>(g, x, tiles, mo, mx, y, dy, dx, flag, s);
+    return launch_dx_pair_nt<64>(g, x, tiles, mo, mx, y, dy, dx, flag, s);
+}
+
+cudaError_t launch_mex_doff_pair(const MexGeo& g, const float* x, const float* mo, const float* mx, const float* y, const float* dy,
+                                 float* part, int* splits_out, int* flag, cudaStream_t s) {
+    const DoPairPlan plan = dopair_plan(g);
+    *splits_out = plan.splits;
+    int nt, mt;
+    dopair_tiling(g, nt, mt);
+    if (nt == 128) return launch_doff_pair_t<128, 1, 1>(g, plan, x, mo, mx, y, dy, part, flag, s);
+    return launch_doff_pair_t<64, 1, 2>(g, plan, x, mo, mx, y, dy, part, flag, s);
+}
+
+}  // namespace simnets

@@ -374,13 +374,18 @@ __global__ void __launch_bounds__(256) mex_doff_tiled(MexGeo g, const float* __r
 // doff[r][m][k] (+)= Eo[r][m][k] * sum over splits, in split order (deterministic)
 __global__ void __launch_bounds__(256) mex_doff_reduce(long long n, int K, int splits, const float* __restrict__ part, const float* __restrict__ eo,
                                                        float* __restrict__ doff, int accumulate, const int* __restrict__ flag) {
-    if (*flag) return;
+    if (flag[0] | flag[1]) return;               // unsafe spread, or a tensor-core launch gave up on a wait: the exact kernel behind does the work
     for (long long i = blockIdx.x * 256LL + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
         float s = 0.f;
         for (int p = 0; p < splits; ++p) s += part[(size_t)p * n + i];
         s *= eo[(i / K) * pad4(K) + i % K];
         doff[i] = accumulate ? doff[i] + s : s;
     }
+}
+
+// Pair tiles: sibling regions alternate along the width and every tensor allows 8-byte accesses of pixel pairs.
+bool use_pair_kernels(const MexGeo& g, uint32_t flags, const void* a, const void* b, const void* c, const void* d) {
+    return !(flags & (SIMNETS_FLAG_MEX_NO_PAIR_TILES | SIMNETS_FLAG_MEX_TC_ONE_TILE)) && mex_pair_shape(g) && mex_pair_aligned(a, b, c, d);
 }
 
 bool blocks_disjoint(const MexGeo& g) { return g.sc >= g.bc && g.sh >= g.bh && g.sw >= g.bw; }
@@ -453,6 +458,13 @@ cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* o
     cudaError_t e = run_prepasses(g, w, x, off, s);
     if (e != cudaSuccess) return e;
     if (use_tc_kernels(g, flags)) {
+        if (use_pair_kernels(g, flags, x, y, y, y)) {
+            e = launch_mex_tc_prep(g, false, w.eo, w.tc_tiles, s, mex_pair_nt_fwd(g));
+            if (e != cudaSuccess) return e;
+            e = launch_mex_fwd_pair(g, x, w.tc_tiles, w.mo, w.mx, y, w.flag, (flags & SIMNETS_FLAG_MEX_TEST_EXPIRE_WAIT) != 0, s);
+            if (e != cudaSuccess) return e;
+            return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);
+        }
         e = launch_mex_tc_prep(g, false, w.eo, w.tc_tiles, s);
         if (e != cudaSuccess) return e;
         e = (flags & SIMNETS_FLAG_MEX_TC_ONE_TILE) ? launch_mex_fwd_tc(g, x, w.tc_tiles, w.mo, w.mx, y, w.flag, patches_inside_input(g), s)
@@ -531,6 +543,13 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
         if (e != cudaSuccess) return e;
         return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
     }
+    if (use_tc_kernels(g, flags) && use_pair_kernels(g, flags, x, y, dy, dx)) {
+        e = launch_mex_tc_prep(g, true, w.eot, w.tc_tiles, s, mex_pair_nt_dx(g));
+        if (e != cudaSuccess) return e;
+        e = launch_mex_dx_pair(g, x, w.tc_tiles, w.mo, w.mx, y, dy, dx, w.flag, s);
+        if (e != cudaSuccess) return e;
+        return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
+    }
     if (use_tc_kernels(g, flags)) {
         e = launch_mex_tc_prep(g, true, w.eot, w.tc_tiles, s);
         if (e != cudaSuccess) return e;
@@ -567,8 +586,9 @@ cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* 
     cudaError_t e = (prepped || forward_primes_workspace(g, flags)) ? cudaSuccess : run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags));
     if (e != cudaSuccess) return e;
     if (use_tc_kernels(g, flags)) {
-        const int tsplits = mex_tc_doff_splits(g);
-        e = launch_mex_doff_tc(g, x, w.mo, w.mx, y, dy, w.part, tsplits, w.flag, s);
+        int tsplits = mex_tc_doff_splits(g);
+        e = use_pair_kernels(g, flags, x, y, dy, dy) ? launch_mex_doff_pair(g, x, w.mo, w.mx, y, dy, w.part, &tsplits, w.flag, s)
+                                                     : launch_mex_doff_tc(g, x, w.mo, w.mx, y, dy, w.part, tsplits, w.flag, s);
         if (e != cudaSuccess) return e;
         const long long n = (long long)g.R * g.M * g.K;
         mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, g.K, tsplits, w.part, w.eo, doff, accumulate, w.flag);

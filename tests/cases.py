@@ -84,7 +84,7 @@ def _sim_small():
 
 SIM_SMALL = _sim_small()
 
-# BASELINE configs (synthetic stand-ins): cfg1 at full size, cfg4 variants at a sub-batch,
+# BASELINE configs (seeded synthetic stand-ins): cfg1 at full size, cfg4 variants at a sub-batch,
 # cfg5's first layer at a sub-batch.
 SIM_CONFIGS = [
     sim_case("cfg1", (64, 1, 28, 28), 32, "L2", (2, 2), (2, 2), (2, 2), norm=True, ignore_nan=True, oob=NAN, seed=0, x_dist="uniform"),
@@ -184,6 +184,19 @@ MEX_CONFIGS = [
     mex_case("cfg3_mex4_sub", (6, 256, 2, 2), 512, (256, 1, 1), (256, 1, 1), softmax=True, unshared_region=(2,), seed=8, normalize=True),
     mex_case("tc_many_tiles", (8, 48, 50, 50), 48, (48, 1, 1), (48, 1, 1), softmax=True, unshared=False, shared_region=(-1,), seed=6, normalize=True),
     mex_case("cfg5_head_sub", (4, 512, 4, 4), 10, (512, 4, 4), (1, 1, 1), softmax=True, seed=4, normalize=True),
+]
+
+
+# Layers whose unshared regions alternate along the width run on the pair-tile tensor-core kernels: instance and tap
+# counts that are not multiples of the 16-wide chunks or of the tile widths, two-pixel-wide maps, several channel
+# blocks, a negative epsilon and a position count that is not a multiple of a tile.
+MEX_PAIR = [
+    mex_case("pair_tails", (5, 70, 6, 10), 90, (70, 1, 1), (70, 1, 1), eps=0.7, softmax=True, unshared_region=(2,), seed=401, normalize=True),
+    mex_case("pair_channel_blocks", (3, 96, 4, 6), 64, (48, 1, 1), (48, 1, 1), softmax=True, unshared_region=(2,), seed=402, normalize=True),
+    mex_case("pair_two_wide", (9, 64, 3, 2), 130, (64, 1, 1), (64, 1, 1), softmax=False, unshared_region=(1, 1, 2), seed=403),
+    mex_case("pair_eps_neg", (4, 52, 8, 8), 60, (52, 1, 1), (52, 1, 1), eps=-1.5, softmax=True, unshared_region=(2,), seed=404),
+    mex_case("pair_short_patches", (6, 24, 8, 12), 80, (24, 1, 1), (24, 1, 1), softmax=True, unshared_region=(2,), seed=405, normalize=True),
+    mex_case("pair_long_patches", (3, 300, 4, 4), 150, (300, 1, 1), (300, 1, 1), softmax=True, unshared_region=(2,), seed=406, normalize=True),
 ]
 
 

@@ -37,6 +37,67 @@ def test_tensor_core_shapes_one_tile_kernels(port, c):
     gpu_util.check_mex(port, c, flags=abi.FLAG_MEX_TC_ONE_TILE, f64_tiebreak=True)
 
 
+_PAIRED = [c for c in cases.MEX_SMALL + cases.MEX_CONFIGS if c["name"].startswith(("tc_", "cfg5_mex", "cfg2", "cfg3_mex"))] + cases.MEX_PAIR
+
+
+@pytest.mark.parametrize("c", cases.MEX_PAIR, ids=lambda c: c["name"])
+def test_pair_tile_shapes(port, c):
+    """Layers whose sibling regions alternate along the width take the pair-tile kernels (8-byte accesses of pixel pairs)."""
+    gpu_util.check_mex(port, c, f64_tiebreak=True)
+    gpu_util.check_mex_pooled_dy(port, c)          # (None for an odd output height)
+
+
+@pytest.mark.parametrize("c", _PAIRED, ids=lambda c: c["name"])
+def test_pair_tile_shapes_on_one_region_kernels(port, c):
+    """SIMNETS_FLAG_MEX_NO_PAIR_TILES keeps such layers on the kernels that give a CTA the positions of one region."""
+    gpu_util.check_mex(port, c, flags=abi.FLAG_MEX_NO_PAIR_TILES, f64_tiebreak=True)
+    gpu_util.check_mex_pooled_dy(port, c, flags=abi.FLAG_MEX_NO_PAIR_TILES)
+
+
+def test_pair_tiles_need_8_byte_alignment(port):
+    """Tensors that start on an odd float cannot be read as pixel pairs: the library takes the one-region kernels."""
+    c = cases.MEX_PAIR[0]
+    d = cases.mex_desc(c)
+    x, off, dy = cases.mex_inputs(c, port.mex_offsets_shape(d), port.mex_out_shape(d))
+    ry = port.mex_forward(d, x, off)
+
+    def odd(a):
+        buf = torch.empty(a.size + 1, device="cuda")
+        v = buf[1:].view(a.shape)
+        v.copy_(torch.from_numpy(a))
+        assert v.data_ptr() % 8 == 4 and v.is_contiguous()
+        return v
+    xd, dyd, ryd = odd(x), odd(dy), odd(ry)
+    od = gpu_util.dev(off)
+    attrs = cases.mex_attrs(c)
+    cases.assert_parity(mex_ops.mex_forward(xd, od, c["M"], **attrs).cpu().numpy(), ry, what="y")
+    dx, doff = mex_ops.mex_backward(xd, od, ryd, dyd, c["M"], **attrs)
+    cases.assert_parity(dx.cpu().numpy(), port.mex_input_grad(d, x, off, ry, dy), what="dx")
+    cases.assert_parity(doff.cpu().numpy(), port.mex_offsets_grad(d, x, off, ry, dy), tol=2e-5, what="doff")
+
+
+def test_a_wait_that_runs_out_is_reported_and_recomputed(port, cuda_lib):
+    """SIMNETS_FLAG_MEX_TEST_EXPIRE_WAIT: the tensor-core forward kernel's MMA role withholds one completion signal and
+    all waits are short, so a bounded wait runs out.  The kernel must return (no hang, no fault), word 1 of the
+    workspace status must be set, and the output must still be right because the exact kernel behind redoes it."""
+    import ctypes as C
+    c = next(c for c in cases.MEX_CONFIGS if c["name"] == "cfg5_mex1_sub")
+    d = cases.mex_desc(c)
+    x, off, _ = cases.mex_inputs(c, port.mex_offsets_shape(d), port.mex_out_shape(d))
+    xd, od = gpu_util.dev(x), gpu_util.dev(off)
+    attrs = cases.mex_attrs(c)
+    ry = port.mex_forward(d, x, off)
+    stream = torch.cuda.current_stream().cuda_stream
+    status = (C.c_int32 * 2)(7, 7)
+    for flags, want in ((0, 0), (abi.FLAG_MEX_TEST_EXPIRE_WAIT, 1), (0, 0)):
+        ws = mex_ops.mex_layer_workspace(xd, c["M"], flags=flags, **attrs)
+        y = mex_ops.mex_forward(xd, od, c["M"], flags=flags, workspace=ws, **attrs)
+        assert cuda_lib.simnets_mex_workspace_status(ws.data_ptr(), stream, status) == 0
+        torch.cuda.synchronize()
+        assert (status[0], status[1]) == (0, want)
+        cases.assert_parity(y.cpu().numpy(), ry, what="y with flags %d" % flags)
+
+
 @pytest.mark.parametrize("c", cases.MEX_SMALL[::3], ids=lambda c: c["name"])
 def test_small_grid_float64(port, c):
     gpu_util.check_mex(port, c, dtype=abi.F64, tol=1e-12)
