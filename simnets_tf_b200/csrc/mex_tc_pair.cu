@@ -45,14 +45,19 @@ struct PairShared {
     volatile int failed;
 };
 
-// Bounded wait that also ends when another role of the CTA has given up.
-__device__ __forceinline__ bool pair_wait(volatile int& failed, uint64_t* bar, uint32_t parity, uint32_t tries) {
+// Bounded wait that also ends when another role of the CTA has given up.  A failed try is followed by a sleep that
+// doubles up to `cap_ns`: a polling warp takes issue slots from the warps that do the work (with a fixed 64 ns sleep
+// the polling loops of the ten waiting warps were half of all instructions executed), so roles that can afford a
+// late wake-up (the epilogue behind a double-buffered accumulator) pass a long cap, the MMA warp a short one.
+__device__ __forceinline__ bool pair_wait(volatile int& failed, uint64_t* bar, uint32_t parity, uint32_t tries, uint32_t cap_ns = 256) {
     const uint32_t addr = smem_u32(bar);
     if (mbar_try(addr, parity)) return true;
+    uint32_t ns = 32;
     for (uint32_t it = 0; it < tries; ++it) {
         if (failed) return false;
-        __nanosleep(64);
+        __nanosleep(ns);
         if (mbar_try(addr, parity)) return true;
+        ns = ns < cap_ns ? ns * 2 : cap_ns;
     }
     return false;
 }
@@ -83,6 +88,9 @@ __device__ __forceinline__ void pair_async8(uint32_t sdst, const void* gsrc, boo
 }
 __device__ __forceinline__ void pair_async4(uint32_t sdst, const void* gsrc, bool valid) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(sdst), "l"(gsrc), "r"(valid ? 4u : 0u) : "memory");
+}
+__device__ __forceinline__ void pair_async16(uint32_t sdst, const void* gsrc, bool valid) {      // L2 only: streamed once
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(sdst), "l"(gsrc), "r"(valid ? 16u : 0u) : "memory");
 }
 __device__ __forceinline__ void pair_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void pair_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -162,7 +170,7 @@ __device__ __forceinline__ void pair_loader_role(PairShared<STAGES>& sh, unsigne
             const float* src1 = src0 + per_region;
             bool ok = true;
             for (int c = 0; c < chunks; ++c, src0 += 2 * NT * kTcKT, src1 += 2 * NT * kTcKT) {
-                if (ring.fill >= 1 && !pair_wait(sh.failed, &sh.empty[ring.stage], (ring.fill - 1) & 1u, tries)) { ok = false; break; }
+                if (ring.fill >= 1 && !pair_wait(sh.failed, &sh.empty[ring.stage], (ring.fill - 1) & 1u, tries, 512)) { ok = false; break; }
                 unsigned char* dst = dsm + ring.stage * STAGE_BYTES + 4 * kPairA;
                 bulk_expect(&sh.bfull[ring.stage], 2 * B2);
                 bulk_copy_raw(dst, src0, B2, &sh.bfull[ring.stage]);
@@ -202,7 +210,7 @@ __device__ __forceinline__ void pair_mma_role(PairShared<STAGES>& sh, unsigned c
         bool ok = true;
         for (int c = 0; c < chunks; ++c) {
             const int stage = ring.stage;
-            if (!pair_wait(sh.failed, &sh.full[stage], ring.fill & 1u, tries) || !pair_wait(sh.failed, &sh.bfull[stage], ring.fill & 1u, tries)) { ok = false; break; }
+            if (!pair_wait(sh.failed, &sh.full[stage], ring.fill & 1u, tries, 64) || !pair_wait(sh.failed, &sh.bfull[stage], ring.fill & 1u, tries, 64)) { ok = false; break; }
             ring.advance(1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) {
@@ -235,6 +243,10 @@ __device__ __forceinline__ void pair_mma_role(PairShared<STAGES>& sh, unsigned c
     __syncwarp();
     if (!mbar_wait(&sh.drain, 0)) sh.failed = 1;
 }
+
+// TF32 split without a conversion: the hi plane may hold v itself (the tensor core reads the sign, the exponent and the top
+// 10 mantissa bits and ignores the rest); lo = v minus that truncation, exactly.
+__device__ __forceinline__ float tf32_lo(float v) { return v - __uint_as_float(__float_as_uint(v) & 0xffffe000u); }
 
 // split 8 values into TF32 hi / lo and store them as the two 16-byte groups (k0, k0 + 4) of row `row`
 __device__ __forceinline__ void store_split8(unsigned char* a_hi, unsigned char* a_lo, int row, int k0, const float (&e)[8]) {
@@ -367,7 +379,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) mex_fwd_pair(MexGeo g, const 
             const PairColumn col = pair_column_of(g, it.r, (long long)it.jt * kTcPos + quarter * 32 + lane, P, mx);
             const float cadd0 = col.mx0 + c_add, cadd1 = col.mx1 + c_add;
             float* yb = y + (col.base >= 0 ? col.base : 0) + (long long)m0 * g.N;
-            if (!pair_wait(sh.failed, &sh.acc_full[buf], (uint32_t(li) >> 1) & 1u, tries)) { sh.failed = 1; break; }
+            if (!pair_wait(sh.failed, &sh.acc_full[buf], (uint32_t(li) >> 1) & 1u, tries, 1024)) { sh.failed = 1; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (int c0 = 0; c0 < NT / 2; c0 += 16) {
@@ -400,95 +412,89 @@ __global__ void __launch_bounds__(kPairThreads, 1) mex_fwd_pair(MexGeo g, const 
 // ---- input gradient ----------------------------------------------------------------------------------------------
 // item = (region pair, tap tile of NT, tile of 128 pixel pairs); a stage holds 16 instances.  Q[j, m] = dy * 2^(a ((mx_j
 // - y) + mo_m) + c'); T = Q Eo; dx = Ex * T.  dy may be given pooled 2x2: both pixels of a pair then read one value.
-template <int NT, int DEPTH>
-__global__ void __launch_bounds__(kPairThreads, 1) mex_dx_pair(MexGeo g, const float* __restrict__ x, const float* __restrict__ tiles,
-                                                              const float* __restrict__ mo, const float* __restrict__ mx,
-                                                              const float* __restrict__ y, const float* __restrict__ dy,
-                                                              float* __restrict__ dx, WsPlan plan, int* __restrict__ flag) {
+//
+// Roles: 4 raw-loader warps (thread = pixel-pair row) issue the asynchronous copies of y and dy, DEPTH stages ahead, into a
+// slot ring ([DEPTH][y, dy][16 instances][128 rows] float2) and publish a slot through an mbarrier that their copies
+// arrive on; 8 converter warps turn a slot into the split-TF32 position operand of a stage; 1 thread issues the MMAs;
+// 1 thread copies the offsets operand; 8 epilogue warps finish dx.  Loading has warps of its own because a warp that
+// issues copies faster than memory takes them stalls in the load/store unit: measured on the converters of an earlier
+// version, 38 % of their time went into issuing copies, during which they converted nothing, and while they converted
+// nothing was being requested from memory.
+constexpr int kDxRawWarps = 4;
+constexpr int kDxFirstRawWarp = kPairLoaderWarp + 1;
+constexpr int kDxThreads = (kDxFirstRawWarp + kDxRawWarps) * 32;      // 704
+constexpr int kDxSlotBytes = 2 * kTcKT * kTcPos * 8;                   // 32 KiB: y and dy, 16 instances x 128 rows of float2
+
+__device__ __forceinline__ void async_arrive_noinc(uint64_t* bar) {   // arrives once this thread's earlier asynchronous copies have landed
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 8 consecutive tensor-memory columns of this thread's lane (no wait: pair it with tmem_ld_wait)
+__device__ __forceinline__ void tmem_ld8_issue(uint32_t taddr, uint32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr) : "memory");
+}
+
+// WIDE: every tensor is 16-byte aligned and the map width is a multiple of 4, so two neighbouring pixel pairs of a tile are
+// 16 contiguous bytes: a raw loader then copies two rows at a time (half the copy instructions).
+template <int NT, int DEPTH, bool WIDE>
+__global__ void __launch_bounds__(kDxThreads, 1) mex_dx_pair(MexGeo g, const float* __restrict__ x, const float* __restrict__ tiles,
+                                                            const float* __restrict__ mo, const float* __restrict__ mx,
+                                                            const float* __restrict__ y, const float* __restrict__ dy,
+                                                            float* __restrict__ dx, WsPlan plan, int* __restrict__ flag) {
     constexpr int STAGES = pair_stages<NT>();
     constexpr int STAGE_BYTES = pair_stage_bytes<NT>();
     constexpr uint32_t TMEM_COLS = 4 * NT;
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ PairShared<STAGES> sh;
+    __shared__ uint64_t raw_full[DEPTH], raw_empty[DEPTH];
     if (flag[0]) return;
 
     const long long P = (long long)g.B * g.rs;
     const int ktiles = (g.K + NT - 1) / NT, mchunks = (g.M + kTcKT - 1) / kTcKT;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int my_items = plan.items > int(blockIdx.x) ? (plan.items - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x) : 0;
+    const int total = my_items * mchunks;
     const uint32_t tries = kWaitTries;
-    const uint32_t tmem = pair_setup(sh, TMEM_COLS);
+    if (threadIdx.x == 0)
+        for (int d = 0; d < DEPTH; ++d) { mbar_init(&raw_full[d], kDxRawWarps * 32); mbar_init(&raw_empty[d], kPairProducers); }
+    const uint32_t tmem = pair_setup(sh, TMEM_COLS);          // (its fence and barrier publish the two rings above as well)
     const float a = float(g.eps) * 1.4426950408889634f, c2 = float(g.cst) * 1.4426950408889634f;
+    unsigned char* rawbase = dsm + STAGES * STAGE_BYTES;
 
     if (warp < kPairProducerWarps) {
-        // ---------------- producers: thread % 128 = pixel-pair row, thread / 128 = which 8 of the stage's 16 instances
+        // ---------------- converters: thread % 128 = pixel-pair row, thread / 128 = which 8 of the stage's 16 instances
         const int prow = threadIdx.x % kTcPos, mhalf = threadIdx.x / kTcPos;
-        const int M = g.M, total = my_items * mchunks;
-        const unsigned Nu = unsigned(g.N), Ngu = unsigned(g.Ng);
+        const int M = g.M;
         const bool pooled = g.gp == 2;
-        // raw y and dy pairs: per-thread asynchronous copies DEPTH stages ahead into [DEPTH][2][8 instances][256 threads] float2
-        float2* raw = reinterpret_cast<float2*>(dsm + STAGES * STAGE_BYTES) + threadIdx.x;
-        struct Meta { float mx0, mx1; int mleft, m0, pair; };
-        Meta meta[DEPTH];
-        StepCursor cur = {0, 0};
-        PairColumn col;
-        int pair = 0;
-        if (my_items > 0) {
-            const WsItem it = ws_item(plan, int(blockIdx.x));
-            pair = it.r;
-            col = pair_column_of(g, it.r, (long long)it.jt * kTcPos + prow, P, mx);
-        }
-        auto issue = [&](Meta& m, int d) {
-            const int m0 = cur.c * kTcKT + mhalf * 8;
-            m.m0 = m0; m.pair = pair;
-            m.mleft = col.base >= 0 ? M - m0 : 0;          // a dead row must not read a stranger's y: 0 * 2^(big) = NaN
-            m.mx0 = col.mx0; m.mx1 = col.mx1;
-            const float* yp = y + (col.base >= 0 ? col.base : 0) + (size_t)m0 * Nu;
-            const float* gp = dy + (col.base >= 0 ? col.gbase : 0) + (size_t)m0 * Ngu;
-            const uint32_t dsty = smem_u32(raw + d * 16 * kPairProducers), dstg = dsty + 8 * kPairProducers * 8;
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const bool in = u < m.mleft;
-                pair_async8(dsty + u * kPairProducers * 8, in ? yp + u * Nu : y, in);
-                if (pooled) pair_async4(dstg + u * kPairProducers * 8, in ? gp + u * Ngu : dy, in);
-                else pair_async8(dstg + u * kPairProducers * 8, in ? gp + u * Ngu : dy, in);
-            }
-            if (cur.advance(mchunks) && cur.li < my_items) {
-                const WsItem it = ws_item(plan, int(blockIdx.x) + cur.li * int(gridDim.x));
-                pair = it.r;
-                col = pair_column_of(g, it.r, (long long)it.jt * kTcPos + prow, P, mx);
-            }
-        };
-#pragma unroll
-        for (int d = 0; d < DEPTH; ++d) { if (d < total) issue(meta[d], d); pair_async_commit(); }
         WsRing<STAGES> ring = {0, 0u};
-        bool alive = true;
-        for (int s0 = 0; s0 < total && alive; s0 += DEPTH) {
-#pragma unroll
-            for (int d = 0; d < DEPTH; ++d) {
-                const int step = s0 + d;
-                if (step >= total || !alive) break;
-                pair_async_wait<DEPTH - 1>();
-                const Meta m = meta[d];
+        WsRing<DEPTH> slot = {0, 0u};
+        for (int li = 0; li < my_items && !sh.failed; ++li) {
+            const WsItem it = ws_item(plan, int(blockIdx.x) + li * int(gridDim.x));
+            const PairColumn col = pair_column_of(g, it.r, (long long)it.jt * kTcPos + prow, P, mx);
+            const float* mor0 = mo + (2 * it.r) * M + mhalf * 8;              // offset maxima (same address in every lane)
+            bool ok = true;
+            for (int c = 0; c < mchunks; ++c) {
+                const int mleft = col.base >= 0 ? M - c * kTcKT - mhalf * 8 : 0;     // a dead row contributes nothing
+                if (!pair_wait(sh.failed, &raw_full[slot.stage], slot.fill & 1u, tries)) { ok = false; break; }
+                const float2* ry = reinterpret_cast<const float2*>(rawbase + slot.stage * kDxSlotBytes) + (mhalf * 8) * kTcPos + prow;
+                const float2* rg = ry + kTcKT * kTcPos;
                 float q0[8], q1[8];
-                {
-                    const float* mor0 = mo + (2 * m.pair) * M + m.m0;       // offset maxima of these instances (same address in every lane)
-                    const float* mor1 = mor0 + M;
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const bool in = u < m.mleft;
-                        const float2 yv = raw[(d * 16 + u) * kPairProducers];
-                        float2 gv = raw[(d * 16 + 8 + u) * kPairProducers];
-                        if (pooled) gv.y = gv.x;
-                        const float m0v = in ? __ldg(mor0 + u) : 0.f, m1v = in ? __ldg(mor1 + u) : 0.f;
-                        q0[u] = in ? gv.x * ex2_ftz(fmaf(a, (m.mx0 - yv.x) + m0v, c2)) : 0.f;
-                        q1[u] = in ? gv.y * ex2_ftz(fmaf(a, (m.mx1 - yv.y) + m1v, c2)) : 0.f;
-                    }
+                for (int u = 0; u < 8; ++u) {
+                    const bool in = u < mleft;
+                    const float2 yv = ry[u * kTcPos];
+                    float2 gv = rg[u * kTcPos];
+                    if (pooled) gv.y = gv.x;
+                    const float m0v = in ? __ldg(mor0 + c * kTcKT + u) : 0.f, m1v = in ? __ldg(mor0 + M + c * kTcKT + u) : 0.f;
+                    q0[u] = in ? gv.x * ex2_ftz(fmaf(a, (col.mx0 - yv.x) + m0v, c2)) : 0.f;
+                    q1[u] = in ? gv.y * ex2_ftz(fmaf(a, (col.mx1 - yv.y) + m1v, c2)) : 0.f;
                 }
-                if (step + DEPTH < total) issue(meta[d], d);
-                pair_async_commit();
+                mbar_arrive(&raw_empty[slot.stage]);                          // the slot may be refilled
+                slot.advance(1);
                 const int stage = ring.stage;
-                if (sh.failed || (ring.fill >= 1 && !pair_wait(sh.failed, &sh.empty[stage], (ring.fill - 1) & 1u, tries))) { sh.failed = 1; alive = false; break; }
+                if (ring.fill >= 1 && !pair_wait(sh.failed, &sh.empty[stage], (ring.fill - 1) & 1u, tries)) { ok = false; break; }
                 unsigned char* sA = dsm + stage * STAGE_BYTES;
                 store_split8(sA, sA + kPairA, prow, mhalf * 8, q0);
                 store_split8(sA + 2 * kPairA, sA + 3 * kPairA, prow, mhalf * 8, q1);
@@ -496,14 +502,70 @@ __global__ void __launch_bounds__(kPairThreads, 1) mex_dx_pair(MexGeo g, const f
                 mbar_arrive(&sh.full[stage]);
                 ring.advance(1);
             }
+            if (!ok) { sh.failed = 1; break; }
         }
-        pair_async_wait<0>();
     } else if (warp == kPairLoaderWarp) {
         pair_loader_role<NT, STAGES>(sh, dsm, tiles, plan, my_items, ktiles, mchunks, tries);
     } else if (warp == kPairMmaWarp) {
         pair_mma_role<NT, STAGES>(sh, dsm, tmem, my_items, mchunks, tries, -1);
+    } else if (warp >= kDxFirstRawWarp) {
+        // ---------------- raw loaders.  8-byte copies: thread = pixel-pair row, all 16 instances of a stage.  WIDE: thread =
+        // (two neighbouring rows, half of the instances), 16-byte copies.
+        const int lt = int(threadIdx.x) - kDxFirstRawWarp * 32;
+        const int row = WIDE ? 2 * (lt & 63) : lt, mfirst = WIDE ? 8 * (lt >> 6) : 0;
+        constexpr int NM = WIDE ? 8 : 16;
+        const int M = g.M;
+        const unsigned Nu = unsigned(g.N), Ngu = unsigned(g.Ng);
+        const bool pooled = g.gp == 2;
+        WsRing<DEPTH> slot = {0, 0u};
+        for (int li = 0; li < my_items && !sh.failed; ++li) {
+            const WsItem it = ws_item(plan, int(blockIdx.x) + li * int(gridDim.x));
+            const Column col = column_of(g, 2 * it.r, (long long)it.jt * kTcPos + row, P, nullptr);
+            const bool live = col.base >= 0;
+            const float* yp = y + (live ? col.base : 0) + (size_t)mfirst * Nu;
+            const float* gp = dy + (live ? col.gbase : 0) + (size_t)mfirst * Ngu;
+            bool ok = true;
+            for (int c = 0; c < mchunks; ++c, yp += (size_t)kTcKT * Nu, gp += (size_t)kTcKT * Ngu) {
+                if (slot.fill >= 1 && !pair_wait(sh.failed, &raw_empty[slot.stage], (slot.fill - 1) & 1u, tries)) { ok = false; break; }
+                const uint32_t dsty = smem_u32(rawbase + slot.stage * kDxSlotBytes) + (mfirst * kTcPos + row) * 8, dstg = dsty + kTcKT * kTcPos * 8;
+                const int mleft = live ? M - c * kTcKT - mfirst : 0;         // a dead row must not read a stranger's y: zero fill
+                if (mleft >= NM) {
+#pragma unroll
+                    for (int u = 0; u < NM; ++u) {
+                        if (WIDE) {
+                            pair_async16(dsty + u * kTcPos * 8, yp + u * Nu, true);
+                            if (pooled) { pair_async4(dstg + u * kTcPos * 8, gp + u * Ngu, true); pair_async4(dstg + u * kTcPos * 8 + 8, gp + u * Ngu + 1, true); }
+                            else pair_async16(dstg + u * kTcPos * 8, gp + u * Ngu, true);
+                        } else {
+                            pair_async8(dsty + u * kTcPos * 8, yp + u * Nu, true);
+                            if (pooled) pair_async4(dstg + u * kTcPos * 8, gp + u * Ngu, true);
+                            else pair_async8(dstg + u * kTcPos * 8, gp + u * Ngu, true);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < NM; ++u) {
+                        const bool in = u < mleft;
+                        if (WIDE) {
+                            pair_async16(dsty + u * kTcPos * 8, in ? yp + u * Nu : y, in);
+                            if (pooled) { pair_async4(dstg + u * kTcPos * 8, in ? gp + u * Ngu : dy, in); pair_async4(dstg + u * kTcPos * 8 + 8, in ? gp + u * Ngu + 1 : dy, in); }
+                            else pair_async16(dstg + u * kTcPos * 8, in ? gp + u * Ngu : dy, in);
+                        } else {
+                            pair_async8(dsty + u * kTcPos * 8, in ? yp + u * Nu : y, in);
+                            if (pooled) pair_async4(dstg + u * kTcPos * 8, in ? gp + u * Ngu : dy, in);
+                            else pair_async8(dstg + u * kTcPos * 8, in ? gp + u * Ngu : dy, in);
+                        }
+                    }
+                }
+                async_arrive_noinc(&raw_full[slot.stage]);
+                slot.advance(1);
+            }
+            if (!ok) { sh.failed = 1; break; }
+        }
+        pair_async_commit();
+        pair_async_wait<0>();                                  // nothing of this thread's may still be in flight at exit
     } else {
-        // ---------------- epilogue: lane = pixel pair, registers = taps of both tiles
+        // ---------------- epilogue: lane = pixel pair, registers = taps of both tiles, 8 taps at a time
         const int ew = warp - kPairProducerWarps, quarter = warp & 3, half = ew >> 2;
         const unsigned hw = unsigned(g.H) * unsigned(g.W);
         for (int li = 0; li < my_items; ++li) {
@@ -514,21 +576,25 @@ __global__ void __launch_bounds__(kPairThreads, 1) mex_dx_pair(MexGeo g, const f
             const int k_first = it.mt * NT + half * (NT / 2);
             const float* xb = x + col.xbase + (size_t)k_first * hw;
             float* db = dx + col.xbase + (size_t)k_first * hw;
-            if (!pair_wait(sh.failed, &sh.acc_full[buf], (uint32_t(li) >> 1) & 1u, tries)) { sh.failed = 1; break; }
+            int kleft = col.base >= 0 ? g.K - k_first : 0;
+            float2 xr[8], xn[8];                                    // x of the block at hand and of the next one, in flight
+#pragma unroll
+            for (int i = 0; i < 8; ++i) xr[i] = i < kleft ? ldg2(xb + (size_t)i * hw) : make_float2(0.f, 0.f);
+            if (!pair_wait(sh.failed, &sh.acc_full[buf], (uint32_t(li) >> 1) & 1u, tries, 1024)) { sh.failed = 1; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-            for (int c0 = 0; c0 < NT / 2; c0 += 16) {
-                uint32_t v0[16], v1[16];
+            for (int c0 = 0; c0 < NT / 2; c0 += 8) {
+                uint32_t v0[8], v1[8];
                 const uint32_t taddr = tmem + uint32_t(buf * 2 * NT + half * (NT / 2) + c0) + (uint32_t(quarter * 32) << 16);
-                tmem_ld16_issue(taddr, v0);
-                tmem_ld16_issue(taddr + NT, v1);
-                const int kleft = col.base >= 0 ? g.K - k_first - c0 : 0;
-                float2 xr[16];
+                tmem_ld8_issue(taddr, v0);
+                tmem_ld8_issue(taddr + NT, v1);
+                if (c0 + 8 < NT / 2) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) xr[i] = i < kleft ? ldg2(xb + (size_t)(c0 + i) * hw) : make_float2(0.f, 0.f);
+                    for (int i = 0; i < 8; ++i) xn[i] = 8 + i < kleft ? ldg2(xb + (size_t)(c0 + 8 + i) * hw) : make_float2(0.f, 0.f);
+                }
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
+                for (int i = 0; i < 8; ++i) {
                     if (i < kleft) {
                         float2 o;
                         o.x = ex2_ftz(a * (xr[i].x - col.mx0)) * __uint_as_float(v0[i]);
@@ -536,6 +602,9 @@ __global__ void __launch_bounds__(kPairThreads, 1) mex_dx_pair(MexGeo g, const f
                         *reinterpret_cast<float2*>(db + (size_t)(c0 + i) * hw) = o;
                     }
                 }
+                kleft -= 8;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) xr[i] = xn[i];
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(&sh.acc_empty[buf]);
@@ -545,63 +614,77 @@ __global__ void __launch_bounds__(kPairThreads, 1) mex_dx_pair(MexGeo g, const f
 }
 
 // ---- offsets gradient --------------------------------------------------------------------------------------------
-// U[m, k] = sum over positions j of Q[m, j] * Ex[k, j] per region.  A CTA owns (region pair, MT instance tiles of 128, one
-// tap tile of NT) and a contiguous share of the pair's positions, walked in chunks of 16 pixel pairs (two MMA k-steps);
-// its 2 x MT accumulators (128 lanes x NT columns each) stay in tensor memory until the last chunk.  Both operands are
+// U[m, k] = sum over positions j of Q[m, j] * Ex[k, j] per region.  A CTA owns (region pair, MT tiles of 128 instances, one
+// tile of NT taps) and a contiguous share of the pair's positions, walked in chunks of CP pixel pairs (CP / 8 MMA k-steps);
+// its 2 * MT accumulators (128 lanes x NT columns each) stay in tensor memory until the last chunk.  Both operands are
 // computed: A = Q^T (rows = instances), B = Ex^T (rows = taps), reduction along positions, stored one float at a time in
-// the K-major core-matrix layout with a leading byte offset of 144, which spreads the 16 positions of a row and the
-// rows m, m + 4 of a warp's two half-warps over all 32 banks.
-constexpr int kDoPairKT = 16, kDoPairLBO = 144, kDoPairSBO = (kDoPairKT / 4) * kDoPairLBO;      // 576
-constexpr int kDoPairThreads = (kPairProducerWarps + 1) * 32;                                    // 288: producers + the MMA warp
-constexpr int kDoPairAPlane = (128 / 8) * kDoPairSBO;                                            // 9216
-template <int NT> __host__ __device__ constexpr int dopair_b_plane() { return (NT / 8) * kDoPairSBO; }
-template <int NT, int MT> __host__ __device__ constexpr int dopair_tile_bytes() { return 2 * MT * kDoPairAPlane + 2 * dopair_b_plane<NT>(); }
-template <int NT, int MT> __host__ __device__ constexpr int dopair_stage_bytes() { return 2 * dopair_tile_bytes<NT, MT>(); }
-template <int NT, int MT> __host__ __device__ constexpr int dopair_stages() { return 2; }
-// the producers' raw slot ring: DEPTH chunks of (2 * QROWS + XROWS) float2 per producer thread
-template <int NT, int MT, int DEPTH> __host__ __device__ constexpr int dopair_raw_bytes() { return DEPTH * (2 * (MT * 128 / 16) + NT / 16) * kPairProducers * 8; }
+// the K-major core-matrix layout with a leading byte offset of 144, which spreads the positions of a row and the rows a
+// warp stores at once over all 32 banks.  (MT, NT, CP) = (1, 64, 16) for layers up to 128 instances and 64 taps, else CP = 8
+// with up to two instance tiles and 128 taps, so that larger layers read y, dy and x once too.
+// Roles: 4 raw-loader warps copy a chunk's y, dy, x pairs and per-position maxima into a slot ring ([DEPTH][y rows, dy rows,
+// x rows, mx][CP pairs] float2), 16 converter warps turn a slot into the operands of a stage, one thread issues the MMAs;
+// the converters write the partial sums out at the end.
+constexpr int kDoLBO = 144;
+constexpr int kDoConvWarps = 16, kDoConv = kDoConvWarps * 32;                                    // 512 converters
+constexpr int kDoMmaWarp = kDoConvWarps, kDoFirstRawWarp = kDoMmaWarp + 1, kDoRawWarps = 4;
+constexpr int kDoPairThreads = (kDoFirstRawWarp + kDoRawWarps) * 32;                             // 672
+constexpr int kDoStages = 2, kDoDepth = 2;
 
-template <int STAGES>
+template <int MT, int NT, int CP>
+struct DoCfg {
+    static constexpr int SBO = (CP / 4) * kDoLBO;
+    static constexpr int A_PLANE = (128 / 8) * SBO, B_PLANE = (NT / 8) * SBO;
+    static constexpr int TILE_BYTES = 2 * MT * A_PLANE + 2 * B_PLANE;            // one tile of the pair: MT x (A hi, A lo), B hi, B lo
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int QR = MT * 128, XR = NT;                                 // rows of y (and of dy) and of x in a slot
+    static constexpr int SLOT_BYTES = (2 * QR + XR + 1) * CP * 8;
+    static constexpr int SMEM = kDoStages * STAGE_BYTES + kDoDepth * SLOT_BYTES;
+    static constexpr int ROWSLOTS = kDoConv / CP;                                // 32 (CP = 16) or 64 (CP = 8) rows converted at once
+    static constexpr int QROWS = QR / ROWSLOTS, XROWS = XR / ROWSLOTS;
+    static_assert(SMEM <= 227 * 1024, "stages and slot ring must fit the shared memory of one CTA");
+    static_assert(2 * MT * NT <= 512, "accumulators must fit the tensor memory");
+};
+
 struct DoPairShared {
-    uint64_t full[STAGES];       // producers -> MMA (256 arrivals)
-    uint64_t empty[STAGES];      // MMA -> producers
-    uint64_t acc_full;           // MMA -> epilogue (the producers, after their last chunk)
+    uint64_t full[kDoStages];        // converters -> MMA (512 arrivals)
+    uint64_t empty[kDoStages];       // MMA -> converters
+    uint64_t raw_full[kDoDepth];     // raw loaders' copies -> converters (128 arrivals)
+    uint64_t raw_empty[kDoDepth];    // converters -> raw loaders (512 arrivals)
+    uint64_t acc_full;               // MMA -> converters, after the last chunk
     uint32_t tmem;
     volatile int failed;
 };
 
 struct DoPairPlan { int units, mgroups, ktiles, splits; };
 
-template <int NT, int MT, int DEPTH>
+template <int MT, int NT, int CP, bool WIDE>
 __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, const float* __restrict__ x, const float* __restrict__ mo,
                                                                   const float* __restrict__ mx, const float* __restrict__ y,
                                                                   const float* __restrict__ dy, float* __restrict__ part,
                                                                   DoPairPlan plan, int* __restrict__ flag) {
-    constexpr int STAGES = dopair_stages<NT, MT>();
-    constexpr int STAGE_BYTES = dopair_stage_bytes<NT, MT>(), TILE_BYTES = dopair_tile_bytes<NT, MT>();
-    constexpr int B_PLANE = dopair_b_plane<NT>();
-    constexpr uint32_t TMEM_COLS = (2 * MT * NT) < 32 ? 32 : 2 * MT * NT;
-    constexpr int QROWS = MT * 128 / 16, XROWS = NT / 16;         // rows of Q / of Ex a producer thread converts per chunk
+    using Cfg = DoCfg<MT, NT, CP>;
+    constexpr uint32_t TMEM_COLS = 2 * MT * NT;
     extern __shared__ __align__(128) unsigned char dsm[];
-    __shared__ DoPairShared<STAGES> sh;
+    __shared__ DoPairShared sh;
     if (flag[0]) return;
 
     const long long P = (long long)g.B * g.rs;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int unit = int(blockIdx.x) % plan.units, split = int(blockIdx.x) / plan.units;
     const int kt = unit % plan.ktiles, mg = (unit / plan.ktiles) % plan.mgroups, pair = unit / (plan.ktiles * plan.mgroups);
-    const long long chunks = (P + kDoPairKT - 1) / kDoPairKT;
+    const long long chunks = (P + CP - 1) / CP;
     const long long c_begin = chunks * split / plan.splits, c_end = chunks * (split + 1) / plan.splits;
     const int nchunks = int(c_end - c_begin);
     const uint32_t tries = kWaitTries;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(&sh.full[s], kPairProducers); mbar_init(&sh.empty[s], 1); }
+        for (int s = 0; s < kDoStages; ++s) { mbar_init(&sh.full[s], kDoConv); mbar_init(&sh.empty[s], 1); }
+        for (int d = 0; d < kDoDepth; ++d) { mbar_init(&sh.raw_full[d], kDoRawWarps * 32); mbar_init(&sh.raw_empty[d], kDoConv); }
         mbar_init(&sh.acc_full, 1);
         sh.failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == kPairProducerWarps) {
+    if (warp == kDoMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -612,129 +695,94 @@ __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, con
 
     const int M = g.M, K = g.K;
     const int m_first = mg * MT * 128, k_first = kt * NT;
+    unsigned char* rawbase = dsm + kDoStages * Cfg::STAGE_BYTES;
 
-    if (warp < kPairProducerWarps) {
-        // ---------------- producers: lane % 16 = pixel pair of the chunk; the two half-warps take rows rb and rb + 4
-        const int j = lane & 15;
-        const int rb = (warp & 3) + 4 * (lane >> 4) + 8 * (warp >> 2);         // 0..15: row inside every block of 16 rows
+    if (warp < kDoConvWarps) {
+        // ---------------- converters: the lanes of a warp cover the CP pairs of the chunk and 32 / CP rows of a block of ROWSLOTS
+        // rows, chosen 4 (CP = 16) or 2 (CP = 8) apart so that their one-float stores fall into different banks
+        const int j = lane & (CP - 1);
+        const int rb = CP == 16 ? (warp & 3) + 4 * (lane >> 4) + 8 * (warp >> 2) : (warp & 1) + 2 * (lane >> 3) + 8 * (warp >> 1);
         const float a = float(g.eps) * 1.4426950408889634f, c2 = float(g.cst) * 1.4426950408889634f;
-        const unsigned Nu = unsigned(g.N), Ngu = unsigned(g.Ng), hw = unsigned(g.H) * unsigned(g.W);
         const bool pooled = g.gp == 2;
-        // offset maxima of this thread's instances, both regions
-        float mo0[QROWS], mo1[QROWS];
+        float mo0[Cfg::QROWS], mo1[Cfg::QROWS];      // offset maxima of this thread's instances, both regions
 #pragma unroll
-        for (int i = 0; i < QROWS; ++i) {
-            const int m = m_first + 16 * i + rb;
+        for (int i = 0; i < Cfg::QROWS; ++i) {
+            const int m = m_first + Cfg::ROWSLOTS * i + rb;
             mo0[i] = m < M ? __ldg(mo + (2 * pair) * M + m) : 0.f;
             mo1[i] = m < M ? __ldg(mo + (2 * pair + 1) * M + m) : 0.f;
         }
-        // Raw y, dy and x pairs of a chunk travel global -> shared by per-thread asynchronous copies, DEPTH chunks ahead,
-        // into a private slot ring behind the operand stages ([DEPTH][RROWS][256 threads] float2); a thread reads back
-        // only what it copied itself, right before it reuses the slot for a later chunk.
-        constexpr int RROWS = 2 * QROWS + XROWS;
-        float2* raw = reinterpret_cast<float2*>(dsm + STAGES * STAGE_BYTES) + threadIdx.x;
-        struct Meta { float mx0, mx1; bool live; };
-        Meta meta[DEPTH];
-        int lc = 0;                                                     // chunk under the load cursor
-        auto issue = [&](Meta& m, int d) {
-            const PairColumn col = pair_column_of(g, pair, (c_begin + lc) * kDoPairKT + j, P, mx);
-            ++lc;
-            m.live = col.base >= 0; m.mx0 = col.mx0; m.mx1 = col.mx1;
-            const float* yp = y + (m.live ? col.base : 0) + (size_t)(m_first + rb) * Nu;
-            const float* gp = dy + (m.live ? col.gbase : 0) + (size_t)(m_first + rb) * Ngu;
-            const float* xp = x + col.xbase + (size_t)(k_first + rb) * hw;
-            const uint32_t dst = smem_u32(raw + d * RROWS * kPairProducers);
-#pragma unroll
-            for (int i = 0; i < QROWS; ++i) {
-                const bool in = m.live && m_first + 16 * i + rb < M;        // else zero fill: dy = 0 and y = 0, no contribution, no NaN
-                pair_async8(dst + i * kPairProducers * 8, in ? yp + (size_t)(16 * i) * Nu : y, in);
-                if (pooled) pair_async4(dst + (QROWS + i) * kPairProducers * 8, in ? gp + (size_t)(16 * i) * Ngu : dy, in);
-                else pair_async8(dst + (QROWS + i) * kPairProducers * 8, in ? gp + (size_t)(16 * i) * Ngu : dy, in);
-            }
-#pragma unroll
-            for (int i = 0; i < XROWS; ++i) {
-                const bool in = m.live && k_first + 16 * i + rb < K;
-                pair_async8(dst + (2 * QROWS + i) * kPairProducers * 8, in ? xp + (size_t)(16 * i) * hw : x, in);
-            }
-        };
-#pragma unroll
-        for (int d = 0; d < DEPTH; ++d) { if (d < nchunks) issue(meta[d], d); pair_async_commit(); }
-        WsRing<STAGES> ring = {0, 0u};
+        WsRing<kDoStages> ring = {0, 0u};
+        WsRing<kDoDepth> slot = {0, 0u};
         bool alive = true;
-        for (int s0 = 0; s0 < nchunks && alive; s0 += DEPTH) {
+        for (int c = 0; c < nchunks; ++c) {
+            if (sh.failed || !pair_wait(sh.failed, &sh.raw_full[slot.stage], slot.fill & 1u, tries)) { alive = false; break; }
+            const float2* rs = reinterpret_cast<const float2*>(rawbase + slot.stage * Cfg::SLOT_BYTES) + j;
+            const float2 mxv = rs[(2 * Cfg::QR + Cfg::XR) * CP];
+            float2 yv[Cfg::QROWS], gv[Cfg::QROWS], xv[Cfg::XROWS];
 #pragma unroll
-            for (int d = 0; d < DEPTH; ++d) {
-                const int step = s0 + d;
-                if (step >= nchunks || !alive) break;
-                pair_async_wait<DEPTH - 1>();                        // this chunk's copies have landed
-                const Meta m = meta[d];
-                float2 yv[QROWS], gv[QROWS], xv[XROWS];
-#pragma unroll
-                for (int i = 0; i < QROWS; ++i) {
-                    yv[i] = raw[(d * RROWS + i) * kPairProducers];
-                    gv[i] = raw[(d * RROWS + QROWS + i) * kPairProducers];
-                    if (pooled) gv[i].y = gv[i].x;
-                }
-#pragma unroll
-                for (int i = 0; i < XROWS; ++i) xv[i] = raw[(d * RROWS + 2 * QROWS + i) * kPairProducers];
-                if (step + DEPTH < nchunks) issue(meta[d], d);       // reuses the slot just read
-                pair_async_commit();
-                const int stage = ring.stage;
-                if (sh.failed || (ring.fill >= 1 && !pair_wait(sh.failed, &sh.empty[stage], (ring.fill - 1) & 1u, tries))) { sh.failed = 1; alive = false; break; }
-                unsigned char* t0 = dsm + stage * STAGE_BYTES;
-                unsigned char* t1 = t0 + TILE_BYTES;
-                // A: Q^T, MT tiles of 128 rows; plane order per tile of the pair: [MT x (hi, lo)] then B (hi, lo)
-#pragma unroll
-                for (int i = 0; i < QROWS; ++i) {
-                    const int row = 16 * i + rb;                               // row inside the CTA's MT * 128 instances
-                    const int mt = row >> 7, r7 = row & 127;
-                    const int off = mt * 2 * kDoPairAPlane + core_off<kDoPairKT, kDoPairLBO>(r7, j);
-                    const bool in = m.live && m_first + row < M;
-                    float hi, lo;
-                    split_tf32_trunc(in ? gv[i].x * ex2_ftz(fmaf(a, (m.mx0 - yv[i].x) + mo0[i], c2)) : 0.f, hi, lo);
-                    *reinterpret_cast<float*>(t0 + off) = hi;
-                    *reinterpret_cast<float*>(t0 + off + kDoPairAPlane) = lo;
-                    split_tf32_trunc(in ? gv[i].y * ex2_ftz(fmaf(a, (m.mx1 - yv[i].y) + mo1[i], c2)) : 0.f, hi, lo);
-                    *reinterpret_cast<float*>(t1 + off) = hi;
-                    *reinterpret_cast<float*>(t1 + off + kDoPairAPlane) = lo;
-                }
-                // B: Ex^T (zero for a dead column or a tap past K)
-#pragma unroll
-                for (int i = 0; i < XROWS; ++i) {
-                    const int row = 16 * i + rb;
-                    const bool in = m.live && k_first + row < K;
-                    const int off = MT * 2 * kDoPairAPlane + core_off<kDoPairKT, kDoPairLBO>(row, j);
-                    float hi, lo;
-                    split_tf32_trunc(in ? ex2_ftz(a * (xv[i].x - m.mx0)) : 0.f, hi, lo);
-                    *reinterpret_cast<float*>(t0 + off) = hi;
-                    *reinterpret_cast<float*>(t0 + off + B_PLANE) = lo;
-                    split_tf32_trunc(in ? ex2_ftz(a * (xv[i].y - m.mx1)) : 0.f, hi, lo);
-                    *reinterpret_cast<float*>(t1 + off) = hi;
-                    *reinterpret_cast<float*>(t1 + off + B_PLANE) = lo;
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(&sh.full[stage]);
-                ring.advance(1);
+            for (int i = 0; i < Cfg::QROWS; ++i) {
+                yv[i] = rs[(Cfg::ROWSLOTS * i + rb) * CP];
+                gv[i] = rs[(Cfg::QR + Cfg::ROWSLOTS * i + rb) * CP];
+                if (pooled) gv[i].y = gv[i].x;
             }
+#pragma unroll
+            for (int i = 0; i < Cfg::XROWS; ++i) xv[i] = rs[(2 * Cfg::QR + Cfg::ROWSLOTS * i + rb) * CP];
+            // Rows past M or K and dead positions hold zeros (zero-filled copies): they give Q = 0 or are never stored.  An
+            // instance row past M may turn into 0 * inf = NaN; it feeds only accumulator rows that are never written out.
+            float qa[Cfg::QROWS], qb[Cfg::QROWS], ea[Cfg::XROWS], eb[Cfg::XROWS];
+#pragma unroll
+            for (int i = 0; i < Cfg::QROWS; ++i) {
+                qa[i] = gv[i].x * ex2_ftz(fmaf(a, (mxv.x - yv[i].x) + mo0[i], c2));
+                qb[i] = gv[i].y * ex2_ftz(fmaf(a, (mxv.y - yv[i].y) + mo1[i], c2));
+            }
+#pragma unroll
+            for (int i = 0; i < Cfg::XROWS; ++i) {
+                ea[i] = ex2_ftz(a * (xv[i].x - mxv.x));
+                eb[i] = ex2_ftz(a * (xv[i].y - mxv.y));
+            }
+            mbar_arrive(&sh.raw_empty[slot.stage]);
+            slot.advance(1);
+            const int stage = ring.stage;
+            if (ring.fill >= 1 && !pair_wait(sh.failed, &sh.empty[stage], (ring.fill - 1) & 1u, tries)) { alive = false; break; }
+            unsigned char* t0 = dsm + stage * Cfg::STAGE_BYTES;
+            unsigned char* t1 = t0 + Cfg::TILE_BYTES;
+#pragma unroll
+            for (int i = 0; i < Cfg::QROWS; ++i) {                              // A: Q^T, per instance tile planes hi, lo
+                const int row = Cfg::ROWSLOTS * i + rb;
+                const int off = (row >> 7) * 2 * Cfg::A_PLANE + core_off<CP, kDoLBO>(row & 127, j);
+                *reinterpret_cast<float*>(t0 + off) = qa[i];
+                *reinterpret_cast<float*>(t0 + off + Cfg::A_PLANE) = tf32_lo(qa[i]);
+                *reinterpret_cast<float*>(t1 + off) = qb[i];
+                *reinterpret_cast<float*>(t1 + off + Cfg::A_PLANE) = tf32_lo(qb[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < Cfg::XROWS; ++i) {                              // B: Ex^T, planes hi, lo
+                const int off = 2 * MT * Cfg::A_PLANE + core_off<CP, kDoLBO>(Cfg::ROWSLOTS * i + rb, j);
+                *reinterpret_cast<float*>(t0 + off) = ea[i];
+                *reinterpret_cast<float*>(t0 + off + Cfg::B_PLANE) = tf32_lo(ea[i]);
+                *reinterpret_cast<float*>(t1 + off) = eb[i];
+                *reinterpret_cast<float*>(t1 + off + Cfg::B_PLANE) = tf32_lo(eb[i]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(&sh.full[stage]);
+            ring.advance(1);
         }
-        pair_async_wait<0>();
-        // ---------------- epilogue by the same warps: lane = instance row, registers = taps
+        // ---------------- the partial sums: lane = instance row, registers = taps
         bool good = alive && !sh.failed;
         if (good && nchunks > 0) good = pair_wait(sh.failed, &sh.acc_full, 0, tries);
         if (!good) sh.failed = 1;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (good) {
-            const int quarter = warp & 3, half = warp >> 2;           // lanes of tensor memory this warp may read; half of the 2 * MT accumulators
+            const int quarter = warp & 3, t = (warp >> 2) & 1, chalf = warp >> 3;      // lane quarter, tile of the pair, half of the columns
 #pragma unroll 1
-            for (int acc = half * MT; acc < (half + 1) * MT; ++acc) {            // acc = tile-of-pair * MT + instance tile; half = tile of the pair
-                const int t = acc / MT, mt = acc % MT;
+            for (int mt = 0; mt < MT; ++mt) {
                 const int m = m_first + mt * 128 + quarter * 32 + lane;
                 float* dst = part + (((size_t)split * g.R + (2 * pair + t)) * M + (m < M ? m : 0)) * K + k_first;
 #pragma unroll 1
-                for (int c0 = 0; c0 < NT; c0 += 16) {
+                for (int c0 = chalf * (NT / 2); c0 < (chalf + 1) * (NT / 2); c0 += 16) {
                     uint32_t v[16];
                     if (nchunks > 0) {
-                        tmem_ld16_issue(tmem + uint32_t(acc * NT + c0) + (uint32_t(quarter * 32) << 16), v);
+                        tmem_ld16_issue(tmem + uint32_t((t * MT + mt) * NT + c0) + (uint32_t(quarter * 32) << 16), v);
                         tmem_ld_wait();
                     }
                     if (m < M) {
@@ -745,31 +793,30 @@ __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, con
                 }
             }
         }
-    } else {
-        // ---------------- MMA warp
+    } else if (warp == kDoMmaWarp) {
         constexpr uint32_t idesc = umma_idesc(NT);
-        WsRing<STAGES> ring = {0, 0u};
+        WsRing<kDoStages> ring = {0, 0u};
         bool ok = true;
         for (int c = 0; c < nchunks; ++c) {
             const int stage = ring.stage;
-            if (sh.failed || !pair_wait(sh.failed, &sh.full[stage], ring.fill & 1u, tries)) { ok = false; break; }
+            if (sh.failed || !pair_wait(sh.failed, &sh.full[stage], ring.fill & 1u, tries, 64)) { ok = false; break; }
             ring.advance(1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) {
-                const uint32_t base = smem_u32(dsm + stage * STAGE_BYTES);
+                const uint32_t base = smem_u32(dsm + stage * Cfg::STAGE_BYTES);
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
-                    const uint32_t tb = base + t * TILE_BYTES;
-                    const uint32_t b_hi = tb + MT * 2 * kDoPairAPlane, b_lo = b_hi + B_PLANE;
+                    const uint32_t tb = base + t * Cfg::TILE_BYTES;
+                    const uint32_t b_hi = tb + 2 * MT * Cfg::A_PLANE, b_lo = b_hi + Cfg::B_PLANE;
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
-                        const uint32_t a_hi = tb + mt * 2 * kDoPairAPlane, a_lo = a_hi + kDoPairAPlane;
+                        const uint32_t a_hi = tb + mt * 2 * Cfg::A_PLANE, a_lo = a_hi + Cfg::A_PLANE;
                         const uint32_t tmem_d = tmem + uint32_t((t * MT + mt) * NT);
 #pragma unroll
-                        for (int ks = 0; ks < kDoPairKT / 8; ++ks) {
-                            const uint32_t o = ks * 2 * kDoPairLBO;
-                            const uint64_t dah = umma_desc(a_hi + o, kDoPairLBO, kDoPairSBO), dal = umma_desc(a_lo + o, kDoPairLBO, kDoPairSBO);
-                            const uint64_t dbh = umma_desc(b_hi + o, kDoPairLBO, kDoPairSBO), dbl = umma_desc(b_lo + o, kDoPairLBO, kDoPairSBO);
+                        for (int ks = 0; ks < CP / 8; ++ks) {
+                            const uint32_t o = ks * 2 * kDoLBO;
+                            const uint64_t dah = umma_desc(a_hi + o, kDoLBO, Cfg::SBO), dal = umma_desc(a_lo + o, kDoLBO, Cfg::SBO);
+                            const uint64_t dbh = umma_desc(b_hi + o, kDoLBO, Cfg::SBO), dbl = umma_desc(b_lo + o, kDoLBO, Cfg::SBO);
                             umma_tf32(tmem_d, dal, dbh, idesc, (c | ks) != 0);
                             umma_tf32(tmem_d, dah, dbl, idesc, 1);
                             umma_tf32(tmem_d, dah, dbh, idesc, 1);
@@ -785,11 +832,64 @@ __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, con
         if (lane == 0 && nchunks > 0) umma_commit(&sh.acc_full);
         __syncwarp();
         if (nchunks > 0 && !mbar_wait(&sh.acc_full, 0)) sh.failed = 1;
+    } else {
+        // ---------------- raw loaders; zero fill past M, K and for dead pairs.  8-byte copies: one pixel pair per thread;
+        // WIDE: two neighbouring pairs per thread, 16-byte copies.  The 128 threads cover CP pairs x RS row slots.
+        const int lt = int(threadIdx.x) - kDoFirstRawWarp * 32;
+        constexpr int PT = WIDE ? CP / 2 : CP;                                 // threads along the pairs of the chunk
+        constexpr int RS = kDoRawWarps * 32 / PT;                              // row slots: rows rsl, rsl + RS, ...
+        const int j = WIDE ? 2 * (lt % PT) : (lt % PT), rsl = lt / PT;
+        const unsigned Nu = unsigned(g.N), Ngu = unsigned(g.Ng), hw = unsigned(g.H) * unsigned(g.W);
+        const bool pooled = g.gp == 2;
+        WsRing<kDoDepth> slot = {0, 0u};
+        for (int c = 0; c < nchunks; ++c) {
+            if (sh.failed) break;
+            if (slot.fill >= 1 && !pair_wait(sh.failed, &sh.raw_empty[slot.stage], (slot.fill - 1) & 1u, tries)) { sh.failed = 1; break; }
+            const Column col = column_of(g, 2 * pair, (c_begin + c) * CP + j, P, nullptr);
+            const bool live = col.base >= 0;
+            const float* yp = y + (live ? col.base : 0) + (size_t)(m_first + rsl) * Nu;
+            const float* gp = dy + (live ? col.gbase : 0) + (size_t)(m_first + rsl) * Ngu;
+            const float* xp = x + (live ? (((size_t)col.n * g.C + col.c0 + k_first + rsl) * g.H + col.h0) * g.W + col.w0 : 0);
+            const uint32_t dst = smem_u32(rawbase + slot.stage * Cfg::SLOT_BYTES) + (rsl * CP + j) * 8;
+            const bool full = live && m_first + Cfg::QR <= M && k_first + NT <= K;
+#pragma unroll
+            for (int i = 0; i < Cfg::QR / RS; ++i) {
+                const bool in = full || (live && m_first + rsl + RS * i < M);
+                const float* ys = in ? yp + (size_t)(RS * i) * Nu : y;
+                const float* gs = in ? gp + (size_t)(RS * i) * Ngu : dy;
+                const uint32_t dy_ = dst + (RS * i) * CP * 8, dg_ = dy_ + Cfg::QR * CP * 8;
+                if (WIDE) {
+                    pair_async16(dy_, ys, in);
+                    if (pooled) { pair_async4(dg_, gs, in); pair_async4(dg_ + 8, in ? gs + 1 : gs, in); }
+                    else pair_async16(dg_, gs, in);
+                } else {
+                    pair_async8(dy_, ys, in);
+                    if (pooled) pair_async4(dg_, gs, in);
+                    else pair_async8(dg_, gs, in);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < Cfg::XR / RS; ++i) {
+                const bool in = full || (live && k_first + rsl + RS * i < K);
+                const float* xs = in ? xp + (size_t)(RS * i) * hw : x;
+                if (WIDE) pair_async16(dst + (2 * Cfg::QR + RS * i) * CP * 8, xs, in);
+                else pair_async8(dst + (2 * Cfg::QR + RS * i) * CP * 8, xs, in);
+            }
+            if (rsl == 0) {                                                     // the per-position maxima of the pairs
+                const float* ms = live ? mx + (col.base - (long long)col.n * (M - 1) * g.N) : mx;
+                if (WIDE) pair_async16(dst + (2 * Cfg::QR + Cfg::XR) * CP * 8, ms, live);
+                else pair_async8(dst + (2 * Cfg::QR + Cfg::XR) * CP * 8, ms, live);
+            }
+            async_arrive_noinc(&sh.raw_full[slot.stage]);
+            slot.advance(1);
+        }
+        pair_async_commit();
+        pair_async_wait<0>();
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == kPairProducerWarps)
+    if (warp == kDoMmaWarp)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     if (threadIdx.x == 0 && sh.failed) atomicExch(&flag[1], 1);
 }
@@ -801,6 +901,12 @@ __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, con
         if (e_ != cudaSuccess) return e_;                                       \
         KERNEL<<<GRID, THREADS, SMEM, s>>>(__VA_ARGS__);                         \
     } while (0)
+
+// two neighbouring pixel pairs of a tile are 16 contiguous, 16-byte aligned bytes in every tensor
+inline bool mex_pair_wide(const MexGeo& g, const void* a, const void* b, const void* c, const void* d) {
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) | reinterpret_cast<uintptr_t>(d);
+    return g.W % 4 == 0 && (bits & 15u) == 0;
+}
 
 inline int pair_nt(int n) { return n > 64 ? 128 : 64; }
 
@@ -828,27 +934,28 @@ cudaError_t launch_dx_pair_nt(const MexGeo& g, const float* x, const float* tile
     if (items >= 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     const WsPlan plan = {int(items), make_fastdiv(pairs), make_fastdiv(ktiles)};
     const int grid = int(std::min<long long>(items, ws_sm_count()));
-    constexpr int smem = pair_stages<NT>() * pair_stage_bytes<NT>() + pair_raw_bytes<2, 16>();
-    PAIR_RUN((mex_dx_pair<NT, 2>), kPairThreads, smem, grid, g, x, tiles, mo, mx, y, dy, dx, plan, flag);
+    constexpr int smem = pair_stages<NT>() * pair_stage_bytes<NT>() + 2 * kDxSlotBytes;
+    if (mex_pair_wide(g, x, y, dy, dx)) PAIR_RUN((mex_dx_pair<NT, 2, true>), kDxThreads, smem, grid, g, x, tiles, mo, mx, y, dy, dx, plan, flag);
+    else PAIR_RUN((mex_dx_pair<NT, 2, false>), kDxThreads, smem, grid, g, x, tiles, mo, mx, y, dy, dx, plan, flag);
     count_launch();
     return cudaGetLastError();
 }
 
-// tiling of the offsets gradient: tap tile width and instance tiles per CTA (2 * MT * NT <= 512 columns of tensor memory,
-// and two operand stages plus the raw slot ring within one CTA's shared memory)
-inline void dopair_tiling(const MexGeo& g, int& nt, int& mt) {
-    nt = g.K > 64 ? 128 : 64;       // wider tap tiles or two instance tiles per CTA leave no room for the raw slot ring
-    mt = 1;
+// tiling of the offsets gradient: instance tiles per CTA, tap tile width and pairs per chunk
+inline void dopair_tiling(const MexGeo& g, int& mt, int& nt, int& cp) {
+    mt = g.M > 128 ? 2 : 1;
+    nt = g.K > 64 ? 128 : 64;
+    cp = (mt == 1 && nt == 64) ? 16 : 8;
 }
 
 inline DoPairPlan dopair_plan(const MexGeo& g) {
-    int nt, mt;
-    dopair_tiling(g, nt, mt);
+    int mt, nt, cp;
+    dopair_tiling(g, mt, nt, cp);
     DoPairPlan p;
     p.mgroups = ((g.M + 127) / 128 + mt - 1) / mt;
     p.ktiles = (g.K + nt - 1) / nt;
     p.units = (g.R / 2) * p.mgroups * p.ktiles;
-    const long long chunks = ((long long)g.B * g.rs + kDoPairKT - 1) / kDoPairKT;
+    const long long chunks = ((long long)g.B * g.rs + cp - 1) / cp;
     long long s = ws_sm_count() / p.units;
     if (s > chunks) s = chunks;
     if (s < 1) s = 1;
@@ -856,14 +963,14 @@ inline DoPairPlan dopair_plan(const MexGeo& g) {
     return p;
 }
 
-template <int NT, int MT, int DEPTH>
-cudaError_t launch_doff_pair_t(const MexGeo& g, const DoPairPlan& plan, const float* x, const float* mo, const float* mx, const float* y,
-                               const float* dy, float* part, int* flag, cudaStream_t s) {
-    constexpr int smem = dopair_stages<NT, MT>() * dopair_stage_bytes<NT, MT>() + dopair_raw_bytes<NT, MT, DEPTH>();
-    static_assert(smem <= 227 * 1024, "stages and raw ring must fit the shared memory of one CTA");
+template <int MT, int NT, int CP>
+cudaError_t launch_doff_pair_t(const MexGeo& g, const DoPairPlan& plan, bool wide, const float* x, const float* mo, const float* mx,
+                               const float* y, const float* dy, float* part, int* flag, cudaStream_t s) {
+    constexpr int smem = DoCfg<MT, NT, CP>::SMEM;
     const long long grid = (long long)plan.units * plan.splits;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    PAIR_RUN((mex_doff_pair<NT, MT, DEPTH>), kDoPairThreads, smem, int(grid), g, x, mo, mx, y, dy, part, plan, flag);
+    if (wide) PAIR_RUN((mex_doff_pair<MT, NT, CP, true>), kDoPairThreads, smem, int(grid), g, x, mo, mx, y, dy, part, plan, flag);
+    else PAIR_RUN((mex_doff_pair<MT, NT, CP, false>), kDoPairThreads, smem, int(grid), g, x, mo, mx, y, dy, part, plan, flag);
     count_launch();
     return cudaGetLastError();
 }
@@ -902,10 +1009,13 @@ cudaError_t launch_mex_doff_pair(const MexGeo& g, const float* x, const float* m
                                  float* part, int* splits_out, int* flag, cudaStream_t s) {
     const DoPairPlan plan = dopair_plan(g);
     *splits_out = plan.splits;
-    int nt, mt;
-    dopair_tiling(g, nt, mt);
-    if (nt == 128) return launch_doff_pair_t<128, 1, 1>(g, plan, x, mo, mx, y, dy, part, flag, s);
-    return launch_doff_pair_t<64, 1, 2>(g, plan, x, mo, mx, y, dy, part, flag, s);
+    int mt, nt, cp;
+    dopair_tiling(g, mt, nt, cp);
+    const bool wide = mex_pair_wide(g, x, y, dy, mx);
+    if (mt == 1 && nt == 64) return launch_doff_pair_t<1, 64, 16>(g, plan, wide, x, mo, mx, y, dy, part, flag, s);
+    if (mt == 1) return launch_doff_pair_t<1, 128, 8>(g, plan, wide, x, mo, mx, y, dy, part, flag, s);
+    if (nt == 64) return launch_doff_pair_t<2, 64, 8>(g, plan, wide, x, mo, mx, y, dy, part, flag, s);
+    return launch_doff_pair_t<2, 128, 8>(g, plan, wide, x, mo, mx, y, dy, part, flag, s);
 }
 
 }  // namespace simnets

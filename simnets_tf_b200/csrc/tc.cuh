@@ -32,9 +32,11 @@ __device__ __forceinline__ bool mbar_try(uint32_t addr, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_u32(bar);
     if (mbar_try(addr, parity)) return true;
+    uint32_t ns = 32;
     for (uint32_t it = 0; it < kWaitTries; ++it) {
-        __nanosleep(64);
+        __nanosleep(ns);
         if (mbar_try(addr, parity)) return true;
+        if (ns < 256) ns *= 2;                      // back off: polling competes with the working warps for issue slots
     }
     return false;
 }

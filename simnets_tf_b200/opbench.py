@@ -35,6 +35,9 @@ LAYERS = {
     "cfg5_mex1": ("mex", (64, 32, 32), 128, dict(blocks=[64, 1, 1], strides=[64, 1, 1], softmax_mode=True, unshared_offset_region=[2]), 2048, 0.0),
     "cfg5_mex2": ("mex", (128, 16, 16), 256, dict(blocks=[128, 1, 1], strides=[128, 1, 1], softmax_mode=True, unshared_offset_region=[2]), 2048, 0.0),
     "cfg5_mex3": ("mex", (256, 8, 8), 512, dict(blocks=[256, 1, 1], strides=[256, 1, 1], softmax_mode=True, unshared_offset_region=[2]), 2048, 0.0),
+    # diagnostics: the cfg5_mex1 GEMM sizes on maps whose sibling regions are laid out differently in memory
+    "diag_rows_contiguous": ("mex", (64, 16, 64), 128, dict(blocks=[64, 1, 1], strides=[64, 1, 1], softmax_mode=True, unshared_offset_region=[1, 1, 2]), 2048, 0.0),
+    "diag_rows_256B": ("mex", (64, 16, 64), 128, dict(blocks=[64, 1, 1], strides=[64, 1, 1], softmax_mode=True, unshared_offset_region=[2]), 2048, 0.0),
     "cfg5_head": ("mex", (512, 4, 4), 10, dict(blocks=[512, 4, 4], strides=[512, 4, 4], softmax_mode=True), 2048, 0.0),
 }
 
