@@ -97,7 +97,7 @@ class ClockSampler(object):
 def cpu_net(workload, threads):
     from oracle import oracle
     from oracle.simnet_cpu import CpuSimNet
-    from simnets_tf_b200.simnet import SPECS
+    from simnets_tf_b200.netspec import SPECS
     if not oracle.available("port") and not oracle.available("reference"):
         oracle.build()
     kind = "reference" if oracle.available("reference") else "port"
@@ -131,7 +131,7 @@ def run_reference(args):
     if rank != 0:
         return
     from oracle.simnet_cpu import host_cores
-    from simnets_tf_b200.simnet import SPECS
+    from simnets_tf_b200.netspec import SPECS
     workload = args.workload
     x, labels = make_data(workload, SPECS[workload])
     cores = host_cores()

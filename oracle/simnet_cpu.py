@@ -14,7 +14,7 @@ import torch
 import torch.nn.functional as F
 
 from simnets_tf_b200 import abi
-from simnets_tf_b200.simnet import init_parameters
+from simnets_tf_b200 import netspec
 
 
 def host_cores():
@@ -119,7 +119,14 @@ class CpuSimNet(object):
         self.dtype = np.dtype(dtype)
         self.ops = CpuOps(oracle, threads, abi.F64 if self.dtype == np.float64 else abi.F32)
         self.params = []
-        for entry, values in zip(spec["layers"], init_parameters(spec, seed)):
+
+        def nregions(chw, num_instances, blocks, strides, kw):      # the checker's own dimension code, not the CUDA library's
+            d = abi.make_mex_desc([1] + list(chw), num_instances, kw.get("softmax_mode", False), [0, 0, 0], strides, blocks,
+                                  kw.get("epsilon", 1.0), 0.0, True, kw.get("use_unshared_regions", True),
+                                  kw.get("shared_offset_region", [-1]), kw.get("unshared_offset_region", [-1]))
+            return oracle.mex_dims(d).num_regions
+
+        for entry, values in zip(spec["layers"], netspec.init_parameters(spec, seed, nregions)):
             if values is None:
                 self.params.append(None)
             else:

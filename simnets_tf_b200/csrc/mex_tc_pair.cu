@@ -423,7 +423,9 @@ __global__ void __launch_bounds__(kPairThreads, 1) mex_fwd_pair(MexGeo g, const 
 constexpr int kDxRawWarps = 4;
 constexpr int kDxFirstRawWarp = kPairLoaderWarp + 1;
 constexpr int kDxThreads = (kDxFirstRawWarp + kDxRawWarps) * 32;      // 704
-constexpr int kDxSlotBytes = 2 * kTcKT * kTcPos * 8;                   // 32 KiB: y and dy, 16 instances x 128 rows of float2
+// a slot: y as [16 instances][128 rows] float2, then dy likewise, or as [16][128] float when dy is given pooled (one value per pair)
+template <bool POOLED> __host__ __device__ constexpr int dx_slot_bytes() { return kTcKT * kTcPos * (POOLED ? 12 : 16); }
+template <bool POOLED> __host__ __device__ constexpr int dx_depth() { return POOLED ? 3 : 2; }      // slots: all but one can be in flight
 
 __device__ __forceinline__ void async_arrive_noinc(uint64_t* bar) {   // arrives once this thread's earlier asynchronous copies have landed
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -438,12 +440,12 @@ __device__ __forceinline__ void tmem_ld8_issue(uint32_t taddr, uint32_t (&v)[8])
 
 // WIDE: every tensor is 16-byte aligned and the map width is a multiple of 4, so two neighbouring pixel pairs of a tile are
 // 16 contiguous bytes: a raw loader then copies two rows at a time (half the copy instructions).
-template <int NT, int DEPTH, bool WIDE>
+template <int NT, bool POOLED, bool WIDE>
 __global__ void __launch_bounds__(kDxThreads, 1) mex_dx_pair(MexGeo g, const float* __restrict__ x, const float* __restrict__ tiles,
                                                             const float* __restrict__ mo, const float* __restrict__ mx,
                                                             const float* __restrict__ y, const float* __restrict__ dy,
                                                             float* __restrict__ dx, WsPlan plan, int* __restrict__ flag) {
-    constexpr int STAGES = pair_stages<NT>();
+    constexpr int STAGES = pair_stages<NT>(), DEPTH = dx_depth<POOLED>(), kDxSlotBytes = dx_slot_bytes<POOLED>();
     constexpr int STAGE_BYTES = pair_stage_bytes<NT>();
     constexpr uint32_t TMEM_COLS = 4 * NT;
     extern __shared__ __align__(128) unsigned char dsm[];
@@ -467,7 +469,6 @@ __global__ void __launch_bounds__(kDxThreads, 1) mex_dx_pair(MexGeo g, const flo
         // ---------------- converters: thread % 128 = pixel-pair row, thread / 128 = which 8 of the stage's 16 instances
         const int prow = threadIdx.x % kTcPos, mhalf = threadIdx.x / kTcPos;
         const int M = g.M;
-        const bool pooled = g.gp == 2;
         WsRing<STAGES> ring = {0, 0u};
         WsRing<DEPTH> slot = {0, 0u};
         for (int li = 0; li < my_items && !sh.failed; ++li) {
@@ -479,14 +480,16 @@ __global__ void __launch_bounds__(kDxThreads, 1) mex_dx_pair(MexGeo g, const flo
                 const int mleft = col.base >= 0 ? M - c * kTcKT - mhalf * 8 : 0;     // a dead row contributes nothing
                 if (!pair_wait(sh.failed, &raw_full[slot.stage], slot.fill & 1u, tries)) { ok = false; break; }
                 const float2* ry = reinterpret_cast<const float2*>(rawbase + slot.stage * kDxSlotBytes) + (mhalf * 8) * kTcPos + prow;
-                const float2* rg = ry + kTcKT * kTcPos;
+                const float2* rg = ry + kTcKT * kTcPos;                                   // dy as pairs
+                const float* rgp = reinterpret_cast<const float*>(rawbase + slot.stage * kDxSlotBytes + kTcKT * kTcPos * 8) + (mhalf * 8) * kTcPos + prow;   // dy pooled
                 float q0[8], q1[8];
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
                     const bool in = u < mleft;
                     const float2 yv = ry[u * kTcPos];
-                    float2 gv = rg[u * kTcPos];
-                    if (pooled) gv.y = gv.x;
+                    float2 gv;
+                    if (POOLED) { gv.x = rgp[u * kTcPos]; gv.y = gv.x; }
+                    else gv = rg[u * kTcPos];
                     const float m0v = in ? __ldg(mor0 + c * kTcKT + u) : 0.f, m1v = in ? __ldg(mor0 + M + c * kTcKT + u) : 0.f;
                     q0[u] = in ? gv.x * ex2_ftz(fmaf(a, (col.mx0 - yv.x) + m0v, c2)) : 0.f;
                     q1[u] = in ? gv.y * ex2_ftz(fmaf(a, (col.mx1 - yv.y) + m1v, c2)) : 0.f;
@@ -516,7 +519,6 @@ __global__ void __launch_bounds__(kDxThreads, 1) mex_dx_pair(MexGeo g, const flo
         constexpr int NM = WIDE ? 8 : 16;
         const int M = g.M;
         const unsigned Nu = unsigned(g.N), Ngu = unsigned(g.Ng);
-        const bool pooled = g.gp == 2;
         WsRing<DEPTH> slot = {0, 0u};
         for (int li = 0; li < my_items && !sh.failed; ++li) {
             const WsItem it = ws_item(plan, int(blockIdx.x) + li * int(gridDim.x));
@@ -527,19 +529,21 @@ __global__ void __launch_bounds__(kDxThreads, 1) mex_dx_pair(MexGeo g, const flo
             bool ok = true;
             for (int c = 0; c < mchunks; ++c, yp += (size_t)kTcKT * Nu, gp += (size_t)kTcKT * Ngu) {
                 if (slot.fill >= 1 && !pair_wait(sh.failed, &raw_empty[slot.stage], (slot.fill - 1) & 1u, tries)) { ok = false; break; }
-                const uint32_t dsty = smem_u32(rawbase + slot.stage * kDxSlotBytes) + (mfirst * kTcPos + row) * 8, dstg = dsty + kTcKT * kTcPos * 8;
+                const uint32_t dsty = smem_u32(rawbase + slot.stage * kDxSlotBytes) + (mfirst * kTcPos + row) * 8;
+                const uint32_t dstg = smem_u32(rawbase + slot.stage * kDxSlotBytes) + kTcKT * kTcPos * 8 + (mfirst * kTcPos + row) * (POOLED ? 4 : 8);
+                constexpr int GP = kTcPos * (POOLED ? 4 : 8);                 // bytes between instances in the dy part
                 const int mleft = live ? M - c * kTcKT - mfirst : 0;         // a dead row must not read a stranger's y: zero fill
                 if (mleft >= NM) {
 #pragma unroll
                     for (int u = 0; u < NM; ++u) {
                         if (WIDE) {
                             pair_async16(dsty + u * kTcPos * 8, yp + u * Nu, true);
-                            if (pooled) { pair_async4(dstg + u * kTcPos * 8, gp + u * Ngu, true); pair_async4(dstg + u * kTcPos * 8 + 8, gp + u * Ngu + 1, true); }
-                            else pair_async16(dstg + u * kTcPos * 8, gp + u * Ngu, true);
+                            if (POOLED) pair_async8(dstg + u * GP, gp + u * Ngu, true);          // the pooled values of two neighbouring pairs
+                            else pair_async16(dstg + u * GP, gp + u * Ngu, true);
                         } else {
                             pair_async8(dsty + u * kTcPos * 8, yp + u * Nu, true);
-                            if (pooled) pair_async4(dstg + u * kTcPos * 8, gp + u * Ngu, true);
-                            else pair_async8(dstg + u * kTcPos * 8, gp + u * Ngu, true);
+                            if (POOLED) pair_async4(dstg + u * GP, gp + u * Ngu, true);
+                            else pair_async8(dstg + u * GP, gp + u * Ngu, true);
                         }
                     }
                 } else {
@@ -548,12 +552,12 @@ __global__ void __launch_bounds__(kDxThreads, 1) mex_dx_pair(MexGeo g, const flo
                         const bool in = u < mleft;
                         if (WIDE) {
                             pair_async16(dsty + u * kTcPos * 8, in ? yp + u * Nu : y, in);
-                            if (pooled) { pair_async4(dstg + u * kTcPos * 8, in ? gp + u * Ngu : dy, in); pair_async4(dstg + u * kTcPos * 8 + 8, in ? gp + u * Ngu + 1 : dy, in); }
-                            else pair_async16(dstg + u * kTcPos * 8, in ? gp + u * Ngu : dy, in);
+                            if (POOLED) pair_async8(dstg + u * GP, in ? gp + u * Ngu : dy, in);
+                            else pair_async16(dstg + u * GP, in ? gp + u * Ngu : dy, in);
                         } else {
                             pair_async8(dsty + u * kTcPos * 8, in ? yp + u * Nu : y, in);
-                            if (pooled) pair_async4(dstg + u * kTcPos * 8, in ? gp + u * Ngu : dy, in);
-                            else pair_async8(dstg + u * kTcPos * 8, in ? gp + u * Ngu : dy, in);
+                            if (POOLED) pair_async4(dstg + u * GP, in ? gp + u * Ngu : dy, in);
+                            else pair_async8(dstg + u * GP, in ? gp + u * Ngu : dy, in);
                         }
                     }
                 }
@@ -628,17 +632,19 @@ constexpr int kDoLBO = 144;
 constexpr int kDoConvWarps = 16, kDoConv = kDoConvWarps * 32;                                    // 512 converters
 constexpr int kDoMmaWarp = kDoConvWarps, kDoFirstRawWarp = kDoMmaWarp + 1, kDoRawWarps = 4;
 constexpr int kDoPairThreads = (kDoFirstRawWarp + kDoRawWarps) * 32;                             // 672
-constexpr int kDoStages = 2, kDoDepth = 2;
+constexpr int kDoStages = 2;
 
-template <int MT, int NT, int CP>
+template <int MT, int NT, int CP, bool POOLED>
 struct DoCfg {
+    static constexpr int DEPTH = POOLED ? 3 : 2;                                 // slots of the raw ring: all but one can be in flight
     static constexpr int SBO = (CP / 4) * kDoLBO;
     static constexpr int A_PLANE = (128 / 8) * SBO, B_PLANE = (NT / 8) * SBO;
     static constexpr int TILE_BYTES = 2 * MT * A_PLANE + 2 * B_PLANE;            // one tile of the pair: MT x (A hi, A lo), B hi, B lo
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
     static constexpr int QR = MT * 128, XR = NT;                                 // rows of y (and of dy) and of x in a slot
-    static constexpr int SLOT_BYTES = (2 * QR + XR + 1) * CP * 8;
-    static constexpr int SMEM = kDoStages * STAGE_BYTES + kDoDepth * SLOT_BYTES;
+    static constexpr int G_OFF = QR * CP * 8, X_OFF = G_OFF + QR * CP * (POOLED ? 4 : 8), MX_OFF = X_OFF + XR * CP * 8;   // dy pooled: one float per pair
+    static constexpr int SLOT_BYTES = MX_OFF + CP * 8;
+    static constexpr int SMEM = kDoStages * STAGE_BYTES + DEPTH * SLOT_BYTES;
     static constexpr int ROWSLOTS = kDoConv / CP;                                // 32 (CP = 16) or 64 (CP = 8) rows converted at once
     static constexpr int QROWS = QR / ROWSLOTS, XROWS = XR / ROWSLOTS;
     static_assert(SMEM <= 227 * 1024, "stages and slot ring must fit the shared memory of one CTA");
@@ -648,8 +654,8 @@ struct DoCfg {
 struct DoPairShared {
     uint64_t full[kDoStages];        // converters -> MMA (512 arrivals)
     uint64_t empty[kDoStages];       // MMA -> converters
-    uint64_t raw_full[kDoDepth];     // raw loaders' copies -> converters (128 arrivals)
-    uint64_t raw_empty[kDoDepth];    // converters -> raw loaders (512 arrivals)
+    uint64_t raw_full[3];            // raw loaders' copies -> converters (128 arrivals)
+    uint64_t raw_empty[3];           // converters -> raw loaders (512 arrivals)
     uint64_t acc_full;               // MMA -> converters, after the last chunk
     uint32_t tmem;
     volatile int failed;
@@ -657,12 +663,13 @@ struct DoPairShared {
 
 struct DoPairPlan { int units, mgroups, ktiles, splits; };
 
-template <int MT, int NT, int CP, bool WIDE>
+template <int MT, int NT, int CP, bool POOLED, bool WIDE>
 __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, const float* __restrict__ x, const float* __restrict__ mo,
                                                                   const float* __restrict__ mx, const float* __restrict__ y,
                                                                   const float* __restrict__ dy, float* __restrict__ part,
                                                                   DoPairPlan plan, int* __restrict__ flag) {
-    using Cfg = DoCfg<MT, NT, CP>;
+    using Cfg = DoCfg<MT, NT, CP, POOLED>;
+    constexpr int kDoDepth = Cfg::DEPTH;
     constexpr uint32_t TMEM_COLS = 2 * MT * NT;
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ DoPairShared sh;
@@ -703,7 +710,6 @@ __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, con
         const int j = lane & (CP - 1);
         const int rb = CP == 16 ? (warp & 3) + 4 * (lane >> 4) + 8 * (warp >> 2) : (warp & 1) + 2 * (lane >> 3) + 8 * (warp >> 1);
         const float a = float(g.eps) * 1.4426950408889634f, c2 = float(g.cst) * 1.4426950408889634f;
-        const bool pooled = g.gp == 2;
         float mo0[Cfg::QROWS], mo1[Cfg::QROWS];      // offset maxima of this thread's instances, both regions
 #pragma unroll
         for (int i = 0; i < Cfg::QROWS; ++i) {
@@ -716,17 +722,21 @@ __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, con
         bool alive = true;
         for (int c = 0; c < nchunks; ++c) {
             if (sh.failed || !pair_wait(sh.failed, &sh.raw_full[slot.stage], slot.fill & 1u, tries)) { alive = false; break; }
-            const float2* rs = reinterpret_cast<const float2*>(rawbase + slot.stage * Cfg::SLOT_BYTES) + j;
-            const float2 mxv = rs[(2 * Cfg::QR + Cfg::XR) * CP];
+            const unsigned char* sb = rawbase + slot.stage * Cfg::SLOT_BYTES;
+            const float2* rs = reinterpret_cast<const float2*>(sb) + j;
+            const float2* rgf = reinterpret_cast<const float2*>(sb + Cfg::G_OFF) + j;
+            const float* rgp = reinterpret_cast<const float*>(sb + Cfg::G_OFF) + j;
+            const float2* rx = reinterpret_cast<const float2*>(sb + Cfg::X_OFF) + j;
+            const float2 mxv = reinterpret_cast<const float2*>(sb + Cfg::MX_OFF)[j];
             float2 yv[Cfg::QROWS], gv[Cfg::QROWS], xv[Cfg::XROWS];
 #pragma unroll
             for (int i = 0; i < Cfg::QROWS; ++i) {
                 yv[i] = rs[(Cfg::ROWSLOTS * i + rb) * CP];
-                gv[i] = rs[(Cfg::QR + Cfg::ROWSLOTS * i + rb) * CP];
-                if (pooled) gv[i].y = gv[i].x;
+                if (POOLED) { gv[i].x = rgp[(Cfg::ROWSLOTS * i + rb) * CP]; gv[i].y = gv[i].x; }
+                else gv[i] = rgf[(Cfg::ROWSLOTS * i + rb) * CP];
             }
 #pragma unroll
-            for (int i = 0; i < Cfg::XROWS; ++i) xv[i] = rs[(2 * Cfg::QR + Cfg::ROWSLOTS * i + rb) * CP];
+            for (int i = 0; i < Cfg::XROWS; ++i) xv[i] = rx[(Cfg::ROWSLOTS * i + rb) * CP];
             // Rows past M or K and dead positions hold zeros (zero-filled copies): they give Q = 0 or are never stored.  An
             // instance row past M may turn into 0 * inf = NaN; it feeds only accumulator rows that are never written out.
             float qa[Cfg::QROWS], qb[Cfg::QROWS], ea[Cfg::XROWS], eb[Cfg::XROWS];
@@ -840,7 +850,6 @@ __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, con
         constexpr int RS = kDoRawWarps * 32 / PT;                              // row slots: rows rsl, rsl + RS, ...
         const int j = WIDE ? 2 * (lt % PT) : (lt % PT), rsl = lt / PT;
         const unsigned Nu = unsigned(g.N), Ngu = unsigned(g.Ng), hw = unsigned(g.H) * unsigned(g.W);
-        const bool pooled = g.gp == 2;
         WsRing<kDoDepth> slot = {0, 0u};
         for (int c = 0; c < nchunks; ++c) {
             if (sh.failed) break;
@@ -850,21 +859,24 @@ __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, con
             const float* yp = y + (live ? col.base : 0) + (size_t)(m_first + rsl) * Nu;
             const float* gp = dy + (live ? col.gbase : 0) + (size_t)(m_first + rsl) * Ngu;
             const float* xp = x + (live ? (((size_t)col.n * g.C + col.c0 + k_first + rsl) * g.H + col.h0) * g.W + col.w0 : 0);
-            const uint32_t dst = smem_u32(rawbase + slot.stage * Cfg::SLOT_BYTES) + (rsl * CP + j) * 8;
+            const uint32_t sbase = smem_u32(rawbase + slot.stage * Cfg::SLOT_BYTES);
+            const uint32_t dst = sbase + (rsl * CP + j) * 8;
+            const uint32_t dstg = sbase + Cfg::G_OFF + (rsl * CP + j) * (POOLED ? 4 : 8), dstx = sbase + Cfg::X_OFF + (rsl * CP + j) * 8;
+            constexpr int GB = POOLED ? 4 : 8;                                  // bytes per pair in the dy part
             const bool full = live && m_first + Cfg::QR <= M && k_first + NT <= K;
 #pragma unroll
             for (int i = 0; i < Cfg::QR / RS; ++i) {
                 const bool in = full || (live && m_first + rsl + RS * i < M);
                 const float* ys = in ? yp + (size_t)(RS * i) * Nu : y;
                 const float* gs = in ? gp + (size_t)(RS * i) * Ngu : dy;
-                const uint32_t dy_ = dst + (RS * i) * CP * 8, dg_ = dy_ + Cfg::QR * CP * 8;
+                const uint32_t dy_ = dst + (RS * i) * CP * 8, dg_ = dstg + (RS * i) * CP * GB;
                 if (WIDE) {
                     pair_async16(dy_, ys, in);
-                    if (pooled) { pair_async4(dg_, gs, in); pair_async4(dg_ + 8, in ? gs + 1 : gs, in); }
+                    if (POOLED) pair_async8(dg_, gs, in);                       // the pooled values of two neighbouring pairs
                     else pair_async16(dg_, gs, in);
                 } else {
                     pair_async8(dy_, ys, in);
-                    if (pooled) pair_async4(dg_, gs, in);
+                    if (POOLED) pair_async4(dg_, gs, in);
                     else pair_async8(dg_, gs, in);
                 }
             }
@@ -872,13 +884,13 @@ __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, con
             for (int i = 0; i < Cfg::XR / RS; ++i) {
                 const bool in = full || (live && k_first + rsl + RS * i < K);
                 const float* xs = in ? xp + (size_t)(RS * i) * hw : x;
-                if (WIDE) pair_async16(dst + (2 * Cfg::QR + RS * i) * CP * 8, xs, in);
-                else pair_async8(dst + (2 * Cfg::QR + RS * i) * CP * 8, xs, in);
+                if (WIDE) pair_async16(dstx + (RS * i) * CP * 8, xs, in);
+                else pair_async8(dstx + (RS * i) * CP * 8, xs, in);
             }
             if (rsl == 0) {                                                     // the per-position maxima of the pairs
                 const float* ms = live ? mx + (col.base - (long long)col.n * (M - 1) * g.N) : mx;
-                if (WIDE) pair_async16(dst + (2 * Cfg::QR + Cfg::XR) * CP * 8, ms, live);
-                else pair_async8(dst + (2 * Cfg::QR + Cfg::XR) * CP * 8, ms, live);
+                if (WIDE) pair_async16(sbase + Cfg::MX_OFF + j * 8, ms, live);
+                else pair_async8(sbase + Cfg::MX_OFF + j * 8, ms, live);
             }
             async_arrive_noinc(&sh.raw_full[slot.stage]);
             slot.advance(1);
@@ -925,7 +937,7 @@ cudaError_t launch_fwd_pair_nt(const MexGeo& g, const float* x, const float* til
     return cudaGetLastError();
 }
 
-template <int NT>
+template <int NT, bool POOLED>
 cudaError_t launch_dx_pair_nt(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, const float* y,
                               const float* dy, float* dx, int* flag, cudaStream_t s) {
     const long long P = (long long)g.B * g.rs;
@@ -934,9 +946,10 @@ cudaError_t launch_dx_pair_nt(const MexGeo& g, const float* x, const float* tile
     if (items >= 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     const WsPlan plan = {int(items), make_fastdiv(pairs), make_fastdiv(ktiles)};
     const int grid = int(std::min<long long>(items, ws_sm_count()));
-    constexpr int smem = pair_stages<NT>() * pair_stage_bytes<NT>() + 2 * kDxSlotBytes;
-    if (mex_pair_wide(g, x, y, dy, dx)) PAIR_RUN((mex_dx_pair<NT, 2, true>), kDxThreads, smem, grid, g, x, tiles, mo, mx, y, dy, dx, plan, flag);
-    else PAIR_RUN((mex_dx_pair<NT, 2, false>), kDxThreads, smem, grid, g, x, tiles, mo, mx, y, dy, dx, plan, flag);
+    constexpr int smem = pair_stages<NT>() * pair_stage_bytes<NT>() + dx_depth<POOLED>() * dx_slot_bytes<POOLED>();
+    static_assert(smem <= 227 * 1024, "stages and slot ring must fit the shared memory of one CTA");
+    if (mex_pair_wide(g, x, y, dy, dx)) PAIR_RUN((mex_dx_pair<NT, POOLED, true>), kDxThreads, smem, grid, g, x, tiles, mo, mx, y, dy, dx, plan, flag);
+    else PAIR_RUN((mex_dx_pair<NT, POOLED, false>), kDxThreads, smem, grid, g, x, tiles, mo, mx, y, dy, dx, plan, flag);
     count_launch();
     return cudaGetLastError();
 }
@@ -963,16 +976,23 @@ inline DoPairPlan dopair_plan(const MexGeo& g) {
     return p;
 }
 
+template <int MT, int NT, int CP, bool POOLED>
+cudaError_t launch_doff_pair_p(const MexGeo& g, const DoPairPlan& plan, bool wide, const float* x, const float* mo, const float* mx,
+                               const float* y, const float* dy, float* part, int* flag, cudaStream_t s) {
+    constexpr int smem = DoCfg<MT, NT, CP, POOLED>::SMEM;
+    const long long grid = (long long)plan.units * plan.splits;
+    if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    if (wide) PAIR_RUN((mex_doff_pair<MT, NT, CP, POOLED, true>), kDoPairThreads, smem, int(grid), g, x, mo, mx, y, dy, part, plan, flag);
+    else PAIR_RUN((mex_doff_pair<MT, NT, CP, POOLED, false>), kDoPairThreads, smem, int(grid), g, x, mo, mx, y, dy, part, plan, flag);
+    count_launch();
+    return cudaGetLastError();
+}
+
 template <int MT, int NT, int CP>
 cudaError_t launch_doff_pair_t(const MexGeo& g, const DoPairPlan& plan, bool wide, const float* x, const float* mo, const float* mx,
                                const float* y, const float* dy, float* part, int* flag, cudaStream_t s) {
-    constexpr int smem = DoCfg<MT, NT, CP>::SMEM;
-    const long long grid = (long long)plan.units * plan.splits;
-    if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    if (wide) PAIR_RUN((mex_doff_pair<MT, NT, CP, true>), kDoPairThreads, smem, int(grid), g, x, mo, mx, y, dy, part, plan, flag);
-    else PAIR_RUN((mex_doff_pair<MT, NT, CP, false>), kDoPairThreads, smem, int(grid), g, x, mo, mx, y, dy, part, plan, flag);
-    count_launch();
-    return cudaGetLastError();
+    return g.gp == 2 ? launch_doff_pair_p<MT, NT, CP, true>(g, plan, wide, x, mo, mx, y, dy, part, flag, s)
+                     : launch_doff_pair_p<MT, NT, CP, false>(g, plan, wide, x, mo, mx, y, dy, part, flag, s);
 }
 
 }  // namespace
@@ -1001,8 +1021,10 @@ cudaError_t launch_mex_fwd_pair(const MexGeo& g, const float* x, const float* ti
 
 cudaError_t launch_mex_dx_pair(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, const float* y,
                                const float* dy, float* dx, int* flag, cudaStream_t s) {
-    if (pair_nt(g.K) == 128) return launch_dx_pair_nt<128>(g, x, tiles, mo, mx, y, dy, dx, flag, s);
-    return launch_dx_pair_nt<64>(g, x, tiles, mo, mx, y, dy, dx, flag, s);
+    if (g.gp == 2) return pair_nt(g.K) == 128 ? launch_dx_pair_nt<128, true>(g, x, tiles, mo, mx, y, dy, dx, flag, s)
+                                              : launch_dx_pair_nt<64, true>(g, x, tiles, mo, mx, y, dy, dx, flag, s);
+    return pair_nt(g.K) == 128 ? launch_dx_pair_nt<128, false>(g, x, tiles, mo, mx, y, dy, dx, flag, s)
+                               : launch_dx_pair_nt<64, false>(g, x, tiles, mo, mx, y, dy, dx, flag, s);
 }
 
 cudaError_t launch_mex_doff_pair(const MexGeo& g, const float* x, const float* mo, const float* mx, const float* y, const float* dy,

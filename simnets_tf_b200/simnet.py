@@ -18,69 +18,20 @@ import torch.nn.functional as F
 from . import keras as layers
 
 
-def _mex_c(num_instances, channels):
-    return ("mex", dict(num_instances=num_instances, blocks=[channels, 1, 1], strides=[channels, 1, 1], softmax_mode=True,
-                        normalize_offsets=True, use_unshared_regions=True, unshared_offset_region=[2]))
+from .netspec import SPECS  # noqa: F401
+from . import netspec
 
 
-SPECS = {
-    "cfg3": dict(
-        input_shape=(1, 28, 28), classes=10,
-        layers=[("similarity", dict(num_instances=32, similarity_function="L2", blocks=[2, 2], strides=[2, 2], padding=[2, 2],
-                                    normalization_term=True, ignore_nan_input=True, out_of_bounds_value=float("nan"))),
-                _mex_c(64, 32), ("sumpool", 2), _mex_c(128, 64), ("sumpool", 2), _mex_c(256, 128), ("sumpool", 2),
-                _mex_c(512, 256), ("sumpool", 2),
-                ("mex", dict(num_instances=10, blocks=[512, 1, 1], strides=[512, 1, 1], softmax_mode=True, normalize_offsets=True,
-                             use_unshared_regions=True, shared_offset_region=[1])),
-                ("flatten",)]),
-    "cfg5": dict(
-        input_shape=(3, 32, 32), classes=10,
-        layers=[("similarity", dict(num_instances=64, similarity_function="L2", blocks=[3, 3], strides=[1, 1], padding=[1, 1],
-                                    normalization_term=False, ignore_nan_input=False, out_of_bounds_value=0.0)),
-                _mex_c(128, 64), ("sumpool", 2), _mex_c(256, 128), ("sumpool", 2), _mex_c(512, 256), ("sumpool", 2),
-                ("mex", dict(num_instances=10, blocks=[512, 4, 4], strides=[512, 4, 4], softmax_mode=True, normalize_offsets=True,
-                             use_unshared_regions=True, unshared_offset_region=[-1])),
-                ("flatten",)]),
-}
+def _library_nregions(input_chw, num_instances, blocks, strides, kw):
+    return layers._mex_dims_helper(input_chw, num_instances, blocks, [0, 0, 0], strides,
+                                   use_unshared_regions=kw.get("use_unshared_regions", True),
+                                   shared_offset_region=kw.get("shared_offset_region", [-1]),
+                                   unshared_offset_region=kw.get("unshared_offset_region", [-1]))
 
 
 def init_parameters(spec, seed):
-    """Deterministic host-side initial values for every layer of a specification, in layer order:
-    similarity -> (templates ~ N(0, 0.05), weights = 1); mex -> log Dirichlet(1) offsets.
-    Returned as numpy arrays so that the CUDA network and the CPU checker start from the same bytes."""
-    rng = np.random.default_rng(seed)
-    c, h, w = spec["input_shape"]
-    out = []
-    for entry in spec["layers"]:
-        kind = entry[0]
-        if kind == "similarity":
-            kw = entry[1]
-            shape = (kw["num_instances"], c, kw["blocks"][0], kw["blocks"][1])
-            out.append(dict(templates=rng.normal(0, 0.05, size=shape).astype(np.float32), weights=np.ones(shape, np.float32)))
-            h = (h + 2 * kw["padding"][0] - kw["blocks"][0]) // kw["strides"][0] + 1
-            w = (w + 2 * kw["padding"][1] - kw["blocks"][1]) // kw["strides"][1] + 1
-            c = kw["num_instances"]
-        elif kind == "mex":
-            kw = entry[1]
-            blocks = layers._expand_dim_specification([c, h, w], kw["blocks"])
-            strides = layers._expand_dim_specification([c, h, w], kw["strides"])
-            nreg = layers._mex_dims_helper([c, h, w], kw["num_instances"], blocks, [0, 0, 0], strides,
-                                           use_unshared_regions=kw.get("use_unshared_regions", True),
-                                           shared_offset_region=kw.get("shared_offset_region", [-1]),
-                                           unshared_offset_region=kw.get("unshared_offset_region", [-1]))
-            k = blocks[0] * blocks[1] * blocks[2]
-            off = np.log(rng.dirichlet([1.0] * k, size=(nreg, kw["num_instances"]))).astype(np.float32)
-            out.append(dict(offsets=off.reshape((nreg, kw["num_instances"]) + tuple(blocks))))
-            co = (c - blocks[0]) // strides[0] + 1
-            h = (h - blocks[1]) // strides[1] + 1
-            w = (w - blocks[2]) // strides[2] + 1
-            c = co * kw["num_instances"]
-        elif kind == "sumpool":
-            h //= entry[1]; w //= entry[1]
-            out.append(None)
-        else:
-            out.append(None)
-    return out
+    """`netspec.init_parameters` with the library's `get_mex_offsets_nregions` for the region counts."""
+    return netspec.init_parameters(spec, seed, _library_nregions)
 
 
 class _SumPool(torch.autograd.Function):
