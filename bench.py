@@ -159,6 +159,71 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------- GPU leg
+TF32_FRACTION_OF_BF16 = 0.5      # dense TF32 tensor throughput is half the BF16 figure of MEASURED_PEAKS.json (no TF32 peak is measured)
+# arithmetic FP32 lane operations per (instance, tap, position) term of the Similarity kernels, by op and function
+SIM_OPS_PER_TERM = {"similarity_forward": 3, "similarity_input_grad": 3, "similarity_params_grad": 5}
+
+
+def op_roofline(key, r, hbm_gbs, tf32_tflops, fp32_tfma):
+    """Which roofline binds one operator call and what fraction of it the call reaches.
+    MEX: the slower of HBM time for the algorithmic bytes and tensor-core time for the three split-TF32 products of
+    every term.  Similarity: HBM time against FP32-pipe time at SIM_OPS_PER_TERM lane operations per term."""
+    ms = r["ms"] / r["calls"]
+    nbytes, terms = r["bytes"] / r["calls"], r["terms"] / r["calls"]
+    name = key.split("[")[0]
+    t_hbm = nbytes / (hbm_gbs * 1e9) * 1e3
+    out = {"hbm_GBps": round(nbytes / (ms * 1e-3) / 1e9, 1), "hbm_frac": round(t_hbm / ms, 4)}
+    if name.startswith("mex"):
+        t_alt = terms * 2 * 3 / (tf32_tflops * 1e12) * 1e3
+        out.update(bound="tensor" if t_alt > t_hbm else "hbm", tensor_frac=round(t_alt / ms, 4),
+                   tensor_TFLOPs=round(terms * 6 / (ms * 1e-3) / 1e12, 1))
+    else:
+        t_alt = terms * SIM_OPS_PER_TERM.get(name, 3) / (fp32_tfma * 1e12) * 1e3 if fp32_tfma else 0.0
+        out.update(bound="fp32" if t_alt > t_hbm else "hbm", fp32_frac=round(t_alt / ms, 4))
+    out["frac"] = round(max(t_hbm, t_alt) / ms, 4)
+    return out
+
+
+def fp32_peak(torch, dev):
+    """Measured FP32 fused multiply-adds per second (scalar and packed instruction), by the library's probe kernel."""
+    from simnets_tf_b200 import _lib
+    scratch = torch.zeros(4, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    out = {}
+    for name, packed in (("scalar", 0), ("packed", 1)):
+        best = 0.0
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            n = _lib.lib().simnets_fp32_fma_probe(packed, 4096, scratch.data_ptr(), stream)
+            e1.record()
+            e1.synchronize()
+            if n > 0:
+                best = max(best, n / (e0.elapsed_time(e1) * 1e-3))
+        out[name] = best / 1e12
+    return out
+
+
+def cfg4_section(torch, dev, hbm_gbs, tf32_tflops):
+    """The op pair of BASELINE configs[3] (N=256, C=64, 32x32, 20 % NaN; Similarity 256 x 3x3 then MEX 256 x [4,2,2]) through
+    the C ABI at the configuration's batch: device time per call, terms/s and fractions of the FP32 pipe and of HBM.
+    (4a = L2 with NaN-aware normalisation, the variant of the invalid literal config that the reference accepts.)"""
+    from simnets_tf_b200 import opbench
+    peak = fp32_peak(torch, dev)
+    fma = max(peak.values())
+    out = {"fp32_peak_TFMAs": {k: round(v, 2) for k, v in peak.items()}, "fp32_nominal_TFMAs": round(148 * 128 * 1.965e9 / 1e12, 2),
+           "batch": 256, "sim": {}, "mex": {}}
+    for layer, group, ops in (("cfg4_sim", "sim", ("forward", "input_grad", "params_grad")),
+                              ("cfg4_mex", "mex", ("forward", "input_grad", "offsets_grad"))):
+        for op in ops:
+            r = opbench.run(layer, op, 256, 10, 3)
+            row = {"calls": 1, "ms": r["ms_per_call"], "bytes": r["algorithmic_bytes"], "terms": r["terms"]}
+            rf = op_roofline(r["op"], row, hbm_gbs, tf32_tflops, fma)
+            rf.update(ms=round(r["ms_per_call"], 4), Tterms_per_s=round(r["Gterms_per_s"] / 1e3, 3))
+            out[group][op] = rf
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -188,17 +253,6 @@ def run_ours(args):
     net = SimNet(spec, seed=DATA_SEED[workload], device=dev)
     bucket = dp.GradBucket(net.parameters())
 
-    def compute(xd, ld):
-        bucket.zero()
-        loss = net.loss(xd, ld, gb)
-        loss.backward()
-        return loss
-
-    def step(xd, ld):
-        loss = compute(xd, ld)
-        bucket.all_reduce()
-        return loss
-
     def barrier():
         if world > 1:
             dist.barrier()
@@ -211,83 +265,117 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- forward + backward as ONE CUDA graph: at 256 samples per GPU the step is a few ms of device time behind
-    # ~600 launches, so replaying a graph keeps the host off the critical path.  The bucket all-reduce is enqueued
-    # eagerly right behind each replay (one launch), on the same stream; it is not part of the capture.
-    graph, loss_static, launches_per_step = None, None, 0
+    # ---- do the N-way sharded gradients, summed by NCCL, equal the gradients of the whole batch on one GPU?
+    # 64 samples: every rank differentiates its shard, the bucket is all-reduced, rank 0 differentiates all 64 as well.
+    grad_check = None
+    if world > 1:
+        nchk = 64
+        clo, chi = dp.shard_bounds(nchk, world, rank)
+        xc, lc = torch.from_numpy(x_all[:nchk]).to(dev), torch.from_numpy(l_all[:nchk]).to(dev)
+        bucket.zero()
+        if chi > clo:
+            net.loss(xc[clo:chi], lc[clo:chi], nchk).backward()
+        bucket.all_reduce()
+        summed = bucket.flat.clone()
+        bucket.zero()
+        worst = 0.0
+        if rank == 0:
+            net.loss(xc, lc, nchk).backward()
+            off = 0
+            for p in bucket.params:
+                a, b = summed[off:off + p.numel()], bucket.flat[off:off + p.numel()]
+                worst = max(worst, float((a - b).abs().max() / b.abs().max().clamp_min(1e-30)))
+                off += p.numel()
+        barrier()
+        grad_check = {"samples": nchk, "max_rel_err": worst, "tolerance": 1e-4, "ok": bool(worst <= 1e-4),
+                      "what": "per parameter tensor, max |sum over ranks - one GPU| / max |one GPU|"}
+
+    # ---- forward + backward as two CUDA graphs around the cut of dp.OverlappedStep (at 256 samples per GPU the step is
+    # about a millisecond behind ~60 launches, so replaying graphs keeps the host off the critical path); the two
+    # all-reduces are enqueued eagerly, the first on a second stream while the second graph runs.
     for _ in range(args.warmup):
-        step(x_dev, l_dev)
+        bucket.zero()
+        net.loss(x_dev, l_dev, gb).backward()
+        bucket.all_reduce()
     barrier()
-    if not args.no_graph:
-        side = torch.cuda.Stream(device=dev)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for _ in range(2):
-                compute(x_dev, l_dev)
-        torch.cuda.current_stream().wait_stream(side)
-        barrier()
-        graph = torch.cuda.CUDAGraph()
-        n0 = _lib.launch_count()
-        with torch.cuda.graph(graph):
-            loss_static = compute(x_dev, l_dev)
-        launches_per_step = _lib.launch_count() - n0
-        barrier()
-
-    def run_step():
-        if graph is not None:
-            graph.replay()
-            bucket.all_reduce()
-            return loss_static
-        return step(x_dev, l_dev)
-
+    n0 = _lib.launch_count()
+    stepper = dp.OverlappedStep(net, bucket, x_dev, l_dev, gb, graphs=not args.no_graph)
+    launches_per_step = (_lib.launch_count() - n0) // 3 if not args.no_graph else 0      # two warm-up passes + the capture
     for _ in range(2):
-        run_step()
+        stepper.run()
     barrier()
 
-    # ---- device-resident timing (inputs already in HBM)
+    # ---- device-resident timing (inputs already in HBM): R repeats of K steps, each repeat bracketed by a barrier and
+    # a device synchronisation; the reported time is the median repeat (max over ranks per repeat)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     launches0 = _lib.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        run_step()
-    e1.record()
-    barrier()
-    ms = max_over_ranks(e0.elapsed_time(e1))
-    launches = launches_per_step * args.steps if graph is not None else _lib.launch_count() - launches0
+    repeat_ms = []
+    for _ in range(args.repeats):
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            stepper.run()
+        e1.record()
+        barrier()
+        repeat_ms.append(max_over_ranks(e0.elapsed_time(e1)))
+    ms = statistics.median(repeat_ms)
+    launches = launches_per_step * args.steps if not args.no_graph else (_lib.launch_count() - launches0) // args.repeats
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---- per-operator device time: the same K steps again, launched eagerly with CUDA events around every call of
-    # the library (events cannot bracket kernels inside a replayed graph)
+    # ---- per-operator device time: K steps launched eagerly with CUDA events around every call of the library
+    # (events cannot bracket kernels inside a replayed graph)
+    eager = dp.OverlappedStep(net, bucket, x_dev, l_dev, gb, graphs=False)
+    eager.run()
     PROFILE.start()
     for _ in range(args.steps):
-        step(x_dev, l_dev)
+        eager.run()
     ops = PROFILE.stop()
     barrier()
 
-    # ---- end to end: pinned host inputs -> device, step, loss back to the host, every step
+    # ---- end to end: pinned host inputs -> device, step, loss back to the host, every step.  The next step's inputs
+    # travel on a copy stream while the current step computes; a device-to-device copy hands them to the graphs' buffers.
     h2d = x_host.numel() * x_host.element_size() + l_host.numel() * l_host.element_size()
     loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+    copy_stream = torch.cuda.Stream(device=dev)
+    x_next, l_next = torch.empty_like(x_dev), torch.empty_like(l_dev)
+    arrived, consumed = torch.cuda.Event(), torch.cuda.Event()
+
+    def prefetch():
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed)              # the staging buffers have been handed over
+            x_next.copy_(x_host, non_blocking=True)
+            l_next.copy_(l_host, non_blocking=True)
+            arrived.record(copy_stream)
 
     def e2e_step():
-        x_dev.copy_(x_host, non_blocking=True)        # the graph reads these two buffers
-        l_dev.copy_(l_host, non_blocking=True)
-        loss = run_step()
+        main = torch.cuda.current_stream()
+        main.wait_event(arrived)
+        x_dev.copy_(x_next, non_blocking=True)            # the graphs read these two buffers
+        l_dev.copy_(l_next, non_blocking=True)
+        consumed.record(main)
+        prefetch()                                        # the step after this one
+        loss = stepper.run()
         loss_host.copy_(loss.detach(), non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        main.synchronize()
         return float(loss_host)
 
-    for _ in range(min(args.warmup, 2)):
+    consumed.record(torch.cuda.current_stream())
+    prefetch()
+    for _ in range(2):
         e2e_step()
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        last_loss = e2e_step()
-    e1.record()
-    barrier()
-    ms_e2e = max_over_ranks(e0.elapsed_time(e1))
+    e2e_ms = []
+    for _ in range(max(1, args.repeats // 5)):
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            last_loss = e2e_step()
+        e1.record()
+        barrier()
+        e2e_ms.append(max_over_ranks(e0.elapsed_time(e1)))
+    ms_e2e = statistics.median(e2e_ms)
 
     if rank != 0:
         if world > 1:
@@ -296,13 +384,16 @@ def run_ours(args):
 
     peaks, peak_src = measured_peaks()
     hbm_peak = float(peaks["hbm_gbs"])
-    # dominant operator call group by device time inside the timed region
+    tf32_peak = float(peaks.get("bf16_tflops", 1590.0)) * TF32_FRACTION_OF_BF16
+    fma_peak = max(fp32_peak(torch, dev).values())
+    # operator call groups by device time inside the eager pass, each with the roofline that binds it
     table = []
     for key, r in ops.items():
         avg_ms = r["ms"] / r["calls"]
-        table.append({"op": key, "calls": r["calls"], "ms_total": round(r["ms"], 4), "ms_per_call": round(avg_ms, 5),
-                      "GBps": round(r["bytes"] / r["calls"] / (avg_ms * 1e-3) / 1e9, 2),
-                      "Gterms_per_s": round(r["terms"] / r["calls"] / (avg_ms * 1e-3) / 1e9, 2)})
+        row = {"op": key, "calls": r["calls"], "ms_total": round(r["ms"], 4), "ms_per_call": round(avg_ms, 5),
+               "Gterms_per_s": round(r["terms"] / r["calls"] / (avg_ms * 1e-3) / 1e9, 2)}
+        row.update(op_roofline(key, r, hbm_peak, tf32_peak, fma_peak))
+        table.append(row)
     table.sort(key=lambda r: -r["ms_total"])
     top = table[0]
     # DRAM traffic of the dominant call from one ncu capture at a smaller batch, scaled to this batch (every byte these
@@ -310,25 +401,36 @@ def run_ours(args):
     m = re.match(r"(\w+)\[B(\d+) (.*)\]$", top["op"])
     per_sample = NCU_DRAM_BYTES_PER_SAMPLE.get("%s[%s]" % (m.group(1), m.group(3))) if m else None
     traffic = int(per_sample * int(m.group(2))) if per_sample else None
-    roofline = {"kernel": top["op"], "bound": "hbm", "achieved": top["GBps"], "peak": hbm_peak, "unit": "GB/s",
-                "frac": round(top["GBps"] / hbm_peak, 4), "peak_source": "of " + peak_src, "traffic": traffic,
-                "share_of_step": round(top["ms_total"] / ms, 4),
-                "fp32": {"Gterms_per_s": top["Gterms_per_s"], "nominal_fp32_tflops": round(NOMINAL_FP32_TFLOPS, 2)}}
+    if top["bound"] == "tensor":
+        roofline = {"kernel": top["op"], "bound": "tensor", "achieved": top["tensor_TFLOPs"], "peak": tf32_peak, "unit": "TFLOP/s",
+                    "frac": top["tensor_frac"], "peak_source": "half the BF16 burst of " + peak_src + " peaks (TF32)", "traffic": traffic}
+    else:
+        roofline = {"kernel": top["op"], "bound": "hbm", "achieved": top["hbm_GBps"], "peak": hbm_peak, "unit": "GB/s",
+                    "frac": top["hbm_frac"], "peak_source": "of " + peak_src, "traffic": traffic}
+    roofline["share_of_step"] = round(top["ms_total"] / args.steps / (ms / args.steps), 4)
 
     line = {
         "metric": "similarity_mex_fwd_bwd_samples_per_s", "value": gb * args.steps / (ms * 1e-3), "unit": "samples/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload, "global_batch": gb, "per_gpu_batch": hi - lo, "parallelism": "dp%d" % world, "launch": "eager" if graph is None else "cuda graph replay",
+        "config": {"workload": workload, "global_batch": gb, "per_gpu_batch": hi - lo, "parallelism": "dp%d" % world,
+                   "launch": "eager" if args.no_graph else "two cuda graphs per step, all-reduce of the deep layers' gradients overlapped with the rest of the backward pass",
                    "input": list(spec["input_shape"]), "l2": "per-step working set (>0.5 GB of activations per 256 samples) exceeds the 126 MB L2",
-                   "grad_bucket_bytes": bucket.nbytes()},
+                   "grad_bucket_bytes": bucket.nbytes(), "repeats": args.repeats,
+                   "timing": "median over %d repeats of %d steps (min %.3f, max %.3f ms per step)" % (
+                       args.repeats, args.steps, min(repeat_ms) / args.steps, max(repeat_ms) / args.steps)},
         "clocks": clocks,
         "e2e": {"value": gb * args.steps / (ms_e2e * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
-                "ms_per_step": ms_e2e / args.steps, "loss": last_loss},
+                "ms_per_step": ms_e2e / args.steps, "loss": last_loss,
+                "how": "inputs prefetched from pinned memory on a copy stream one step ahead; the loss is read back and the stream synchronised every step"},
         "gpu_launches": launches,
         "roofline": roofline,
         "ops": table[:12],
     }
+    if grad_check is not None:
+        line["grad_check"] = grad_check
+    if world == 1 and not args.no_cfg4:
+        line["cfg4"] = cfg4_section(torch, dev, hbm_peak, tf32_peak)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(workload, x_all, l_all)
     print(json.dumps(line))
@@ -345,7 +447,9 @@ def main():
     ap.add_argument("--workload", choices=sorted(GLOBAL_BATCH), default="cfg5")
     ap.add_argument("--ref-sample", type=int, default=0, help="samples per reference step (default: one per host core, at least 8)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying one CUDA graph")
+    ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying CUDA graphs")
+    ap.add_argument("--repeats", type=int, default=25, help="timed repeats of the K steps; the median repeat is reported")
+    ap.add_argument("--no-cfg4", action="store_true", help="skip the single-operator section of the large op pair")
     ap.add_argument("--global-batch", type=int, default=0,
                     help="diagnostics only: another global batch than the configuration's (e.g. 256 on one GPU = the per-GPU share of 8)")
     args = ap.parse_args()

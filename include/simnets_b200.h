@@ -266,6 +266,14 @@ SIMNETS_API int simnets_mex_backward(const simnets_mex_desc* d,
                                      const void* x, const void* offsets, const void* y, const void* dy,
                                      void* dx, void* doffsets, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- measurement probe ---------------------------------------------------- */
+/* Launches a register-only kernel of independent FP32 fused multiply-adds on every SM (packed != 0: the packed
+ * two-lane instruction) and returns the number of fused multiply-adds it executes, or a negative value on error.
+ * Time it with events on `stream`: FMAs / seconds is the FP32-pipe peak that "fraction of FP32 peak" figures of
+ * the Similarity kernels are quoted against.  `scratch`: at least 4 bytes of device memory (never written).
+ * No counterpart in the reference. */
+SIMNETS_API int64_t simnets_fp32_fma_probe(int32_t packed, int32_t iters, void* scratch, void* stream);
+
 /* ---- sum pooling ----------------------------------------------------------- */
 /* y[p, h, w] = x[p, 2h, 2w] + x[p, 2h, 2w+1] + x[p, 2h+1, 2w] + x[p, 2h+1, 2w+1] over a dense float32 tensor
  * [planes, height, width] (planes = batch * channels); height and width even, else SIMNETS_E_UNSUPPORTED.

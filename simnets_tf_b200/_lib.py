@@ -51,6 +51,8 @@ def lib():
         l.simnets_normalize_offsets_forward.argtypes = [C.c_int64, C.c_int32, _P, _P, _P]
         l.simnets_normalize_offsets_backward.argtypes = [C.c_int64, C.c_int32, _P, _P, _P, _P]
         l.simnets_sum_pool2x2_forward.argtypes = [C.c_int64, C.c_int32, C.c_int32, _P, _P, _P]
+        l.simnets_fp32_fma_probe.restype = C.c_int64
+        l.simnets_fp32_fma_probe.argtypes = [C.c_int32, C.c_int32, _P, _P]
         l.get_mex_offsets_nregions.restype = C.c_int
         _lib = l
     return _lib

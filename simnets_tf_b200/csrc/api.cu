@@ -243,6 +243,14 @@ int simnets_normalize_offsets_backward(int64_t rows, int32_t k, const void* off,
     return from_cuda(launch_normalize_offsets_bwd(rows, k, (const float*)off, (const float*)dout, (float*)doff, as_stream(stream)));
 }
 
+int64_t simnets_fp32_fma_probe(int32_t packed, int32_t iters, void* scratch, void* stream) {
+    if (iters < 1 || !scratch) return SIMNETS_E_DESC;
+    const int blocks = device_sm_count() * 2;                       // two CTAs of 1024 threads fill an SM
+    const cudaError_t e = launch_fp32_probe(packed != 0, blocks, iters, (float*)scratch, as_stream(stream));
+    if (e != cudaSuccess) return -int64_t(e) - 1000;
+    return int64_t(blocks) * 1024 * 16 * iters;
+}
+
 int simnets_sum_pool2x2_forward(int64_t planes, int32_t height, int32_t width, const void* x, void* y, void* stream) {
     if (planes < 0 || height < 0 || width < 0) return SIMNETS_E_DESC;
     if (height % 2 || width % 2) return SIMNETS_E_UNSUPPORTED;

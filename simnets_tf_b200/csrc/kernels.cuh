@@ -13,6 +13,9 @@ void count_launch(int n = 1);
 cudaError_t launch_normalize_offsets_fwd(long long rows, int K, const float* off, float* out, cudaStream_t);
 cudaError_t launch_normalize_offsets_bwd(long long rows, int K, const float* off, const float* dout, float* doff, cudaStream_t);
 
+// probe.cu
+cudaError_t launch_fp32_probe(bool packed, int blocks, int iters, float* out, cudaStream_t);
+
 // pool.cu
 cudaError_t launch_sum_pool2(long long planes, int H, int W, const float* x, float* y, cudaStream_t);
 
@@ -48,6 +51,14 @@ cudaError_t launch_mex_dx_smallm(const MexGeo&, const float* x, const float* eo,
                                  float* dx, const int* flag, cudaStream_t);
 cudaError_t launch_mex_doff_smallm(const MexGeo&, const float* x, const float* mo, const float* mx, const float* y, const float* dy,
                                    float* part, int splits, const int* flag, cudaStream_t);
+// the head: a single region of contiguous patches (whole samples), several positions per CTA, both gradients from one read of x
+bool mex_head_shape(const MexGeo&);
+int mex_head_splits(const MexGeo&);
+cudaError_t launch_mex_fwd_head(const MexGeo&, const float* x, const float* eot, const float* mo, float* mx, float* y,
+                                const int* flag, cudaStream_t);
+cudaError_t launch_mex_bwd_head(const MexGeo&, bool want_dx, bool want_doff, const float* x, const float* eo, const float* mo,
+                                const float* mx, const float* y, const float* dy, float* dx, float* part, int splits,
+                                const int* flag, cudaStream_t);
 // mex_smallk.cu -- one thread per position, for K <= 32 (HBM-bound streaming regime)
 cudaError_t launch_mex_fwd_smallk(const MexGeo&, const float* x, const float* eo, const float* mo, float* y, const int* flag, cudaStream_t);
 cudaError_t launch_mex_dx_smallk(const MexGeo&, const float* x, const float* eo, const float* mo, const float* y, const float* dy,

@@ -102,6 +102,7 @@ __host__ inline MexWs carve(const MexGeo& g, void* base) {
     w.fwd_bytes = off;
     int max_splits = (tc_shape(g) || tc_smallk_shape(g)) ? std::max(doff_splits(g), mex_tc_doff_splits(g)) : doff_splits(g);
     if ((tc_shape(g) || tc_smallk_shape(g)) && mex_pair_shape(g)) max_splits = std::max(max_splits, mex_pair_doff_splits(g));
+    if (mex_head_shape(g)) max_splits = std::max(max_splits, mex_head_splits(g));
     w.part = reinterpret_cast<float*>(take(sizeof(float) * (size_t)max_splits * g.R * g.M * g.K));
     w.tc_tiles = reinterpret_cast<float*>(take((tc_shape(g) || tc_smallk_shape(g)) ? sizeof(float) * mex_tc_tile_floats(g) : 0));
     w.bytes = off;

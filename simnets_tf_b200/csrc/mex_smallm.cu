@@ -22,6 +22,7 @@ __device__ __forceinline__ float warp_min(float v) {
     for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
+__device__ __forceinline__ float ex2_approx(float v) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v)); return r; }
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -209,6 +210,184 @@ __global__ void __launch_bounds__(kT) mex_doff_smallm(MexGeo g, const float* __r
     }
 }
 
+
+// ---- contiguous patches: the classifier head over whole samples -----------------------------------------------------
+// When every patch is one contiguous run of K floats (patches_contiguous) and there is a single offsets region, the op
+// is a sliver GEMM [positions x K] x [K x M <= 16] whose cost is reading x.  One CTA per position (above) re-reads the
+// whole offsets table (M K floats) for every position; here a CTA takes several positions, so that the table is read
+// once per group, and the backward pass produces the input gradient and the offsets-gradient partial sums from ONE read
+// of x.  The forward kernel stores the per-position maxima, which primes the workspace for the gradients.
+constexpr int kHeadPB = 8;         // positions per CTA in the forward pass
+
+template <int MP>
+__global__ void __launch_bounds__(kT) mex_fwd_head(MexGeo g, int pb, const float* __restrict__ x, const float* __restrict__ eot,
+                                                   const float* __restrict__ mo, float* __restrict__ mx, float* __restrict__ y,
+                                                   const int* __restrict__ flag) {
+    __shared__ float red[kT / 32][kHeadPB];
+    __shared__ float racc[kT / 32][kHeadPB][MP];
+    __shared__ float mxs[kHeadPB];
+    if (*flag) return;
+    const long long P = (long long)g.B * g.N;                      // positions (one region)
+    const long long p0 = (long long)blockIdx.x * pb;
+    const int np = int(min((long long)pb, P - p0));
+    const int K = g.K, M = g.M, ldm = pad4(g.M);
+    const bool up = g.eps > 0;
+    const float a = float(g.eps) * 1.4426950408889634f;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // position p of the group: sample n = p / N, patch = channels [c0, c0 + bc) of that sample, contiguous
+    const float* xp[kHeadPB];
+#pragma unroll
+    for (int p = 0; p < kHeadPB; ++p) {
+        const long long q = p0 + (p < np ? p : 0);
+        const int n = int(q / g.N), pos = int(q % g.N);
+        xp[p] = x + ((size_t)n * g.C + (size_t)(pos / (g.Wo * g.Ho)) * g.sc) * g.H * g.W;
+    }
+    // pass 1: maxima (NaN taps ignored, as fmaxf / fminf do)
+    float v[kHeadPB];
+#pragma unroll
+    for (int p = 0; p < kHeadPB; ++p) v[p] = up ? -CUDART_INF_F : CUDART_INF_F;
+    for (int k = threadIdx.x; k < K; k += kT) {
+#pragma unroll
+        for (int p = 0; p < kHeadPB; ++p) {
+            const float t = __ldg(xp[p] + k);
+            v[p] = up ? fmaxf(v[p], t) : fminf(v[p], t);
+        }
+    }
+#pragma unroll
+    for (int p = 0; p < kHeadPB; ++p) {
+        v[p] = up ? warp_max(v[p]) : warp_min(v[p]);
+        if (lane == 0) red[warp][p] = v[p];
+    }
+    __syncthreads();
+    if (threadIdx.x < kHeadPB) {
+        float r = red[0][threadIdx.x];
+        for (int w = 1; w < kT / 32; ++w) r = up ? fmaxf(r, red[w][threadIdx.x]) : fminf(r, red[w][threadIdx.x]);
+        mxs[threadIdx.x] = r;
+        if (threadIdx.x < np) mx[p0 + threadIdx.x] = r;
+    }
+    __syncthreads();
+    float mxv[kHeadPB];
+#pragma unroll
+    for (int p = 0; p < kHeadPB; ++p) mxv[p] = mxs[p];
+    // pass 2 (x comes from the caches now): sums over taps for every instance
+    float acc[kHeadPB][MP];
+#pragma unroll
+    for (int p = 0; p < kHeadPB; ++p)
+#pragma unroll
+        for (int m = 0; m < MP; ++m) acc[p][m] = 0.f;
+    for (int k = threadIdx.x; k < K; k += kT) {
+        float eo[MP];
+        const float4* row = reinterpret_cast<const float4*>(eot + (size_t)k * ldm);
+#pragma unroll
+        for (int q = 0; q < MP / 4; ++q) {
+            const float4 t = __ldg(row + q);                      // MP = ldm; columns past M hold stale bytes and are never stored
+            eo[q * 4] = t.x; eo[q * 4 + 1] = t.y; eo[q * 4 + 2] = t.z; eo[q * 4 + 3] = t.w;
+        }
+#pragma unroll
+        for (int p = 0; p < kHeadPB; ++p) {
+            const float e = ex2_approx(a * (__ldg(xp[p] + k) - mxv[p]));
+#pragma unroll
+            for (int m = 0; m < MP; ++m) acc[p][m] = fmaf(e, eo[m], acc[p][m]);
+        }
+    }
+#pragma unroll
+    for (int p = 0; p < kHeadPB; ++p)
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+            const float t = warp_sum(acc[p][m]);
+            if (lane == 0) racc[warp][p][m] = t;
+        }
+    __syncthreads();
+    for (int i = threadIdx.x; i < np * M; i += kT) {
+        const int p = i / M, m = i % M;
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kT / 32; ++w) sum += racc[w][p][m];
+        const long long q = p0 + p;
+        const int n = int(q / g.N), pos = int(q % g.N);
+        y[((long long)n * M + m) * g.N + pos] = mxs[p] + mo[m] + (fast_log(sum) + float(g.cst)) / float(g.eps);
+    }
+}
+
+// Backward: CTA = (tile of kT * KPT taps, split of the positions).  Per position: Q[m] = dy * exp(eps (mx + mo - y) + c);
+// per tap of the tile: Ex once, then dx = Ex * sum_m Eo[m, k] Q[m] and U[m, k] += Q[m] * Ex.
+constexpr int kHeadKPT = 4;        // taps per thread
+
+template <int MP, bool DX, bool DOFF>
+__global__ void __launch_bounds__(kT) mex_bwd_head(MexGeo g, const float* __restrict__ x, const float* __restrict__ eo,
+                                                   const float* __restrict__ mo, const float* __restrict__ mx,
+                                                   const float* __restrict__ y, const float* __restrict__ dy,
+                                                   float* __restrict__ dx, float* __restrict__ part, int splits,
+                                                   const int* __restrict__ flag) {
+    __shared__ float Qs[2][kMaxM + 1];
+    if (*flag) return;
+    const long long P = (long long)g.B * g.N;
+    const int K = g.K, M = g.M, ldk = pad4(g.K);
+    const int ktiles = (K + kT * kHeadKPT - 1) / (kT * kHeadKPT);
+    const int kt = blockIdx.x % ktiles, split = blockIdx.x / ktiles;
+    const long long p_begin = P * split / splits, p_end = P * (split + 1) / splits;
+    const float a = float(g.eps) * 1.4426950408889634f, c2 = float(g.cst) * 1.4426950408889634f;
+    const int kbase = kt * kT * kHeadKPT + threadIdx.x;            // this thread's taps: kbase + i * kT
+    float eor[MP][kHeadKPT];                                     // Eo of this thread's taps
+#pragma unroll
+    for (int m = 0; m < MP; ++m)
+#pragma unroll
+        for (int i = 0; i < kHeadKPT; ++i)
+            eor[m][i] = (DX && m < M && kbase + i * kT < K) ? __ldg(eo + (size_t)m * ldk + kbase + i * kT) : 0.f;
+    float acc[MP][kHeadKPT];
+#pragma unroll
+    for (int m = 0; m < MP; ++m)
+#pragma unroll
+        for (int i = 0; i < kHeadKPT; ++i) acc[m][i] = 0.f;
+    for (long long q = p_begin; q < p_end; ++q) {
+        const int n = int(q / g.N), pos = int(q % g.N);
+        const int buf = int(q - p_begin) & 1;
+        if (threadIdx.x < kMaxM) {
+            const int m = threadIdx.x;
+            float qv = 0.f;
+            if (m < M) {
+                const long long o = ((long long)n * M + m) * g.N + pos;
+                qv = __ldg(dy + o) * ex2_approx(fmaf(a, (__ldg(mx + q) - __ldg(y + o)) + mo[m], c2));
+            }
+            Qs[buf][m] = qv;
+        }
+        if (threadIdx.x == kMaxM) Qs[buf][kMaxM] = __ldg(mx + q);
+        __syncthreads();                                           // (double buffered: one barrier per position)
+        const float mxv = Qs[buf][kMaxM];
+        const size_t base = ((size_t)n * g.C + (size_t)(pos / (g.Wo * g.Ho)) * g.sc) * g.H * g.W;
+        float e[kHeadKPT];
+#pragma unroll
+        for (int i = 0; i < kHeadKPT; ++i) e[i] = kbase + i * kT < K ? ex2_approx(a * (__ldg(x + base + kbase + i * kT) - mxv)) : 0.f;
+        float qm[MP];
+#pragma unroll
+        for (int m = 0; m < MP; ++m) qm[m] = Qs[buf][m];
+        if (DX) {
+#pragma unroll
+            for (int i = 0; i < kHeadKPT; ++i) {
+                float s = 0.f;
+#pragma unroll
+                for (int m = 0; m < MP; ++m) s = fmaf(eor[m][i], qm[m], s);
+                if (kbase + i * kT < K) dx[base + kbase + i * kT] = e[i] * s;
+            }
+        }
+        if (DOFF) {
+#pragma unroll
+            for (int m = 0; m < MP; ++m)
+#pragma unroll
+                for (int i = 0; i < kHeadKPT; ++i) acc[m][i] = fmaf(qm[m], e[i], acc[m][i]);
+        }
+    }
+    if (DOFF) {
+        float* dst = part + (size_t)split * M * K;
+#pragma unroll
+        for (int m = 0; m < MP; ++m)
+            if (m < M)
+#pragma unroll
+                for (int i = 0; i < kHeadKPT; ++i)
+                    if (kbase + i * kT < K) dst[(size_t)m * K + kbase + i * kT] = acc[m][i];
+    }
+}
+
 }  // namespace
 
 cudaError_t launch_mex_colmax_wide(const MexGeo& g, const float* x, float* mx, const int* flag, cudaStream_t s) {
@@ -244,6 +423,60 @@ cudaError_t launch_mex_doff_smallm(const MexGeo& g, const float* x, const float*
     const int blocks = ((g.K + kT - 1) / kT) * g.R * splits;
     if (g.bh == 1 && g.bw == 1) mex_doff_smallm<true><<<blocks, kT, 0, s>>>(g, x, mo, mx, y, dy, part, splits, flag);
     else mex_doff_smallm<false><<<blocks, kT, 0, s>>>(g, x, mo, mx, y, dy, part, splits, flag);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// ---- the contiguous-patch head
+bool mex_head_shape(const MexGeo& g) {
+    return smallm_shape(g) && g.R == 1 && g.bw == g.W && g.pw == 0 && g.bh == g.H && g.ph == 0 && g.pc == 0 &&
+           (g.Co - 1) * g.sc + g.bc <= g.C && g.Ho == 1 && g.Wo == 1;
+}
+
+int mex_head_splits(const MexGeo& g) {
+    const int ktiles = (g.K + kT * kHeadKPT - 1) / (kT * kHeadKPT);
+    const long long P = (long long)g.B * g.N;
+    long long s = (2LL * device_sm_count() + ktiles - 1) / ktiles;
+    if (s > P) s = P;
+    if (s < 1) s = 1;
+    return int(s);
+}
+
+cudaError_t launch_mex_fwd_head(const MexGeo& g, const float* x, const float* eot, const float* mo, float* mx, float* y,
+                                const int* flag, cudaStream_t s) {
+    const long long P = (long long)g.B * g.N;
+    int pb = kHeadPB;
+    while (pb > 1 && (P + pb - 1) / pb < device_sm_count()) pb >>= 1;          // small batches: fewer positions per CTA, more CTAs
+    const long long blocks = (P + pb - 1) / pb;
+    if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    switch (pad4(g.M)) {
+    case 4: mex_fwd_head<4><<<int(blocks), kT, 0, s>>>(g, pb, x, eot, mo, mx, y, flag); break;
+    case 8: mex_fwd_head<8><<<int(blocks), kT, 0, s>>>(g, pb, x, eot, mo, mx, y, flag); break;
+    case 12: mex_fwd_head<12><<<int(blocks), kT, 0, s>>>(g, pb, x, eot, mo, mx, y, flag); break;
+    default: mex_fwd_head<16><<<int(blocks), kT, 0, s>>>(g, pb, x, eot, mo, mx, y, flag); break;
+    }
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_mex_bwd_head(const MexGeo& g, bool want_dx, bool want_doff, const float* x, const float* eo, const float* mo,
+                                const float* mx, const float* y, const float* dy, float* dx, float* part, int splits,
+                                const int* flag, cudaStream_t s) {
+    const int ktiles = (g.K + kT * kHeadKPT - 1) / (kT * kHeadKPT);
+    const int blocks = ktiles * splits;
+#define HEAD_BWD(MP)                                                                                                          \
+    do {                                                                                                                      \
+        if (want_dx && want_doff) mex_bwd_head<MP, true, true><<<blocks, kT, 0, s>>>(g, x, eo, mo, mx, y, dy, dx, part, splits, flag); \
+        else if (want_dx) mex_bwd_head<MP, true, false><<<blocks, kT, 0, s>>>(g, x, eo, mo, mx, y, dy, dx, part, splits, flag);        \
+        else mex_bwd_head<MP, false, true><<<blocks, kT, 0, s>>>(g, x, eo, mo, mx, y, dy, dx, part, splits, flag);                     \
+    } while (0)
+    switch (pad4(g.M)) {
+    case 4: HEAD_BWD(4); break;
+    case 8: HEAD_BWD(8); break;
+    case 12: HEAD_BWD(12); break;
+    default: HEAD_BWD(16); break;
+    }
+#undef HEAD_BWD
     count_launch();
     return cudaGetLastError();
 }

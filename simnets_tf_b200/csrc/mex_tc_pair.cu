@@ -783,23 +783,27 @@ __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, con
         if (!good) sh.failed = 1;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (good) {
+            // lane = instance row in tensor memory; a warp turns each 32 x 32 block through shared memory (the operand
+            // stages are free by now) so that a store instruction writes 32 consecutive taps of ONE row: whole 128-byte
+            // lines instead of 32 scattered floats (the scattered form cost more than the main loop at small batches)
             const int quarter = warp & 3, t = (warp >> 2) & 1, chalf = warp >> 3;      // lane quarter, tile of the pair, half of the columns
+            float* tb = reinterpret_cast<float*>(dsm) + warp * (32 * 33);
 #pragma unroll 1
             for (int mt = 0; mt < MT; ++mt) {
-                const int m = m_first + mt * 128 + quarter * 32 + lane;
-                float* dst = part + (((size_t)split * g.R + (2 * pair + t)) * M + (m < M ? m : 0)) * K + k_first;
+                const int m0 = m_first + mt * 128 + quarter * 32;
+                float* dst = part + (((size_t)split * g.R + (2 * pair + t)) * M + m0) * K + k_first;
 #pragma unroll 1
-                for (int c0 = chalf * (NT / 2); c0 < (chalf + 1) * (NT / 2); c0 += 16) {
-                    uint32_t v[16];
-                    if (nchunks > 0) {
-                        tmem_ld16_issue(tmem + uint32_t((t * MT + mt) * NT + c0) + (uint32_t(quarter * 32) << 16), v);
-                        tmem_ld_wait();
-                    }
-                    if (m < M) {
+                for (int c0 = chalf * (NT / 2); c0 < (chalf + 1) * (NT / 2); c0 += 32) {
+                    uint32_t v[32];
+                    if (nchunks > 0) tmem_ld32(tmem + uint32_t((t * MT + mt) * NT + c0) + (uint32_t(quarter * 32) << 16), v);
 #pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            if (k_first + c0 + i < K) dst[c0 + i] = nchunks > 0 ? __uint_as_float(v[i]) : 0.f;
-                    }
+                    for (int i = 0; i < 32; ++i) tb[lane * 33 + i] = nchunks > 0 ? __uint_as_float(v[i]) : 0.f;
+                    __syncwarp();
+                    const bool kin = k_first + c0 + lane < K;
+#pragma unroll 4
+                    for (int r = 0; r < 32; ++r)
+                        if (kin && m0 + r < M) dst[(size_t)r * K + c0 + lane] = tb[r * 33 + lane];
+                    __syncwarp();
                 }
             }
         }

@@ -423,7 +423,7 @@ cudaError_t run_prepasses(const MexGeo& g, const MexWs& w, const float* x, const
 bool forward_primes_workspace(MexGeo g, uint32_t flags) {
     if (!(flags & SIMNETS_FLAG_MEX_WORKSPACE_PRIMED)) return false;
     g.gp = 1; g.Ng = g.N;        // the forward pass never sees a pooled dy
-    return !smallm_shape(g) && !use_smallk_kernels(g, flags);
+    return (!smallm_shape(g) || mex_head_shape(g)) && !use_smallk_kernels(g, flags);
 }
 
 }  // namespace
@@ -451,7 +451,8 @@ cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* o
     if (smallm_shape(g)) {
         cudaError_t e = run_prepasses(g, w, x, off, s, false);
         if (e != cudaSuccess) return e;
-        e = launch_mex_fwd_smallm(g, x, w.eot, w.mo, y, w.flag, s);
+        e = mex_head_shape(g) ? launch_mex_fwd_head(g, x, w.eot, w.mo, w.mx, y, w.flag, s)        // (also leaves the maxima for the gradients)
+                              : launch_mex_fwd_smallm(g, x, w.eot, w.mo, y, w.flag, s);
         if (e != cudaSuccess) return e;
         return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);
     }
@@ -560,6 +561,15 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
         if (e != cudaSuccess) return e;
         return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
     }
+    if (small && smallm_shape(g) && mex_head_shape(g)) {
+        if (!(prepped || forward_primes_workspace(g, flags))) {              // run_prepasses skipped the maxima for this family
+            e = launch_mex_colmax_wide(g, x, w.mx, w.flag, s);
+            if (e != cudaSuccess) return e;
+        }
+        e = launch_mex_bwd_head(g, true, false, x, w.eo, w.mo, w.mx, y, dy, dx, nullptr, 1, w.flag, s);
+        if (e != cudaSuccess) return e;
+        return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
+    }
     if (small) {
         e = launch_mex_dx_smallm(g, x, w.eo, w.mo, y, dy, dx, w.flag, s);
         if (e != cudaSuccess) return e;
@@ -608,6 +618,17 @@ cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* 
         if (e != cudaSuccess) return e;
         return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
     }
+    if (smallm_shape(g) && mex_head_shape(g)) {
+        const int hs = mex_head_splits(g);
+        e = launch_mex_bwd_head(g, false, true, x, w.eo, w.mo, w.mx, y, dy, nullptr, w.part, hs, w.flag, s);
+        if (e != cudaSuccess) return e;
+        const long long n = (long long)g.R * g.M * g.K;
+        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, g.K, hs, w.part, w.eo, doff, accumulate, w.flag);
+        count_launch();
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
+    }
     if (smallm_shape(g)) {
         e = launch_mex_doff_smallm(g, x, w.mo, w.mx, y, dy, w.part, splits, w.flag, s);
         if (e != cudaSuccess) return e;
@@ -639,6 +660,24 @@ cudaError_t launch_mex_backward_tiled(const MexGeo& g, const float* x, const flo
     const MexWs w = carve(g, ws);
     cudaError_t e = forward_primes_workspace(g, flags) ? cudaSuccess : run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags));
     if (e != cudaSuccess) return e;
+    if (smallm_shape(g) && mex_head_shape(g) && blocks_disjoint(g)) {
+        // the head: input gradient and the partial sums of the offsets gradient from one read of x
+        const int hs = mex_head_splits(g);
+        if (!blocks_cover_input(g)) {
+            e = cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)g.B * g.C * g.H * g.W, s);
+            if (e != cudaSuccess) return e;
+        }
+        e = launch_mex_bwd_head(g, true, true, x, w.eo, w.mo, w.mx, y, dy, dx, w.part, hs, w.flag, s);
+        if (e != cudaSuccess) return e;
+        const long long n = (long long)g.R * g.M * g.K;
+        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, g.K, hs, w.part, w.eo, doff, accumulate, w.flag);
+        count_launch();
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        e = launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
+        if (e != cudaSuccess) return e;
+        return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
+    }
     e = launch_mex_dx_tiled(g, x, off, y, dy, dx, ws, flags, s, true);
     if (e != cudaSuccess) return e;
     return launch_mex_doff_tiled(g, x, off, y, dy, doff, accumulate, ws, flags, s, true);

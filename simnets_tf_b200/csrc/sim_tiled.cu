@@ -43,6 +43,10 @@ __host__ int dp_splits(const SimGeo& g) {
     // the narrow tile runs four CTAs of 128 threads per SM (128 registers per thread): two waves of those
     const int ctas = dp_tn(g) == 32 ? 148 * 8 : 148 * 4;                  // (the wide tile: two CTAs of 256 threads per SM)
     long long s = (ctas + tiles - 1) / tiles;
+    // every split costs one set of partial sums (3 M K floats written and read again): at small batches a split keeps
+    // at least 1024 positions, or the partial sums outweigh the operands
+    const long long by_work = std::max<long long>(1, P / 1024);
+    if (s > by_work) s = by_work;
     if (s > chunks) s = chunks;
     if (s < 1) s = 1;
     if (s > 2048) s = 2048;
@@ -474,17 +478,20 @@ __global__ void __launch_bounds__(256) sim_dx_tiled(SimGeo g, const float* __res
 __global__ void __launch_bounds__(512) sim_dparams_reduce(SimGeo g, int splits, const float* __restrict__ part,
                                                           const float* __restrict__ wt, float* __restrict__ dt, float* __restrict__ dw,
                                                           int accumulate) {
-    __shared__ float red[3][16][32];
+    // a CTA sums 8 consecutive outputs (one 32-byte sector per split) over all splits: 64 slices of the splits in
+    // parallel, then the slices in a fixed order (deterministic).  Few outputs per CTA so that the short patches of a
+    // first layer (M K = 1728) still spread over a couple of hundred CTAs.
+    __shared__ float red[3][64][8];
     const int mk = g.M * g.K;
     const float fudge = float(g.fudge);
     const bool third = g.mode == SIM_L2N || g.mode == SIM_L2N_NAN;
-    const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
-    for (int first = blockIdx.x * 32; first < mk; first += gridDim.x * 32) {
+    const int lane = threadIdx.x & 7, slice = threadIdx.x >> 3;
+    for (int first = blockIdx.x * 8; first < mk; first += gridDim.x * 8) {
         const int i = first + lane;
         float a = 0.f, b = 0.f, c = 0.f;
         if (i < mk) {
 #pragma unroll 4
-            for (int s = slice; s < splits; s += 16) {
+            for (int s = slice; s < splits; s += 64) {
                 const float* p = part + (size_t)s * 3 * mk;
                 a += p[i]; b += p[mk + i];
                 if (third) c += p[2 * mk + i];
@@ -493,8 +500,8 @@ __global__ void __launch_bounds__(512) sim_dparams_reduce(SimGeo g, int splits, 
         red[0][slice][lane] = a; red[1][slice][lane] = b; red[2][slice][lane] = c;
         __syncthreads();
         if (slice == 0 && i < mk) {
-#pragma unroll
-            for (int q = 1; q < 16; ++q) { a += red[0][q][lane]; b += red[1][q][lane]; c += red[2][q][lane]; }
+#pragma unroll 8
+            for (int q = 1; q < 64; ++q) { a += red[0][q][lane]; b += red[1][q][lane]; c += red[2][q][lane]; }
             const float w = wt[i];
             float gt, gw;
             if (g.mode == SIM_L1 || g.mode == SIM_L1_SKIP) { gt = w * a; gw = -b; }
@@ -604,7 +611,7 @@ cudaError_t launch_sim_dparams_tiled(const SimGeo& g, const float* x, const floa
     }
 #undef DP
     const int mk = g.M * g.K;
-    sim_dparams_reduce<<<std::min((mk + 31) / 32, 148 * 8), 512, 0, s>>>(g, splits, W.part, w, dt, dw, accumulate);
+    sim_dparams_reduce<<<std::min((mk + 7) / 8, device_sm_count() * 8), 512, 0, s>>>(g, splits, W.part, w, dt, dw, accumulate);
     count_launch(2);
     return cudaGetLastError();
 }

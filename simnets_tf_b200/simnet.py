@@ -79,8 +79,27 @@ class SimNet(torch.nn.Module):
         self._plan = [(e, m) for e, m in zip(spec["layers"], mods)]
 
     def forward(self, x):
-        plan, i = self._plan, 0
-        while i < len(plan):
+        return self.forward_range(x, 0, len(self._plan))
+
+    def split_point(self):
+        """Index into the layer plan that leaves the last two MEX layers (the largest offsets tensors) behind it: their
+        gradients are the first that a backward pass finishes, so a data-parallel step can start reducing them while
+        the layers in front are still being differentiated.  0 when the network has fewer than three MEX layers."""
+        mex = [i for i, (e, _) in enumerate(self._plan) if e[0] == "mex"]
+        return mex[-2] if len(mex) >= 3 else 0
+
+    def parameters_from(self, begin):
+        """Parameters of the layers plan[begin:], in `parameters()` order (they are its tail)."""
+        out = []
+        for _, m in self._plan[begin:]:
+            if m is not None:
+                out.extend(m.parameters())
+        return out
+
+    def forward_range(self, x, begin, end):
+        """Layers plan[begin:end] (a MEX + sum-pool pair is never split: `begin` and `end` are layer starts)."""
+        plan, i = self._plan, begin
+        while i < end:
             entry, mod = plan[i]
             if entry[0] == "mex" and self.fuse_pooling and i + 1 < len(plan) and plan[i + 1][0] == ("sumpool", 2):
                 x = mod(x, sum_pool2=True)          # MEX + 2x2 sum pooling, pooling gradient inside the MEX gradient kernels
@@ -95,8 +114,10 @@ class SimNet(torch.nn.Module):
             i += 1
         return x
 
+    def loss_of_logits(self, logits, labels, global_batch=None):
+        total = F.cross_entropy(logits, labels, reduction="sum")
+        return total / float(global_batch if global_batch else logits.shape[0])
+
     def loss(self, x, labels, global_batch=None):
         """Softmax cross-entropy summed over this shard and divided by the global batch."""
-        logits = self.forward(x)
-        total = F.cross_entropy(logits, labels, reduction="sum")
-        return total / float(global_batch if global_batch else x.shape[0])
+        return self.loss_of_logits(self.forward(x), labels, global_batch)

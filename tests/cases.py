@@ -200,6 +200,17 @@ MEX_PAIR = [
 ]
 
 
+# Few instances over whole-sample patches with one offsets region: the classifier-head kernels (several positions per
+# CTA forward, both gradients from one read of x backward).  Tap counts off the tile sizes, 3 to 13 instances, several
+# channel blocks, a negative epsilon, no softmax.
+MEX_HEAD = [
+    mex_case("head_taps_tail", (5, 37, 3, 3), 13, (37, 3, 3), (37, 3, 3), softmax=True, seed=411, normalize=True),
+    mex_case("head_channel_blocks", (6, 96, 3, 3), 6, (48, 3, 3), (48, 3, 3), softmax=True, unshared=False, shared_region=(-1,), seed=412, normalize=True),
+    mex_case("head_eps_neg", (9, 64, 2, 2), 3, (64, 2, 2), (64, 2, 2), eps=-0.8, softmax=False, seed=413),
+    mex_case("head_long", (3, 300, 4, 4), 10, (300, 4, 4), (300, 4, 4), softmax=True, eps=2.0, seed=414, normalize=True),
+]
+
+
 # ------------------------------------------------------------------------- acceptance rule
 def rel_err(a, b):
     """max |a-b| over finite entries of b, relative to max |b| (0 for empty)."""

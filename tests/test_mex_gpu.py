@@ -54,6 +54,34 @@ def test_pair_tile_shapes_on_one_region_kernels(port, c):
     gpu_util.check_mex_pooled_dy(port, c, flags=abi.FLAG_MEX_NO_PAIR_TILES)
 
 
+@pytest.mark.parametrize("c", cases.MEX_HEAD, ids=lambda c: c["name"])
+def test_head_shapes(port, c):
+    """Whole-sample patches under few instances and one offsets region: the head kernels."""
+    gpu_util.check_mex(port, c, f64_tiebreak=True)
+
+
+@pytest.mark.parametrize("c", cases.MEX_HEAD + [c for c in cases.MEX_CONFIGS if c["name"] == "cfg5_head_sub"], ids=lambda c: c["name"])
+def test_head_gradients_from_the_forward_pass_workspace(port, c):
+    """The head's forward kernel leaves the per-position maxima in the workspace; primed gradients must not change."""
+    d = cases.mex_desc(c)
+    x, off, dy = cases.mex_inputs(c, port.mex_offsets_shape(d), port.mex_out_shape(d))
+    xd, od, dyd = (gpu_util.dev(a) for a in (x, off, dy))
+    attrs = cases.mex_attrs(c)
+    ws = mex_ops.mex_layer_workspace(xd, c["M"], **attrs)
+    yd = mex_ops.mex_forward(xd, od, c["M"], workspace=ws, **attrs)
+    ry = port.mex_forward(d, x, off)
+    cases.assert_parity(yd.cpu().numpy(), ry, what="y")
+    ryd = gpu_util.dev(ry)
+    mex_ops.mex_forward(xd, od, c["M"], workspace=ws, **attrs)
+    dx, doff = mex_ops.mex_backward(xd, od, ryd, dyd, c["M"], primed_workspace=ws, **attrs)
+    cases.assert_parity(dx.cpu().numpy(), port.mex_input_grad(d, x, off, ry, dy), tol=2e-5, what="dx")
+    cases.assert_parity(doff.cpu().numpy(), port.mex_offsets_grad(d, x, off, ry, dy), tol=2e-5, what="doff")
+    cases.assert_parity(mex_ops.mex_input_grad(xd, od, ryd, dyd, c["M"], primed_workspace=ws, **attrs).cpu().numpy(),
+                        port.mex_input_grad(d, x, off, ry, dy), tol=2e-5, what="dx alone")
+    cases.assert_parity(mex_ops.mex_offsets_grad(xd, od, ryd, dyd, c["M"], primed_workspace=ws, **attrs).cpu().numpy(),
+                        port.mex_offsets_grad(d, x, off, ry, dy), tol=2e-5, what="doff alone")
+
+
 def test_pair_tiles_need_8_byte_alignment(port):
     """Tensors that start on an odd float cannot be read as pixel pairs: the library takes the one-region kernels."""
     c = cases.MEX_PAIR[0]
