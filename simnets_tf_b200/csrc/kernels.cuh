@@ -41,6 +41,9 @@ cudaError_t launch_sim_fwd_tiled(const SimGeo&, const float* x, const float* t, 
 cudaError_t launch_sim_dx_tiled(const SimGeo&, const float* x, const float* t, const float* w, const float* dy, float* dx, void* ws, cudaStream_t);
 cudaError_t launch_sim_dparams_tiled(const SimGeo&, const float* x, const float* t, const float* w, const float* dy,
                                      float* dt, float* dw, bool accumulate, void* ws, cudaStream_t);
+// sim_smallk.cu -- forward for short patches (K <= 32): patches in registers, two positions per thread
+bool sim_smallk_shape(const SimGeo&);
+cudaError_t launch_sim_fwd_smallk(const SimGeo&, const float* x, const float* planes, const float* cm, const int2* taps, float* y, cudaStream_t);
 bool mex_use_tiled(const MexGeo&, bool f64, uint32_t flags);
 size_t mex_workspace_bytes(const MexGeo&, bool f64, uint32_t flags);
 cudaError_t launch_mex_fwd_tiled(const MexGeo&, const float* x, const float* off, float* y, void* ws, uint32_t flags, cudaStream_t);
@@ -54,8 +57,9 @@ cudaError_t launch_mex_doff_smallm(const MexGeo&, const float* x, const float* m
 // the head: a single region of contiguous patches (whole samples), several positions per CTA, both gradients from one read of x
 bool mex_head_shape(const MexGeo&);
 int mex_head_splits(const MexGeo&);
+size_t mex_head_fwd_scratch_floats(const MexGeo&);
 cudaError_t launch_mex_fwd_head(const MexGeo&, const float* x, const float* eot, const float* mo, float* mx, float* y,
-                                const int* flag, cudaStream_t);
+                                float* scratch, const int* flag, cudaStream_t);
 cudaError_t launch_mex_bwd_head(const MexGeo&, bool want_dx, bool want_doff, const float* x, const float* eo, const float* mo,
                                 const float* mx, const float* y, const float* dy, float* dx, float* part, int splits,
                                 const int* flag, cudaStream_t);

@@ -17,6 +17,7 @@ struct MexWs {           // workspace carve-up, every part 256-byte aligned
     float* mx;           // [B][N]
     float* part;         // [S][R][M][K] split-q partial sums of the offsets gradient
     float* tc_tiles;     // Eo split into TF32 hi / lo planes, tile by tile in the tensor-core operand layout
+    float* tc_tiles_dx;  // the same for the input gradient of the pair-tile kernels (rows = taps), written together with tc_tiles
     size_t bytes;
     size_t fwd_bytes;    // bytes the forward pass touches (everything before `part`)
 };
@@ -103,8 +104,12 @@ __host__ inline MexWs carve(const MexGeo& g, void* base) {
     int max_splits = (tc_shape(g) || tc_smallk_shape(g)) ? std::max(doff_splits(g), mex_tc_doff_splits(g)) : doff_splits(g);
     if ((tc_shape(g) || tc_smallk_shape(g)) && mex_pair_shape(g)) max_splits = std::max(max_splits, mex_pair_doff_splits(g));
     if (mex_head_shape(g)) max_splits = std::max(max_splits, mex_head_splits(g));
-    w.part = reinterpret_cast<float*>(take(sizeof(float) * (size_t)max_splits * g.R * g.M * g.K));
+    size_t part_floats = (size_t)max_splits * g.R * g.M * g.K;
+    if (mex_head_shape(g)) part_floats = std::max(part_floats, mex_head_fwd_scratch_floats(g));      // the head's forward pass parks its slice sums here
+    w.part = reinterpret_cast<float*>(take(sizeof(float) * part_floats));
+    if (mex_head_shape(g)) w.fwd_bytes = off;                      // (so the forward pass of that shape reaches this far)
     w.tc_tiles = reinterpret_cast<float*>(take((tc_shape(g) || tc_smallk_shape(g)) ? sizeof(float) * mex_tc_tile_floats(g) : 0));
+    w.tc_tiles_dx = reinterpret_cast<float*>(take(((tc_shape(g) || tc_smallk_shape(g)) && mex_pair_shape(g)) ? sizeof(float) * mex_tc_tile_floats(g) : 0));
     w.bytes = off;
     return w;
 }

@@ -218,19 +218,28 @@ __global__ void __launch_bounds__(kT) mex_doff_smallm(MexGeo g, const float* __r
 // once per group, and the backward pass produces the input gradient and the offsets-gradient partial sums from ONE read
 // of x.  The forward kernel stores the per-position maxima, which primes the workspace for the gradients.
 constexpr int kHeadPB = 8;         // positions per CTA in the forward pass
+constexpr int kHeadSlices = 8;     // tap slices: a CTA takes one slice of the patches of its positions
 
+// Forward: CTA = (group of up to 8 positions, slice of the taps).  Each CTA stabilises with the maximum of ITS slice (the
+// slice of x is 32 KiB at most and stays in L1 for the second pass, so x is read from memory once and no separate maximum
+// pass exists), leaves per-position partial sums S_s[m] and maxima mx_s in the workspace, and the CTA that finishes a
+// group last combines them: mx = max_s mx_s, S[m] = sum_s S_s[m] * exp(eps (mx_s - mx)) -- the same value as with one
+// global maximum, up to rounding.  It then writes y and the per-position maxima (which prime the gradients).
 template <int MP>
-__global__ void __launch_bounds__(kT) mex_fwd_head(MexGeo g, int pb, const float* __restrict__ x, const float* __restrict__ eot,
+__global__ void __launch_bounds__(kT) mex_fwd_head(MexGeo g, int pb, int slices, const float* __restrict__ x, const float* __restrict__ eot,
                                                    const float* __restrict__ mo, float* __restrict__ mx, float* __restrict__ y,
-                                                   const int* __restrict__ flag) {
+                                                   float* __restrict__ partial, int* __restrict__ tickets, const int* __restrict__ flag) {
     __shared__ float red[kT / 32][kHeadPB];
     __shared__ float racc[kT / 32][kHeadPB][MP];
     __shared__ float mxs[kHeadPB];
+    __shared__ int last;
     if (*flag) return;
     const long long P = (long long)g.B * g.N;                      // positions (one region)
-    const long long p0 = (long long)blockIdx.x * pb;
+    const int group = blockIdx.x / slices, slice = blockIdx.x % slices;
+    const long long p0 = (long long)group * pb;
     const int np = int(min((long long)pb, P - p0));
     const int K = g.K, M = g.M, ldm = pad4(g.M);
+    const int kper = ((K + slices - 1) / slices + 3) & ~3, k_begin = slice * kper, k_end = min(K, k_begin + kper);
     const bool up = g.eps > 0;
     const float a = float(g.eps) * 1.4426950408889634f;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -242,13 +251,14 @@ __global__ void __launch_bounds__(kT) mex_fwd_head(MexGeo g, int pb, const float
         const int n = int(q / g.N), pos = int(q % g.N);
         xp[p] = x + ((size_t)n * g.C + (size_t)(pos / (g.Wo * g.Ho)) * g.sc) * g.H * g.W;
     }
-    // pass 1: maxima (NaN taps ignored, as fmaxf / fminf do)
+    // pass 1: maxima of the slice (NaN taps ignored, as fmaxf / fminf do)
     float v[kHeadPB];
 #pragma unroll
     for (int p = 0; p < kHeadPB; ++p) v[p] = up ? -CUDART_INF_F : CUDART_INF_F;
-    for (int k = threadIdx.x; k < K; k += kT) {
+    for (int k = k_begin + threadIdx.x; k < k_end; k += kT) {
 #pragma unroll
         for (int p = 0; p < kHeadPB; ++p) {
+            if (p >= np) break;
             const float t = __ldg(xp[p] + k);
             v[p] = up ? fmaxf(v[p], t) : fminf(v[p], t);
         }
@@ -263,19 +273,18 @@ __global__ void __launch_bounds__(kT) mex_fwd_head(MexGeo g, int pb, const float
         float r = red[0][threadIdx.x];
         for (int w = 1; w < kT / 32; ++w) r = up ? fmaxf(r, red[w][threadIdx.x]) : fminf(r, red[w][threadIdx.x]);
         mxs[threadIdx.x] = r;
-        if (threadIdx.x < np) mx[p0 + threadIdx.x] = r;
     }
     __syncthreads();
     float mxv[kHeadPB];
 #pragma unroll
     for (int p = 0; p < kHeadPB; ++p) mxv[p] = mxs[p];
-    // pass 2 (x comes from the caches now): sums over taps for every instance
+    // pass 2 (x comes from L1 now): sums over the slice's taps for every instance
     float acc[kHeadPB][MP];
 #pragma unroll
     for (int p = 0; p < kHeadPB; ++p)
 #pragma unroll
         for (int m = 0; m < MP; ++m) acc[p][m] = 0.f;
-    for (int k = threadIdx.x; k < K; k += kT) {
+    for (int k = k_begin + threadIdx.x; k < k_end; k += kT) {
         float eo[MP];
         const float4* row = reinterpret_cast<const float4*>(eot + (size_t)k * ldm);
 #pragma unroll
@@ -285,7 +294,8 @@ __global__ void __launch_bounds__(kT) mex_fwd_head(MexGeo g, int pb, const float
         }
 #pragma unroll
         for (int p = 0; p < kHeadPB; ++p) {
-            const float e = ex2_approx(a * (__ldg(xp[p] + k) - mxv[p]));
+            if (p >= np) break;
+            const float e = ex2_approx(a * (__ldg(xp[p] + k) - mxv[p]));      // (an empty slice never gets here: its -inf maximum is unused)
 #pragma unroll
             for (int m = 0; m < MP; ++m) acc[p][m] = fmaf(e, eo[m], acc[p][m]);
         }
@@ -298,14 +308,46 @@ __global__ void __launch_bounds__(kT) mex_fwd_head(MexGeo g, int pb, const float
             if (lane == 0) racc[warp][p][m] = t;
         }
     __syncthreads();
-    for (int i = threadIdx.x; i < np * M; i += kT) {
-        const int p = i / M, m = i % M;
-        float sum = 0.f;
+    // this slice's partial sums and maxima: partial[group][slice][p < pb][MP + 1]
+    float* mine = partial + ((size_t)group * slices + slice) * pb * (MP + 1);
+    for (int i = threadIdx.x; i < pb * (MP + 1); i += kT) {
+        const int p = i / (MP + 1), m = i % (MP + 1);
+        float sum = mxs[p];
+        if (m < MP) {
+            sum = 0.f;
 #pragma unroll
-        for (int w = 0; w < kT / 32; ++w) sum += racc[w][p][m];
+            for (int w = 0; w < kT / 32; ++w) sum += racc[w][p][m];
+        }
+        mine[i] = sum;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(tickets + group, 1) == slices - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    // the last CTA of the group: combine the slices in slice order (deterministic)
+    const float* all = partial + (size_t)group * slices * pb * (MP + 1);
+    for (int i = threadIdx.x; i < np * MP; i += kT) {
+        const int p = i / MP, m = i % MP;
+        float gm = up ? -CUDART_INF_F : CUDART_INF_F;
+        for (int s2 = 0; s2 < slices; ++s2) {
+            const float t = __ldcg(all + ((size_t)s2 * pb + p) * (MP + 1) + MP);
+            gm = up ? fmaxf(gm, t) : fminf(gm, t);
+        }
+        float sum = 0.f;
+        for (int s2 = 0; s2 < slices; ++s2) {
+            const float* ps = all + ((size_t)s2 * pb + p) * (MP + 1);
+            const float ms = __ldcg(ps + MP);
+            const float part_sum = __ldcg(ps + m);
+            if (part_sum != 0.f) sum = fmaf(part_sum, ex2_approx(a * (ms - gm)), sum);      // (skips empty slices, whose maximum is infinite)
+        }
         const long long q = p0 + p;
-        const int n = int(q / g.N), pos = int(q % g.N);
-        y[((long long)n * M + m) * g.N + pos] = mxs[p] + mo[m] + (fast_log(sum) + float(g.cst)) / float(g.eps);
+        if (m == 0) mx[q] = gm;
+        if (m < M) {
+            const int n = int(q / g.N), pos = int(q % g.N);
+            y[((long long)n * M + m) * g.N + pos] = gm + mo[m] + (fast_log(sum) + float(g.cst)) / float(g.eps);
+        }
     }
 }
 
@@ -319,7 +361,8 @@ __global__ void __launch_bounds__(kT) mex_bwd_head(MexGeo g, const float* __rest
                                                    const float* __restrict__ y, const float* __restrict__ dy,
                                                    float* __restrict__ dx, float* __restrict__ part, int splits,
                                                    const int* __restrict__ flag) {
-    __shared__ float Qs[2][kMaxM + 1];
+    constexpr int GP = 8;                                           // positions staged together
+    __shared__ float Qs[2][GP][kMaxM + 1];                          // Q of a group's positions and, in the last column, their maxima
     if (*flag) return;
     const long long P = (long long)g.B * g.N;
     const int K = g.K, M = g.M, ldk = pad4(g.K);
@@ -328,7 +371,8 @@ __global__ void __launch_bounds__(kT) mex_bwd_head(MexGeo g, const float* __rest
     const long long p_begin = P * split / splits, p_end = P * (split + 1) / splits;
     const float a = float(g.eps) * 1.4426950408889634f, c2 = float(g.cst) * 1.4426950408889634f;
     const int kbase = kt * kT * kHeadKPT + threadIdx.x;            // this thread's taps: kbase + i * kT
-    float eor[MP][kHeadKPT];                                     // Eo of this thread's taps
+    const size_t hwc = (size_t)g.H * g.W;
+    float eor[MP][kHeadKPT];                                        // Eo of this thread's taps
 #pragma unroll
     for (int m = 0; m < MP; ++m)
 #pragma unroll
@@ -339,42 +383,58 @@ __global__ void __launch_bounds__(kT) mex_bwd_head(MexGeo g, const float* __rest
     for (int m = 0; m < MP; ++m)
 #pragma unroll
         for (int i = 0; i < kHeadKPT; ++i) acc[m][i] = 0.f;
-    for (long long q = p_begin; q < p_end; ++q) {
-        const int n = int(q / g.N), pos = int(q % g.N);
-        const int buf = int(q - p_begin) & 1;
-        if (threadIdx.x < kMaxM) {
-            const int m = threadIdx.x;
+    int buf = 0;
+    for (long long q0 = p_begin; q0 < p_end; q0 += GP, buf ^= 1) {
+        // the group's Q values: GP x 16 threads, one (position, instance) each; all their loads are in flight together
+        if (threadIdx.x < GP * kMaxM) {
+            const int p = threadIdx.x / kMaxM, m = threadIdx.x % kMaxM;
+            const long long q = q0 + p;
             float qv = 0.f;
-            if (m < M) {
+            if (q < p_end && m < M) {
+                const int n = int(q / g.N), pos = int(q % g.N);
                 const long long o = ((long long)n * M + m) * g.N + pos;
                 qv = __ldg(dy + o) * ex2_approx(fmaf(a, (__ldg(mx + q) - __ldg(y + o)) + mo[m], c2));
             }
-            Qs[buf][m] = qv;
+            Qs[buf][p][m] = qv;
+            if (m == 0) Qs[buf][p][kMaxM] = q < p_end ? __ldg(mx + q) : 0.f;
         }
-        if (threadIdx.x == kMaxM) Qs[buf][kMaxM] = __ldg(mx + q);
-        __syncthreads();                                           // (double buffered: one barrier per position)
-        const float mxv = Qs[buf][kMaxM];
-        const size_t base = ((size_t)n * g.C + (size_t)(pos / (g.Wo * g.Ho)) * g.sc) * g.H * g.W;
-        float e[kHeadKPT];
+        // x of the whole group goes in flight before the barrier
+        float xv[GP][kHeadKPT];
+        size_t base[GP];
 #pragma unroll
-        for (int i = 0; i < kHeadKPT; ++i) e[i] = kbase + i * kT < K ? ex2_approx(a * (__ldg(x + base + kbase + i * kT) - mxv)) : 0.f;
-        float qm[MP];
+        for (int p = 0; p < GP; ++p) {
+            const long long q = q0 + p < p_end ? q0 + p : p_end - 1;
+            const int n = int(q / g.N), pos = int(q % g.N);
+            base[p] = ((size_t)n * g.C + (size_t)(pos / (g.Wo * g.Ho)) * g.sc) * hwc;
 #pragma unroll
-        for (int m = 0; m < MP; ++m) qm[m] = Qs[buf][m];
-        if (DX) {
+            for (int i = 0; i < kHeadKPT; ++i) xv[p][i] = kbase + i * kT < K ? __ldg(x + base[p] + kbase + i * kT) : 0.f;
+        }
+        __syncthreads();                                           // (double buffered: one barrier per group)
 #pragma unroll
-            for (int i = 0; i < kHeadKPT; ++i) {
-                float s = 0.f;
+        for (int p = 0; p < GP; ++p) {
+            if (q0 + p >= p_end) break;
+            const float mxv = Qs[buf][p][kMaxM];
+            float e[kHeadKPT];
 #pragma unroll
-                for (int m = 0; m < MP; ++m) s = fmaf(eor[m][i], qm[m], s);
-                if (kbase + i * kT < K) dx[base + kbase + i * kT] = e[i] * s;
+            for (int i = 0; i < kHeadKPT; ++i) e[i] = kbase + i * kT < K ? ex2_approx(a * (xv[p][i] - mxv)) : 0.f;
+            float qm[MP];
+#pragma unroll
+            for (int m = 0; m < MP; ++m) qm[m] = Qs[buf][p][m];
+            if (DX) {
+#pragma unroll
+                for (int i = 0; i < kHeadKPT; ++i) {
+                    float s = 0.f;
+#pragma unroll
+                    for (int m = 0; m < MP; ++m) s = fmaf(eor[m][i], qm[m], s);
+                    if (kbase + i * kT < K) dx[base[p] + kbase + i * kT] = e[i] * s;
+                }
             }
-        }
-        if (DOFF) {
+            if (DOFF) {
 #pragma unroll
-            for (int m = 0; m < MP; ++m)
+                for (int m = 0; m < MP; ++m)
 #pragma unroll
-                for (int i = 0; i < kHeadKPT; ++i) acc[m][i] = fmaf(qm[m], e[i], acc[m][i]);
+                    for (int i = 0; i < kHeadKPT; ++i) acc[m][i] = fmaf(qm[m], e[i], acc[m][i]);
+            }
         }
     }
     if (DOFF) {
@@ -442,18 +502,32 @@ int mex_head_splits(const MexGeo& g) {
     return int(s);
 }
 
-cudaError_t launch_mex_fwd_head(const MexGeo& g, const float* x, const float* eot, const float* mo, float* mx, float* y,
-                                const int* flag, cudaStream_t s) {
+// scratch of the forward head kernel behind `part`-sized storage: partial sums then tickets
+size_t mex_head_fwd_scratch_floats(const MexGeo& g) {
     const long long P = (long long)g.B * g.N;
+    return size_t(P + kHeadPB) * kHeadSlices * (pad4(g.M) + 1) + size_t(P + 1);       // groups of at least one position each
+}
+
+cudaError_t launch_mex_fwd_head(const MexGeo& g, const float* x, const float* eot, const float* mo, float* mx, float* y,
+                                float* scratch, const int* flag, cudaStream_t s) {
+    const long long P = (long long)g.B * g.N;
+    // Large batches: 8 positions per CTA over whole patches (measured fastest: the offsets table is read once per 8
+    // positions and nothing is combined).  Small batches, where that leaves most SMs idle: smaller groups and tap slices.
     int pb = kHeadPB;
-    while (pb > 1 && (P + pb - 1) / pb < device_sm_count()) pb >>= 1;          // small batches: fewer positions per CTA, more CTAs
-    const long long blocks = (P + pb - 1) / pb;
-    if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    while (pb > 2 && ((P + pb - 1) / pb) * kHeadSlices < device_sm_count()) pb >>= 1;
+    const long long groups = (P + pb - 1) / pb;
+    const int slices = (g.K >= kHeadSlices * 64 && 2 * groups < device_sm_count()) ? kHeadSlices : 1;
+    if (groups * slices > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    float* partial = scratch;
+    int* tickets = reinterpret_cast<int*>(scratch + size_t(P + kHeadPB) * kHeadSlices * (pad4(g.M) + 1));
+    cudaError_t e = cudaMemsetAsync(tickets, 0, sizeof(int) * size_t(groups), s);
+    if (e != cudaSuccess) return e;
+    const int blocks = int(groups * slices);
     switch (pad4(g.M)) {
-    case 4: mex_fwd_head<4><<<int(blocks), kT, 0, s>>>(g, pb, x, eot, mo, mx, y, flag); break;
-    case 8: mex_fwd_head<8><<<int(blocks), kT, 0, s>>>(g, pb, x, eot, mo, mx, y, flag); break;
-    case 12: mex_fwd_head<12><<<int(blocks), kT, 0, s>>>(g, pb, x, eot, mo, mx, y, flag); break;
-    default: mex_fwd_head<16><<<int(blocks), kT, 0, s>>>(g, pb, x, eot, mo, mx, y, flag); break;
+    case 4: mex_fwd_head<4><<<blocks, kT, 0, s>>>(g, pb, slices, x, eot, mo, mx, y, partial, tickets, flag); break;
+    case 8: mex_fwd_head<8><<<blocks, kT, 0, s>>>(g, pb, slices, x, eot, mo, mx, y, partial, tickets, flag); break;
+    case 12: mex_fwd_head<12><<<blocks, kT, 0, s>>>(g, pb, slices, x, eot, mo, mx, y, partial, tickets, flag); break;
+    default: mex_fwd_head<16><<<blocks, kT, 0, s>>>(g, pb, slices, x, eot, mo, mx, y, partial, tickets, flag); break;
     }
     count_launch();
     return cudaGetLastError();

@@ -32,23 +32,36 @@ namespace simnets {
 namespace {
 
 // ------------------------------------------------------------------ prepasses
-// One block per (region, instance): stabiliser mo, Eo in both layouts, and the safety flag.
-__global__ void __launch_bounds__(128) mex_prep_offsets(MexGeo g, const float* __restrict__ off, float* __restrict__ mo,
-                                                        float* __restrict__ eo, float* __restrict__ eot, int* __restrict__ flag) {
-    __shared__ float s_hi[128], s_lo[128];
-    __shared__ int s_bad[128];
-    const int rm = blockIdx.x, r = rm / g.M, m = rm % g.M;
+// One block per (region, instance): stabiliser mo, Eo in both layouts, and the safety flag.  With tile pointers the block
+// also writes its part of the tensor-core operand tiles (Eo split into TF32 hi / lo, laid out as the MMA reads it: what
+// mex_tc_prep produces in a launch of its own): tf = forward tiles, rows = instances in tiles of ntf, reduction = taps;
+// td = input-gradient tiles, rows = taps in tiles of ntd, reduction = instances.  The grid then also covers the rows that
+// pad the last instance tile or chunk (gridDim.x = R * Mp, Mp >= M): those blocks write zeros only.
+__device__ __forceinline__ float prep_tf32_hi(float v) { uint32_t r; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v)); return __uint_as_float(r); }
+__device__ __forceinline__ int prep_core_offset(int row, int k) { return (row >> 3) * 128 + (k >> 2) * 32 + (row & 7) * 4 + (k & 3); }   // floats, 16-wide chunks
+
+__global__ void __launch_bounds__(512) mex_prep_offsets(MexGeo g, int Mp, const float* __restrict__ off, float* __restrict__ mo,
+                                                        float* __restrict__ eo, float* __restrict__ eot, int* __restrict__ flag,
+                                                        float* __restrict__ tf, int ntf, float* __restrict__ td, int ntd) {
+    __shared__ float s_hi[512], s_lo[512];
+    __shared__ int s_bad[512];
+    const int nt = blockDim.x;                       // 128, or 512 for long rows
+    const int r = blockIdx.x / Mp, m = blockIdx.x % Mp;
+    const bool real = m < g.M;
+    const int rm = r * g.M + m;
     const float* o = off + (size_t)rm * g.K;
     float hi = -CUDART_INF_F, lo = CUDART_INF_F;
     int bad = 0;
-    for (int k = threadIdx.x; k < g.K; k += 128) {
-        const float v = o[k];
-        if (!isfinite(v)) bad = 1;
-        hi = fmaxf(hi, v); lo = fminf(lo, v);
+    if (real) {
+        for (int k = threadIdx.x; k < g.K; k += nt) {
+            const float v = o[k];
+            if (!isfinite(v)) bad = 1;
+            hi = fmaxf(hi, v); lo = fminf(lo, v);
+        }
     }
     s_hi[threadIdx.x] = hi; s_lo[threadIdx.x] = lo; s_bad[threadIdx.x] = bad;
     __syncthreads();
-    for (int s = 64; s > 0; s >>= 1) {
+    for (int s = nt / 2; s > 0; s >>= 1) {
         if (threadIdx.x < s) {
             s_hi[threadIdx.x] = fmaxf(s_hi[threadIdx.x], s_hi[threadIdx.x + s]);
             s_lo[threadIdx.x] = fminf(s_lo[threadIdx.x], s_lo[threadIdx.x + s]);
@@ -59,14 +72,33 @@ __global__ void __launch_bounds__(128) mex_prep_offsets(MexGeo g, const float* _
     hi = s_hi[0]; lo = s_lo[0]; bad = s_bad[0];
     const float eps = float(g.eps);
     const float ref = eps > 0.f ? hi : lo;
-    if (threadIdx.x == 0) {
+    if (real && threadIdx.x == 0) {
         mo[rm] = ref;
         if (bad || !(fabsf(eps) * (hi - lo) <= kSafeSpread)) atomicOr(flag, 1);
     }
-    for (int k = threadIdx.x; k < g.K; k += 128) {
-        const float e = fast_exp(eps * (o[k] - ref));
-        eo[(size_t)rm * pad4(g.K) + k] = e;
-        eot[((size_t)r * g.K + k) * pad4(g.M) + m] = e;
+    // taps up to the padding of the tiles: chunks of 16 for the forward tiles, whole tap tiles for the input-gradient tiles
+    const int kchunks = (g.K + 15) / 16, mchunks = (g.M + 15) / 16;
+    const int mtiles = tf ? (g.M + ntf - 1) / ntf : 0, ktiles = td ? (g.K + ntd - 1) / ntd : 0;
+    int kend = g.K;
+    if (tf && m < mtiles * ntf) kend = max(kend, kchunks * 16);
+    if (td && m < mchunks * 16) kend = max(kend, ktiles * ntd);
+    for (int k = threadIdx.x; k < kend; k += nt) {
+        const float e = (real && k < g.K) ? fast_exp(eps * (o[k] - ref)) : 0.f;
+        if (real && k < g.K) {
+            eo[(size_t)rm * pad4(g.K) + k] = e;
+            eot[((size_t)r * g.K + k) * pad4(g.M) + m] = e;
+        }
+        const float eh = prep_tf32_hi(e), el = prep_tf32_hi(e - eh);
+        if (tf && m < mtiles * ntf && k < kchunks * 16) {
+            float* tile = tf + (((size_t)r * mtiles + m / ntf) * kchunks + k / 16) * 2 * ntf * 16;
+            const int q = prep_core_offset(m % ntf, k % 16);
+            tile[q] = eh; tile[ntf * 16 + q] = el;
+        }
+        if (td && m < mchunks * 16 && k < ktiles * ntd) {
+            float* tile = td + (((size_t)r * ktiles + k / ntd) * mchunks + m / 16) * 2 * ntd * 16;
+            const int q = prep_core_offset(k % ntd, m % 16);
+            tile[q] = eh; tile[ntd * 16 + q] = el;
+        }
     }
 }
 
@@ -388,6 +420,12 @@ bool use_pair_kernels(const MexGeo& g, uint32_t flags, const void* a, const void
     return !(flags & (SIMNETS_FLAG_MEX_NO_PAIR_TILES | SIMNETS_FLAG_MEX_TC_ONE_TILE)) && mex_pair_shape(g) && mex_pair_aligned(a, b, c, d);
 }
 
+// The prepass also writes the pair-tile kernels' operand tiles: decided by shape and flags alone (not by pointer
+// alignment), so that a gradient call on a primed workspace knows what the forward call left there.
+bool pair_prep(const MexGeo& g, uint32_t flags) {
+    return use_tc_kernels(g, flags) && !(flags & (SIMNETS_FLAG_MEX_NO_PAIR_TILES | SIMNETS_FLAG_MEX_TC_ONE_TILE)) && mex_pair_shape(g);
+}
+
 bool blocks_disjoint(const MexGeo& g) { return g.sc >= g.bc && g.sh >= g.bh && g.sw >= g.bw; }
 
 bool blocks_cover_input(const MexGeo& g) {
@@ -395,10 +433,18 @@ bool blocks_cover_input(const MexGeo& g) {
     return full(g.C, g.bc, g.sc, g.pc) && full(g.H, g.bh, g.sh, g.ph) && full(g.W, g.bw, g.sw, g.pw);
 }
 
-cudaError_t run_prepasses(const MexGeo& g, const MexWs& w, const float* x, const float* off, cudaStream_t s, bool need_mx = true) {
+cudaError_t run_prepasses(const MexGeo& g, const MexWs& w, const float* x, const float* off, cudaStream_t s, bool need_mx = true,
+                          bool pair_tiles = false) {
     cudaError_t e = cudaMemsetAsync(w.flag, 0, 16, s);
     if (e != cudaSuccess) return e;
-    mex_prep_offsets<<<g.R * g.M, 128, 0, s>>>(g, off, w.mo, w.eo, w.eot, w.flag);
+    if (pair_tiles) {
+        // the pair-tile kernels' operand tiles (forward and input gradient) come out of the same launch
+        const int ntf = mex_pair_nt_fwd(g), ntd = mex_pair_nt_dx(g);
+        const int Mp = std::max(((g.M + ntf - 1) / ntf) * ntf, ((g.M + 15) / 16) * 16);
+        mex_prep_offsets<<<g.R * Mp, g.K >= 2048 ? 512 : 128, 0, s>>>(g, Mp, off, w.mo, w.eo, w.eot, w.flag, w.tc_tiles, ntf, w.tc_tiles_dx, ntd);
+    } else {
+        mex_prep_offsets<<<g.R * g.M, g.K >= 2048 ? 512 : 128, 0, s>>>(g, g.M, off, w.mo, w.eo, w.eot, w.flag, nullptr, 0, nullptr, 0);
+    }
     if (!need_mx) { count_launch(); return cudaGetLastError(); }
     // long patches over few positions are contiguous per position: reduce them with one CTA each
     if (g.K >= 256 && g.N <= 16) { count_launch(); return launch_mex_colmax_wide(g, x, w.mx, w.flag, s); }
@@ -451,17 +497,15 @@ cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* o
     if (smallm_shape(g)) {
         cudaError_t e = run_prepasses(g, w, x, off, s, false);
         if (e != cudaSuccess) return e;
-        e = mex_head_shape(g) ? launch_mex_fwd_head(g, x, w.eot, w.mo, w.mx, y, w.flag, s)        // (also leaves the maxima for the gradients)
+        e = mex_head_shape(g) ? launch_mex_fwd_head(g, x, w.eot, w.mo, w.mx, y, w.part, w.flag, s)        // (also leaves the maxima for the gradients)
                               : launch_mex_fwd_smallm(g, x, w.eot, w.mo, y, w.flag, s);
         if (e != cudaSuccess) return e;
         return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);
     }
-    cudaError_t e = run_prepasses(g, w, x, off, s);
+    cudaError_t e = run_prepasses(g, w, x, off, s, true, pair_prep(g, flags));
     if (e != cudaSuccess) return e;
     if (use_tc_kernels(g, flags)) {
         if (use_pair_kernels(g, flags, x, y, y, y)) {
-            e = launch_mex_tc_prep(g, false, w.eo, w.tc_tiles, s, mex_pair_nt_fwd(g));
-            if (e != cudaSuccess) return e;
             e = launch_mex_fwd_pair(g, x, w.tc_tiles, w.mo, w.mx, y, w.flag, (flags & SIMNETS_FLAG_MEX_TEST_EXPIRE_WAIT) != 0, s);
             if (e != cudaSuccess) return e;
             return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);
@@ -533,7 +577,7 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
     if (!blocks_disjoint(g)) return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, nullptr);
     const MexWs w = carve(g, ws);
     const bool small = smallm_shape(g) || use_smallk_kernels(g, flags);
-    cudaError_t e = (prepped || forward_primes_workspace(g, flags)) ? cudaSuccess : run_prepasses(g, w, x, off, s, !small);
+    cudaError_t e = (prepped || forward_primes_workspace(g, flags)) ? cudaSuccess : run_prepasses(g, w, x, off, s, !small, pair_prep(g, flags));
     if (e != cudaSuccess) return e;
     if (!blocks_cover_input(g)) {
         e = cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)g.B * g.C * g.H * g.W, s);
@@ -545,9 +589,7 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
         return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
     }
     if (use_tc_kernels(g, flags) && use_pair_kernels(g, flags, x, y, dy, dx)) {
-        e = launch_mex_tc_prep(g, true, w.eot, w.tc_tiles, s, mex_pair_nt_dx(g));
-        if (e != cudaSuccess) return e;
-        e = launch_mex_dx_pair(g, x, w.tc_tiles, w.mo, w.mx, y, dy, dx, w.flag, s);
+        e = launch_mex_dx_pair(g, x, w.tc_tiles_dx, w.mo, w.mx, y, dy, dx, w.flag, s);
         if (e != cudaSuccess) return e;
         return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
     }
@@ -593,7 +635,7 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
 cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* doff,
                                   bool accumulate, void* ws, uint32_t flags, cudaStream_t s, bool prepped) {
     const MexWs w = carve(g, ws);
-    cudaError_t e = (prepped || forward_primes_workspace(g, flags)) ? cudaSuccess : run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags));
+    cudaError_t e = (prepped || forward_primes_workspace(g, flags)) ? cudaSuccess : run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags), pair_prep(g, flags));
     if (e != cudaSuccess) return e;
     if (use_tc_kernels(g, flags)) {
         int tsplits = mex_tc_doff_splits(g);
@@ -658,7 +700,7 @@ cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* 
 cudaError_t launch_mex_backward_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* dx,
                                       float* doff, bool accumulate, void* ws, uint32_t flags, cudaStream_t s) {
     const MexWs w = carve(g, ws);
-    cudaError_t e = forward_primes_workspace(g, flags) ? cudaSuccess : run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags));
+    cudaError_t e = forward_primes_workspace(g, flags) ? cudaSuccess : run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags), pair_prep(g, flags));
     if (e != cudaSuccess) return e;
     if (smallm_shape(g) && mex_head_shape(g) && blocks_disjoint(g)) {
         // the head: input gradient and the partial sums of the offsets gradient from one read of x

@@ -536,6 +536,7 @@ size_t sim_workspace_bytes(const SimGeo& g, bool f64, uint32_t flags) {
 cudaError_t launch_sim_fwd_tiled(const SimGeo& g, const float* x, const float* t, const float* w, float* y, void* ws, cudaStream_t s) {
     const SimWs W = carve(g, ws);
     launch_prep(g, W, t, w, s);
+    if (sim_smallk_shape(g)) return launch_sim_fwd_smallk(g, x, W.planes, W.cm, W.taps, y, s);
     const long long P = (long long)g.B * g.N;
     const bool wide = g.M > 64;
     const long long blocks = ((P + 127) / 128) * ((g.M + (wide ? 127 : 63)) / (wide ? 128 : 64));
