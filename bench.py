@@ -32,8 +32,10 @@ FALLBACK_HBM_GBS = 6650.0          # earlier measurement on this pool, used only
 NOMINAL_FP32_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
 # dram__bytes_read.sum + dram__bytes_write.sum of one whole library call, per sample, from ncu at batch 512
 # (kernel by kernel in profiles/mex_backward_cfg5_mex1.md); key = operator signature without its batch.  The step
-# runs the call on the forward pass's workspace, which skips its two prepasses: their 134.9 MB are taken out.
-NCU_DRAM_BYTES_PER_SAMPLE = {"mex_backward[C64 32x32 M128 K64 N1024 R4 dy/4]": (1249.5e6 - 134.9e6) / 512}
+# runs the call on the forward pass's workspace, which skips its two prepasses, so they are left out: input-gradient
+# kernel 472.2 MB read + 106.9 MB written, offsets-gradient kernel 472.5 MB read + 0.2 MB written, partial-sum
+# reduce 9.9 MB, the three gated exact kernels 0.1 MB.
+NCU_DRAM_BYTES_PER_SAMPLE = {"mex_backward[C64 32x32 M128 K64 N1024 R4 dy/4]": 1061.8e6 / 512}
 
 
 def make_data(workload, spec):

@@ -5,7 +5,9 @@
  * points enqueue work on the caller's CUDA stream (passed as void* so that this
  * header needs no CUDA include), never synchronise, never allocate and never
  * free: the caller owns all buffers, including the scratch workspace whose size
- * the *_workspace_bytes queries return.  Return value: 0 on success, a negative
+ * the *_workspace_bytes queries return.  (One entry point is the exception on
+ * scratch: simnets_mex_forward_static_scratch keeps its scratch in a fixed
+ * device array inside the library; it still allocates nothing.)  Return value: 0 on success, a negative
  * SIMNETS_E_* code for a rejected call, a positive cudaError_t for a launch
  * failure.  simnets_status_string() renders either.
  *
@@ -227,12 +229,18 @@ SIMNETS_API int simnets_mex_workspace_status(const void* workspace, void* stream
  * Some hosts of this library cannot hand it a workspace: an operator plugin loaded into a serving
  * runtime that has pre-assigned every byte of device memory to its own arena, a callback running
  * inside someone else's executor where calling a device allocator is forbidden, or a partitioned
- * GPU whose share is already fully committed.  For them this entry point computes exactly what
- * simnets_mex_forward computes, but keeps its scratch (offset exponentials, per-position maxima,
- * the safety flag) in a fixed device array inside the library, SIMNETS_MEX_STATIC_SCRATCH_BYTES
- * large, which each GPU that loads the library holds until the process exits.  It calls no device
- * allocator and no allocating library routine.
+ * GPU whose share is already fully committed.  For them this entry point computes the function
+ * simnets_mex_forward computes (same descriptor, same output tensor), but keeps its scratch (offset
+ * exponentials, per-position maxima, the safety flag) in a fixed device array inside the library,
+ * SIMNETS_MEX_STATIC_SCRATCH_BYTES large, which each GPU that loads the library holds until the
+ * process exits.  It calls no device allocator and no allocating library routine.
  *
+ *  - Route and tolerance: the call honours d->flags and adds SIMNETS_FLAG_MEX_NO_TENSORCORE, i.e. it
+ *    always runs the CUDA-core kernels (the fixed array has no room for tensor-core operand tiles).
+ *    float64 and the float32 shapes that need no scratch give the bits simnets_mex_forward gives; for
+ *    the float32 shapes that simnets_mex_forward sends to the tensor cores the two results agree to
+ *    the library's float32 bound, |a - b| <= 1e-5 * max(1, |b|), and each is within that bound of the
+ *    reference's float64 result.
  *  - Problems whose forward scratch exceeds the array are rejected with SIMNETS_E_TOO_LARGE before
  *    anything is launched (scratch need = 4 bytes * (batch*N + 2*num_regions*M*K) plus a few hundred
  *    bytes of padding; use simnets_mex_forward with a caller workspace for those).

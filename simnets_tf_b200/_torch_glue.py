@@ -1,6 +1,5 @@
 """Plumbing between torch tensors and the C ABI: dtype codes, pointers, the current stream and a
 per-(device, stream) scratch workspace that grows on demand."""
-import os
 
 import torch
 
@@ -8,9 +7,9 @@ from . import abi
 
 _WORKSPACES = {}
 
-# Descriptor flags OR-ed into every op call (e.g. SIMNETS_FLAGS=2 forces the shape-agnostic kernels,
-# SIMNETS_FLAGS=4 the per-term-exp MEX evaluation): a switch for A/B measurements, not a fallback.
-DEFAULT_FLAGS = int(os.environ.get("SIMNETS_FLAGS", "0"), 0)
+# Descriptor flags OR-ed into every op call of this process; 0 unless a program sets it (an A/B measurement that
+# wants, say, abi.FLAG_MEX_NO_PAIR_TILES on every layer assigns it before the first call).
+DEFAULT_FLAGS = 0
 
 
 def dtype_code(t):

@@ -122,7 +122,7 @@ int get_mex_offsets_nregions(int n_input_dim, const int* input_dim, int n_paddin
                              const int* unshared) {
     if (!input_dim || !padding || !strides || !blocks || !shared || !unshared) return -1;
     if (n_input_dim != 3 || n_blocks != 3) return -1;
-    if ((n_shared != 1 && n_shared != 3) || (n_unshared != 1 && n_unshared != 3)) return -1;
+    if (n_shared < 1 || n_unshared < 1) return -1;
     simnets_mex_desc d = {};
     d.dtype = SIMNETS_F32;
     d.batch = 1; d.channels = input_dim[0]; d.height = input_dim[1]; d.width = input_dim[2];
@@ -138,10 +138,15 @@ int get_mex_offsets_nregions(int n_input_dim, const int* input_dim, int n_paddin
     d.epsilon = 1.0f;
     d.blocks_round_down = blocks_round_down > 0;
     d.use_unshared_regions = use_unshared_regions > 0;
-    for (int a = 0; a < n_shared; ++a) d.shared_offset_region[a] = shared[a];
-    d.n_shared_offset_region = n_shared;
-    for (int a = 0; a < n_unshared; ++a) d.unshared_offset_region[a] = unshared[a];
-    d.n_unshared_offset_region = n_unshared;
+    // A region list that is not three long stands for its first entry applied to height and width, as
+    // MexDimensionsData::CalculateDimensions reads it (src/kernels/mex_kernel_common.cpp:86-93, 113-120); the op itself
+    // accepts one or three entries only (mex_kernel_common.cpp:51-54), this helper any length, like the reference's.
+    auto region = [](int n, const int* v, int32_t* dst, int32_t* n_dst) {
+        if (n == 3) { dst[0] = v[0]; dst[1] = v[1]; dst[2] = v[2]; *n_dst = 3; }
+        else { dst[0] = v[0]; *n_dst = 1; }
+    };
+    region(n_shared, shared, d.shared_offset_region, &d.n_shared_offset_region);
+    region(n_unshared, unshared, d.unshared_offset_region, &d.n_unshared_offset_region);
     simnets_mex_geometry g;
     if (mex_geometry(&d, &g, nullptr)) return -1;
     return g.num_regions;
@@ -179,7 +184,7 @@ int simnets_mex_forward_static_scratch(const simnets_mex_desc* d, const void* x,
     const bool f64 = d->dtype == SIMNETS_F64;
     if (!mex_use_tiled(g, f64, d->flags))        // these shapes run on kernels that need no scratch at all
         return from_cuda(launch_mex_fwd_direct(g, f64, x, off, y, as_stream(stream)));
-    return launch_mex_fwd_static(g, (const float*)x, (const float*)off, (float*)y, as_stream(stream));
+    return launch_mex_fwd_static(g, (const float*)x, (const float*)off, (float*)y, d->flags, as_stream(stream));
 }
 
 int simnets_mex_input_grad(const simnets_mex_desc* d, const void* x, const void* off, const void* y, const void* dy, void* dx,

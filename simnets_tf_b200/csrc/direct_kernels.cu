@@ -333,7 +333,8 @@ cudaError_t launch_mex_dx_direct(const MexGeo& g, bool f64, const void* x, const
 cudaError_t launch_mex_doff_direct(const MexGeo& g, bool f64, const void* x, const void* off, const void* y, const void* dy,
                                    void* doff, bool accumulate, cudaStream_t s, const int* gate) {
     const long long triples = (long long)g.R * g.M * g.K;
-    const int blocks = int(triples < 148 * 16 ? triples : 148 * 16);
+    const long long cap = (long long)device_sm_count() * 16;
+    const int blocks = int(triples < cap ? triples : cap);
     SIMNETS_DTYPE_SWITCH(f64,
         (mex_doff_direct<float><<<blocks, kThreads, 0, s>>>(g, (const float*)x, (const float*)off, (const float*)y, (const float*)dy, (float*)doff, accumulate, gate)),
         (mex_doff_direct<double><<<blocks, kThreads, 0, s>>>(g, (const double*)x, (const double*)off, (const double*)y, (const double*)dy, (double*)doff, accumulate, gate)));

@@ -101,7 +101,7 @@ cudaError_t launch_mex_doff_pair(const MexGeo&, const float* x, const float* mo,
 // number of multiprocessors of the current device (148 when no device answers)
 int device_sm_count();
 // forward on the library's fixed device scratch; returns a status code of simnets_b200.h
-int launch_mex_fwd_static(const MexGeo&, const float* x, const float* off, float* y, cudaStream_t);
+int launch_mex_fwd_static(const MexGeo&, const float* x, const float* off, float* y, uint32_t flags, cudaStream_t);
 cudaError_t launch_mex_dx_tiled(const MexGeo&, const float* x, const float* off, const float* y, const float* dy, float* dx,
                                 void* ws, uint32_t flags, cudaStream_t, bool prepped = false);
 cudaError_t launch_mex_backward_tiled(const MexGeo&, const float* x, const float* off, const float* y, const float* dy, float* dx,

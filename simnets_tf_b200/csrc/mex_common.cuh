@@ -59,7 +59,7 @@ __host__ inline bool patches_inside_input(const MexGeo& g) {
 __host__ inline int doff_splits(const MexGeo& g) {
     if (smallk_shape(g)) {
         const long long P = (long long)g.B * g.rs, tiles = (P + 31) / 32, ctas = (long long)((g.M + 255) / 256) * g.R;
-        long long s = (148 * 3 + ctas - 1) / ctas;
+        long long s = (device_sm_count() * 3 + ctas - 1) / ctas;
         if (s > tiles) s = tiles;
         if (s < 1) s = 1;
         if (s > 512) s = 512;
@@ -67,7 +67,7 @@ __host__ inline int doff_splits(const MexGeo& g) {
     }
     if (smallm_shape(g)) {
         const long long P = (long long)g.B * g.rs, ktiles = (g.K + 255) / 256;
-        long long s = (148 * 4 + ktiles * g.R - 1) / (ktiles * g.R);
+        long long s = (device_sm_count() * 4 + ktiles * g.R - 1) / (ktiles * g.R);
         if (s > (P + 15) / 16) s = (P + 15) / 16;
         if (s < 1) s = 1;
         if (s > 64) s = 64;
@@ -77,7 +77,7 @@ __host__ inline int doff_splits(const MexGeo& g) {
     const long long P = (long long)g.B * g.rs;
     const long long chunks = (P + kc - 1) / kc;
     const long long tiles = (long long)((g.M + tile - 1) / tile) * ((g.K + tile - 1) / tile) * g.R;
-    long long s = (148 * 2 + tiles - 1) / tiles;
+    long long s = (device_sm_count() * 2 + tiles - 1) / tiles;
     if (s > chunks) s = chunks;
     if (s < 1) s = 1;
     if (s > 64) s = 64;

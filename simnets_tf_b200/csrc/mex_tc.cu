@@ -475,7 +475,7 @@ int mex_tc_doff_splits(const MexGeo& g) {
     const long long P = (long long)g.B * g.rs, chunks = (P + kDoKT - 1) / kDoKT;
     const long long tiles = (long long)((g.M + 127) / 128) * ((g.K + nt - 1) / nt) * g.R;
     const int per_sm = nt == 64 ? 3 : 2;                         // CTAs per SM that the register budget allows
-    long long s = (148LL * per_sm) / tiles;                      // one full wave: measured against a half, two and four (the partial sums are 128 x NT floats per CTA)
+    long long s = ((long long)device_sm_count() * per_sm) / tiles;                      // one full wave: measured against a half, two and four (the partial sums are 128 x NT floats per CTA)
     if (s > chunks) s = chunks;
     if (s < 1) s = 1;
     if (s > 512) s = 512;
@@ -485,7 +485,7 @@ int mex_tc_doff_splits(const MexGeo& g) {
 cudaError_t launch_mex_tc_prep(const MexGeo& g, bool transposed, const float* src, float* tiles, cudaStream_t s, int nt) {
     const int rows = transposed ? g.K : g.M, red = transposed ? g.M : g.K, NT = nt > 0 ? nt : pick_nt(rows);
     const long long total = (long long)g.R * ((rows + NT - 1) / NT) * ((red + kTcKT - 1) / kTcKT) * NT * kTcKT;
-    mex_tc_prep<<<int(std::min<long long>((total + 255) / 256, 148LL * 8)), 256, 0, s>>>(g.R, rows, red, pad4(red), NT, src, tiles);
+    mex_tc_prep<<<int(std::min<long long>((total + 255) / 256, (long long)device_sm_count() * 8)), 256, 0, s>>>(g.R, rows, red, pad4(red), NT, src, tiles);
     count_launch();
     return cudaGetLastError();
 }

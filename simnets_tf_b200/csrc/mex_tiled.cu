@@ -450,7 +450,7 @@ cudaError_t run_prepasses(const MexGeo& g, const MexWs& w, const float* x, const
     if (g.K >= 256 && g.N <= 16) { count_launch(); return launch_mex_colmax_wide(g, x, w.mx, w.flag, s); }
     const long long total = (long long)g.B * g.N;
     // (measured on 32x32x64, 16x16x128 and 8x8x256 maps at batches 256 and 2048: eight threads per position win for
-    // long patches while one thread per position would not fill the GPU's 148 x 2048 thread slots)
+    // long patches while one thread per position would not fill the GPU's thread slots: 2048 per multiprocessor)
     if (g.K >= 128 && total < 148LL * 2048) {
         const int grid = int(std::min<long long>((total + 31) / 32, 148LL * 32));
         if (g.bh == 1 && g.bw == 1) mex_colmax_sliced<true><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
@@ -550,7 +550,7 @@ std::mutex g_static_mu;
 void* g_static_ptr[kMaxDevices] = {};
 }  // namespace
 
-int launch_mex_fwd_static(const MexGeo& g, const float* x, const float* off, float* y, cudaStream_t s) {
+int launch_mex_fwd_static(const MexGeo& g, const float* x, const float* off, float* y, uint32_t flags, cudaStream_t s) {
     if (carve(g, nullptr).fwd_bytes > size_t(SIMNETS_MEX_STATIC_SCRATCH_BYTES)) return SIMNETS_E_TOO_LARGE;
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
@@ -568,7 +568,9 @@ int launch_mex_fwd_static(const MexGeo& g, const float* x, const float* off, flo
     }
     // launch_mex_fwd_tiled clears the one word that must start at zero (the safety flag) on every call;
     // everything else in the scratch is fully rewritten by the prepasses before it is read.
-    e = launch_mex_fwd_tiled(g, x, off, y, ptr, SIMNETS_FLAG_MEX_NO_TENSORCORE, s);   // the scratch bound covers the CUDA-core path
+    // The caller's flags stay in force; the tensor-core route is switched off on top of them, because the capacity
+    // check above counts the CUDA-core route's scratch only (no operand tiles).
+    e = launch_mex_fwd_tiled(g, x, off, y, ptr, flags | SIMNETS_FLAG_MEX_NO_TENSORCORE, s);
     return e == cudaSuccess ? SIMNETS_OK : int(e);
 }
 

@@ -39,7 +39,7 @@ cudaError_t launch_sum_pool2(long long planes, int H, int W, const float* x, flo
     if (planes == 0 || Ho == 0 || Wo == 0) return cudaSuccess;
     const bool vec = W % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 7) == 0;
     const long long total = vec ? planes * Ho * (W / 4) : planes * Ho * Wo;
-    const int grid = int(std::min<long long>((total + 255) / 256, 148LL * 16));
+    const int grid = int(std::min<long long>((total + 255) / 256, (long long)device_sm_count() * 16));
     if (vec) sum_pool2_vec4<<<grid, 256, 0, s>>>(total, Ho, W / 4, W, x, y);
     else sum_pool2_scalar<<<grid, 256, 0, s>>>(total, Wo, W, x, y);
     count_launch();

@@ -41,7 +41,7 @@ __host__ int dp_splits(const SimGeo& g) {
     const long long chunks = (P + kDpKC - 1) / kDpKC;
     const long long tiles = (long long)((g.M + kDpTile - 1) / kDpTile) * ((g.K + dp_tn(g) - 1) / dp_tn(g));
     // the narrow tile runs four CTAs of 128 threads per SM (128 registers per thread): two waves of those
-    const int ctas = dp_tn(g) == 32 ? 148 * 8 : 148 * 4;                  // (the wide tile: two CTAs of 256 threads per SM)
+    const int ctas = device_sm_count() * (dp_tn(g) == 32 ? 8 : 4);                  // (the wide tile: two CTAs of 256 threads per SM)
     long long s = (ctas + tiles - 1) / tiles;
     // every split costs one set of partial sums (3 M K floats written and read again): at small batches a split keeps
     // at least 1024 positions, or the partial sums outweigh the operands

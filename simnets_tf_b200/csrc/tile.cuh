@@ -41,13 +41,9 @@ struct TileThread {
     __device__ __forceinline__ TileThread() {
         const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
         constexpr int WJ = Cfg::TJ / 8;                       // warps along j
-#ifdef SIMNETS_LANES_ROWMAJOR
-        const int li = lane >> 3, lj = lane & 7;
-#else
         // 4 x 8 lane grid, rows interleaved in pairs: any 8 consecutive lanes span 2 rows x 4 columns, so a
         // quarter-warp's 16-byte reads touch 2 distinct A vectors and 4 distinct B vectors
         const int li = ((lane >> 4) << 1) | (lane & 1), lj = (lane & 15) >> 1;
-#endif
         ti = (warp / WJ) * 4 + li;
         tj = (warp % WJ) * 8 + lj;
     }

@@ -67,7 +67,8 @@ class OverlappedStep(object):
     cut (their parameter gradients, the tail of the bucket, are then final); piece B = backward of the layers in front.
     Per step: A on the main stream; the tail's all-reduce on a second stream as soon as A is done; B on the main
     stream meanwhile; the head's all-reduce behind B; join.  With `graphs=True` A and B are two CUDA graphs captured
-    once and replayed; the collectives are always enqueued eagerly, outside any capture.  The reference has no
+    once and replayed; the collectives are always enqueued eagerly, outside any capture (capture needs that no autograd
+    graph built on another stream is still alive, e.g. through a loss tensor kept from an earlier step).  The reference has no
     distributed code; the sums continued here are its batch loops (src/kernels/mex_grad_kernel_cpu.cpp:298-368,
     similarity_grad_kernel_cpu.cpp:84-144)."""
 

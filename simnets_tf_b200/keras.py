@@ -6,11 +6,13 @@ variables on first call (the counterpart of Keras' `build(input_shape)`) and run
 `perform_unsupervised_init` (k-means / GMM / PCA initialisation, pure TensorFlow graph code in the
 reference) is outside this library.
 """
+import ctypes as C
 import math
 
 import numpy as np
 import torch
 
+from . import _lib, abi
 from .ops.mex import _expand_dim_specification, _mex_dims_helper
 from .ops.mex import mex as _mex
 from .ops.mex import mex_sum_pool2 as _mex_sum_pool2
@@ -67,6 +69,20 @@ class Similarity(torch.nn.Module):
         shape = (self.num_instances, num_channels, self.blocks[0], self.blocks[1])
         self.sweights = torch.nn.Parameter(_init_tensor(self.weights_initializer, shape, device, dtype, self.generator))
         self.templates = torch.nn.Parameter(_init_tensor(self.templates_initializer, shape, device, dtype, self.generator))
+
+    def compute_output_shape(self, input_shape):
+        """Shape of the layer's output for `input_shape` (batch first), as the Similarity op's shape function infers it
+        in the reference (src/ops/similarity_op.cpp:8-59)."""
+        shape = list(input_shape)
+        if self.channels_last:
+            shape = [shape[0], shape[3], shape[1], shape[2]]
+        d = abi.make_sim_desc([max(int(shape[0]), 1)] + shape[1:], self.num_instances, self.similarity_function, self.blocks,
+                              self.strides, self.padding, self.normalization_term, self.normalization_term_fudge,
+                              self.ignore_nan_input, self.out_of_bounds_value)
+        oh, ow = C.c_int32(), C.c_int32()
+        _lib.check(_lib.lib().simnets_similarity_output_dims(C.byref(d), C.byref(oh), C.byref(ow)))
+        out = [shape[0], self.num_instances, oh.value, ow.value]
+        return tuple([out[0], out[2], out[3], out[1]] if self.channels_last else out)
 
     def forward(self, x):
         if self.templates is None:
@@ -184,6 +200,22 @@ class Mex(torch.nn.Module):
             raise ValueError("invalid MEX geometry for input shape %s" % (input_shape,))
         shape = (nregions, self.num_instances) + tuple(self.blocks)
         self.offsets = torch.nn.Parameter(_init_tensor(self.offsets_initializer, shape, device, dtype))
+
+    def compute_output_shape(self, input_shape):
+        """Shape of the layer's output for `input_shape` (batch first), as the Mex op's shape function infers it in
+        the reference (src/ops/mex_op.cpp:19-56): a matter of blocks, strides, padding and the rounding mode only,
+        so it also answers for region lists the op's kernel would refuse."""
+        if self.offsets is None:
+            self.build(tuple(input_shape))
+        shape = list(input_shape)
+        if self.channels_last:
+            shape = [shape[0], shape[3], shape[1], shape[2]]
+        d = abi.make_mex_desc([max(int(shape[0]), 1)] + shape[1:], self.num_instances, padding=self.padding, strides=self.strides,
+                              blocks=self.blocks, blocks_round_down=self.blocks_round_down)
+        g = abi.MexGeometry()
+        _lib.check(_lib.lib().simnets_mex_dims(C.byref(d), C.byref(g)))
+        out = [shape[0], g.channels_out_total, g.height_out, g.width_out]
+        return tuple([out[0], out[2], out[3], out[1]] if self.channels_last else out)
 
     def effective_offsets(self):
         if not self.normalize_offsets:

@@ -29,10 +29,16 @@ protected:
         d.batch = int32_t(x.dim_size(0)); d.channels = int32_t(x.dim_size(1));
         d.height = int32_t(x.dim_size(2)); d.width = int32_t(x.dim_size(3));
         d.num_instances = num_instances_;
+        // padding: three entries; a pair [h, w] means [-1, h, w], as the reference's ExpandDimSpec turns it
+        // (src/kernels/mex_kernel_common.cpp:8-27); -1 is resolved by the library to the image extent.  Other lengths
+        // index past the end in the reference; here Compute() rejects them (PaddingOk) before this function runs.
+        int32_t pad3[3] = {0, 0, 0};
+        if (padding_.size() == 3) { pad3[0] = padding_[0]; pad3[1] = padding_[1]; pad3[2] = padding_[2]; }
+        else if (padding_.size() == 2) { pad3[0] = -1; pad3[1] = padding_[0]; pad3[2] = padding_[1]; }
         for (int a = 0; a < 3; ++a) {
             d.blocks[a] = blocks_[size_t(a)];
             d.strides[a] = strides_[size_t(a)];
-            d.padding[a] = padding_.size() == 3 ? padding_[size_t(a)] : (padding_.empty() ? 0 : padding_[0]);
+            d.padding[a] = pad3[a];
         }
         d.epsilon = epsilon_; d.softmax_mode = softmax_mode_;
         d.blocks_out_of_bounds_value = blocks_out_of_bounds_value_;
@@ -44,10 +50,19 @@ protected:
         return d;
     }
 
+    bool PaddingOk() const { return padding_.size() == 2 || padding_.size() == 3; }
+
     // offsets: [num_regions, num_instances, block_c, block_h, block_w] (mex_kernel_common.cpp:60-61)
     static bool OffsetsAgree(const Tensor& offsets, const simnets_mex_geometry& g, int num_instances) {
         return offsets.dims() == 5 && offsets.dim_size(0) == g.num_regions && offsets.dim_size(1) == num_instances &&
                offsets.dim_size(2) == g.block_c && offsets.dim_size(3) == g.block_h && offsets.dim_size(4) == g.block_w;
+    }
+
+    // orig_output and output_grad: [batch, num_instances * channels_out, height_out, width_out]; a wrong shape must be an
+    // InvalidArgument, not an out-of-bounds device read
+    static bool OutputAgrees(const Tensor& t, const simnets_mex_desc& d, const simnets_mex_geometry& g) {
+        return t.dims() == 4 && t.dim_size(0) == d.batch && t.dim_size(1) == g.channels_out_total && t.dim_size(2) == g.height_out &&
+               t.dim_size(3) == g.width_out;
     }
 
     static Status Workspace(OpKernelContext* ctx, const simnets_mex_desc& d, Tensor* ws, size_t* bytes) {
@@ -63,6 +78,7 @@ public:
     void Compute(OpKernelContext* ctx) override {
         const Tensor &x = ctx->input(0), &offsets = ctx->input(1);
         OP_REQUIRES(ctx, x.dims() == 4, errors::InvalidArgument("input must be 4-dimensional"));
+        OP_REQUIRES(ctx, PaddingOk(), errors::InvalidArgument("padding should be a list with 2 or 3 elements"));
         const simnets_mex_desc d = Describe<T>(x);
         simnets_mex_geometry g;
         B200_REQUIRES_OK(ctx, simnets_mex_dims(&d, &g));
@@ -84,10 +100,13 @@ public:
     void Compute(OpKernelContext* ctx) override {
         const Tensor &x = ctx->input(0), &offsets = ctx->input(1), &y = ctx->input(2), &dy = ctx->input(3);
         OP_REQUIRES(ctx, x.dims() == 4, errors::InvalidArgument("input must be 4-dimensional"));
+        OP_REQUIRES(ctx, PaddingOk(), errors::InvalidArgument("padding should be a list with 2 or 3 elements"));
         const simnets_mex_desc d = Describe<T>(x);
         simnets_mex_geometry g;
         B200_REQUIRES_OK(ctx, simnets_mex_dims(&d, &g));
         OP_REQUIRES(ctx, OffsetsAgree(offsets, g, num_instances_), errors::InvalidArgument("offsets must be [num_regions, num_instances, block_c, block_h, block_w]"));
+        OP_REQUIRES(ctx, OutputAgrees(y, d, g), errors::InvalidArgument("orig_output must have the shape of the op's output"));
+        OP_REQUIRES(ctx, OutputAgrees(dy, d, g), errors::InvalidArgument("output_grad must have the shape of the op's output"));
         Tensor* dx = nullptr;
         OP_REQUIRES_OK(ctx, ctx->allocate_output(0, x.shape(), &dx));
         Tensor ws; size_t n = 0;
@@ -105,10 +124,13 @@ public:
     void Compute(OpKernelContext* ctx) override {
         const Tensor &x = ctx->input(0), &offsets = ctx->input(1), &y = ctx->input(2), &dy = ctx->input(3);
         OP_REQUIRES(ctx, x.dims() == 4, errors::InvalidArgument("input must be 4-dimensional"));
+        OP_REQUIRES(ctx, PaddingOk(), errors::InvalidArgument("padding should be a list with 2 or 3 elements"));
         const simnets_mex_desc d = Describe<T>(x);
         simnets_mex_geometry g;
         B200_REQUIRES_OK(ctx, simnets_mex_dims(&d, &g));
         OP_REQUIRES(ctx, OffsetsAgree(offsets, g, num_instances_), errors::InvalidArgument("offsets must be [num_regions, num_instances, block_c, block_h, block_w]"));
+        OP_REQUIRES(ctx, OutputAgrees(y, d, g), errors::InvalidArgument("orig_output must have the shape of the op's output"));
+        OP_REQUIRES(ctx, OutputAgrees(dy, d, g), errors::InvalidArgument("output_grad must have the shape of the op's output"));
         Tensor* doff = nullptr;
         OP_REQUIRES_OK(ctx, ctx->allocate_output(0, offsets.shape(), &doff));
         Tensor ws; size_t n = 0;

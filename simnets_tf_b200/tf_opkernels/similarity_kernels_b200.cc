@@ -7,6 +7,7 @@
 // (include/kernels/similarity_kernel_common.hpp), which this file includes from the reference checkout and derives
 // from.  Only Compute() changes: no im2col buffer, no interlaced parameter buffer, one library call per op.
 // The library never allocates: scratch comes from allocate_temp, launches go to TensorFlow's compute stream.
+#include <cstdlib>
 #include <type_traits>
 
 #include "kernels/similarity_kernel_common.hpp"
@@ -19,9 +20,14 @@ namespace {
 #define B200_REQUIRES_OK(ctx, rc) \
     OP_REQUIRES(ctx, (rc) == SIMNETS_OK, errors::Internal("simnets_b200: ", simnets_status_string(rc)))
 
-// Set this to true to add the -0.5*K*log(2*pi) constant (batch - n) times to sample n, as the reference's fast op does
-// (src/kernels/similarity_kernel_cpu.cpp:118-120); false adds it once, as the reference's SimilarityRef op does.
-constexpr bool kLegacyBatchConstant = false;
+// L2 with normalization_term and without ignore_nan_input: the reference's fast op adds the -0.5*K*log(2*pi) constant
+// (batch - n) times to sample n (src/kernels/similarity_kernel_cpu.cpp:118-120), its SimilarityRef op once.  Default:
+// once.  Set the environment variable SIMNETS_B200_LEGACY_BATCH_CONSTANT=1 before the kernels are constructed to
+// reproduce the fast op bit for bit.
+inline bool LegacyBatchConstant() {
+    static const bool on = [] { const char* v = std::getenv("SIMNETS_B200_LEGACY_BATCH_CONSTANT"); return v && v[0] == '1'; }();
+    return on;
+}
 
 class SimilarityB200Base : public SimilarityKernelCommon {
 protected:
@@ -40,14 +46,23 @@ protected:
         d.similarity_function = similarity_function_ == SIM_FUNC_L1 ? SIMNETS_SIM_L1 : SIMNETS_SIM_L2;
         d.normalization_term = normalization_term_; d.ignore_nan_input = ignore_nan_input_;
         d.normalization_term_fudge = normalization_term_fudge_; d.out_of_bounds_value = out_of_bounds_value_;
-        d.flags = kLegacyBatchConstant ? SIMNETS_FLAG_SIM_BATCH_CONST_QUIRK : 0u;
+        d.flags = LegacyBatchConstant() ? SIMNETS_FLAG_SIM_BATCH_CONST_QUIRK : 0u;
         return d;
     }
 
     // shape checks the reference performs in CalculateDimensions (similarity_kernel_common.hpp:158-161)
-    static bool ShapesAgree(const Tensor& x, const Tensor& t, const Tensor& w) {
+    // plus the block extents: templates and weights are [num_instances, channels, block_h, block_w] with the attr's blocks
+    bool ShapesAgree(const Tensor& x, const Tensor& t, const Tensor& w) const {
         return x.dims() == 4 && t.dims() == 4 && w.dims() == 4 && x.dim_size(1) == t.dim_size(1) && x.dim_size(1) == w.dim_size(1) &&
-               t.dim_size(0) == w.dim_size(0);
+               t.dim_size(0) == w.dim_size(0) && t.dim_size(2) == blocks_[0] && t.dim_size(3) == blocks_[1] &&
+               w.dim_size(2) == blocks_[0] && w.dim_size(3) == blocks_[1];
+    }
+
+    // output_grad: [batch, num_instances, height_out, width_out]
+    static bool OutputGradAgrees(const Tensor& dy, const simnets_sim_desc& d) {
+        int32_t oh = 0, ow = 0;
+        if (simnets_similarity_output_dims(&d, &oh, &ow) != SIMNETS_OK) return false;
+        return dy.dims() == 4 && dy.dim_size(0) == d.batch && dy.dim_size(1) == d.num_instances && dy.dim_size(2) == oh && dy.dim_size(3) == ow;
     }
 
     // scratch for one call, from TensorFlow's allocator
@@ -85,6 +100,7 @@ public:
         const Tensor &x = ctx->input(0), &t = ctx->input(1), &w = ctx->input(2), &dy = ctx->input(3);
         OP_REQUIRES(ctx, ShapesAgree(x, t, w), errors::InvalidArgument("Number of channels mismatch between input and templates / weights"));
         const simnets_sim_desc d = Describe<T>(x, t);
+        OP_REQUIRES(ctx, OutputGradAgrees(dy, d), errors::InvalidArgument("output_grad must have the shape of the op's output"));
         Tensor* dx = nullptr;
         OP_REQUIRES_OK(ctx, ctx->allocate_output(0, x.shape(), &dx));
         Tensor ws; size_t n = 0;
@@ -103,6 +119,7 @@ public:
         const Tensor &x = ctx->input(0), &t = ctx->input(1), &w = ctx->input(2), &dy = ctx->input(3);
         OP_REQUIRES(ctx, ShapesAgree(x, t, w), errors::InvalidArgument("Number of channels mismatch between input and templates / weights"));
         const simnets_sim_desc d = Describe<T>(x, t);
+        OP_REQUIRES(ctx, OutputGradAgrees(dy, d), errors::InvalidArgument("output_grad must have the shape of the op's output"));
         Tensor *dt = nullptr, *dw = nullptr;
         OP_REQUIRES_OK(ctx, ctx->allocate_output(0, t.shape(), &dt));
         OP_REQUIRES_OK(ctx, ctx->allocate_output(1, w.shape(), &dw));

@@ -33,6 +33,7 @@ def test_overlapped_step_equals_plain_backward(graphs):
     loss = net.loss(xd, ld, 8)
     loss.backward()
     want, want_loss = bucket.flat.clone(), float(loss.detach())
+    del loss                                 # (an autograd graph of the default stream kept alive would break the capture)
     step = dp.OverlappedStep(net, bucket, xd, ld, 8, graphs=graphs)
     assert 0 < step.cut < len(net._plan) and 0 < step.tail_begin < bucket.flat.numel()
     for _ in range(2):                       # a replay must not accumulate into the previous one

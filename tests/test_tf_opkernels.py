@@ -169,3 +169,99 @@ def test_mex_opkernel_reports_bad_offsets_shape(tfk, port):
                        unshared_offset_region=[-1])
     rc, msg, _ = run(tfk, "Mex", attrs, [x, off], [(2, 3, 6, 6)])
     assert rc == 2 and "offsets must be" in msg
+
+
+@pytest.mark.gpu
+def test_mex_opkernel_takes_a_two_entry_padding_as_the_reference_does(tfk, port):
+    """padding=[h, w] means [-1, h, w] (ExpandDimSpec, src/kernels/mex_kernel_common.cpp:8-27): the channel padding
+    becomes the channel count.  The oracle is given the expanded form."""
+    import gpu_util
+    c = dict(next(c for c in cases.MEX_SMALL if c["name"] == "tiled_regions"))
+    C_ = c["shape"][1]
+    c["padding"] = (C_, 1, 1)
+    d = cases.mex_desc(c)
+    x, off, dy = cases.mex_inputs(c, port.mex_offsets_shape(d), port.mex_out_shape(d))
+    ry = port.mex_forward(d, x, off)
+    xd, od, dyd, ryd = (gpu_util.dev(a) for a in (x, off, dy, ry))
+    attrs = mex_attrs(dict(c, padding=(1, 1)))
+    rc, msg, (y,) = run(tfk, "Mex", attrs, [xd, od], [ry.shape])
+    assert rc == 0, msg
+    assert tuple(y.shape) == ry.shape
+    cases.assert_parity(y.cpu().numpy(), ry, what="y")
+    rc, msg, (dx,) = run(tfk, "MexInputGrad", attrs, [xd, od, ryd, dyd], [x.shape])
+    assert rc == 0, msg
+    cases.assert_parity(dx.cpu().numpy(), port.mex_input_grad(d, x, off, ry, dy), tol=2e-5, what="dx")
+    rc, msg, _ = run(tfk, "Mex", mex_attrs(dict(c, padding=(1,))), [xd, od], [ry.shape])
+    assert rc == 2 and "padding should be" in msg
+
+
+@pytest.mark.gpu
+def test_mex_grad_opkernels_reject_a_wrong_output_shape(tfk, port):
+    import gpu_util
+    c = next(c for c in cases.MEX_SMALL if c["name"] == "tiled_regions")
+    d = cases.mex_desc(c)
+    x, off, dy = cases.mex_inputs(c, port.mex_offsets_shape(d), port.mex_out_shape(d))
+    ry = port.mex_forward(d, x, off)
+    xd, od, dyd, ryd = (gpu_util.dev(a) for a in (x, off, dy, ry))
+    attrs = mex_attrs(c)
+    short = ryd[:, :, :-1].contiguous()
+    for op, out in (("MexInputGrad", x.shape), ("MexOffsetsGrad", off.shape)):
+        rc, msg, _ = run(tfk, op, attrs, [xd, od, short, dyd], [out])
+        assert rc == 2 and "orig_output must have" in msg, (op, rc, msg)
+        rc, msg, _ = run(tfk, op, attrs, [xd, od, ryd, short], [out])
+        assert rc == 2 and "output_grad must have" in msg, (op, rc, msg)
+
+
+@pytest.mark.gpu
+def test_similarity_opkernels_reject_wrong_block_and_gradient_shapes(tfk, port):
+    import gpu_util
+    c = next(c for c in cases.SIM_SMALL if c["name"] == "dims00")
+    d = cases.sim_desc(c)
+    x, t, w, dy = cases.sim_inputs(c, port.sim_out_shape(d))
+    xd, td, wd, dyd = (gpu_util.dev(a) for a in (x, t, w, dy))
+    attrs = sim_attrs(c)
+    import torch
+    wide = torch.zeros(t.shape[:3] + (t.shape[3] + 1,), device="cuda")
+    rc, msg, _ = run(tfk, "Similarity", attrs, [xd, wide, wide], [dy.shape])
+    assert rc == 2 and "mismatch" in msg
+    rc, msg, _ = run(tfk, "Similarity", attrs, [xd, td, wide], [dy.shape])
+    assert rc == 2 and "mismatch" in msg
+    short = dyd[:, :, :-1].contiguous()
+    rc, msg, _ = run(tfk, "SimilarityInputGrad", attrs, [xd, td, wd, short], [x.shape])
+    assert rc == 2 and "output_grad must have" in msg
+    rc, msg, _ = run(tfk, "SimilarityParametersGrad", attrs, [xd, td, wd, short], [t.shape, w.shape])
+    assert rc == 2 and "output_grad must have" in msg
+
+
+_LEGACY_CHILD = r"""
+import os, sys
+sys.path.insert(0, {tests!r}); sys.path.insert(0, {root!r})
+import numpy as np, torch
+import cases, test_tf_opkernels as T
+import ctypes as C
+from simnets_tf_b200 import abi
+from oracle import oracle
+port = oracle.load("port")
+lib = C.CDLL(T.tf_double_build.build())
+lib.tfk_run.argtypes = [C.c_char_p, C.c_int, C.c_char_p, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.POINTER(C.c_longlong),
+                        C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.POINTER(C.c_longlong), C.c_void_p, C.c_ulonglong,
+                        C.c_void_p, C.c_char_p, C.c_int]
+c = next(c for c in cases.SIM_SMALL if c["name"] == "norm_batch3_quirk")
+d = cases.sim_desc(c, flags=abi.FLAG_SIM_BATCH_CONST_QUIRK)
+x, t, w, dy = cases.sim_inputs(c, port.sim_out_shape(d))
+rc, msg, (y,) = T.run(lib, "Similarity", T.sim_attrs(c), [torch.from_numpy(a).cuda() for a in (x, t, w)], [dy.shape])
+assert rc == 0, msg
+cases.assert_parity(y.cpu().numpy(), port.similarity_forward(d, x, t, w), what="y with the batch constant of the fast op")
+print("LEGACY_OK")
+"""
+
+
+@pytest.mark.gpu
+def test_legacy_batch_constant_switch_reproduces_the_fast_op(tfk):
+    """SIMNETS_B200_LEGACY_BATCH_CONSTANT=1 is read once per process, so the check runs in a child process."""
+    import subprocess
+    root = os.path.dirname(HERE)
+    env = dict(os.environ, SIMNETS_B200_LEGACY_BATCH_CONSTANT="1")
+    out = subprocess.run([sys.executable, "-c", _LEGACY_CHILD.format(tests=HERE, root=root)], env=env, capture_output=True, text=True,
+                         timeout=600)
+    assert "LEGACY_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]

@@ -53,7 +53,7 @@ public:
         *out = a.v >= 0 ? a : b; return Status::OK();
     }
     ShapeHandle MakeShape(const std::vector<DimensionHandle>& d) { ShapeHandle s; s.known = true; for (auto& x : d) s.dims.push_back(x.v); return s; }
-    Status Add(DimensionHandle a, DimensionOrConstant b, DimensionHandle* out) { *out = DimensionHandle(a.v < 0 || b.v < 0 && false ? -1 : a.v + b.v); return Status::OK(); }
+    Status Add(DimensionHandle a, DimensionOrConstant b, DimensionHandle* out) { *out = DimensionHandle((a.v < 0 || b.v < 0) ? -1 : a.v + b.v); return Status::OK(); }
     Status Subtract(DimensionHandle a, DimensionOrConstant b, DimensionHandle* out) {
         if (a.v >= 0 && b.v >= 0 && a.v < b.v) return errors::InvalidArgument("Negative dimension size caused by subtracting ", b.v, " from ", a.v);
         *out = DimensionHandle(a.v < 0 ? -1 : a.v - b.v); return Status::OK();
