@@ -58,7 +58,7 @@ cudaError_t launch_mex_doff_smallm(const MexGeo&, const float* x, const float* m
 bool mex_head_shape(const MexGeo&);
 int mex_head_splits(const MexGeo&);
 size_t mex_head_fwd_scratch_floats(const MexGeo&);
-cudaError_t launch_mex_fwd_head(const MexGeo&, const float* x, const float* eot, const float* mo, float* mx, float* y,
+cudaError_t launch_mex_fwd_head(const MexGeo&, const float* x, const float* eo, const float* eot, const float* mo, float* mx, float* y,
                                 float* scratch, const int* flag, cudaStream_t);
 cudaError_t launch_mex_bwd_head(const MexGeo&, bool want_dx, bool want_doff, const float* x, const float* eo, const float* mo,
                                 const float* mx, const float* y, const float* dy, float* dx, float* part, int splits,

@@ -351,6 +351,125 @@ __global__ void __launch_bounds__(kT) mex_fwd_head(MexGeo g, int pb, int slices,
     }
 }
 
+// Forward for aligned patches (K and the patch starts multiples of four floats): CTA = (16 positions, slice of 1024 taps),
+// warp = two positions.  A lane owns taps 4 (lane + 32 i) .. + 3, i < 8, of both positions: sixteen 16-byte loads per
+// thread are issued before anything waits (64 KiB of x in flight per CTA), the slice of the offsets table is staged in
+// shared memory meanwhile (instance-major, so that a lane's 16-byte reads are conflict free), the slice's maximum is a
+// warp reduction, and the sums of a position never leave its warp.  Partial sums, ticket and the combining CTA are the
+// ones of mex_fwd_head.  x is read from memory exactly once.
+constexpr int kWidePB = 16, kWideSlice = 1024;
+
+template <int MP>
+__global__ void __launch_bounds__(kT, 2) mex_fwd_head_wide(MexGeo g, int slices, const float* __restrict__ x, const float* __restrict__ eo,
+                                                           const float* __restrict__ mo, float* __restrict__ mx, float* __restrict__ y,
+                                                           float* __restrict__ partial, int* __restrict__ tickets, const int* __restrict__ flag) {
+    extern __shared__ __align__(16) float seo[];                   // [MP][kWideSlice]
+    __shared__ int last;
+    if (*flag) return;
+    const long long P = (long long)g.B * g.N;
+    const int group = blockIdx.x / slices, slice = blockIdx.x % slices;
+    const long long p0 = (long long)group * kWidePB;
+    const int np = int(min((long long)kWidePB, P - p0));
+    const int K = g.K, M = g.M, ldk = pad4(g.K);
+    const int k_begin = slice * kWideSlice, klen = min(kWideSlice, K - k_begin);
+    const bool up = g.eps > 0;
+    const float a = float(g.eps) * 1.4426950408889634f;
+    const float fill = up ? -CUDART_INF_F : CUDART_INF_F;          // absent taps: never the extremum, exp gives 0
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float4 xv[2][8];
+#pragma unroll
+    for (int pp = 0; pp < 2; ++pp) {
+        const int p = 2 * warp + pp;
+        const long long q = p0 + (p < np ? p : 0);
+        const int n = int(q / g.N), pos = int(q % g.N);
+        const float4* xp = reinterpret_cast<const float4*>(x + ((size_t)n * g.C + (size_t)pos * g.sc) * g.H * g.W + k_begin);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int t = 4 * (lane + 32 * i);
+            xv[pp][i] = (p < np && t < klen) ? __ldcs(xp + lane + 32 * i) : make_float4(fill, fill, fill, fill);
+        }
+    }
+    // the slice of exp(eps (offsets - mo)): rows past M and taps past the slice hold zeros
+    for (int i = threadIdx.x; i < MP * (kWideSlice / 4); i += kT) {
+        const int m = i / (kWideSlice / 4), t = 4 * (i % (kWideSlice / 4));
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (m < M && t < klen) v = __ldg(reinterpret_cast<const float4*>(eo + (size_t)m * ldk + k_begin + t));
+        reinterpret_cast<float4*>(seo)[i] = v;
+    }
+    float mxw[2];
+#pragma unroll
+    for (int pp = 0; pp < 2; ++pp) {
+        float v = fill;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float4 t = xv[pp][i];
+            v = up ? fmaxf(fmaxf(v, t.x), fmaxf(fmaxf(t.y, t.z), t.w)) : fminf(fminf(v, t.x), fminf(fminf(t.y, t.z), t.w));
+        }
+        mxw[pp] = up ? warp_max(v) : warp_min(v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float4& t = xv[pp][i];
+            t.x = ex2_approx(a * (t.x - mxw[pp])); t.y = ex2_approx(a * (t.y - mxw[pp]));
+            t.z = ex2_approx(a * (t.z - mxw[pp])); t.w = ex2_approx(a * (t.w - mxw[pp]));
+        }
+    }
+    __syncthreads();
+    float acc[2][MP];
+#pragma unroll
+    for (int m = 0; m < MP; ++m) acc[0][m] = acc[1][m] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float4 e0 = xv[0][i], e1 = xv[1][i];
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+            const float4 w = reinterpret_cast<const float4*>(seo + m * kWideSlice)[lane + 32 * i];
+            acc[0][m] = fmaf(e0.x, w.x, fmaf(e0.y, w.y, fmaf(e0.z, w.z, fmaf(e0.w, w.w, acc[0][m]))));
+            acc[1][m] = fmaf(e1.x, w.x, fmaf(e1.y, w.y, fmaf(e1.z, w.z, fmaf(e1.w, w.w, acc[1][m]))));
+        }
+    }
+    // this slice's partial sums and maxima: partial[group][slice][p < 16][MP + 1]
+    float* mine = partial + ((size_t)group * slices + slice) * kWidePB * (MP + 1);
+#pragma unroll
+    for (int pp = 0; pp < 2; ++pp) {
+        float keep = mxw[pp];                                       // lane MP keeps the maximum, lane m < MP the sum of instance m
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+            const float t = warp_sum(acc[pp][m]);
+            if (lane == m) keep = t;
+        }
+        if (lane <= MP) mine[(2 * warp + pp) * (MP + 1) + lane] = keep;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(tickets + group, 1) == slices - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    // the last CTA of the group: combine the slices in slice order (deterministic)
+    const float* all = partial + (size_t)group * slices * kWidePB * (MP + 1);
+    for (int i = threadIdx.x; i < np * MP; i += kT) {
+        const int p = i / MP, m = i % MP;
+        float gm = fill;
+        for (int s2 = 0; s2 < slices; ++s2) {
+            const float t = __ldcg(all + ((size_t)s2 * kWidePB + p) * (MP + 1) + MP);
+            gm = up ? fmaxf(gm, t) : fminf(gm, t);
+        }
+        float sum = 0.f;
+        for (int s2 = 0; s2 < slices; ++s2) {
+            const float* ps = all + ((size_t)s2 * kWidePB + p) * (MP + 1);
+            const float ms = __ldcg(ps + MP);
+            const float part_sum = __ldcg(ps + m);
+            if (part_sum != 0.f) sum = fmaf(part_sum, ex2_approx(a * (ms - gm)), sum);
+        }
+        const long long q = p0 + p;
+        if (m == 0) mx[q] = gm;
+        if (m < M) {
+            const int n = int(q / g.N), pos = int(q % g.N);
+            y[((long long)n * M + m) * g.N + pos] = gm + mo[m] + (fast_log(sum) + float(g.cst)) / float(g.eps);
+        }
+    }
+}
+
 // Backward: CTA = (tile of kT * KPT taps, split of the positions).  Per position: Q[m] = dy * exp(eps (mx + mo - y) + c);
 // per tap of the tile: Ex once, then dx = Ex * sum_m Eo[m, k] Q[m] and U[m, k] += Q[m] * Ex.
 constexpr int kHeadKPT = 4;        // taps per thread
@@ -502,15 +621,52 @@ int mex_head_splits(const MexGeo& g) {
     return int(s);
 }
 
-// scratch of the forward head kernel behind `part`-sized storage: partial sums then tickets
+// patches and patch starts on 16-byte boundaries (given a 16-byte aligned x)
+static bool head_wide_shape(const MexGeo& g, const float* x) {
+    const long long hw = (long long)g.H * g.W;
+    return g.K % 4 == 0 && g.K >= kWideSlice / 2 && (g.C * hw) % 4 == 0 && (g.sc * hw) % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+}
+static int head_slices_max(const MexGeo& g) { return std::max(kHeadSlices, (g.K + kWideSlice - 1) / kWideSlice); }
+
+// scratch of the forward head kernels behind `part`-sized storage: partial sums then tickets
 size_t mex_head_fwd_scratch_floats(const MexGeo& g) {
     const long long P = (long long)g.B * g.N;
-    return size_t(P + kHeadPB) * kHeadSlices * (pad4(g.M) + 1) + size_t(P + 1);       // groups of at least one position each
+    return size_t(P + kWidePB) * head_slices_max(g) * (pad4(g.M) + 1) + size_t(P + 1);       // groups of at least one position each
 }
 
-cudaError_t launch_mex_fwd_head(const MexGeo& g, const float* x, const float* eot, const float* mo, float* mx, float* y,
+cudaError_t launch_mex_fwd_head(const MexGeo& g, const float* x, const float* eo, const float* eot, const float* mo, float* mx, float* y,
                                 float* scratch, const int* flag, cudaStream_t s) {
     const long long P = (long long)g.B * g.N;
+    if (head_wide_shape(g, x)) {
+        const long long groups = (P + kWidePB - 1) / kWidePB;
+        const int slices = (g.K + kWideSlice - 1) / kWideSlice;
+        if (groups * slices > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+        float* partial = scratch;
+        int* tickets = reinterpret_cast<int*>(scratch + size_t(P + kWidePB) * head_slices_max(g) * (pad4(g.M) + 1));
+        cudaError_t e = cudaMemsetAsync(tickets, 0, sizeof(int) * size_t(groups), s);
+        if (e != cudaSuccess) return e;
+        const int blocks = int(groups * slices);
+#define HEAD_WIDE(MP)                                                                                                   \
+        do {                                                                                                            \
+            static bool attr_done = false;                                                                              \
+            constexpr int smem = MP * kWideSlice * 4;                                                                   \
+            if (!attr_done) {                                                                                           \
+                e = cudaFuncSetAttribute(mex_fwd_head_wide<MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);     \
+                if (e != cudaSuccess) return e;                                                                         \
+                attr_done = true;                                                                                       \
+            }                                                                                                           \
+            mex_fwd_head_wide<MP><<<blocks, kT, smem, s>>>(g, slices, x, eo, mo, mx, y, partial, tickets, flag);        \
+        } while (0)
+        switch (pad4(g.M)) {
+        case 4: HEAD_WIDE(4); break;
+        case 8: HEAD_WIDE(8); break;
+        case 12: HEAD_WIDE(12); break;
+        default: HEAD_WIDE(16); break;
+        }
+#undef HEAD_WIDE
+        count_launch();
+        return cudaGetLastError();
+    }
     // Large batches: 8 positions per CTA over whole patches (measured fastest: the offsets table is read once per 8
     // positions and nothing is combined).  Small batches, where that leaves most SMs idle: smaller groups and tap slices.
     int pb = kHeadPB;
@@ -519,7 +675,7 @@ cudaError_t launch_mex_fwd_head(const MexGeo& g, const float* x, const float* eo
     const int slices = (g.K >= kHeadSlices * 64 && 2 * groups < device_sm_count()) ? kHeadSlices : 1;
     if (groups * slices > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     float* partial = scratch;
-    int* tickets = reinterpret_cast<int*>(scratch + size_t(P + kHeadPB) * kHeadSlices * (pad4(g.M) + 1));
+    int* tickets = reinterpret_cast<int*>(scratch + size_t(P + kWidePB) * head_slices_max(g) * (pad4(g.M) + 1));
     cudaError_t e = cudaMemsetAsync(tickets, 0, sizeof(int) * size_t(groups), s);
     if (e != cudaSuccess) return e;
     const int blocks = int(groups * slices);

@@ -62,6 +62,16 @@ __device__ __forceinline__ bool pair_wait(volatile int& failed, uint64_t* bar, u
     return false;
 }
 
+// Warp-wide form for the places where a warp-synchronous instruction follows the wait (tcgen05.ld, __syncwarp, the MMA
+// warp's elected issue): the verdict is made uniform by a vote, so that a wait that ran out in one lane takes the whole
+// warp out of its loop together.  (Arrivals stay one per thread: one arrival per warp behind a __syncwarp measured
+// 1 to 5 % slower on the three kernels.)
+__device__ __forceinline__ bool pair_wait_warp(volatile int& failed, uint64_t* bar, uint32_t parity, uint32_t tries, uint32_t cap_ns = 256,
+                                               bool need = true) {
+    const bool ok = !failed && (!need || pair_wait(failed, bar, parity, tries, cap_ns));
+    return __all_sync(0xffffffffu, ok);
+}
+
 __device__ __forceinline__ void bulk_expect(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
@@ -204,13 +214,12 @@ __device__ __forceinline__ void pair_mma_role(PairShared<STAGES>& sh, unsigned c
     for (int li = 0; li < my_items; ++li) {
         const int buf = li & 1;
         const uint32_t round = uint32_t(li) >> 1;
-        if (sh.failed) break;
-        if (round >= 1 && !pair_wait(sh.failed, &sh.acc_empty[buf], (round - 1) & 1u, tries)) { sh.failed = 1; break; }
+        if (!pair_wait_warp(sh.failed, &sh.acc_empty[buf], (round - 1) & 1u, tries, 256, round >= 1)) { sh.failed = 1; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         bool ok = true;
         for (int c = 0; c < chunks; ++c) {
             const int stage = ring.stage;
-            if (!pair_wait(sh.failed, &sh.full[stage], ring.fill & 1u, tries, 64) || !pair_wait(sh.failed, &sh.bfull[stage], ring.fill & 1u, tries, 64)) { ok = false; break; }
+            if (!pair_wait_warp(sh.failed, &sh.full[stage], ring.fill & 1u, tries, 64) || !pair_wait_warp(sh.failed, &sh.bfull[stage], ring.fill & 1u, tries, 64)) { ok = false; break; }
             ring.advance(1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) {
@@ -367,7 +376,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) mex_fwd_pair(MexGeo g, const 
         const unsigned Nu = unsigned(g.N);
         for (int li = 0; li < my_items; ++li) {
             const int buf = li & 1;
-            if (sh.failed) break;
+            if (__any_sync(0xffffffffu, sh.failed)) break;
             const WsItem it = ws_item(plan, int(blockIdx.x) + li * int(gridDim.x));
             const int m0 = it.mt * NT + half * (NT / 2);
             for (int i = lane; i < NT / 2; i += 32) {
@@ -379,7 +388,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) mex_fwd_pair(MexGeo g, const 
             const PairColumn col = pair_column_of(g, it.r, (long long)it.jt * kTcPos + quarter * 32 + lane, P, mx);
             const float cadd0 = col.mx0 + c_add, cadd1 = col.mx1 + c_add;
             float* yb = y + (col.base >= 0 ? col.base : 0) + (long long)m0 * g.N;
-            if (!pair_wait(sh.failed, &sh.acc_full[buf], (uint32_t(li) >> 1) & 1u, tries, 1024)) { sh.failed = 1; break; }
+            if (!pair_wait_warp(sh.failed, &sh.acc_full[buf], (uint32_t(li) >> 1) & 1u, tries, 1024)) { sh.failed = 1; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (int c0 = 0; c0 < NT / 2; c0 += 16) {
@@ -574,7 +583,7 @@ __global__ void __launch_bounds__(kDxThreads, 1) mex_dx_pair(MexGeo g, const flo
         const unsigned hw = unsigned(g.H) * unsigned(g.W);
         for (int li = 0; li < my_items; ++li) {
             const int buf = li & 1;
-            if (sh.failed) break;
+            if (__any_sync(0xffffffffu, sh.failed)) break;
             const WsItem it = ws_item(plan, int(blockIdx.x) + li * int(gridDim.x));        // it.mt = tap tile
             const PairColumn col = pair_column_of(g, it.r, (long long)it.jt * kTcPos + quarter * 32 + lane, P, mx);
             const int k_first = it.mt * NT + half * (NT / 2);
@@ -584,7 +593,7 @@ __global__ void __launch_bounds__(kDxThreads, 1) mex_dx_pair(MexGeo g, const flo
             float2 xr[8], xn[8];                                    // x of the block at hand and of the next one, in flight
 #pragma unroll
             for (int i = 0; i < 8; ++i) xr[i] = i < kleft ? ldg2(xb + (size_t)i * hw) : make_float2(0.f, 0.f);
-            if (!pair_wait(sh.failed, &sh.acc_full[buf], (uint32_t(li) >> 1) & 1u, tries, 1024)) { sh.failed = 1; break; }
+            if (!pair_wait_warp(sh.failed, &sh.acc_full[buf], (uint32_t(li) >> 1) & 1u, tries, 1024)) { sh.failed = 1; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (int c0 = 0; c0 < NT / 2; c0 += 8) {
@@ -780,6 +789,7 @@ __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, con
         // ---------------- the partial sums: lane = instance row, registers = taps
         bool good = alive && !sh.failed;
         if (good && nchunks > 0) good = pair_wait(sh.failed, &sh.acc_full, 0, tries);
+        good = __all_sync(0xffffffffu, good);                                   // the warp-wide loads and syncs below need one verdict
         if (!good) sh.failed = 1;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (good) {
@@ -813,7 +823,7 @@ __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, con
         bool ok = true;
         for (int c = 0; c < nchunks; ++c) {
             const int stage = ring.stage;
-            if (sh.failed || !pair_wait(sh.failed, &sh.full[stage], ring.fill & 1u, tries, 64)) { ok = false; break; }
+            if (!pair_wait_warp(sh.failed, &sh.full[stage], ring.fill & 1u, tries, 64)) { ok = false; break; }
             ring.advance(1);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) {

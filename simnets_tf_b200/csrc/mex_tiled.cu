@@ -497,7 +497,7 @@ cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* o
     if (smallm_shape(g)) {
         cudaError_t e = run_prepasses(g, w, x, off, s, false);
         if (e != cudaSuccess) return e;
-        e = mex_head_shape(g) ? launch_mex_fwd_head(g, x, w.eot, w.mo, w.mx, y, w.part, w.flag, s)        // (also leaves the maxima for the gradients)
+        e = mex_head_shape(g) ? launch_mex_fwd_head(g, x, w.eo, w.eot, w.mo, w.mx, y, w.part, w.flag, s)        // (also leaves the maxima for the gradients)
                               : launch_mex_fwd_smallm(g, x, w.eot, w.mo, y, w.flag, s);
         if (e != cudaSuccess) return e;
         return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);

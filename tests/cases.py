@@ -208,6 +208,10 @@ MEX_HEAD = [
     mex_case("head_channel_blocks", (6, 96, 3, 3), 6, (48, 3, 3), (48, 3, 3), softmax=True, unshared=False, shared_region=(-1,), seed=412, normalize=True),
     mex_case("head_eps_neg", (9, 64, 2, 2), 3, (64, 2, 2), (64, 2, 2), eps=-0.8, softmax=False, seed=413),
     mex_case("head_long", (3, 300, 4, 4), 10, (300, 4, 4), (300, 4, 4), softmax=True, eps=2.0, seed=414, normalize=True),
+    # aligned patches of at least 512 taps: slices of 1024 taps, groups of 16 positions (last group and last slice ragged)
+    mex_case("head_wide_blocks", (19, 128, 4, 4), 16, (64, 4, 4), (64, 4, 4), softmax=True, unshared=False, shared_region=(-1,), seed=415, normalize=True),
+    mex_case("head_wide_neg", (17, 40, 4, 4), 5, (40, 4, 4), (40, 4, 4), eps=-0.7, softmax=False, seed=416),
+    mex_case("head_wide_m3", (33, 96, 4, 4), 3, (96, 4, 4), (96, 4, 4), softmax=True, eps=1.5, seed=417, normalize=True),
 ]
 
 
