@@ -81,6 +81,14 @@ enum { SIMNETS_SIM_L1 = 0, SIMNETS_SIM_L2 = 1 };
  * (simnets_mex_workspace_status) and the exact kernels launched behind the tensor-core kernel redo the work. */
 #define SIMNETS_FLAG_MEX_TEST_EXPIRE_WAIT (1u << 10)
 
+/* simnets_similarity_forward only, float32, L2 without ignore_nan_input (other calls ignore the flag): evaluate the
+ * squared differences through their expansion  sum s x^2 - 2 sum (s t) x + sum s t^2  as ONE matrix product on the
+ * tensor cores (split-TF32 operands, FP32 accumulation) instead of term by term as the reference does
+ * (include/utils/similarity_utils.hpp:26-36).  Opt-in because the expansion cancels where the reference's form does
+ * not: TOLERANCE |y - y_ref| <= 1e-3 * max|y_ref| (the default kernels hold 1e-5); inputs must be finite.  The
+ * gradients always use the term-by-term kernels. */
+#define SIMNETS_FLAG_SIM_L2_TENSORCORE (1u << 11)
+
 /* MEX gradient entry points only: dy is given at half resolution, dy[batch, M * channels_out, height_out / 2,
  * width_out / 2], each value standing for the 2x2 window of output positions that a 2x2 / stride-2 sum pooling
  * added up (the gradient of such a pooling copies its dy to the four inputs; with this flag the copy is never
@@ -131,6 +139,12 @@ SIMNETS_API size_t simnets_similarity_workspace_bytes(const simnets_sim_desc* d)
 SIMNETS_API int simnets_similarity_forward(const simnets_sim_desc* d,
                                            const void* x, const void* templates, const void* weights,
                                            void* y, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Status words of a Similarity workspace after simnets_similarity_forward used it, copied to host_out[0..1] as
+ * simnets_mex_workspace_status does.  host_out[0] is always 0; host_out[1] != 0: the tensor-core kernel of
+ * SIMNETS_FLAG_SIM_L2_TENSORCORE gave up on a bounded wait between its roles and the term-by-term kernel launched
+ * behind it recomputed the output (valid, only slow).  No counterpart in the reference. */
+SIMNETS_API int simnets_similarity_workspace_status(const void* workspace, void* stream, int32_t* host_out);
 
 /* dL/dinput.  Replaces SimilarityInputGradKernelGPU (src/kernels/similarity_grad_kernel_gpu.cu:155-269),
  * oracle SimilarityInputGradKernelCPU (src/kernels/similarity_grad_kernel_cpu.cpp:158-270). */

@@ -75,7 +75,7 @@ int simnets_similarity_forward(const simnets_sim_desc* d, const void* x, const v
     const bool f64 = d->dtype == SIMNETS_F64;
     if (sim_use_tiled(g, f64, d->flags)) {
         if (!ws || ws_bytes < sim_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;
-        return from_cuda(launch_sim_fwd_tiled(g, (const float*)x, (const float*)t, (const float*)w, (float*)y, ws, as_stream(stream)));
+        return from_cuda(launch_sim_fwd_tiled(g, (const float*)x, (const float*)t, (const float*)w, (float*)y, ws, d->flags, as_stream(stream)));
     }
     return from_cuda(launch_sim_fwd_direct(g, f64, x, t, w, y, as_stream(stream)));
 }
@@ -169,6 +169,11 @@ int simnets_mex_forward(const simnets_mex_desc* d, const void* x, const void* of
         return from_cuda(launch_mex_fwd_tiled(g, (const float*)x, (const float*)off, (float*)y, ws, d->flags, as_stream(stream)));
     }
     return from_cuda(launch_mex_fwd_direct(g, f64, x, off, y, as_stream(stream)));
+}
+
+int simnets_similarity_workspace_status(const void* ws, void* stream, int32_t* host_out) {
+    if (!ws || !host_out) return SIMNETS_E_NULL;
+    return from_cuda(cudaMemcpyAsync(host_out, ws, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, as_stream(stream)));
 }
 
 int simnets_mex_workspace_status(const void* ws, void* stream, int32_t* host_out) {

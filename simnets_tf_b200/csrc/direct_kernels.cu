@@ -44,7 +44,8 @@ __device__ __forceinline__ T block_sum(T v, T* smem) {
 // ------------------------------------------------------------------ Similarity
 template <typename T>
 __global__ void __launch_bounds__(kThreads) sim_fwd_direct(SimGeo g, const T* __restrict__ x, const T* __restrict__ tm,
-                                                           const T* __restrict__ wt, T* __restrict__ y) {
+                                                           const T* __restrict__ wt, T* __restrict__ y, const int* __restrict__ gate) {
+    if (gate && gate[1] == 0) return;
     const long long total = (long long)g.B * g.M * g.N;
     const T oob = T(g.oob), fudge = T(g.fudge);
     for (long long idx = blockIdx.x * (long long)kThreads + threadIdx.x; idx < total; idx += (long long)gridDim.x * kThreads) {
@@ -280,12 +281,13 @@ inline int grid_for(long long total, bool gated = false) {
 
 #define SIMNETS_DTYPE_SWITCH(is_f64, CALL32, CALL64) do { if (is_f64) { CALL64; } else { CALL32; } } while (0)
 
-cudaError_t launch_sim_fwd_direct(const SimGeo& g, bool f64, const void* x, const void* t, const void* w, void* y, cudaStream_t s) {
+cudaError_t launch_sim_fwd_direct(const SimGeo& g, bool f64, const void* x, const void* t, const void* w, void* y, cudaStream_t s,
+                                  const int* gate) {
     const long long total = (long long)g.B * g.M * g.N;
     if (total == 0) return cudaSuccess;
     SIMNETS_DTYPE_SWITCH(f64,
-        (sim_fwd_direct<float><<<grid_for(total), kThreads, 0, s>>>(g, (const float*)x, (const float*)t, (const float*)w, (float*)y)),
-        (sim_fwd_direct<double><<<grid_for(total), kThreads, 0, s>>>(g, (const double*)x, (const double*)t, (const double*)w, (double*)y)));
+        (sim_fwd_direct<float><<<grid_for(total), kThreads, 0, s>>>(g, (const float*)x, (const float*)t, (const float*)w, (float*)y, gate)),
+        (sim_fwd_direct<double><<<grid_for(total), kThreads, 0, s>>>(g, (const double*)x, (const double*)t, (const double*)w, (double*)y, gate)));
     count_launch();
     return cudaGetLastError();
 }

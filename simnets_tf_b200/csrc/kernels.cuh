@@ -20,7 +20,9 @@ cudaError_t launch_fp32_probe(bool packed, int blocks, int iters, float* out, cu
 cudaError_t launch_sum_pool2(long long planes, int H, int W, const float* x, float* y, cudaStream_t);
 
 // direct_kernels.cu -- any shape, float32 and float64
-cudaError_t launch_sim_fwd_direct(const SimGeo&, bool f64, const void* x, const void* t, const void* w, void* y, cudaStream_t);
+// gate: when given, the kernel runs only if gate[1] is non-zero (the redo behind the tensor-core forward kernel)
+cudaError_t launch_sim_fwd_direct(const SimGeo&, bool f64, const void* x, const void* t, const void* w, void* y, cudaStream_t,
+                                  const int* gate = nullptr);
 cudaError_t launch_sim_dx_direct(const SimGeo&, bool f64, const void* x, const void* t, const void* w, const void* dy, void* dx, cudaStream_t);
 cudaError_t launch_sim_dparams_direct(const SimGeo&, bool f64, const void* x, const void* t, const void* w, const void* dy,
                                       void* dt, void* dw, bool accumulate, cudaStream_t);
@@ -37,7 +39,11 @@ namespace simnets {
 // tiled_*.cu -- float32 generalized-GEMM tile kernels for the hot shapes
 bool sim_use_tiled(const SimGeo&, bool f64, uint32_t flags);
 size_t sim_workspace_bytes(const SimGeo&, bool f64, uint32_t flags);
-cudaError_t launch_sim_fwd_tiled(const SimGeo&, const float* x, const float* t, const float* w, float* y, void* ws, cudaStream_t);
+cudaError_t launch_sim_fwd_tiled(const SimGeo&, const float* x, const float* t, const float* w, float* y, void* ws, uint32_t flags, cudaStream_t);
+bool sim_tc_shape(const SimGeo&, uint32_t flags);
+size_t sim_tc_tile_floats(const SimGeo&);
+cudaError_t launch_sim_fwd_tc(const SimGeo&, const float* x, const float* planes, const float* cm, const int2* taps, float* tiles,
+                              float* bias, int* flag, float* y, cudaStream_t);
 cudaError_t launch_sim_dx_tiled(const SimGeo&, const float* x, const float* t, const float* w, const float* dy, float* dx, void* ws, cudaStream_t);
 cudaError_t launch_sim_dparams_tiled(const SimGeo&, const float* x, const float* t, const float* w, const float* dy,
                                      float* dt, float* dw, bool accumulate, void* ws, cudaStream_t);

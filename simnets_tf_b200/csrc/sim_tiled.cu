@@ -22,11 +22,14 @@ constexpr double kLog2Pi = 1.8378770664093454835606594728112;
 constexpr int kDpTile = 64, kDpKC = 32;
 
 struct SimWs {
+    int* flag;       // [2]: word 1 = a bounded wait of the tensor-core forward kernel ran out (its output is redone)
     float* planes;   // [3][K][Mp]: t, scale (-w or -0.5w), per-term constant; Mp = M rounded up to 4 floats
     float* cm;       // [M] per-instance constant added once per output
     int2* taps;      // [K]: {offset of tap inside a sample, (kh << 16) | kw}
     float* part;     // [S][3][M][K] split partial sums of the parameter gradients
     float* dxp;      // [2][bh*bw*M][Cp]: t and s*w (s = 2 for plain L2, else 1), channel-contiguous, for the input gradient
+    float* tc_tiles; // pre-split parameter tiles of the tensor-core forward kernel
+    float* tc_bias;  // [M] its per-instance constant
     size_t bytes;
 };
 
@@ -58,11 +61,14 @@ __host__ SimWs carve(const SimGeo& g, void* base) {
     char* p = static_cast<char*>(base);
     size_t off = 0;
     auto take = [&](size_t bytes) { char* r = p ? p + off : nullptr; off += align256(bytes); return r; };
+    w.flag = reinterpret_cast<int*>(take(sizeof(int) * 2));
     w.planes = reinterpret_cast<float*>(take(sizeof(float) * 3 * (size_t)g.K * pad4(g.M)));
     w.cm = reinterpret_cast<float*>(take(sizeof(float) * g.M));
     w.taps = reinterpret_cast<int2*>(take(sizeof(int2) * g.K));
     w.part = reinterpret_cast<float*>(take(sizeof(float) * 3 * (size_t)dp_splits(g) * g.M * g.K));
     w.dxp = reinterpret_cast<float*>(take(sizeof(float) * 2 * (size_t)g.bh * g.bw * g.M * pad4(g.C)));
+    w.tc_tiles = reinterpret_cast<float*>(take(sizeof(float) * sim_tc_tile_floats(g)));
+    w.tc_bias = reinterpret_cast<float*>(take(sizeof(float) * g.M));
     w.bytes = off;
     return w;
 }
@@ -70,9 +76,10 @@ __host__ SimWs carve(const SimGeo& g, void* base) {
 // One block per instance m: tap-major parameter planes, the per-instance constant, and (block 0) the tap table.
 __global__ void __launch_bounds__(128) sim_prep(SimGeo g, const float* __restrict__ tm, const float* __restrict__ wt,
                                                 float* __restrict__ planes, float* __restrict__ cm, int2* __restrict__ taps,
-                                                float* __restrict__ dxp) {
+                                                float* __restrict__ dxp, int* __restrict__ flag) {
     __shared__ float red[128];
     const int m = blockIdx.x;
+    if (m == 0 && threadIdx.x < 2) flag[threadIdx.x] = 0;
     const float fudge = float(g.fudge);
     const int ldm = pad4(g.M);
     const size_t plane = (size_t)g.K * ldm;
@@ -515,7 +522,7 @@ __global__ void __launch_bounds__(512) sim_dparams_reduce(SimGeo g, int splits, 
 }
 
 void launch_prep(const SimGeo& g, const SimWs& w, const float* t, const float* wt, cudaStream_t s) {
-    sim_prep<<<g.M, 128, 0, s>>>(g, t, wt, w.planes, w.cm, w.taps, w.dxp);
+    sim_prep<<<g.M, 128, 0, s>>>(g, t, wt, w.planes, w.cm, w.taps, w.dxp, w.flag);
     count_launch();
 }
 
@@ -533,9 +540,17 @@ size_t sim_workspace_bytes(const SimGeo& g, bool f64, uint32_t flags) {
     return carve(g, nullptr).bytes;
 }
 
-cudaError_t launch_sim_fwd_tiled(const SimGeo& g, const float* x, const float* t, const float* w, float* y, void* ws, cudaStream_t s) {
+cudaError_t launch_sim_fwd_tiled(const SimGeo& g, const float* x, const float* t, const float* w, float* y, void* ws, uint32_t flags,
+                                 cudaStream_t s) {
     const SimWs W = carve(g, ws);
     launch_prep(g, W, t, w, s);
+    if (sim_tc_shape(g, flags)) {
+        // opt-in: the expanded square on the tensor cores; behind it the term-by-term kernel, which runs only if a
+        // bounded wait of the tensor-core kernel ran out (word 1 of the flags)
+        const cudaError_t e = launch_sim_fwd_tc(g, x, W.planes, W.cm, W.taps, W.tc_tiles, W.tc_bias, W.flag, y, s);
+        if (e != cudaSuccess) return e;
+        return launch_sim_fwd_direct(g, false, x, t, w, y, s, W.flag);
+    }
     if (sim_smallk_shape(g)) return launch_sim_fwd_smallk(g, x, W.planes, W.cm, W.taps, y, s);
     const long long P = (long long)g.B * g.N;
     const bool wide = g.M > 64;

@@ -28,6 +28,7 @@ LAYERS = {
     "cfg4_sim": ("sim", (64, 32, 32), 256, dict(similarity_function="L2", blocks=[3, 3], strides=[1, 1], padding=[1, 1],
                                                 normalization_term=True, ignore_nan_input=True, out_of_bounds_value=0.0), 256, 0.2),
     "cfg4_sim_l1": ("sim", (64, 32, 32), 256, dict(similarity_function="L1", blocks=[3, 3], strides=[1, 1], padding=[1, 1]), 256, 0.0),
+    "cfg4_sim_l2": ("sim", (64, 32, 32), 256, dict(similarity_function="L2", blocks=[3, 3], strides=[1, 1], padding=[1, 1]), 256, 0.0),
     "cfg5_sim": ("sim", (3, 32, 32), 64, dict(similarity_function="L2", blocks=[3, 3], strides=[1, 1], padding=[1, 1]), 2048, 0.0),
     "cfg2_mex": ("mex", (32, 16, 16), 64, dict(blocks=[32, 1, 1], strides=[32, 1, 1], softmax_mode=True, unshared_offset_region=[2]), 64, 0.0),
     "cfg4_mex": ("mex", (256, 32, 32), 256, dict(blocks=[4, 2, 2], strides=[4, 2, 2], epsilon=0.5, softmax_mode=True,

@@ -106,3 +106,50 @@ def test_full_size_properties():
     dx12 = sim_ops.similarity_input_grad(x, t, w, 3 * dy1, **attrs)
     assert (dx1[torch.isnan(x)] == 0).all()
     assert cases.rel_err((3 * dx1).cpu().numpy(), dx12.cpu().numpy()) < 1e-5
+
+
+# ---- opt-in tensor-core evaluation of L2 (SIMNETS_FLAG_SIM_L2_TENSORCORE): tolerance 1e-3 of the largest output magnitude
+SIM_TC = [
+    cases.sim_case("tc_cfg5_layer", (8, 3, 32, 32), 64, "L2", (3, 3), (1, 1), (1, 1), seed=601, x_dist="uniform"),
+    cases.sim_case("tc_cfg4_style", (2, 64, 32, 32), 256, "L2", (3, 3), (1, 1), (1, 1), seed=602),
+    cases.sim_case("tc_norm_stride2", (3, 5, 13, 11), 70, "L2", (3, 2), (2, 2), (1, 0), norm=True, seed=603),
+    cases.sim_case("tc_few_instances_oob", (5, 2, 9, 9), 5, "L2", (2, 2), (1, 1), (1, 1), oob=0.7, seed=604),
+    cases.sim_case("tc_ragged_tile", (1, 7, 20, 19), 130, "L2", (1, 1), (1, 1), (0, 0), norm=True, seed=605),
+]
+
+
+@pytest.mark.parametrize("c", SIM_TC, ids=lambda c: c["name"])
+def test_tensor_core_l2_forward_within_its_stated_tolerance(port, cuda_lib, c):
+    import ctypes as C
+    d = cases.sim_desc(c)
+    x, t, w, dy = cases.sim_inputs(c, port.sim_out_shape(d))
+    xd, td, wd = (gpu_util.dev(a) for a in (x, t, w))
+    attrs = cases.sim_attrs(c)
+    ref = port.similarity_forward(d, x, t, w)
+    y = sim_ops.similarity_forward(xd, td, wd, flags=abi.FLAG_SIM_L2_TENSORCORE, **attrs).cpu().numpy()
+    err = cases.assert_parity(y, ref, tol=1e-3, what=c["name"] + " y (tensor cores)")
+    print(c["name"], "tensor-core L2 relative error", err)
+    # through the C ABI once more, to read the status words: no bounded wait ran out, nothing was redone
+    dd = cases.sim_desc(c, flags=abi.FLAG_SIM_L2_TENSORCORE)
+    n = cuda_lib.simnets_similarity_workspace_bytes(C.byref(dd))
+    ws = torch.empty(n, dtype=torch.uint8, device="cuda")
+    y2 = torch.empty(ref.shape, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert cuda_lib.simnets_similarity_forward(C.byref(dd), xd.data_ptr(), td.data_ptr(), wd.data_ptr(), y2.data_ptr(), ws.data_ptr(), n, stream) == 0
+    status = (C.c_int32 * 2)(7, 7)
+    assert cuda_lib.simnets_similarity_workspace_status(ws.data_ptr(), stream, status) == 0
+    torch.cuda.synchronize()
+    assert list(status) == [0, 0]
+    assert np.array_equal(y2.cpu().numpy(), y)
+
+
+def test_tensor_core_flag_is_ignored_where_the_expansion_does_not_apply(port):
+    """L1, and L2 with ignore_nan_input, keep their term-by-term kernels: same bits with and without the flag."""
+    for name in ("l1_stride2", "params_norm_nan"):
+        c = next(c for c in cases.SIM_SMALL if c["name"] == name)
+        d = cases.sim_desc(c)
+        x, t, w, dy = cases.sim_inputs(c, port.sim_out_shape(d))
+        xd, td, wd = (gpu_util.dev(a) for a in (x, t, w))
+        a = sim_ops.similarity_forward(xd, td, wd, flags=c["flags"], **cases.sim_attrs(c)).cpu().numpy()
+        b = sim_ops.similarity_forward(xd, td, wd, flags=c["flags"] | abi.FLAG_SIM_L2_TENSORCORE, **cases.sim_attrs(c)).cpu().numpy()
+        assert np.array_equal(a, b, equal_nan=True)
