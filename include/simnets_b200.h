@@ -89,6 +89,12 @@ enum { SIMNETS_SIM_L1 = 0, SIMNETS_SIM_L2 = 1 };
  * gradients always use the term-by-term kernels. */
 #define SIMNETS_FLAG_SIM_L2_TENSORCORE (1u << 11)
 
+/* Similarity entry points: `weights` holds raw values and the op works on their absolute value, as the reference's
+ * Keras layer feeds K.abs(weights) to the op (python/simnets/keras.py:65); simnets_similarity_params_grad then returns
+ * the gradient with respect to the raw values, sign(weights) * dL/d|weights| (0 where a weight is 0).  Saves the
+ * separate abs, sign and multiply passes over the weights. */
+#define SIMNETS_FLAG_SIM_ABS_WEIGHTS   (1u << 12)
+
 /* MEX gradient entry points only: dy is given at half resolution, dy[batch, M * channels_out, height_out / 2,
  * width_out / 2], each value standing for the 2x2 window of output positions that a 2x2 / stride-2 sum pooling
  * added up (the gradient of such a pooling copies its dy to the four inputs; with this flag the copy is never
@@ -305,6 +311,20 @@ SIMNETS_API int64_t simnets_fp32_fma_probe(int32_t packed, int32_t iters, void* 
  * (SIMNETS_FLAG_MEX_DY_POOLED2). */
 SIMNETS_API int simnets_sum_pool2x2_forward(int64_t planes, int32_t height, int32_t width,
                                             const void* x, void* y, void* stream);
+
+/* ---- softmax cross-entropy -------------------------------------------------- */
+/* The loss of the reference's example networks (README.md:108-111: softmax + categorical cross-entropy, in TensorFlow
+ * a chain of softmax / log / multiply / reduce kernels and their gradients) and its gradient in one launch:
+ *   loss[0]             = scale * sum_b (logsumexp(logits[b, :]) - logits[b, labels[b]])
+ *   dlogits[b, c]       = scale * (softmax(logits[b, :])[c] - (c == labels[b]))         (dlogits may be NULL)
+ * logits, dlogits: float32 [batch, classes] on the device; labels: int64 [batch] on the device (a label outside
+ * [0, classes) contributes neither loss nor gradient); loss: one float32 on the device.  scale = 1 / global batch
+ * gives the mean over a data-parallel job's whole batch.  The sum over the batch is taken in a fixed order.
+ * No counterpart in the reference's own sources. */
+SIMNETS_API size_t simnets_softmax_cross_entropy_workspace_bytes(int32_t batch);
+SIMNETS_API int simnets_softmax_cross_entropy(int32_t batch, int32_t classes, float scale,
+                                              const float* logits, const int64_t* labels, float* loss, float* dlogits,
+                                              void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- normalize_offsets ------------------------------------------------------ */
 /* The `normalize_offsets` option of the reference's Keras Mex layer (python/simnets/keras.py:155-160): each of the

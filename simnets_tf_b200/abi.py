@@ -21,6 +21,7 @@ FLAG_MEX_WORKSPACE_PRIMED = 1 << 8
 FLAG_MEX_NO_PAIR_TILES = 1 << 9
 FLAG_MEX_TEST_EXPIRE_WAIT = 1 << 10
 FLAG_SIM_L2_TENSORCORE = 1 << 11
+FLAG_SIM_ABS_WEIGHTS = 1 << 12
 
 OK = 0
 E_NULL, E_DESC, E_DTYPE, E_WORKSPACE, E_UNSUPPORTED, E_TOO_LARGE = -1, -2, -3, -4, -5, -6

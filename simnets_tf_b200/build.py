@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 ROOT = os.path.dirname(HERE)
 LIB = os.path.join(HERE, "libsimnets_b200.so")
-SOURCES = ["api.cu", "host_dims.cpp", "direct_kernels.cu", "mex_tiled.cu", "mex_smallm.cu", "mex_smallk.cu", "mex_tc.cu", "mex_tc_ws.cu", "mex_tc_pair.cu", "sim_tiled.cu", "sim_smallk.cu", "sim_tc.cu", "pool.cu", "probe.cu", "offsets_norm.cu"]
+SOURCES = ["api.cu", "host_dims.cpp", "direct_kernels.cu", "mex_tiled.cu", "mex_smallm.cu", "mex_smallk.cu", "mex_tc.cu", "mex_tc_ws.cu", "mex_tc_pair.cu", "sim_tiled.cu", "sim_smallk.cu", "sim_tc.cu", "pool.cu", "loss.cu", "probe.cu", "offsets_norm.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

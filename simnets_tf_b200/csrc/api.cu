@@ -171,6 +171,17 @@ int simnets_mex_forward(const simnets_mex_desc* d, const void* x, const void* of
     return from_cuda(launch_mex_fwd_direct(g, f64, x, off, y, as_stream(stream)));
 }
 
+size_t simnets_softmax_cross_entropy_workspace_bytes(int32_t batch) { return softmax_xent_workspace_bytes(batch < 0 ? 0 : batch); }
+
+int simnets_softmax_cross_entropy(int32_t batch, int32_t classes, float scale, const float* logits, const int64_t* labels, float* loss,
+                                  float* dlogits, void* ws, size_t ws_bytes, void* stream) {
+    if (batch < 0 || classes < 1) return SIMNETS_E_DESC;
+    if (!loss || (batch > 0 && (!logits || !labels))) return SIMNETS_E_NULL;
+    if (!ws || ws_bytes < softmax_xent_workspace_bytes(batch)) return SIMNETS_E_WORKSPACE;
+    return from_cuda(launch_softmax_xent(batch, classes, scale, logits, reinterpret_cast<const long long*>(labels), loss, dlogits, ws,
+                                         as_stream(stream)));
+}
+
 int simnets_similarity_workspace_status(const void* ws, void* stream, int32_t* host_out) {
     if (!ws || !host_out) return SIMNETS_E_NULL;
     return from_cuda(cudaMemcpyAsync(host_out, ws, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, as_stream(stream)));

@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(kThreads) sim_fwd_direct(SimGeo g, const T* __
                 for (int kw = 0; kw < g.bw; ++kw, ++k) {
                     const int hh = ho * g.sh - g.ph + kh, ww = wo * g.sw - g.pw + kw;
                     const T v = (hh >= 0 && hh < g.H && ww >= 0 && ww < g.W) ? xs[((size_t)c * g.H + hh) * g.W + ww] : oob;
-                    const T t = tp[k], w = wp[k], d = t - v;
+                    const T t = tp[k], w = g.absw ? dev_abs(wp[k]) : wp[k], d = t - v;
                     switch (g.mode) {
                     case SIM_L1: sum += -w * dev_abs(d); break;
                     case SIM_L1_SKIP: if (!is_nan(v)) sum += -w * dev_abs(d); break;
@@ -107,7 +107,8 @@ __global__ void __launch_bounds__(kThreads) sim_dx_direct(SimGeo g, const T* __r
                 const int j = ho * g.ow + wo;
                 T sum = T(0);
                 for (int m = 0; m < g.M; ++m) {
-                    const T t = tm[(size_t)m * g.K + k], w = wt[(size_t)m * g.K + k], err = g_n[(size_t)m * g.N + j];
+                    const T wr = wt[(size_t)m * g.K + k];
+                    const T t = tm[(size_t)m * g.K + k], w = g.absw ? dev_abs(wr) : wr, err = g_n[(size_t)m * g.N + j];
                     switch (g.mode) {
                     case SIM_L1: sum += err * w * sign_of(t - v); break;
                     case SIM_L1_SKIP: if (!is_nan(v)) sum += err * w * sign_of(t - v); break;
@@ -132,7 +133,8 @@ __global__ void __launch_bounds__(kThreads) sim_dparams_direct(SimGeo g, const T
     const int mk = blockIdx.x;
     const int m = mk / g.K, k = mk % g.K;
     const int kw = k % g.bw, kh = (k / g.bw) % g.bh, c = k / (g.bw * g.bh);
-    const T t = tm[mk], w = wt[mk], oob = T(g.oob), fudge = T(g.fudge);
+    const T wraw = wt[mk];
+    const T t = tm[mk], w = g.absw ? dev_abs(wraw) : wraw, oob = T(g.oob), fudge = T(g.fudge);
     T st = T(0), sw_ = T(0);
     const long long total = (long long)g.B * g.N;
     for (long long i = threadIdx.x; i < total; i += kThreads) {
@@ -151,7 +153,8 @@ __global__ void __launch_bounds__(kThreads) sim_dparams_direct(SimGeo g, const T
         }
     }
     const T rt = block_sum(st, smem);
-    const T rw = block_sum(sw_, smem);
+    T rw = block_sum(sw_, smem);
+    if (g.absw) rw *= sign_of(wraw);                   // d|w|/dw, 0 at w = 0
     if (threadIdx.x == 0) {
         dt[mk] = accumulate ? dt[mk] + rt : rt;
         dw[mk] = accumulate ? dw[mk] + rw : rw;

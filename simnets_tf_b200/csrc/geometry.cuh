@@ -17,6 +17,7 @@ struct SimGeo {
     int K, N;              // K = C*bh*bw taps per patch, N = oh*ow positions per sample
     int mode;              // SimMode
     int batch_quirk;       // add the L2N constant (B - n) times to sample n
+    int absw;              // the weights tensor holds raw values: the op uses |w| and returns dL/dw_raw = sign(w_raw) dL/d|w|
     double fudge, oob;
 };
 

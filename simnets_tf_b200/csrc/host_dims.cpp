@@ -45,6 +45,7 @@ int sim_geometry(const simnets_sim_desc* d, SimGeo* g) {
     g->K = int(K); g->N = int(N);
     g->mode = l1 ? (l1_skip ? SIM_L1_SKIP : SIM_L1) : (!d->normalization_term ? SIM_L2 : (d->ignore_nan_input ? SIM_L2N_NAN : SIM_L2N));
     g->batch_quirk = (d->flags & SIMNETS_FLAG_SIM_BATCH_CONST_QUIRK) != 0;
+    g->absw = (d->flags & SIMNETS_FLAG_SIM_ABS_WEIGHTS) != 0;
     g->fudge = d->normalization_term_fudge;
     g->oob = d->out_of_bounds_value;
     return SIMNETS_OK;

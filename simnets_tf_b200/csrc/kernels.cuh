@@ -106,6 +106,10 @@ cudaError_t launch_mex_doff_pair(const MexGeo&, const float* x, const float* mo,
                                  float* part, int* splits_out, int* flag, cudaStream_t);
 // number of multiprocessors of the current device (148 when no device answers)
 int device_sm_count();
+
+size_t softmax_xent_workspace_bytes(int batch);
+cudaError_t launch_softmax_xent(int batch, int classes, float scale, const float* logits, const long long* labels, float* loss,
+                                float* dlogits, void* ws, cudaStream_t);
 // forward on the library's fixed device scratch; returns a status code of simnets_b200.h
 int launch_mex_fwd_static(const MexGeo&, const float* x, const float* off, float* y, uint32_t flags, cudaStream_t);
 cudaError_t launch_mex_dx_tiled(const MexGeo&, const float* x, const float* off, const float* y, const float* dy, float* dx,

@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(128) sim_prep(SimGeo g, const float* __restric
     const size_t plane = (size_t)g.K * ldm;
     float csum = 0.f;
     for (int k = threadIdx.x; k < g.K; k += 128) {
-        const float t = tm[(size_t)m * g.K + k], w = wt[(size_t)m * g.K + k];
+        const float t = tm[(size_t)m * g.K + k], w = g.absw ? fabsf(wt[(size_t)m * g.K + k]) : wt[(size_t)m * g.K + k];
         float scale = -w, c = 0.f;
         if (g.mode == SIM_L2N) { scale = -0.5f * w; csum += 0.5f * logf(w + fudge); }
         if (g.mode == SIM_L2N_NAN) { scale = -0.5f * w; c = float(0.5 * (double(logf(w + fudge)) - kLog2Pi)); }
@@ -509,11 +509,12 @@ __global__ void __launch_bounds__(512) sim_dparams_reduce(SimGeo g, int splits, 
         if (slice == 0 && i < mk) {
 #pragma unroll 8
             for (int q = 1; q < 64; ++q) { a += red[0][q][lane]; b += red[1][q][lane]; c += red[2][q][lane]; }
-            const float w = wt[i];
+            const float wraw = wt[i], w = g.absw ? fabsf(wraw) : wraw;
             float gt, gw;
             if (g.mode == SIM_L1 || g.mode == SIM_L1_SKIP) { gt = w * a; gw = -b; }
             else if (g.mode == SIM_L2) { gt = 2.f * w * a; gw = -b; }
             else { gt = w * a; gw = 0.5f * (c / (w + fudge) - b); }
+            if (g.absw) gw *= wraw > 0.f ? 1.f : (wraw < 0.f ? -1.f : 0.f);          // d|w|/dw, 0 at w = 0
             dt[i] = accumulate ? dt[i] + gt : gt;
             dw[i] = accumulate ? dw[i] + gw : gw;
         }

@@ -16,7 +16,7 @@ from . import _lib, abi
 from .ops.mex import _expand_dim_specification, _mex_dims_helper
 from .ops.mex import mex as _mex
 from .ops.mex import mex_sum_pool2 as _mex_sum_pool2
-from .ops.similarity import similarity as _similarity
+from .ops.similarity import similarity_of_raw_weights as _similarity_of_raw_weights
 
 
 def _init_tensor(spec, shape, device, dtype, generator=None):
@@ -89,11 +89,12 @@ class Similarity(torch.nn.Module):
             self.build(tuple(x.shape), x.device, x.dtype)
         if self.channels_last:
             x = x.permute(0, 3, 1, 2)
-        y = _similarity(x, self.templates, torch.abs(self.sweights), similarity_function=self.similarity_function,
-                        blocks=self.blocks, strides=self.strides, padding=self.padding,
-                        normalization_term=self.normalization_term,
-                        normalization_term_fudge=self.normalization_term_fudge,
-                        ignore_nan_input=self.ignore_nan_input, out_of_bounds_value=self.out_of_bounds_value)
+        # |weights| and its gradient are taken inside the op's kernels
+        y = _similarity_of_raw_weights(x, self.templates, self.sweights, similarity_function=self.similarity_function,
+                                       blocks=self.blocks, strides=self.strides, padding=self.padding,
+                                       normalization_term=self.normalization_term,
+                                       normalization_term_fudge=self.normalization_term_fudge,
+                                       ignore_nan_input=self.ignore_nan_input, out_of_bounds_value=self.out_of_bounds_value)
         return y.permute(0, 2, 3, 1) if self.channels_last else y
 
     def get_config(self):

@@ -110,20 +110,20 @@ def similarity_parameters_grad(input, templates, weights, output_grad, flags=0, 
 
 class _Similarity(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, input, templates, weights, attrs):
-        ctx.attrs = attrs
+    def forward(ctx, input, templates, weights, attrs, flags=0):
+        ctx.attrs, ctx.flags = attrs, flags
         ctx.save_for_backward(input, templates, weights)
-        return similarity_forward(input, templates, weights, **attrs)
+        return similarity_forward(input, templates, weights, flags=flags, **attrs)
 
     @staticmethod
     def backward(ctx, grad):
         input, templates, weights = ctx.saved_tensors
         gi = gt = gw = None
         if ctx.needs_input_grad[0]:
-            gi = similarity_input_grad(input, templates, weights, grad, **ctx.attrs)
+            gi = similarity_input_grad(input, templates, weights, grad, flags=ctx.flags, **ctx.attrs)
         if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
-            gt, gw = similarity_parameters_grad(input, templates, weights, grad, **ctx.attrs)
-        return gi, gt, gw, None
+            gt, gw = similarity_parameters_grad(input, templates, weights, grad, flags=ctx.flags, **ctx.attrs)
+        return gi, gt, gw, None, None
 
 
 def similarity(input, templates, weights, similarity_function=None, blocks=None, strides=None, padding=None,
@@ -141,3 +141,10 @@ def similarity(input, templates, weights, similarity_function=None, blocks=None,
                    normalization_term=normalization_term, normalization_term_fudge=normalization_term_fudge,
                    ignore_nan_input=ignore_nan_input, out_of_bounds_value=out_of_bounds_value)
     return _Similarity.apply(input, templates, weights, attrs)
+
+
+def similarity_of_raw_weights(input, templates, raw_weights, flags=0, **attrs):
+    """`similarity(input, templates, abs(raw_weights), ...)`, differentiable w.r.t. all three tensors, with the absolute
+    value and its gradient taken inside the library's kernels (abi.FLAG_SIM_ABS_WEIGHTS): what the reference's Keras
+    layer computes with `K.abs(self.sweights)` in front of the op (python/simnets/keras.py:65)."""
+    return _Similarity.apply(input, templates, raw_weights, _attrs(**attrs), flags | abi.FLAG_SIM_ABS_WEIGHTS)

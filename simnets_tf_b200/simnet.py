@@ -16,6 +16,7 @@ import torch
 import torch.nn.functional as F
 
 from . import keras as layers
+from .ops.loss import softmax_cross_entropy
 
 
 from .netspec import SPECS  # noqa: F401
@@ -115,8 +116,10 @@ class SimNet(torch.nn.Module):
         return x
 
     def loss_of_logits(self, logits, labels, global_batch=None):
-        total = F.cross_entropy(logits, labels, reduction="sum")
-        return total / float(global_batch if global_batch else logits.shape[0])
+        n = float(global_batch if global_batch else logits.shape[0])
+        if logits.is_cuda and logits.dtype == torch.float32 and labels.dtype == torch.int64:
+            return softmax_cross_entropy(logits, labels, 1.0 / n)       # loss and gradient in one library launch
+        return F.cross_entropy(logits, labels, reduction="sum") / n
 
     def loss(self, x, labels, global_batch=None):
         """Softmax cross-entropy summed over this shard and divided by the global batch."""
