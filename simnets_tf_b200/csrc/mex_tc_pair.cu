@@ -261,9 +261,9 @@ __device__ __forceinline__ float tf32_lo(float v) { return v - __uint_as_float(_
 __device__ __forceinline__ void store_split8(unsigned char* a_hi, unsigned char* a_lo, int row, int k0, const float (&e)[8]) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        float4 hi, lo;
-        split_tf32_trunc(e[4 * h], hi.x, lo.x); split_tf32_trunc(e[4 * h + 1], hi.y, lo.y);
-        split_tf32_trunc(e[4 * h + 2], hi.z, lo.z); split_tf32_trunc(e[4 * h + 3], hi.w, lo.w);
+        // hi plane: the values themselves (the tensor core reads their top 19 bits); lo plane: what that drops
+        const float4 hi = make_float4(e[4 * h], e[4 * h + 1], e[4 * h + 2], e[4 * h + 3]);
+        const float4 lo = make_float4(tf32_lo(hi.x), tf32_lo(hi.y), tf32_lo(hi.z), tf32_lo(hi.w));
         const int off = core_offset(row, k0 + 4 * h);
         *reinterpret_cast<float4*>(a_hi + off) = hi;
         *reinterpret_cast<float4*>(a_lo + off) = lo;
@@ -433,7 +433,9 @@ constexpr int kDxRawWarps = 4;
 constexpr int kDxFirstRawWarp = kPairLoaderWarp + 1;
 constexpr int kDxThreads = (kDxFirstRawWarp + kDxRawWarps) * 32;      // 704
 // a slot: y as [16 instances][128 rows] float2, then dy likewise, or as [16][128] float when dy is given pooled (one value per pair)
-template <bool POOLED> __host__ __device__ constexpr int dx_slot_bytes() { return kTcKT * kTcPos * (POOLED ? 12 : 16); }
+// y and dy of 16 instances x 128 pixel pairs, then the offset maxima of those instances in both regions (2 x 16 floats)
+template <bool POOLED> __host__ __device__ constexpr int dx_mo_off() { return kTcKT * kTcPos * (POOLED ? 12 : 16); }
+template <bool POOLED> __host__ __device__ constexpr int dx_slot_bytes() { return dx_mo_off<POOLED>() + 2 * kTcKT * 4; }
 template <bool POOLED> __host__ __device__ constexpr int dx_depth() { return POOLED ? 3 : 2; }      // slots: all but one can be in flight
 
 __device__ __forceinline__ void async_arrive_noinc(uint64_t* bar) {   // arrives once this thread's earlier asynchronous copies have landed
@@ -483,7 +485,6 @@ __global__ void __launch_bounds__(kDxThreads, 1) mex_dx_pair(MexGeo g, const flo
         for (int li = 0; li < my_items && !sh.failed; ++li) {
             const WsItem it = ws_item(plan, int(blockIdx.x) + li * int(gridDim.x));
             const PairColumn col = pair_column_of(g, it.r, (long long)it.jt * kTcPos + prow, P, mx);
-            const float* mor0 = mo + (2 * it.r) * M + mhalf * 8;              // offset maxima (same address in every lane)
             bool ok = true;
             for (int c = 0; c < mchunks; ++c) {
                 const int mleft = col.base >= 0 ? M - c * kTcKT - mhalf * 8 : 0;     // a dead row contributes nothing
@@ -491,6 +492,11 @@ __global__ void __launch_bounds__(kDxThreads, 1) mex_dx_pair(MexGeo g, const flo
                 const float2* ry = reinterpret_cast<const float2*>(rawbase + slot.stage * kDxSlotBytes) + (mhalf * 8) * kTcPos + prow;
                 const float2* rg = ry + kTcKT * kTcPos;                                   // dy as pairs
                 const float* rgp = reinterpret_cast<const float*>(rawbase + slot.stage * kDxSlotBytes + kTcKT * kTcPos * 8) + (mhalf * 8) * kTcPos + prow;   // dy pooled
+                // the offset maxima of this thread's 8 instances in both regions (same addresses in every lane: broadcasts)
+                const float4* ms = reinterpret_cast<const float4*>(rawbase + slot.stage * kDxSlotBytes + dx_mo_off<POOLED>()) + mhalf * 2;
+                const float4 ma0 = ms[0], ma1 = ms[1], mb0 = ms[4], mb1 = ms[5];
+                const float mo0v[8] = {ma0.x, ma0.y, ma0.z, ma0.w, ma1.x, ma1.y, ma1.z, ma1.w};
+                const float mo1v[8] = {mb0.x, mb0.y, mb0.z, mb0.w, mb1.x, mb1.y, mb1.z, mb1.w};
                 float q0[8], q1[8];
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
@@ -499,9 +505,8 @@ __global__ void __launch_bounds__(kDxThreads, 1) mex_dx_pair(MexGeo g, const flo
                     float2 gv;
                     if (POOLED) { gv.x = rgp[u * kTcPos]; gv.y = gv.x; }
                     else gv = rg[u * kTcPos];
-                    const float m0v = in ? __ldg(mor0 + c * kTcKT + u) : 0.f, m1v = in ? __ldg(mor0 + M + c * kTcKT + u) : 0.f;
-                    q0[u] = in ? gv.x * ex2_ftz(fmaf(a, (col.mx0 - yv.x) + m0v, c2)) : 0.f;
-                    q1[u] = in ? gv.y * ex2_ftz(fmaf(a, (col.mx1 - yv.y) + m1v, c2)) : 0.f;
+                    q0[u] = in ? gv.x * ex2_ftz(fmaf(a, (col.mx0 - yv.x) + mo0v[u], c2)) : 0.f;
+                    q1[u] = in ? gv.y * ex2_ftz(fmaf(a, (col.mx1 - yv.y) + mo1v[u], c2)) : 0.f;
                 }
                 mbar_arrive(&raw_empty[slot.stage]);                          // the slot may be refilled
                 slot.advance(1);
@@ -569,6 +574,12 @@ __global__ void __launch_bounds__(kDxThreads, 1) mex_dx_pair(MexGeo g, const flo
                             else pair_async8(dstg + u * GP, in ? gp + u * Ngu : dy, in);
                         }
                     }
+                }
+                if (lt < 2 * kTcKT) {                                         // offset maxima of the stage's instances: region lt / 16, instance lt % 16
+                    const int mi = c * kTcKT + (lt & (kTcKT - 1));
+                    const bool in = mi < M;
+                    pair_async4(smem_u32(rawbase + slot.stage * kDxSlotBytes + dx_mo_off<POOLED>()) + lt * 4,
+                                in ? mo + (2 * it.r + (lt >> 4)) * M + mi : mo, in);
                 }
                 async_arrive_noinc(&raw_full[slot.stage]);
                 slot.advance(1);
@@ -639,7 +650,7 @@ __global__ void __launch_bounds__(kDxThreads, 1) mex_dx_pair(MexGeo g, const flo
 // the converters write the partial sums out at the end.
 constexpr int kDoLBO = 144;
 constexpr int kDoConvWarps = 16, kDoConv = kDoConvWarps * 32;                                    // 512 converters
-constexpr int kDoMmaWarp = kDoConvWarps, kDoFirstRawWarp = kDoMmaWarp + 1, kDoRawWarps = 4;
+constexpr int kDoMmaWarp = kDoConvWarps, kDoFirstRawWarp = kDoMmaWarp + 1, kDoRawWarps = 8;
 constexpr int kDoPairThreads = (kDoFirstRawWarp + kDoRawWarps) * 32;                             // 672
 constexpr int kDoStages = 2;
 
