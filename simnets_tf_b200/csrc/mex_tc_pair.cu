@@ -20,6 +20,9 @@
 // Every mbarrier wait is bounded and also gives up as soon as another role has failed: a wait that runs out raises the
 // CTA's failure flag, every role leaves its loop, copies in flight are waited for, tensor memory is freed and word 1
 // of the workspace flags reports it (the exact kernels launched behind then redo the work).
+#include <cstring>
+#include <cuda.h>          // CUtensorMap and the enums of cuTensorMapEncodeTiled (types only: the entry point is looked up at run time)
+
 #include "ws.cuh"
 
 namespace simnets {
@@ -663,7 +666,8 @@ struct DoCfg {
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
     static constexpr int QR = MT * 128, XR = NT;                                 // rows of y (and of dy) and of x in a slot
     static constexpr int G_OFF = QR * CP * 8, X_OFF = G_OFF + QR * CP * (POOLED ? 4 : 8), MX_OFF = X_OFF + XR * CP * 8;   // dy pooled: one float per pair
-    static constexpr int SLOT_BYTES = MX_OFF + CP * 8;
+    static constexpr int SLOT_DATA = MX_OFF + CP * 8;                             // bytes one chunk brings in
+    static constexpr int SLOT_BYTES = (SLOT_DATA + 127) & ~127;                   // slots start on 128-byte boundaries (tensor-map copies)
     static constexpr int SMEM = kDoStages * STAGE_BYTES + DEPTH * SLOT_BYTES;
     static constexpr int ROWSLOTS = kDoConv / CP;                                // 32 (CP = 16) or 64 (CP = 8) rows converted at once
     static constexpr int QROWS = QR / ROWSLOTS, XROWS = XR / ROWSLOTS;
@@ -683,11 +687,32 @@ struct DoPairShared {
 
 struct DoPairPlan { int units, mgroups, ktiles, splits; };
 
-template <int MT, int NT, int CP, bool POOLED, bool WIDE>
-__global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, const float* __restrict__ x, const float* __restrict__ mo,
+// Tensor maps of the offsets-gradient kernel's raw loader (LOAD == 2): y, dy, x and the per-position maxima seen as
+// (w, row parity class, row within the class, instance or channel, sample), so that the pixel pairs of one chunk -- a run
+// of one image row, or a few whole rows, of the region pair's rows -- times all instances are ONE box.  Plain per-CTA
+// tiled copies from this GPU's own tensors, no multicast.
+struct DoMaps { CUtensorMap y, dy, x, mx; };
+
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3, int c4) {
+    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+// LOAD: how the raw loaders fetch a chunk.  0: 8-byte asynchronous copies, one pixel pair per thread; 1: 16-byte copies,
+// two neighbouring pairs per thread; 2: four tensor-map box copies per chunk issued by one thread (see DoMaps).
+constexpr int do_pair_threads(int load) { return load == 2 ? (kDoFirstRawWarp + 1) * 32 : kDoPairThreads; }      // one loader warp suffices for box copies
+
+template <int MT, int NT, int CP, bool POOLED, int LOAD>
+__global__ void __launch_bounds__(do_pair_threads(LOAD), 1) mex_doff_pair(MexGeo g, const float* __restrict__ x, const float* __restrict__ mo,
                                                                   const float* __restrict__ mx, const float* __restrict__ y,
                                                                   const float* __restrict__ dy, float* __restrict__ part,
-                                                                  DoPairPlan plan, int* __restrict__ flag) {
+                                                                  DoPairPlan plan, int* __restrict__ flag,
+                                                                  const __grid_constant__ DoMaps maps) {
+    constexpr bool WIDE = LOAD == 1;
     using Cfg = DoCfg<MT, NT, CP, POOLED>;
     constexpr int kDoDepth = Cfg::DEPTH;
     constexpr uint32_t TMEM_COLS = 2 * MT * NT;
@@ -706,7 +731,7 @@ __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, con
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kDoStages; ++s) { mbar_init(&sh.full[s], kDoConv); mbar_init(&sh.empty[s], 1); }
-        for (int d = 0; d < kDoDepth; ++d) { mbar_init(&sh.raw_full[d], kDoRawWarps * 32); mbar_init(&sh.raw_empty[d], kDoConv); }
+        for (int d = 0; d < kDoDepth; ++d) { mbar_init(&sh.raw_full[d], LOAD == 2 ? 1 : kDoRawWarps * 32); mbar_init(&sh.raw_empty[d], kDoConv); }
         mbar_init(&sh.acc_full, 1);
         sh.failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -867,6 +892,39 @@ __global__ void __launch_bounds__(kDoPairThreads, 1) mex_doff_pair(MexGeo g, con
         if (lane == 0 && nchunks > 0) umma_commit(&sh.acc_full);
         __syncwarp();
         if (nchunks > 0 && !mbar_wait(&sh.acc_full, 0)) sh.failed = 1;
+    } else if (LOAD == 2) {
+        // ---------------- raw loader, tensor-map form: one thread, four box copies per chunk onto the slot's barrier.  Rows
+        // past M, channels past K and samples past the batch lie outside the maps' extents and arrive as zeros.
+        if (threadIdx.x == kDoFirstRawWarp * 32) {
+            const int rh = pair % g.oh;                                           // row class of this region pair (regions 2 pair, 2 pair + 1)
+            const int rw = g.rw;                                                  // pixel pairs per image row
+            WsRing<kDoDepth> slot = {0, 0u};
+            int issued = 0;
+            for (int c = 0; c < nchunks; ++c) {
+                if (sh.failed) break;
+                if (slot.fill >= 1 && !pair_wait(sh.failed, &sh.raw_empty[slot.stage], (slot.fill - 1) & 1u, tries)) { sh.failed = 1; break; }
+                const long long j0 = (c_begin + c) * CP;                          // first pixel pair of the chunk (whole rows or a run inside one)
+                const int n = int(j0 / g.rs), l = int(j0 % g.rs);
+                const int lh = l / rw, lw = l - lh * rw;
+                uint64_t* bar = &sh.raw_full[slot.stage];
+                const uint32_t sbase = smem_u32(rawbase + slot.stage * Cfg::SLOT_BYTES);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(uint32_t(Cfg::SLOT_DATA)) : "memory");
+                tma_load_5d(sbase, &maps.y, bar, 2 * lw, rh, lh, m_first, n);
+                if (POOLED) tma_load_4d(sbase + Cfg::G_OFF, &maps.dy, bar, lw, lh, m_first, n);
+                else tma_load_5d(sbase + Cfg::G_OFF, &maps.dy, bar, 2 * lw, rh, lh, m_first, n);
+                tma_load_5d(sbase + Cfg::X_OFF, &maps.x, bar, 2 * lw, rh, lh, k_first, n);
+                tma_load_4d(sbase + Cfg::MX_OFF, &maps.mx, bar, 2 * lw, rh, lh, n);
+                slot.advance(1);
+                if (issued < kDoDepth) ++issued;
+            }
+            // copies still in flight must land before the CTA may exit (they have, on the normal path): walk back over
+            // the last `issued` slots
+            for (int d = 0; d < issued; ++d) {
+                if (slot.stage == 0) { slot.stage = kDoDepth; --slot.fill; }
+                --slot.stage;
+                if (!mbar_wait(&sh.raw_full[slot.stage], slot.fill & 1u)) sh.failed = 1;
+            }
+        }
     } else {
         // ---------------- raw loaders; zero fill past M, K and for dead pairs.  8-byte copies: one pixel pair per thread;
         // WIDE: two neighbouring pairs per thread, 16-byte copies.  The 128 threads cover CP pairs x RS row slots.
@@ -1001,14 +1059,79 @@ inline DoPairPlan dopair_plan(const MexGeo& g) {
     return p;
 }
 
+// cuTensorMapEncodeTiled of the driver, looked up once (the library links no driver stub); nullptr if unavailable
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult st;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &st) != cudaSuccess || st != cudaDriverEntryPointSuccess) p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// A float32 tensor seen as rank-4 or rank-5 (dims fastest first, strides in floats for dims 1..), one box per copy
+inline bool encode_f32_map(CUtensorMap* map, const float* base, int rank, const long long* dims, const long long* strides, const int* box) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    cuuint64_t gd[5], gs[4];
+    cuuint32_t bd[5], es[5];
+    for (int i = 0; i < rank; ++i) { gd[i] = cuuint64_t(dims[i]); bd[i] = cuuint32_t(box[i]); es[i] = 1; }
+    for (int i = 0; i + 1 < rank; ++i) gs[i] = cuuint64_t(strides[i]) * 4;
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, cuuint32_t(rank), const_cast<float*>(base), gd, gs, bd, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The box copies need: one channel block and one region along the channels; rows of the region pair a fixed number of rows
+// apart with the height a multiple of it; every global stride a multiple of 16 bytes (width a multiple of 4, of 8 for a
+// pooled dy) and 16-byte aligned tensors; chunks that are runs of one row or whole rows and never straddle two samples.
+template <int MT, int NT, int CP, bool POOLED>
+bool doff_tma_maps(const MexGeo& g, const float* x, const float* mx, const float* y, const float* dy, DoMaps* maps) {
+    const int rw = g.rw;                                     // pixel pairs per row
+    if (g.Co != 1 || g.oc != 1 || g.rc != 1 || g.H % g.oh != 0 || g.rh * g.oh != g.H || g.W % 4 != 0 || g.rs % CP != 0) return false;
+    if (!(rw % CP == 0 || CP % rw == 0)) return false;
+    if (POOLED && (g.oh != 2 || g.W % 8 != 0)) return false;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(mx) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(dy)) & 15u) return false;
+    const int cols = rw >= CP ? CP : rw, rows = rw >= CP ? 1 : CP / rw;      // pixel pairs per box row, box rows
+    const long long W = g.W, H = g.H, N = g.N;
+    {   // y[B][M][H][W] as (w, row class, row in class, instance, sample)
+        const long long dims[5] = {W, g.oh, H / g.oh, g.M, g.B}, strides[4] = {W, W * g.oh, N, (long long)g.M * N};
+        const int box[5] = {2 * cols, 1, rows, MT * 128, 1};
+        if (!encode_f32_map(&maps->y, y, 5, dims, strides, box)) return false;
+        if (!POOLED && !encode_f32_map(&maps->dy, dy, 5, dims, strides, box)) return false;
+    }
+    if (POOLED) {   // dy[B][M][H/2][W/2] as (w / 2, h / 2, instance, sample): one value per pixel pair and row pair
+        const long long dims[4] = {W / 2, H / 2, g.M, g.B}, strides[3] = {W / 2, g.Ng, (long long)g.M * g.Ng};
+        const int box[4] = {cols, rows, MT * 128, 1};
+        if (!encode_f32_map(&maps->dy, dy, 4, dims, strides, box)) return false;
+    }
+    {   // x[B][C][H][W], channels of the block only
+        const long long dims[5] = {W, g.oh, H / g.oh, g.K, g.B}, strides[4] = {W, W * g.oh, H * W, (long long)g.C * H * W};
+        const int box[5] = {2 * cols, 1, rows, NT, 1};
+        if (!encode_f32_map(&maps->x, x, 5, dims, strides, box)) return false;
+    }
+    {   // mx[B][H][W]
+        const long long dims[4] = {W, g.oh, H / g.oh, g.B}, strides[3] = {W, W * g.oh, N};
+        const int box[4] = {2 * cols, 1, rows, 1};
+        if (!encode_f32_map(&maps->mx, mx, 4, dims, strides, box)) return false;
+    }
+    return true;
+}
+
 template <int MT, int NT, int CP, bool POOLED>
 cudaError_t launch_doff_pair_p(const MexGeo& g, const DoPairPlan& plan, bool wide, const float* x, const float* mo, const float* mx,
                                const float* y, const float* dy, float* part, int* flag, cudaStream_t s) {
     constexpr int smem = DoCfg<MT, NT, CP, POOLED>::SMEM;
     const long long grid = (long long)plan.units * plan.splits;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    if (wide) PAIR_RUN((mex_doff_pair<MT, NT, CP, POOLED, true>), kDoPairThreads, smem, int(grid), g, x, mo, mx, y, dy, part, plan, flag);
-    else PAIR_RUN((mex_doff_pair<MT, NT, CP, POOLED, false>), kDoPairThreads, smem, int(grid), g, x, mo, mx, y, dy, part, plan, flag);
+    DoMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    if (doff_tma_maps<MT, NT, CP, POOLED>(g, x, mx, y, dy, &maps))
+        PAIR_RUN((mex_doff_pair<MT, NT, CP, POOLED, 2>), do_pair_threads(2), smem, int(grid), g, x, mo, mx, y, dy, part, plan, flag, maps);
+    else if (wide) PAIR_RUN((mex_doff_pair<MT, NT, CP, POOLED, 1>), kDoPairThreads, smem, int(grid), g, x, mo, mx, y, dy, part, plan, flag, maps);
+    else PAIR_RUN((mex_doff_pair<MT, NT, CP, POOLED, 0>), kDoPairThreads, smem, int(grid), g, x, mo, mx, y, dy, part, plan, flag, maps);
     count_launch();
     return cudaGetLastError();
 }

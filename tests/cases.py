@@ -197,6 +197,11 @@ MEX_PAIR = [
     mex_case("pair_eps_neg", (4, 52, 8, 8), 60, (52, 1, 1), (52, 1, 1), eps=-1.5, softmax=True, unshared_region=(2,), seed=404),
     mex_case("pair_short_patches", (6, 24, 8, 12), 80, (24, 1, 1), (24, 1, 1), softmax=True, unshared_region=(2,), seed=405, normalize=True),
     mex_case("pair_long_patches", (3, 300, 4, 4), 150, (300, 1, 1), (300, 1, 1), softmax=True, unshared_region=(2,), seed=406, normalize=True),
+    # shapes whose offsets-gradient chunks are boxes of a tensor map: whole rows (two per chunk), runs inside a row,
+    # ragged instance and tap tiles, a second tap tile of two channels, two instance groups, a batch that ends mid-way
+    mex_case("pair_box_rows", (5, 40, 8, 16), 70, (40, 1, 1), (40, 1, 1), softmax=True, unshared_region=(2,), seed=407, normalize=True),
+    mex_case("pair_box_runs", (3, 130, 4, 32), 200, (130, 1, 1), (130, 1, 1), eps=0.5, softmax=True, unshared_region=(2,), seed=408, normalize=True),
+    mex_case("pair_box_groups", (2, 64, 16, 8), 300, (64, 1, 1), (64, 1, 1), softmax=False, unshared_region=(2,), seed=409),
 ]
 
 
