@@ -153,3 +153,18 @@ def test_tensor_core_flag_is_ignored_where_the_expansion_does_not_apply(port):
         a = sim_ops.similarity_forward(xd, td, wd, flags=c["flags"], **cases.sim_attrs(c)).cpu().numpy()
         b = sim_ops.similarity_forward(xd, td, wd, flags=c["flags"] | abi.FLAG_SIM_L2_TENSORCORE, **cases.sim_attrs(c)).cpu().numpy()
         assert np.array_equal(a, b, equal_nan=True)
+
+
+def test_cfg4_parameter_gradients_summed_over_eight_samples(port):
+    """The batch-summed parameter gradients of the cfg4 layer (8 x 1024 positions per sum: 8192 terms) against the
+    float64 oracle, beside the two-sample cases of test_baseline_configs."""
+    c = dict(next(c for c in cases.SIM_CONFIGS if c["name"] == "cfg4a_sub"), shape=(8, 64, 32, 32), name="cfg4a_b8")
+    d32, d64 = cases.sim_desc(c), cases.sim_desc(c, dtype=abi.F64)
+    x, t, w, dy = cases.sim_inputs(c, port.sim_out_shape(d32))
+    xd, td, wd, dyd = (gpu_util.dev(a) for a in (x, t, w, dy))
+    dt, dw = sim_ops.similarity_parameters_grad(xd, td, wd, dyd, flags=c["flags"], **cases.sim_attrs(c))
+    r64 = port.similarity_params_grad(d64, *(a.astype(np.float64) for a in (x, t, w, dy)))
+    for name, ours, ref in (("dt", dt, r64[0]), ("dw", dw, r64[1])):
+        err = cases.rel_err(ours.cpu().numpy(), ref)
+        print("cfg4a batch 8 %s: %.2e from the float64 oracle" % (name, err))
+        assert err <= 1e-5, (name, err)

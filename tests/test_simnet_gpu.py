@@ -55,4 +55,5 @@ def test_network_step_matches_cpu_oracle(port, name, batch):
     assert abs(f_loss - loss64) <= 2e-5 * max(1.0, float(np.abs(logits64).max()))
     for i, (a, b32, b64) in enumerate(zip(f_grads, grads32, grads64)):
         ours, ref = cases.rel_err(a, b64), cases.rel_err(b32, b64)
+        print("%s f32 gradient %d %s: GPU %.2e, f32 oracle %.2e from the f64 oracle" % (name, i, tuple(a.shape), ours, ref))
         assert ours <= max(1e-4, 10 * ref), "%s f32 grad %d %s: %.3g from the f64 oracle, f32 oracle %.3g" % (name, i, a.shape, ours, ref)
