@@ -231,6 +231,17 @@ SIMNETS_API int simnets_mex_forward(const simnets_mex_desc* d,
                                     const void* x, const void* offsets, void* y,
                                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* MEX forward plus the 2x2 / stride-2 sum pooling of its output, the pair of layers the reference's example networks
+ * repeat (README.md:114-131, there `4 * AveragePooling2D(2)` behind the Mex layer): y as simnets_mex_forward writes it
+ * (the gradient entry points need it) and y_pooled[batch, num_instances * channels_out, height_out / 2, width_out / 2].
+ * float32 only, height_out and width_out even, else SIMNETS_E_UNSUPPORTED.  On the pair-tile kernels the pooling is
+ * done by the forward kernel's epilogue (y is not read again); elsewhere a pooling kernel runs behind the forward
+ * kernels.  Each pooled value is (y00 + y01) + (y10 + y11).  No counterpart in the reference, whose graphs use
+ * TensorFlow's pooling op. */
+SIMNETS_API int simnets_mex_forward_pool2x2(const simnets_mex_desc* d,
+                                            const void* x, const void* offsets, void* y, void* y_pooled,
+                                            void* workspace, size_t workspace_bytes, void* stream);
+
 /* Status words of a MEX workspace after the calls that used it, copied to host_out[0..1] by one 8-byte asynchronous
  * device-to-host copy on `stream` (synchronise the stream before reading; pinned host memory keeps the copy
  * asynchronous).  No counterpart in the reference, whose kernels have nothing to report.

@@ -182,6 +182,23 @@ int simnets_softmax_cross_entropy(int32_t batch, int32_t classes, float scale, c
                                          as_stream(stream)));
 }
 
+int simnets_mex_forward_pool2x2(const simnets_mex_desc* d, const void* x, const void* off, void* y, void* y_pooled, void* ws, size_t ws_bytes,
+                                void* stream) {
+    MexGeo g;
+    const int rc = mex_geometry(d, nullptr, &g);
+    if (rc) return rc;
+    if (d->dtype != SIMNETS_F32 || g.Ho % 2 || g.Wo % 2) return SIMNETS_E_UNSUPPORTED;
+    if (!off || (g.B > 0 && (!x || !y || !y_pooled))) return SIMNETS_E_NULL;
+    if (g.B == 0) return SIMNETS_OK;
+    if (mex_use_tiled(g, false, d->flags)) {
+        if (!ws || ws_bytes < mex_workspace_bytes(g, false, d->flags)) return SIMNETS_E_WORKSPACE;
+        return from_cuda(launch_mex_fwd_tiled(g, (const float*)x, (const float*)off, (float*)y, ws, d->flags, as_stream(stream), (float*)y_pooled));
+    }
+    const cudaError_t e = launch_mex_fwd_direct(g, false, x, off, y, as_stream(stream));
+    if (e != cudaSuccess) return from_cuda(e);
+    return from_cuda(launch_sum_pool2((long long)g.B * g.M * g.Co, g.Ho, g.Wo, (const float*)y, (float*)y_pooled, as_stream(stream)));
+}
+
 int simnets_similarity_workspace_status(const void* ws, void* stream, int32_t* host_out) {
     if (!ws || !host_out) return SIMNETS_E_NULL;
     return from_cuda(cudaMemcpyAsync(host_out, ws, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, as_stream(stream)));

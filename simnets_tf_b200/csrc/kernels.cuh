@@ -17,7 +17,8 @@ cudaError_t launch_normalize_offsets_bwd(long long rows, int K, const float* off
 cudaError_t launch_fp32_probe(bool packed, int blocks, int iters, float* out, cudaStream_t);
 
 // pool.cu
-cudaError_t launch_sum_pool2(long long planes, int H, int W, const float* x, float* y, cudaStream_t);
+// gate: when given, the kernel runs only if gate[0] | gate[1] is non-zero (the pooling behind a recomputed forward pass)
+cudaError_t launch_sum_pool2(long long planes, int H, int W, const float* x, float* y, cudaStream_t, const int* gate = nullptr);
 
 // direct_kernels.cu -- any shape, float32 and float64
 // gate: when given, the kernel runs only if gate[1] is non-zero (the redo behind the tensor-core forward kernel)
@@ -52,7 +53,9 @@ bool sim_smallk_shape(const SimGeo&);
 cudaError_t launch_sim_fwd_smallk(const SimGeo&, const float* x, const float* planes, const float* cm, const int2* taps, float* y, cudaStream_t);
 bool mex_use_tiled(const MexGeo&, bool f64, uint32_t flags);
 size_t mex_workspace_bytes(const MexGeo&, bool f64, uint32_t flags);
-cudaError_t launch_mex_fwd_tiled(const MexGeo&, const float* x, const float* off, float* y, void* ws, uint32_t flags, cudaStream_t);
+// pooled: when given, the 2x2 sum pooling of y is produced as well (fused into the pair-tile kernel, a pooling launch behind the others)
+cudaError_t launch_mex_fwd_tiled(const MexGeo&, const float* x, const float* off, float* y, void* ws, uint32_t flags, cudaStream_t,
+                                 float* pooled = nullptr);
 // mex_smallm.cu -- one CTA per position, for M <= 16 and K >= 256
 cudaError_t launch_mex_colmax_wide(const MexGeo&, const float* x, float* mx, const int* flag, cudaStream_t);
 cudaError_t launch_mex_fwd_smallm(const MexGeo&, const float* x, const float* eot, const float* mo, float* y, const int* flag, cudaStream_t);
@@ -98,8 +101,9 @@ bool mex_pair_aligned(const void*, const void*, const void*, const void*);
 int mex_pair_nt_fwd(const MexGeo&);
 int mex_pair_nt_dx(const MexGeo&);
 int mex_pair_doff_splits(const MexGeo&);
+// pooled: when given, also the 2x2 sum pooling of y ([B, M * Co, Ho / 2, Wo / 2]; Ho and Wo even), added up by the epilogue
 cudaError_t launch_mex_fwd_pair(const MexGeo&, const float* x, const float* tiles, const float* mo, const float* mx, float* y,
-                                int* flag, int test_expire, cudaStream_t);
+                                float* pooled, int* flag, int test_expire, cudaStream_t);
 cudaError_t launch_mex_dx_pair(const MexGeo&, const float* x, const float* tiles, const float* mo, const float* mx, const float* y,
                                const float* dy, float* dx, int* flag, cudaStream_t);
 cudaError_t launch_mex_doff_pair(const MexGeo&, const float* x, const float* mo, const float* mx, const float* y, const float* dy,

@@ -284,7 +284,8 @@ struct StepCursor {
 template <int NT, int DEPTH>
 __global__ void __launch_bounds__(kPairThreads, 1) mex_fwd_pair(MexGeo g, const float* __restrict__ x, const float* __restrict__ tiles,
                                                                const float* __restrict__ mo, const float* __restrict__ mx,
-                                                               float* __restrict__ y, WsPlan plan, int* __restrict__ flag, int test_expire) {
+                                                               float* __restrict__ y, float* __restrict__ pooled, WsPlan plan,
+                                                               int* __restrict__ flag, int test_expire) {
     constexpr int STAGES = pair_stages<NT>();
     constexpr int STAGE_BYTES = pair_stage_bytes<NT>();
     constexpr uint32_t TMEM_COLS = 4 * NT;
@@ -391,6 +392,17 @@ __global__ void __launch_bounds__(kPairThreads, 1) mex_fwd_pair(MexGeo g, const 
             const PairColumn col = pair_column_of(g, it.r, (long long)it.jt * kTcPos + quarter * 32 + lane, P, mx);
             const float cadd0 = col.mx0 + c_add, cadd1 = col.mx1 + c_add;
             float* yb = y + (col.base >= 0 ? col.base : 0) + (long long)m0 * g.N;
+            // 2x2 sum pooling of the output, fused: a pixel pair is the upper or the lower half of a pooling window, and the
+            // other half belongs to the sibling region pair (another work item).  Each half is added to a zeroed tensor by
+            // one reduction: 0 + a + b with two addends is the same number in either order, so the sum is deterministic.
+            float* pb = nullptr;
+            if (pooled != nullptr && col.base >= 0) {
+                const long long mn = (long long)g.M * g.N;
+                const int n = int(col.base / mn), pos = int(col.base - (long long)n * mn);
+                const int w = pos % g.Wo, hc = pos / g.Wo, h = hc % g.Ho, cc = hc / g.Ho;
+                const int Ng = g.N >> 2;
+                pb = pooled + (long long)n * g.M * Ng + (cc * (g.Ho >> 1) + (h >> 1)) * (g.Wo >> 1) + (w >> 1) + (long long)m0 * Ng;
+            }
             if (!pair_wait_warp(sh.failed, &sh.acc_full[buf], (uint32_t(li) >> 1) & 1u, tries, 1024)) { sh.failed = 1; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
@@ -409,6 +421,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) mex_fwd_pair(MexGeo g, const 
                             o.x = fmaf(lg2_ftz(__uint_as_float(v0[i])), k_log, cadd0 + mow0[c0 + i]);
                             o.y = fmaf(lg2_ftz(__uint_as_float(v1[i])), k_log, cadd1 + mow1[c0 + i]);
                             __stcs(reinterpret_cast<float2*>(yp + i * Nu), o);
+                            if (pb != nullptr) atomicAdd(pb + (size_t)(c0 + i) * (Nu >> 2), o.x + o.y);
                         }
                     }
                 }
@@ -1006,8 +1019,8 @@ inline bool mex_pair_wide(const MexGeo& g, const void* a, const void* b, const v
 inline int pair_nt(int n) { return n > 64 ? 128 : 64; }
 
 template <int NT>
-cudaError_t launch_fwd_pair_nt(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, float* y, int* flag,
-                               int test_expire, cudaStream_t s) {
+cudaError_t launch_fwd_pair_nt(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, float* y, float* pooled,
+                               int* flag, int test_expire, cudaStream_t s) {
     const long long P = (long long)g.B * g.rs;
     const int mtiles = (g.M + NT - 1) / NT, pairs = g.R / 2;
     const long long items = ((P + kTcPos - 1) / kTcPos) * mtiles * pairs;
@@ -1015,7 +1028,7 @@ cudaError_t launch_fwd_pair_nt(const MexGeo& g, const float* x, const float* til
     const WsPlan plan = {int(items), make_fastdiv(pairs), make_fastdiv(mtiles)};
     const int grid = int(std::min<long long>(items, ws_sm_count()));
     constexpr int smem = pair_stages<NT>() * pair_stage_bytes<NT>() + pair_raw_bytes<3, 8>();
-    PAIR_RUN((mex_fwd_pair<NT, 3>), kPairThreads, smem, grid, g, x, tiles, mo, mx, y, plan, flag, test_expire);
+    PAIR_RUN((mex_fwd_pair<NT, 3>), kPairThreads, smem, grid, g, x, tiles, mo, mx, y, pooled, plan, flag, test_expire);
     count_launch();
     return cudaGetLastError();
 }
@@ -1162,9 +1175,13 @@ int mex_pair_nt_dx(const MexGeo& g) { return pair_nt(g.K); }
 int mex_pair_doff_splits(const MexGeo& g) { return dopair_plan(g).splits; }
 
 cudaError_t launch_mex_fwd_pair(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, float* y,
-                                int* flag, int test_expire, cudaStream_t s) {
-    if (pair_nt(g.M) == 128) return launch_fwd_pair_nt<128>(g, x, tiles, mo, mx, y, flag, test_expire, s);
-    return launch_fwd_pair_nt<64>(g, x, tiles, mo, mx, y, flag, test_expire, s);
+                                float* pooled, int* flag, int test_expire, cudaStream_t s) {
+    if (pooled != nullptr) {           // the epilogue adds the two halves of every pooling window onto zeros
+        const cudaError_t e = cudaMemsetAsync(pooled, 0, sizeof(float) * (size_t)g.B * g.M * (g.N >> 2), s);
+        if (e != cudaSuccess) return e;
+    }
+    if (pair_nt(g.M) == 128) return launch_fwd_pair_nt<128>(g, x, tiles, mo, mx, y, pooled, flag, test_expire, s);
+    return launch_fwd_pair_nt<64>(g, x, tiles, mo, mx, y, pooled, flag, test_expire, s);
 }
 
 cudaError_t launch_mex_dx_pair(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, const float* y,

@@ -485,7 +485,19 @@ size_t mex_workspace_bytes(const MexGeo& g, bool f64, uint32_t flags) {
     return carve(g, nullptr).bytes;
 }
 
-cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* off, float* y, void* ws, uint32_t flags, cudaStream_t s) {
+static cudaError_t mex_fwd_tiled_body(const MexGeo& g, const float* x, const float* off, float* y, void* ws, uint32_t flags, cudaStream_t s,
+                                      float* pooled, bool* pooled_done);
+
+cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* off, float* y, void* ws, uint32_t flags, cudaStream_t s,
+                                 float* pooled) {
+    bool pooled_done = false;
+    const cudaError_t e = mex_fwd_tiled_body(g, x, off, y, ws, flags, s, pooled, &pooled_done);
+    if (e != cudaSuccess || pooled == nullptr || pooled_done) return e;
+    return launch_sum_pool2((long long)g.B * g.M * g.Co, g.Ho, g.Wo, y, pooled, s);
+}
+
+static cudaError_t mex_fwd_tiled_body(const MexGeo& g, const float* x, const float* off, float* y, void* ws, uint32_t flags, cudaStream_t s,
+                                      float* pooled, bool* pooled_done) {
     const MexWs w = carve(g, ws);
     if (use_smallk_kernels(g, flags)) {
         cudaError_t e = run_prepasses(g, w, x, off, s, false);
@@ -506,9 +518,15 @@ cudaError_t launch_mex_fwd_tiled(const MexGeo& g, const float* x, const float* o
     if (e != cudaSuccess) return e;
     if (use_tc_kernels(g, flags)) {
         if (use_pair_kernels(g, flags, x, y, y, y)) {
-            e = launch_mex_fwd_pair(g, x, w.tc_tiles, w.mo, w.mx, y, w.flag, (flags & SIMNETS_FLAG_MEX_TEST_EXPIRE_WAIT) != 0, s);
+            const bool fuse = pooled != nullptr && (reinterpret_cast<uintptr_t>(pooled) & 3u) == 0;
+            e = launch_mex_fwd_pair(g, x, w.tc_tiles, w.mo, w.mx, y, fuse ? pooled : nullptr, w.flag,
+                                    (flags & SIMNETS_FLAG_MEX_TEST_EXPIRE_WAIT) != 0, s);
             if (e != cudaSuccess) return e;
-            return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);
+            e = launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);
+            if (e != cudaSuccess || !fuse) return e;
+            *pooled_done = true;
+            // if the exact kernel had to recompute y (a status word is set), the pooling is redone from y as well
+            return launch_sum_pool2((long long)g.B * g.M * g.Co, g.Ho, g.Wo, y, pooled, s, w.flag);
         }
         e = launch_mex_tc_prep(g, false, w.eo, w.tc_tiles, s);
         if (e != cudaSuccess) return e;

@@ -8,7 +8,9 @@ namespace simnets {
 namespace {
 
 // the four addends are summed in window order, ((a + b) + c) + d, like a sequential pooling loop
-__global__ void __launch_bounds__(256) sum_pool2_vec4(long long total, int Ho, int W4, int W, const float* __restrict__ x, float* __restrict__ y) {
+__global__ void __launch_bounds__(256) sum_pool2_vec4(long long total, int Ho, int W4, int W, const float* __restrict__ x, float* __restrict__ y,
+                                                      const int* __restrict__ gate) {
+    if (gate && (gate[0] | gate[1]) == 0) return;
     for (long long i = blockIdx.x * 256LL + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
         const int w4 = int(i % W4);
         const long long ph = i / W4;                          // plane * Ho + h
@@ -22,7 +24,9 @@ __global__ void __launch_bounds__(256) sum_pool2_vec4(long long total, int Ho, i
     (void)Ho;
 }
 
-__global__ void __launch_bounds__(256) sum_pool2_scalar(long long total, int Wo, int W, const float* __restrict__ x, float* __restrict__ y) {
+__global__ void __launch_bounds__(256) sum_pool2_scalar(long long total, int Wo, int W, const float* __restrict__ x, float* __restrict__ y,
+                                                        const int* __restrict__ gate) {
+    if (gate && (gate[0] | gate[1]) == 0) return;
     for (long long i = blockIdx.x * 256LL + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
         const int w = int(i % Wo);
         const long long ph = i / Wo;
@@ -34,14 +38,15 @@ __global__ void __launch_bounds__(256) sum_pool2_scalar(long long total, int Wo,
 }  // namespace
 
 // planes * H * W inputs, H and W even
-cudaError_t launch_sum_pool2(long long planes, int H, int W, const float* x, float* y, cudaStream_t s) {
+cudaError_t launch_sum_pool2(long long planes, int H, int W, const float* x, float* y, cudaStream_t s, const int* gate) {
     const int Ho = H / 2, Wo = W / 2;
     if (planes == 0 || Ho == 0 || Wo == 0) return cudaSuccess;
     const bool vec = W % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 7) == 0;
     const long long total = vec ? planes * Ho * (W / 4) : planes * Ho * Wo;
-    const int grid = int(std::min<long long>((total + 255) / 256, (long long)device_sm_count() * 16));
-    if (vec) sum_pool2_vec4<<<grid, 256, 0, s>>>(total, Ho, W / 4, W, x, y);
-    else sum_pool2_scalar<<<grid, 256, 0, s>>>(total, Wo, W, x, y);
+    // (a gated launch almost always returns at once: one wave of CTAs is enough)
+    const int grid = int(std::min<long long>((total + 255) / 256, (long long)device_sm_count() * (gate ? 4 : 16)));
+    if (vec) sum_pool2_vec4<<<grid, 256, 0, s>>>(total, Ho, W / 4, W, x, y, gate);
+    else sum_pool2_scalar<<<grid, 256, 0, s>>>(total, Wo, W, x, y, gate);
     count_launch();
     return cudaGetLastError();
 }

@@ -16,6 +16,7 @@ namespace simnets {
 namespace {
 
 constexpr int kSkThreads = 128;
+constexpr int kSkBlocksPerSm = 4;      // 128 registers per thread: four CTAs (16 warps) per SM measured 6 % faster than three at 168
 
 struct SkColumn { long long base; int n, h0, w0; };
 
@@ -34,7 +35,7 @@ __device__ __forceinline__ SkColumn sk_column(const SimGeo& g, long long j, long
 // planes: [3][K][ldm] (template, scale, per-term constant) as sim_prep writes them; taps: [K] {offset inside a sample, (kh << 16) | kw}
 // KT = the patch length at compile time (the tap loops are fully unrolled, the patches are register arrays).
 template <int MODE, int KT>
-__global__ void __launch_bounds__(kSkThreads, 3) sim_fwd_smallk(SimGeo g, const float* __restrict__ x, const float* __restrict__ planes,
+__global__ void __launch_bounds__(kSkThreads, kSkBlocksPerSm) sim_fwd_smallk(SimGeo g, const float* __restrict__ x, const float* __restrict__ planes,
                                                                const float* __restrict__ cm, const int2* __restrict__ taps,
                                                                float* __restrict__ y) {
     constexpr bool MASKED = MODE == SIM_L2N_NAN || MODE == SIM_L1_SKIP;
@@ -138,7 +139,7 @@ cudaError_t launch_sk(const SimGeo& g, const float* x, const float* planes, cons
     const long long P = (long long)g.B * g.N;
     const size_t smem = sk_smem_bytes(g);
     const long long want = (P / 2 + kSkThreads - 1) / kSkThreads;
-    const int grid = int(std::max<long long>(1, std::min<long long>(want, 3LL * device_sm_count())));
+    const int grid = int(std::max<long long>(1, std::min<long long>(want, (long long)kSkBlocksPerSm * device_sm_count())));
 #define SK(MODE)                                                                                                       \
     do {                                                                                                               \
         static bool attr_done = false;                                                                                 \

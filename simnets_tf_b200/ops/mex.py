@@ -142,6 +142,25 @@ def mex_forward(input, offsets, num_instances, flags=0, workspace=None, **attrs)
     return y
 
 
+def mex_forward_pool2(input, offsets, num_instances, flags=0, workspace=None, **attrs):
+    """The `Mex` op and the 2x2 sum pooling of its output in one library call: (y, y_pooled).  float32, even output
+    height and width.  On the pair-tile kernels the forward kernel's epilogue does the pooling."""
+    attrs = _attrs(**attrs)
+    dev = require_cuda(input, offsets)
+    input, offsets = input.contiguous(), offsets.contiguous()
+    d = _desc(input, num_instances, attrs, flags)
+    g = _geometry(d)
+    _check_offsets(offsets, g, num_instances)
+    y = torch.empty((input.shape[0], g.channels_out_total, g.height_out, g.width_out), dtype=input.dtype, device=dev)
+    yp = torch.empty((input.shape[0], g.channels_out_total, g.height_out // 2, g.width_out // 2), dtype=input.dtype, device=dev)
+    with torch.cuda.device(dev):
+        ws, n = _ws(d, dev, workspace)
+        with timed("mex_forward", *_cost(d, g, "fwd")):
+            _lib.check(_lib.lib().simnets_mex_forward_pool2x2(C.byref(d), input.data_ptr(), offsets.data_ptr(), y.data_ptr(), yp.data_ptr(),
+                                                              ws, n, stream_ptr(dev)))
+    return y, yp
+
+
 def mex_input_grad(input, offsets, orig_output, output_grad, num_instances, flags=0, primed_workspace=None, pooled=False, **attrs):
     """The `MexInputGrad` op.  pooled=True: `output_grad` is the gradient of a 2x2 sum pooling of the output
     (half height and width); the library reads it in place of its 2x upsampling."""
@@ -228,10 +247,15 @@ def _forward_for_autograd(ctx, input, offsets, num_instances, attrs, pooled):
     ctx.layer_ws = None
     if (ctx.needs_input_grad[0] or ctx.needs_input_grad[1]) and input.is_cuda and input.shape[0] > 0:
         ctx.layer_ws = mex_layer_workspace(input, num_instances, pooled=pooled, **attrs)
-    y = mex_forward(input, offsets, num_instances, workspace=ctx.layer_ws, **attrs)
+    if pooled and input.dtype == torch.float32 and input.shape[0] > 0:
+        y, out = mex_forward_pool2(input, offsets, num_instances, workspace=ctx.layer_ws, **attrs)
+    else:
+        y = out = mex_forward(input, offsets, num_instances, workspace=ctx.layer_ws, **attrs)
+        if pooled:
+            out = torch.nn.functional.avg_pool2d(y, 2) * 4.0
     ctx.attrs, ctx.num_instances = attrs, num_instances
     ctx.save_for_backward(input, offsets, y)
-    return y
+    return out
 
 
 class _Mex(torch.autograd.Function):
@@ -261,8 +285,7 @@ class _MexSumPool2(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, input, offsets, num_instances, attrs):
-        y = _forward_for_autograd(ctx, input, offsets, num_instances, attrs, True)
-        return sum_pool2x2(y) if y.dtype == torch.float32 else torch.nn.functional.avg_pool2d(y, 2) * 4.0
+        return _forward_for_autograd(ctx, input, offsets, num_instances, attrs, True)
 
     @staticmethod
     def backward(ctx, grad):

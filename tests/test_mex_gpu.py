@@ -366,3 +366,53 @@ def test_full_size_properties():
     assert cases.rel_err(per_block_dx.cpu().numpy(), per_block_dy.cpu().numpy()) < 1e-4
     doff = mex_ops.mex_offsets_grad(x[:nb], off2, y2, dy, M, **attrs)
     assert cases.rel_err(doff.sum(dim=(2, 3, 4)).flatten().cpu().numpy(), dy.reshape(nb, M, -1).sum(dim=(0, 2)).cpu().numpy()) < 1e-4
+
+
+# ---- forward with the 2x2 sum pooling of its output (simnets_mex_forward_pool2x2)
+def _pool2(a):
+    a = a.astype(np.float64)
+    return (a[:, :, 0::2, 0::2] + a[:, :, 0::2, 1::2]) + (a[:, :, 1::2, 0::2] + a[:, :, 1::2, 1::2])
+
+
+_POOLABLE = [c for c in cases.MEX_PAIR + cases.MEX_CONFIGS + cases.MEX_SMALL[::4]]
+
+
+@pytest.mark.parametrize("c", _POOLABLE, ids=lambda c: c["name"])
+def test_forward_with_pooled_output(port, c):
+    """y as the plain forward gives it, and the 2x2 sum pooling of y, from one library call: fused into the epilogue
+    on the pair-tile kernels, a pooling launch behind the forward kernels elsewhere."""
+    d = cases.mex_desc(c)
+    x, off, _ = cases.mex_inputs(c, port.mex_offsets_shape(d), port.mex_out_shape(d))
+    ry = port.mex_forward(d, x, off)
+    if ry.shape[2] % 2 or ry.shape[3] % 2:
+        with pytest.raises(RuntimeError):
+            mex_ops.mex_forward_pool2(gpu_util.dev(x), gpu_util.dev(off), c["M"], **cases.mex_attrs(c))
+        return
+    for flags in (0, abi.FLAG_MEX_NO_PAIR_TILES):
+        y, yp = mex_ops.mex_forward_pool2(gpu_util.dev(x), gpu_util.dev(off), c["M"], flags=c["flags"] | flags, **cases.mex_attrs(c))
+        cases.assert_parity(y.cpu().numpy(), ry, what="y")
+        cases.assert_parity(yp.cpu().numpy(), _pool2(ry).astype(np.float32), tol=1e-5, what="pooled y (flags %d)" % flags)
+
+
+def test_pooled_output_on_the_recomputing_routes(port, cuda_lib):
+    """The pooled output must also be right when the exact kernels redo the forward pass: offsets with a spread that makes
+    the factorisation unsafe (status word 0), and a bounded wait that runs out (status word 1)."""
+    import ctypes as C
+    c = next(c for c in cases.MEX_CONFIGS if c["name"] == "cfg5_mex1_sub")
+    d = cases.mex_desc(c)
+    x, off, _ = cases.mex_inputs(c, port.mex_offsets_shape(d), port.mex_out_shape(d))
+    attrs = cases.mex_attrs(c)
+    stream = torch.cuda.current_stream().cuda_stream
+    status = (C.c_int32 * 2)(7, 7)
+    wide = off.copy()
+    wide[0, 0, 0] = 300.0
+    for o, flags, want in ((off, abi.FLAG_MEX_TEST_EXPIRE_WAIT, (0, 1)), (wide, 0, (1, 0)), (off, 0, (0, 0))):
+        ry = port.mex_forward(d, x, o)
+        xd, od = gpu_util.dev(x), gpu_util.dev(o)
+        ws = mex_ops.mex_layer_workspace(xd, c["M"], flags=flags, **attrs)
+        y, yp = mex_ops.mex_forward_pool2(xd, od, c["M"], flags=flags, workspace=ws, **attrs)
+        assert cuda_lib.simnets_mex_workspace_status(ws.data_ptr(), stream, status) == 0
+        torch.cuda.synchronize()
+        assert (status[0], status[1]) == want
+        cases.assert_parity(y.cpu().numpy(), ry, what="y")
+        cases.assert_parity(yp.cpu().numpy(), _pool2(ry).astype(np.float32), tol=1e-5, what="pooled y")
