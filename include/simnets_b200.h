@@ -95,6 +95,10 @@ enum { SIMNETS_SIM_L1 = 0, SIMNETS_SIM_L2 = 1 };
  * separate abs, sign and multiply passes over the weights. */
 #define SIMNETS_FLAG_SIM_ABS_WEIGHTS   (1u << 12)
 
+/* simnets_mex_forward / simnets_mex_forward_pool2x2: the per-position extrema are already in the workspace
+ * (see simnets_mex_workspace_maxima); ignored by shapes for which that function returns NULL. */
+#define SIMNETS_FLAG_MEX_MAXIMA_GIVEN  (1u << 13)
+
 /* MEX gradient entry points only: dy is given at half resolution, dy[batch, M * channels_out, height_out / 2,
  * width_out / 2], each value standing for the 2x2 window of output positions that a 2x2 / stride-2 sum pooling
  * added up (the gradient of such a pooling copies its dy to the four inputs; with this flag the copy is never
@@ -145,6 +149,18 @@ SIMNETS_API size_t simnets_similarity_workspace_bytes(const simnets_sim_desc* d)
 SIMNETS_API int simnets_similarity_forward(const simnets_sim_desc* d,
                                            const void* x, const void* templates, const void* weights,
                                            void* y, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Similarity forward that also leaves, per sample and output position, the maximum and the minimum of y over the
+ * instances: ch_max[batch, out_h, out_w], ch_min likewise (either may be NULL; NaN entries are ignored as by fmax).
+ * A MEX layer whose blocks span exactly the channels of one pixel (block [C, 1, 1]) needs that extremum of every
+ * patch to stabilise its log-sum-exp, and in a SimNet the Similarity layer always feeds such a MEX layer
+ * (README.md:114-131): written straight into the MEX workspace (simnets_mex_workspace_maxima) it saves the MEX forward
+ * pass its own pass over the input (SIMNETS_FLAG_MEX_MAXIMA_GIVEN).  The short-patch kernels produce the extrema on the
+ * way, the other forward kernels by a small kernel behind them.  float32 only.  No counterpart in the reference. */
+SIMNETS_API int simnets_similarity_forward_extrema(const simnets_sim_desc* d,
+                                                   const void* x, const void* templates, const void* weights,
+                                                   void* y, void* ch_max, void* ch_min,
+                                                   void* workspace, size_t workspace_bytes, void* stream);
 
 /* Status words of a Similarity workspace after simnets_similarity_forward used it, copied to host_out[0..1] as
  * simnets_mex_workspace_status does.  host_out[0] is always 0; host_out[1] != 0: the tensor-core kernel of
@@ -230,6 +246,14 @@ SIMNETS_API size_t simnets_mex_workspace_bytes(const simnets_mex_desc* d);
 SIMNETS_API int simnets_mex_forward(const simnets_mex_desc* d,
                                     const void* x, const void* offsets, void* y,
                                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* Where simnets_mex_forward reads the per-position extrema of the patches from (float32 [batch, N], N = positions per
+ * sample; the maximum for epsilon > 0, the minimum for epsilon < 0), inside a workspace of this descriptor; NULL for
+ * shapes whose forward kernels find the extrema themselves.  A caller that fills it (e.g. with
+ * simnets_similarity_forward_extrema of the layer in front, when every patch is exactly the channels of one pixel)
+ * passes SIMNETS_FLAG_MEX_MAXIMA_GIVEN to simnets_mex_forward / simnets_mex_forward_pool2x2, which then skip their
+ * pass over the input; wrong values there break the numerical safety of the evaluation, not just its speed. */
+SIMNETS_API void* simnets_mex_workspace_maxima(const simnets_mex_desc* d, void* workspace);
 
 /* MEX forward plus the 2x2 / stride-2 sum pooling of its output, the pair of layers the reference's example networks
  * repeat (README.md:114-131, there `4 * AveragePooling2D(2)` behind the Mex layer): y as simnets_mex_forward writes it

@@ -45,6 +45,9 @@ def lib():
         l.simnets_mex_forward.argtypes = [md, _P, _P, _P, _P, C.c_size_t, _P]
         l.simnets_mex_workspace_status.argtypes = [_P, _P, C.POINTER(C.c_int32)]
         l.simnets_mex_forward_pool2x2.argtypes = [md, _P, _P, _P, _P, _P, C.c_size_t, _P]
+        l.simnets_mex_workspace_maxima.restype = C.c_void_p
+        l.simnets_mex_workspace_maxima.argtypes = [md, _P]
+        l.simnets_similarity_forward_extrema.argtypes = [sd, _P, _P, _P, _P, _P, _P, _P, C.c_size_t, _P]
         l.simnets_similarity_workspace_status.argtypes = [_P, _P, C.POINTER(C.c_int32)]
         l.simnets_softmax_cross_entropy_workspace_bytes.restype = C.c_size_t
         l.simnets_softmax_cross_entropy_workspace_bytes.argtypes = [C.c_int32]

@@ -80,6 +80,31 @@ int simnets_similarity_forward(const simnets_sim_desc* d, const void* x, const v
     return from_cuda(launch_sim_fwd_direct(g, f64, x, t, w, y, as_stream(stream)));
 }
 
+int simnets_similarity_forward_extrema(const simnets_sim_desc* d, const void* x, const void* t, const void* w, void* y, void* ch_max, void* ch_min,
+                                       void* ws, size_t ws_bytes, void* stream) {
+    SimGeo g;
+    const int rc = sim_geometry(d, &g);
+    if (rc) return rc;
+    if (d->dtype != SIMNETS_F32) return SIMNETS_E_UNSUPPORTED;
+    if (!t || !w || (g.B > 0 && (!x || !y))) return SIMNETS_E_NULL;
+    if (g.B == 0) return SIMNETS_OK;
+    if (sim_use_tiled(g, false, d->flags)) {
+        if (!ws || ws_bytes < sim_workspace_bytes(g, false, d->flags)) return SIMNETS_E_WORKSPACE;
+        return from_cuda(launch_sim_fwd_tiled(g, (const float*)x, (const float*)t, (const float*)w, (float*)y, ws, d->flags, as_stream(stream),
+                                              (float*)ch_max, (float*)ch_min));
+    }
+    const cudaError_t e = launch_sim_fwd_direct(g, false, x, t, w, y, as_stream(stream));
+    if (e != cudaSuccess) return from_cuda(e);
+    return from_cuda(launch_sim_extrema(g, (const float*)y, (float*)ch_max, (float*)ch_min, as_stream(stream)));
+}
+
+void* simnets_mex_workspace_maxima(const simnets_mex_desc* d, void* workspace) {
+    MexGeo g;
+    if (!d || !workspace || mex_geometry(d, nullptr, &g)) return nullptr;
+    if (!mex_use_tiled(g, d->dtype == SIMNETS_F64, d->flags)) return nullptr;
+    return mex_workspace_maxima(g, workspace, d->flags);
+}
+
 int simnets_similarity_input_grad(const simnets_sim_desc* d, const void* x, const void* t, const void* w, const void* dy,
                                   void* dx, void* ws, size_t ws_bytes, void* stream) {
     SimGeo g;

@@ -40,8 +40,13 @@ namespace simnets {
 // tiled_*.cu -- float32 generalized-GEMM tile kernels for the hot shapes
 bool sim_use_tiled(const SimGeo&, bool f64, uint32_t flags);
 size_t sim_workspace_bytes(const SimGeo&, bool f64, uint32_t flags);
-cudaError_t launch_sim_fwd_tiled(const SimGeo&, const float* x, const float* t, const float* w, float* y, void* ws, uint32_t flags, cudaStream_t);
+// ch_max / ch_min: when given, also the per-pixel extrema of y over the instances ([B][N] each)
+cudaError_t launch_sim_fwd_tiled(const SimGeo&, const float* x, const float* t, const float* w, float* y, void* ws, uint32_t flags, cudaStream_t,
+                                 float* ch_max = nullptr, float* ch_min = nullptr);
 bool sim_tc_shape(const SimGeo&, uint32_t flags);
+float* mex_workspace_maxima(const MexGeo&, void* ws, uint32_t flags);
+// per-pixel maximum and minimum over the instances of a Similarity output y[B][M][N] (NaN entries ignored); either may be null
+cudaError_t launch_sim_extrema(const SimGeo&, const float* y, float* ch_max, float* ch_min, cudaStream_t);
 size_t sim_tc_tile_floats(const SimGeo&);
 cudaError_t launch_sim_fwd_tc(const SimGeo&, const float* x, const float* planes, const float* cm, const int2* taps, float* tiles,
                               float* bias, int* flag, float* y, cudaStream_t);
@@ -50,7 +55,8 @@ cudaError_t launch_sim_dparams_tiled(const SimGeo&, const float* x, const float*
                                      float* dt, float* dw, bool accumulate, void* ws, cudaStream_t);
 // sim_smallk.cu -- forward for short patches (K <= 32): patches in registers, two positions per thread
 bool sim_smallk_shape(const SimGeo&);
-cudaError_t launch_sim_fwd_smallk(const SimGeo&, const float* x, const float* planes, const float* cm, const int2* taps, float* y, cudaStream_t);
+cudaError_t launch_sim_fwd_smallk(const SimGeo&, const float* x, const float* planes, const float* cm, const int2* taps, float* y,
+                                  float* ch_max, float* ch_min, cudaStream_t);
 bool mex_use_tiled(const MexGeo&, bool f64, uint32_t flags);
 size_t mex_workspace_bytes(const MexGeo&, bool f64, uint32_t flags);
 // pooled: when given, the 2x2 sum pooling of y is produced as well (fused into the pair-tile kernel, a pooling launch behind the others)

@@ -451,12 +451,12 @@ cudaError_t run_prepasses(const MexGeo& g, const MexWs& w, const float* x, const
     const long long total = (long long)g.B * g.N;
     // (measured on 32x32x64, 16x16x128 and 8x8x256 maps at batches 256 and 2048: eight threads per position win for
     // long patches while one thread per position would not fill the GPU's thread slots: 2048 per multiprocessor)
-    if (g.K >= 128 && total < 148LL * 2048) {
-        const int grid = int(std::min<long long>((total + 31) / 32, 148LL * 32));
+    if (g.K >= 128 && total < (long long)device_sm_count() * 2048) {
+        const int grid = int(std::min<long long>((total + 31) / 32, (long long)device_sm_count() * 32));
         if (g.bh == 1 && g.bw == 1) mex_colmax_sliced<true><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
         else mex_colmax_sliced<false><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
     } else {
-        const int grid = int(std::min<long long>((total + 255) / 256, 148LL * 16));
+        const int grid = int(std::min<long long>((total + 255) / 256, (long long)device_sm_count() * 16));
         if (g.bh == 1 && g.bw == 1) mex_colmax<true><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
         else mex_colmax<false><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
     }
@@ -473,6 +473,12 @@ bool forward_primes_workspace(MexGeo g, uint32_t flags) {
 }
 
 }  // namespace
+
+// where the forward pass of this shape reads the per-position extrema from, or nullptr if it computes them on the fly
+float* mex_workspace_maxima(const MexGeo& g, void* ws, uint32_t flags) {
+    if (use_smallk_kernels(g, flags) || smallm_shape(g)) return nullptr;
+    return carve(g, ws).mx;
+}
 
 bool mex_use_tiled(const MexGeo& g, bool f64, uint32_t flags) {
     if (f64 || !g.finite || g.B == 0) return false;
@@ -514,7 +520,8 @@ static cudaError_t mex_fwd_tiled_body(const MexGeo& g, const float* x, const flo
         if (e != cudaSuccess) return e;
         return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);
     }
-    cudaError_t e = run_prepasses(g, w, x, off, s, true, pair_prep(g, flags));
+    // (the caller may have had the layer in front leave the per-position extrema in the workspace: SIMNETS_FLAG_MEX_MAXIMA_GIVEN)
+    cudaError_t e = run_prepasses(g, w, x, off, s, !(flags & SIMNETS_FLAG_MEX_MAXIMA_GIVEN), pair_prep(g, flags));
     if (e != cudaSuccess) return e;
     if (use_tc_kernels(g, flags)) {
         if (use_pair_kernels(g, flags, x, y, y, y)) {
@@ -663,7 +670,7 @@ cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* 
                                                      : launch_mex_doff_tc(g, x, w.mo, w.mx, y, dy, w.part, tsplits, w.flag, s);
         if (e != cudaSuccess) return e;
         const long long n = (long long)g.R * g.M * g.K;
-        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, g.K, tsplits, w.part, w.eo, doff, accumulate, w.flag);
+        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, (long long)device_sm_count() * 8)), 256, 0, s>>>(n, g.K, tsplits, w.part, w.eo, doff, accumulate, w.flag);
         count_launch();
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
@@ -674,7 +681,7 @@ cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* 
         e = launch_mex_doff_smallk(g, x, w.mo, y, dy, w.part, splits, w.flag, s);
         if (e != cudaSuccess) return e;
         const long long n = (long long)g.R * g.M * g.K;
-        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, g.K, splits, w.part, w.eo, doff, accumulate, w.flag);
+        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, (long long)device_sm_count() * 8)), 256, 0, s>>>(n, g.K, splits, w.part, w.eo, doff, accumulate, w.flag);
         count_launch();
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
@@ -685,7 +692,7 @@ cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* 
         e = launch_mex_bwd_head(g, false, true, x, w.eo, w.mo, w.mx, y, dy, nullptr, w.part, hs, w.flag, s);
         if (e != cudaSuccess) return e;
         const long long n = (long long)g.R * g.M * g.K;
-        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, g.K, hs, w.part, w.eo, doff, accumulate, w.flag);
+        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, (long long)device_sm_count() * 8)), 256, 0, s>>>(n, g.K, hs, w.part, w.eo, doff, accumulate, w.flag);
         count_launch();
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
@@ -695,7 +702,7 @@ cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* 
         e = launch_mex_doff_smallm(g, x, w.mo, w.mx, y, dy, w.part, splits, w.flag, s);
         if (e != cudaSuccess) return e;
         const long long n = (long long)g.R * g.M * g.K;
-        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, g.K, splits, w.part, w.eo, doff, accumulate, w.flag);
+        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, (long long)device_sm_count() * 8)), 256, 0, s>>>(n, g.K, splits, w.part, w.eo, doff, accumulate, w.flag);
         count_launch();
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
@@ -709,7 +716,7 @@ cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* 
     else { if (sp1) DOFF(64, 32, true); else DOFF(64, 32, false); }
 #undef DOFF
     const long long n = (long long)g.R * g.M * g.K;
-    mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, g.K, splits, w.part, w.eo, doff, accumulate, w.flag);
+    mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, (long long)device_sm_count() * 8)), 256, 0, s>>>(n, g.K, splits, w.part, w.eo, doff, accumulate, w.flag);
     count_launch(2);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
@@ -732,7 +739,7 @@ cudaError_t launch_mex_backward_tiled(const MexGeo& g, const float* x, const flo
         e = launch_mex_bwd_head(g, true, true, x, w.eo, w.mo, w.mx, y, dy, dx, w.part, hs, w.flag, s);
         if (e != cudaSuccess) return e;
         const long long n = (long long)g.R * g.M * g.K;
-        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, 148LL * 8)), 256, 0, s>>>(n, g.K, hs, w.part, w.eo, doff, accumulate, w.flag);
+        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, (long long)device_sm_count() * 8)), 256, 0, s>>>(n, g.K, hs, w.part, w.eo, doff, accumulate, w.flag);
         count_launch();
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;

@@ -37,7 +37,7 @@ __device__ __forceinline__ SkColumn sk_column(const SimGeo& g, long long j, long
 template <int MODE, int KT>
 __global__ void __launch_bounds__(kSkThreads, kSkBlocksPerSm) sim_fwd_smallk(SimGeo g, const float* __restrict__ x, const float* __restrict__ planes,
                                                                const float* __restrict__ cm, const int2* __restrict__ taps,
-                                                               float* __restrict__ y) {
+                                                               float* __restrict__ y, float* __restrict__ ch_max, float* __restrict__ ch_min) {
     constexpr bool MASKED = MODE == SIM_L2N_NAN || MODE == SIM_L1_SKIP;
     constexpr bool L1 = MODE == SIM_L1 || MODE == SIM_L1_SKIP;
     constexpr int MQ = 4;                                   // templates walked together: four independent accumulator chains
@@ -85,6 +85,8 @@ __global__ void __launch_bounds__(kSkThreads, kSkBlocksPerSm) sim_fwd_smallk(Sim
             nx[k] = make_float2(-a, -b);
         }
         const bool pair_store = c1.base == c0.base + 1 && ((c0.base & 1) == 0) && ((((long long)g.N) & 1) == 0);
+        // per-pixel extrema over the instances, for a consumer that stabilises a log-sum-exp over them (NaN ignored)
+        float2 vmax = make_float2(-CUDART_INF_F, -CUDART_INF_F), vmin = make_float2(CUDART_INF_F, CUDART_INF_F);
 #pragma unroll 1
         for (int m0 = 0; m0 < Mq; m0 += MQ) {
             float2 acc[MQ];
@@ -119,6 +121,8 @@ __global__ void __launch_bounds__(kSkThreads, kSkBlocksPerSm) sim_fwd_smallk(Sim
                     v.x += cmm; v.y += cmm;
                     if (g.batch_quirk) { v.x += quirk_c * float(g.B - 1 - c0.n); v.y += quirk_c * float(g.B - 1 - c1.n); }
                 }
+                vmax = make_float2(fmaxf(vmax.x, v.x), fmaxf(vmax.y, v.y));
+                vmin = make_float2(fminf(vmin.x, v.x), fminf(vmin.y, v.y));
                 if (c0.base >= 0) {
                     float* dst = y + c0.base + (long long)m * g.N;
                     if (pair_store) __stcs(reinterpret_cast<float2*>(dst), v);
@@ -129,13 +133,31 @@ __global__ void __launch_bounds__(kSkThreads, kSkBlocksPerSm) sim_fwd_smallk(Sim
                 }
             }
         }
+        if (ch_max != nullptr || ch_min != nullptr) {
+            const long long q0 = c0.base - (long long)c0.n * (g.M - 1) * g.N, q1 = c1.base - (long long)c1.n * (g.M - 1) * g.N;      // n * N + pos
+            if (c0.base >= 0) { if (ch_max) ch_max[q0] = vmax.x; if (ch_min) ch_min[q0] = vmin.x; }
+            if (c1.base >= 0) { if (ch_max) ch_max[q1] = vmax.y; if (ch_min) ch_min[q1] = vmin.y; }
+        }
+    }
+}
+
+// The same extrema from a finished output tensor, for the forward kernels that do not produce them on the way
+__global__ void __launch_bounds__(256) sim_extrema(long long P, int M, int N, const float* __restrict__ y, float* __restrict__ ch_max, float* __restrict__ ch_min) {
+    for (long long q = blockIdx.x * 256LL + threadIdx.x; q < P; q += (long long)gridDim.x * 256) {
+        const long long n = q / N;
+        const float* p = y + n * (long long)M * N + (q - n * N);
+        float hi = -CUDART_INF_F, lo = CUDART_INF_F;
+        for (int m = 0; m < M; ++m) { const float v = __ldg(p + (long long)m * N); hi = fmaxf(hi, v); lo = fminf(lo, v); }
+        if (ch_max) ch_max[q] = hi;
+        if (ch_min) ch_min[q] = lo;
     }
 }
 
 size_t sk_smem_bytes(const SimGeo& g) { return (size_t)g.K * ((g.M + 3) / 4 * 4) * (16 + (g.mode == SIM_L2N_NAN ? 8 : 0)); }
 
 template <int KT>
-cudaError_t launch_sk(const SimGeo& g, const float* x, const float* planes, const float* cm, const int2* taps, float* y, cudaStream_t s) {
+cudaError_t launch_sk(const SimGeo& g, const float* x, const float* planes, const float* cm, const int2* taps, float* y, float* ch_max,
+                      float* ch_min, cudaStream_t s) {
     const long long P = (long long)g.B * g.N;
     const size_t smem = sk_smem_bytes(g);
     const long long want = (P / 2 + kSkThreads - 1) / kSkThreads;
@@ -148,7 +170,7 @@ cudaError_t launch_sk(const SimGeo& g, const float* x, const float* planes, cons
             if (e_ != cudaSuccess) return e_;                                                                          \
             attr_done = true;                                                                                          \
         }                                                                                                              \
-        sim_fwd_smallk<MODE, KT><<<grid, kSkThreads, smem, s>>>(g, x, planes, cm, taps, y);                              \
+        sim_fwd_smallk<MODE, KT><<<grid, kSkThreads, smem, s>>>(g, x, planes, cm, taps, y, ch_max, ch_min);              \
     } while (0)
     switch (g.mode) {
     case SIM_L1: SK(SIM_L1); break;
@@ -171,13 +193,21 @@ bool sim_smallk_shape(const SimGeo& g) {
 
 // planes, cm, taps: as sim_prep leaves them in the workspace
 cudaError_t launch_sim_fwd_smallk(const SimGeo& g, const float* x, const float* planes, const float* cm, const int2* taps, float* y,
-                                  cudaStream_t s) {
+                                  float* ch_max, float* ch_min, cudaStream_t s) {
     switch (g.K) {
-    case 4: return launch_sk<4>(g, x, planes, cm, taps, y, s);
-    case 9: return launch_sk<9>(g, x, planes, cm, taps, y, s);
-    case 12: return launch_sk<12>(g, x, planes, cm, taps, y, s);
-    default: return launch_sk<27>(g, x, planes, cm, taps, y, s);
+    case 4: return launch_sk<4>(g, x, planes, cm, taps, y, ch_max, ch_min, s);
+    case 9: return launch_sk<9>(g, x, planes, cm, taps, y, ch_max, ch_min, s);
+    case 12: return launch_sk<12>(g, x, planes, cm, taps, y, ch_max, ch_min, s);
+    default: return launch_sk<27>(g, x, planes, cm, taps, y, ch_max, ch_min, s);
     }
+}
+
+cudaError_t launch_sim_extrema(const SimGeo& g, const float* y, float* ch_max, float* ch_min, cudaStream_t s) {
+    const long long P = (long long)g.B * g.N;
+    if (P == 0 || (ch_max == nullptr && ch_min == nullptr)) return cudaSuccess;
+    sim_extrema<<<int(std::min<long long>((P + 255) / 256, (long long)device_sm_count() * 16)), 256, 0, s>>>(P, g.M, g.N, y, ch_max, ch_min);
+    count_launch();
+    return cudaGetLastError();
 }
 
 }  // namespace simnets

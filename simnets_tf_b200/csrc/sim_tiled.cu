@@ -541,8 +541,19 @@ size_t sim_workspace_bytes(const SimGeo& g, bool f64, uint32_t flags) {
     return carve(g, nullptr).bytes;
 }
 
+static cudaError_t sim_fwd_tiled_body(const SimGeo& g, const float* x, const float* t, const float* w, float* y, void* ws, uint32_t flags,
+                                      cudaStream_t s, float* ch_max, float* ch_min, bool* extrema_done);
+
 cudaError_t launch_sim_fwd_tiled(const SimGeo& g, const float* x, const float* t, const float* w, float* y, void* ws, uint32_t flags,
-                                 cudaStream_t s) {
+                                 cudaStream_t s, float* ch_max, float* ch_min) {
+    bool done = false;
+    const cudaError_t e = sim_fwd_tiled_body(g, x, t, w, y, ws, flags, s, ch_max, ch_min, &done);
+    if (e != cudaSuccess || done) return e;
+    return launch_sim_extrema(g, y, ch_max, ch_min, s);
+}
+
+static cudaError_t sim_fwd_tiled_body(const SimGeo& g, const float* x, const float* t, const float* w, float* y, void* ws, uint32_t flags,
+                                      cudaStream_t s, float* ch_max, float* ch_min, bool* extrema_done) {
     const SimWs W = carve(g, ws);
     launch_prep(g, W, t, w, s);
     if (sim_tc_shape(g, flags)) {
@@ -552,7 +563,7 @@ cudaError_t launch_sim_fwd_tiled(const SimGeo& g, const float* x, const float* t
         if (e != cudaSuccess) return e;
         return launch_sim_fwd_direct(g, false, x, t, w, y, s, W.flag);
     }
-    if (sim_smallk_shape(g)) return launch_sim_fwd_smallk(g, x, W.planes, W.cm, W.taps, y, s);
+    if (sim_smallk_shape(g)) { *extrema_done = true; return launch_sim_fwd_smallk(g, x, W.planes, W.cm, W.taps, y, ch_max, ch_min, s); }
     const long long P = (long long)g.B * g.N;
     const bool wide = g.M > 64;
     const long long blocks = ((P + 127) / 128) * ((g.M + (wide ? 127 : 63)) / (wide ? 128 : 64));

@@ -16,6 +16,8 @@ from . import _lib, abi
 from .ops.mex import _expand_dim_specification, _mex_dims_helper
 from .ops.mex import mex as _mex
 from .ops.mex import mex_sum_pool2 as _mex_sum_pool2
+from .ops.mex import mex_in_workspace as _mex_in_workspace, mex_layer_workspace_for as _mex_layer_workspace_for
+from .ops.mex import mex_workspace_maxima as _mex_workspace_maxima
 from .ops.similarity import similarity_of_raw_weights as _similarity_of_raw_weights
 
 
@@ -84,7 +86,9 @@ class Similarity(torch.nn.Module):
         out = [shape[0], self.num_instances, oh.value, ow.value]
         return tuple([out[0], out[2], out[3], out[1]] if self.channels_last else out)
 
-    def forward(self, x):
+    def forward(self, x, extrema=None):
+        """extrema=(max_address, min_address): also write the per-pixel maximum / minimum of the output over the
+        templates to those device addresses (see Mex.extrema_slot)."""
         if self.templates is None:
             self.build(tuple(x.shape), x.device, x.dtype)
         if self.channels_last:
@@ -94,7 +98,8 @@ class Similarity(torch.nn.Module):
                                        blocks=self.blocks, strides=self.strides, padding=self.padding,
                                        normalization_term=self.normalization_term,
                                        normalization_term_fudge=self.normalization_term_fudge,
-                                       ignore_nan_input=self.ignore_nan_input, out_of_bounds_value=self.out_of_bounds_value)
+                                       ignore_nan_input=self.ignore_nan_input, out_of_bounds_value=self.out_of_bounds_value,
+                                       extrema=extrema)
         return y.permute(0, 2, 3, 1) if self.channels_last else y
 
     def get_config(self):
@@ -226,13 +231,40 @@ class Mex(torch.nn.Module):
         flat = self.offsets.reshape(self.offsets.shape[0] * self.offsets.shape[1], -1)
         return (flat - torch.logsumexp(flat, dim=1, keepdim=True)).reshape(self.offsets.shape)
 
-    def forward(self, x, sum_pool2=False):
+    def _op_attrs(self):
+        return dict(blocks=self.blocks, padding=self.padding, strides=self.strides, use_unshared_regions=self.use_unshared_regions,
+                    shared_offset_region=self.shared_offset_region, blocks_out_of_bounds_value=self.blocks_out_of_bounds_value,
+                    blocks_round_down=self.blocks_round_down, unshared_offset_region=self.unshared_offset_region,
+                    epsilon=self.epsilon, softmax_mode=self.softmax_mode)
+
+    def extrema_slot(self, input_shape, dtype, device, sum_pool2=False):
+        """For a layer whose every patch is exactly the channels of one pixel (blocks [C, 1, 1], unit spatial strides, no
+        padding): (workspace, device address, want_max) -- a layer workspace made ahead of the call and the place in it
+        where the forward pass expects the per-pixel maximum (epsilon > 0) or minimum of its input over the channels.
+        The layer in front writes them there while it produces that input (`Similarity.forward(x, extrema=...)`), and
+        `forward(x, layer_ws=workspace, maxima_given=True)` then skips its own pass over the input.  None otherwise."""
+        if self.channels_last or dtype != torch.float32 or device.type != "cuda":
+            return None
+        if self.offsets is None:
+            self.build(tuple(input_shape), device, dtype)
+        b, c, h, w = [int(e) for e in input_shape]
+        if list(self.blocks) != [c, 1, 1] or list(self.strides)[1:] != [1, 1] or any(int(p) != 0 for p in self.padding) or b == 0:
+            return None
+        ws = _mex_layer_workspace_for((b, c, h, w), dtype, device, self.num_instances, pooled=sum_pool2, **self._op_attrs())
+        ptr = _mex_workspace_maxima((b, c, h, w), dtype, self.num_instances, ws, **self._op_attrs())
+        return None if ptr is None else (ws, ptr, float(self.epsilon) > 0)
+
+    def forward(self, x, sum_pool2=False, layer_ws=None, maxima_given=False):
         """sum_pool2=True returns the 2x2 sum pooling of the layer's output (pooling gradient fused into the
-        MEX gradient kernels)."""
+        MEX gradient kernels).  layer_ws / maxima_given: see extrema_slot."""
         if self.offsets is None:
             self.build(tuple(x.shape), x.device, x.dtype)
         if self.channels_last:
             x = x.permute(0, 3, 1, 2)
+        if layer_ws is not None:
+            y = _mex_in_workspace(x, self.effective_offsets(), self.num_instances, layer_ws,
+                                  fwd_flags=abi.FLAG_MEX_MAXIMA_GIVEN if maxima_given else 0, sum_pool2=sum_pool2, **self._op_attrs())
+            return y.permute(0, 2, 3, 1) if self.channels_last else y
         op = _mex_sum_pool2 if sum_pool2 else _mex
         y = op(x, self.effective_offsets(), self.num_instances, blocks=self.blocks, padding=self.padding,
                  strides=self.strides, use_unshared_regions=self.use_unshared_regions,

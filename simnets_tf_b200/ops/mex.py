@@ -60,13 +60,18 @@ def _expand_dim_specification(image_shape, dim_spec):
     return dim_spec
 
 
-def _desc(input, num_instances, attrs, flags=0):
-    if input.dim() != 4:
+def _desc_of(shape, dtype, num_instances, attrs, flags=0):
+    if len(shape) != 4:
         raise ValueError("input must be 4-D")
-    return abi.make_mex_desc(input.shape, num_instances, attrs["softmax_mode"], attrs["padding"], attrs["strides"],
+    return abi.make_mex_desc(shape, num_instances, attrs["softmax_mode"], attrs["padding"], attrs["strides"],
                              attrs["blocks"], attrs["epsilon"], attrs["blocks_out_of_bounds_value"], attrs["blocks_round_down"],
                              attrs["use_unshared_regions"], attrs["shared_offset_region"], attrs["unshared_offset_region"],
-                             dtype=dtype_code(input), flags=flags | _torch_glue.DEFAULT_FLAGS)
+                             dtype=abi.F32 if dtype == torch.float32 else abi.F64, flags=flags | _torch_glue.DEFAULT_FLAGS)
+
+
+def _desc(input, num_instances, attrs, flags=0):
+    dtype_code(input)           # (rejects anything but float32 / float64)
+    return _desc_of(tuple(input.shape), input.dtype, num_instances, attrs, flags)
 
 
 def _geometry(d):
@@ -112,13 +117,27 @@ def mex_layer_workspace(input, num_instances, pooled=False, flags=0, **attrs):
     """A workspace of one layer's own, large enough for its forward and gradient calls: give it to `mex_forward`
     as `workspace=` and to the gradient ops as `primed_workspace=`, and they reuse the per-position maxima and
     the offsets tables of the forward pass instead of computing them again."""
+    return mex_layer_workspace_for(tuple(input.shape), input.dtype, require_cuda(input), num_instances, pooled=pooled, flags=flags, **attrs)
+
+
+def mex_layer_workspace_for(input_shape, dtype, device, num_instances, pooled=False, flags=0, **attrs):
+    """`mex_layer_workspace` for an input that does not exist yet (shape, dtype and device given)."""
     attrs = _attrs(**attrs)
-    dev = require_cuda(input)
     n = 256
     for f in (flags, flags | (abi.FLAG_MEX_DY_POOLED2 if pooled else 0)):
-        d = _desc(input, num_instances, attrs, f)
+        d = _desc_of(input_shape, dtype, num_instances, attrs, f)
         n = max(n, int(_lib.lib().simnets_mex_workspace_bytes(C.byref(d))))
-    return torch.empty(n, dtype=torch.uint8, device=dev)
+    return torch.empty(n, dtype=torch.uint8, device=device)
+
+
+def mex_workspace_maxima(input_shape, dtype, num_instances, workspace, flags=0, **attrs):
+    """Device address inside `workspace` (a tensor from `mex_layer_workspace`) where the forward pass of this layer reads the
+    per-position extrema of its patches, or None for shapes that find them on the fly.  A layer in front that writes them
+    there (ops.similarity.similarity_forward(..., extrema=...)) lets `mex_forward(..., flags=FLAG_MEX_MAXIMA_GIVEN)` skip
+    its own pass over the input; only valid when every patch is exactly the channels of one pixel."""
+    d = _desc_of(tuple(input_shape), dtype, num_instances, _attrs(**attrs), flags)
+    p = _lib.lib().simnets_mex_workspace_maxima(C.byref(d), workspace.data_ptr())
+    return int(p) if p else None
 
 
 def _primed(flags, primed_workspace):
@@ -242,15 +261,16 @@ def _gradients(ctx, grad, pooled):
     return gi, go, None, None
 
 
-def _forward_for_autograd(ctx, input, offsets, num_instances, attrs, pooled):
+def _forward_for_autograd(ctx, input, offsets, num_instances, attrs, pooled, layer_ws=None, fwd_flags=0):
     # a differentiated layer runs in a workspace of its own, which its gradient pass then finds primed
-    ctx.layer_ws = None
-    if (ctx.needs_input_grad[0] or ctx.needs_input_grad[1]) and input.is_cuda and input.shape[0] > 0:
+    # (layer_ws: the caller made that workspace already, e.g. to have the layer in front fill in the extrema)
+    ctx.layer_ws = layer_ws
+    if layer_ws is None and (ctx.needs_input_grad[0] or ctx.needs_input_grad[1]) and input.is_cuda and input.shape[0] > 0:
         ctx.layer_ws = mex_layer_workspace(input, num_instances, pooled=pooled, **attrs)
     if pooled and input.dtype == torch.float32 and input.shape[0] > 0:
-        y, out = mex_forward_pool2(input, offsets, num_instances, workspace=ctx.layer_ws, **attrs)
+        y, out = mex_forward_pool2(input, offsets, num_instances, flags=fwd_flags, workspace=ctx.layer_ws, **attrs)
     else:
-        y = out = mex_forward(input, offsets, num_instances, workspace=ctx.layer_ws, **attrs)
+        y = out = mex_forward(input, offsets, num_instances, flags=fwd_flags, workspace=ctx.layer_ws, **attrs)
         if pooled:
             out = torch.nn.functional.avg_pool2d(y, 2) * 4.0
     ctx.attrs, ctx.num_instances = attrs, num_instances
@@ -260,12 +280,12 @@ def _forward_for_autograd(ctx, input, offsets, num_instances, attrs, pooled):
 
 class _Mex(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, input, offsets, num_instances, attrs):
-        return _forward_for_autograd(ctx, input, offsets, num_instances, attrs, False)
+    def forward(ctx, input, offsets, num_instances, attrs, layer_ws=None, fwd_flags=0):
+        return _forward_for_autograd(ctx, input, offsets, num_instances, attrs, False, layer_ws, fwd_flags)
 
     @staticmethod
     def backward(ctx, grad):
-        return _gradients(ctx, grad, False)
+        return _gradients(ctx, grad, False) + (None, None)
 
 
 def sum_pool2x2(y):
@@ -284,12 +304,12 @@ class _MexSumPool2(torch.autograd.Function):
     positions it summed) is never written out: the MEX gradient kernels read the pooled dy directly."""
 
     @staticmethod
-    def forward(ctx, input, offsets, num_instances, attrs):
-        return _forward_for_autograd(ctx, input, offsets, num_instances, attrs, True)
+    def forward(ctx, input, offsets, num_instances, attrs, layer_ws=None, fwd_flags=0):
+        return _forward_for_autograd(ctx, input, offsets, num_instances, attrs, True, layer_ws, fwd_flags)
 
     @staticmethod
     def backward(ctx, grad):
-        return _gradients(ctx, grad, True)
+        return _gradients(ctx, grad, True) + (None, None)
 
 
 def mex(input, offsets, num_instances, softmax_mode=None, padding=None, strides=None, blocks=None, epsilon=None,
@@ -308,7 +328,7 @@ def mex(input, offsets, num_instances, softmax_mode=None, padding=None, strides=
     return _Mex.apply(input, offsets, num_instances, attrs)
 
 
-def mex_sum_pool2(input, offsets, num_instances, **kwargs):
+def mex_sum_pool2(input, offsets, num_instances, layer_ws=None, fwd_flags=0, **kwargs):
     """`mex(...)` followed by a 2x2 sum pooling (the MEX + pooling pair of the reference's example networks,
     README.md:114-131, where the pooling is `4 * AveragePooling2D(2)`), with the pooling's backward folded into
     the MEX gradient kernels.  Same keyword arguments as `mex`.  Falls back to the two separate ops when the
@@ -317,4 +337,13 @@ def mex_sum_pool2(input, offsets, num_instances, **kwargs):
     g = _geometry(_desc(input, num_instances, attrs))
     if g.height_out % 2 or g.width_out % 2:
         return torch.nn.functional.avg_pool2d(_Mex.apply(input, offsets, num_instances, attrs), 2) * 4.0
-    return _MexSumPool2.apply(input, offsets, num_instances, attrs)
+    return _MexSumPool2.apply(input, offsets, num_instances, attrs, layer_ws, fwd_flags)
+
+
+def mex_in_workspace(input, offsets, num_instances, layer_ws, fwd_flags=0, sum_pool2=False, **kwargs):
+    """`mex(...)` (or `mex_sum_pool2(...)`) run in a layer workspace the caller made (`mex_layer_workspace_for`), with extra
+    flags for the forward call only, e.g. abi.FLAG_MEX_MAXIMA_GIVEN after the layer in front has filled in the extrema."""
+    attrs = _attrs(**{k: v for k, v in kwargs.items() if k != "name"})
+    if sum_pool2:
+        return mex_sum_pool2(input, offsets, num_instances, layer_ws=layer_ws, fwd_flags=fwd_flags, **attrs)
+    return _Mex.apply(input, offsets, num_instances, attrs, layer_ws, fwd_flags)

@@ -54,8 +54,9 @@ def _ws(d, dev):
     return buf.data_ptr(), buf.numel()
 
 
-def similarity_forward(input, templates, weights, flags=0, **attrs):
-    """The `Similarity` op: [batch, templates, out_h, out_w]."""
+def similarity_forward(input, templates, weights, flags=0, extrema=None, **attrs):
+    """The `Similarity` op: [batch, templates, out_h, out_w].  `extrema=(max_ptr, min_ptr)`: device addresses (or None)
+    that receive the per-pixel maximum / minimum of the output over the templates, float32 [batch, out_h, out_w]."""
     attrs = _attrs(**attrs)
     dev = require_cuda(input, templates, weights)
     input, templates, weights = input.contiguous(), templates.contiguous(), weights.contiguous()
@@ -66,8 +67,12 @@ def similarity_forward(input, templates, weights, flags=0, **attrs):
     with torch.cuda.device(dev):
         ws, n = _ws(d, dev)
         with timed("similarity_forward", *_cost(d, y.numel(), "fwd")):
-            _lib.check(_lib.lib().simnets_similarity_forward(C.byref(d), input.data_ptr(), templates.data_ptr(), weights.data_ptr(),
-                                                             y.data_ptr(), ws, n, stream_ptr(dev)))
+            if extrema is not None and (extrema[0] or extrema[1]):
+                _lib.check(_lib.lib().simnets_similarity_forward_extrema(C.byref(d), input.data_ptr(), templates.data_ptr(), weights.data_ptr(),
+                                                                         y.data_ptr(), extrema[0], extrema[1], ws, n, stream_ptr(dev)))
+            else:
+                _lib.check(_lib.lib().simnets_similarity_forward(C.byref(d), input.data_ptr(), templates.data_ptr(), weights.data_ptr(),
+                                                                 y.data_ptr(), ws, n, stream_ptr(dev)))
     return y
 
 
@@ -110,10 +115,10 @@ def similarity_parameters_grad(input, templates, weights, output_grad, flags=0, 
 
 class _Similarity(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, input, templates, weights, attrs, flags=0):
+    def forward(ctx, input, templates, weights, attrs, flags=0, extrema=None):
         ctx.attrs, ctx.flags = attrs, flags
         ctx.save_for_backward(input, templates, weights)
-        return similarity_forward(input, templates, weights, flags=flags, **attrs)
+        return similarity_forward(input, templates, weights, flags=flags, extrema=extrema, **attrs)
 
     @staticmethod
     def backward(ctx, grad):
@@ -123,7 +128,7 @@ class _Similarity(torch.autograd.Function):
             gi = similarity_input_grad(input, templates, weights, grad, flags=ctx.flags, **ctx.attrs)
         if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
             gt, gw = similarity_parameters_grad(input, templates, weights, grad, flags=ctx.flags, **ctx.attrs)
-        return gi, gt, gw, None, None
+        return gi, gt, gw, None, None, None
 
 
 def similarity(input, templates, weights, similarity_function=None, blocks=None, strides=None, padding=None,
@@ -143,8 +148,8 @@ def similarity(input, templates, weights, similarity_function=None, blocks=None,
     return _Similarity.apply(input, templates, weights, attrs)
 
 
-def similarity_of_raw_weights(input, templates, raw_weights, flags=0, **attrs):
+def similarity_of_raw_weights(input, templates, raw_weights, flags=0, extrema=None, **attrs):
     """`similarity(input, templates, abs(raw_weights), ...)`, differentiable w.r.t. all three tensors, with the absolute
     value and its gradient taken inside the library's kernels (abi.FLAG_SIM_ABS_WEIGHTS): what the reference's Keras
     layer computes with `K.abs(self.sweights)` in front of the op (python/simnets/keras.py:65)."""
-    return _Similarity.apply(input, templates, raw_weights, _attrs(**attrs), flags | abi.FLAG_SIM_ABS_WEIGHTS)
+    return _Similarity.apply(input, templates, raw_weights, _attrs(**attrs), flags | abi.FLAG_SIM_ABS_WEIGHTS, extrema)

@@ -77,6 +77,7 @@ class SimNet(torch.nn.Module):
                 mods.append(None)
         self.stages = torch.nn.ModuleList([m for m in mods if m is not None])
         self.fuse_pooling = True
+        self.fuse_extrema = True
         self._plan = [(e, m) for e, m in zip(spec["layers"], mods)]
 
     def forward(self, x):
@@ -102,7 +103,19 @@ class SimNet(torch.nn.Module):
         plan, i = self._plan, begin
         while i < end:
             entry, mod = plan[i]
-            if entry[0] == "mex" and self.fuse_pooling and i + 1 < len(plan) and plan[i + 1][0] == ("sumpool", 2):
+            pooled_next = lambda j: self.fuse_pooling and j + 1 < len(plan) and plan[j + 1][0] == ("sumpool", 2)
+            if entry[0] == "similarity" and self.fuse_extrema and i + 1 < end and plan[i + 1][0][0] == "mex":
+                # Similarity -> MEX over the channels of each pixel: the Similarity kernel leaves the per-pixel extrema of its
+                # output in the MEX layer's workspace, and the MEX forward pass skips its pass over that tensor
+                nxt = plan[i + 1][1]
+                slot = nxt.extrema_slot(mod.compute_output_shape(tuple(x.shape)), x.dtype, x.device, sum_pool2=pooled_next(i + 1))
+                if slot is not None:
+                    ws, ptr, up = slot
+                    x = mod(x, extrema=(ptr, None) if up else (None, ptr))
+                    x = nxt(x, sum_pool2=pooled_next(i + 1), layer_ws=ws, maxima_given=True)
+                    i += 3 if pooled_next(i + 1) else 2
+                    continue
+            if entry[0] == "mex" and pooled_next(i):
                 x = mod(x, sum_pool2=True)          # MEX + 2x2 sum pooling, pooling gradient inside the MEX gradient kernels
                 i += 2
                 continue

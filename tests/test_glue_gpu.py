@@ -89,3 +89,61 @@ def test_softmax_cross_entropy_autograd_and_ignored_labels():
     (go,) = torch.autograd.grad(ours * 2.0, logits)
     assert torch.allclose(ours, ref, rtol=1e-5, atol=1e-6)
     assert torch.allclose(go, 2.0 * gr, rtol=1e-5, atol=1e-6)
+
+
+# ---- per-pixel extrema of the Similarity output handed to the MEX layer behind it
+@pytest.mark.parametrize("name", ["dims05", "l1_stride2", "wide_M_K", "params_norm_nan"])
+def test_similarity_forward_extrema(port, name):
+    c = next(c for c in cases.SIM_SMALL if c["name"] == name)
+    d = cases.sim_desc(c)
+    x, t, w, _ = cases.sim_inputs(c, port.sim_out_shape(d))
+    ref = port.similarity_forward(d, x, t, w)
+    B, M, oh, ow = ref.shape
+    hi = torch.full((B, oh, ow), 7.0, device="cuda")
+    lo = torch.full((B, oh, ow), 7.0, device="cuda")
+    y = sim_ops.similarity_forward(gpu_util.dev(x), gpu_util.dev(t), gpu_util.dev(w), flags=c["flags"], extrema=(hi.data_ptr(), lo.data_ptr()),
+                                   **cases.sim_attrs(c))
+    cases.assert_parity(y.cpu().numpy(), ref, what="y")
+    # the extrema are those of the tensor the call wrote, NaN entries ignored
+    yn = y.cpu().numpy()
+    assert np.array_equal(hi.cpu().numpy(), np.fmax.reduce(yn, axis=1, initial=-np.inf))
+    assert np.array_equal(lo.cpu().numpy(), np.fmin.reduce(yn, axis=1, initial=np.inf))
+
+
+def test_mex_forward_takes_given_maxima(port, cuda_lib):
+    """SIMNETS_FLAG_MEX_MAXIMA_GIVEN: the per-position extrema are in the workspace already (here written by torch), the
+    forward pass skips its own pass over the input and gives the same bits."""
+    mex_ops = importlib.import_module("simnets_tf_b200.ops.mex")
+    for cname, eps in (("cfg5_mex1_sub", None), ("pair_eps_neg", None)):
+        c = next(c for c in cases.MEX_CONFIGS + cases.MEX_PAIR if c["name"] == cname)
+        d = cases.mex_desc(c)
+        x, off, _ = cases.mex_inputs(c, port.mex_offsets_shape(d), port.mex_out_shape(d))
+        xd, od = gpu_util.dev(x), gpu_util.dev(off)
+        attrs = cases.mex_attrs(c)
+        plain = mex_ops.mex_forward(xd, od, c["M"], **attrs)
+        ws = mex_ops.mex_layer_workspace(xd, c["M"], **attrs)
+        ptr = mex_ops.mex_workspace_maxima(tuple(xd.shape), xd.dtype, c["M"], ws, **attrs)
+        assert ptr is not None and ws.data_ptr() <= ptr < ws.data_ptr() + ws.numel()
+        ext = xd.amax(dim=1) if c["eps"] > 0 else xd.amin(dim=1)                     # [B, H, W]: blocks span all channels of a pixel
+        slot = ws[ptr - ws.data_ptr():ptr - ws.data_ptr() + 4 * ext.numel()].view(torch.float32)
+        slot.copy_(ext.reshape(-1))
+        given = mex_ops.mex_forward(xd, od, c["M"], flags=abi.FLAG_MEX_MAXIMA_GIVEN, workspace=ws, **attrs)
+        assert torch.equal(plain, given)
+        cases.assert_parity(given.cpu().numpy(), port.mex_forward(d, x, off), what="y")
+
+
+def test_network_with_and_without_the_extrema_hand_over():
+    from simnets_tf_b200.simnet import SimNet, SPECS
+    spec = SPECS["cfg5"]
+    rng = np.random.default_rng(3)
+    x = torch.from_numpy(rng.uniform(-0.5, 0.5, size=(6,) + tuple(spec["input_shape"])).astype(np.float32)).cuda()
+    labels = torch.from_numpy(rng.integers(0, spec["classes"], size=6)).cuda()
+    outs = []
+    for fuse in (True, False):
+        net = SimNet(spec, seed=2)
+        net.fuse_extrema = fuse
+        loss = net.loss(x, labels)
+        loss.backward()
+        outs.append([loss.detach()] + [p.grad.clone() for p in net.parameters()])
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
