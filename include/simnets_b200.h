@@ -99,6 +99,14 @@ enum { SIMNETS_SIM_L1 = 0, SIMNETS_SIM_L2 = 1 };
  * (see simnets_mex_workspace_maxima); ignored by shapes for which that function returns NULL. */
 #define SIMNETS_FLAG_MEX_MAXIMA_GIVEN  (1u << 13)
 
+/* MEX entry points that take a workspace, float32: `offsets` holds raw values and the op works on each (region,
+ * instance) row minus its log-sum-exp, as the reference's Keras layer does with `normalize_offsets=True` in front of the
+ * op (python/simnets/keras.py:155-160); the offsets-gradient entry points then return the gradient with respect to
+ * the raw values, d - softmax(row) * sum(d).  Saves the separate normalisation kernels in both directions.  Not accepted
+ * (SIMNETS_E_UNSUPPORTED) by calls that run without a workspace: float64, SIMNETS_FLAG_FORCE_DIRECT, SIMNETS_FLAG_MEX_EXACT,
+ * simnets_mex_forward_static_scratch. */
+#define SIMNETS_FLAG_MEX_NORMALIZED_OFFSETS (1u << 14)
+
 /* MEX gradient entry points only: dy is given at half resolution, dy[batch, M * channels_out, height_out / 2,
  * width_out / 2], each value standing for the 2x2 window of output positions that a 2x2 / stride-2 sum pooling
  * added up (the gradient of such a pooling copies its dy to the four inputs; with this flag the copy is never

@@ -23,6 +23,7 @@ FLAG_MEX_TEST_EXPIRE_WAIT = 1 << 10
 FLAG_SIM_L2_TENSORCORE = 1 << 11
 FLAG_SIM_ABS_WEIGHTS = 1 << 12
 FLAG_MEX_MAXIMA_GIVEN = 1 << 13
+FLAG_MEX_NORMALIZED_OFFSETS = 1 << 14
 
 OK = 0
 E_NULL, E_DESC, E_DTYPE, E_WORKSPACE, E_UNSUPPORTED, E_TOO_LARGE = -1, -2, -3, -4, -5, -6

@@ -189,6 +189,7 @@ int simnets_mex_forward(const simnets_mex_desc* d, const void* x, const void* of
     if (rc) return rc;
     if (!off || (g.B > 0 && (!x || !y))) return SIMNETS_E_NULL;
     const bool f64 = d->dtype == SIMNETS_F64;
+    if ((d->flags & SIMNETS_FLAG_MEX_NORMALIZED_OFFSETS) && g.B > 0 && !mex_use_tiled(g, f64, d->flags)) return SIMNETS_E_UNSUPPORTED;
     if (mex_use_tiled(g, f64, d->flags)) {
         if (!ws || ws_bytes < mex_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;
         return from_cuda(launch_mex_fwd_tiled(g, (const float*)x, (const float*)off, (float*)y, ws, d->flags, as_stream(stream)));
@@ -219,6 +220,7 @@ int simnets_mex_forward_pool2x2(const simnets_mex_desc* d, const void* x, const 
         if (!ws || ws_bytes < mex_workspace_bytes(g, false, d->flags)) return SIMNETS_E_WORKSPACE;
         return from_cuda(launch_mex_fwd_tiled(g, (const float*)x, (const float*)off, (float*)y, ws, d->flags, as_stream(stream), (float*)y_pooled));
     }
+    if (d->flags & SIMNETS_FLAG_MEX_NORMALIZED_OFFSETS) return SIMNETS_E_UNSUPPORTED;
     const cudaError_t e = launch_mex_fwd_direct(g, false, x, off, y, as_stream(stream));
     if (e != cudaSuccess) return from_cuda(e);
     return from_cuda(launch_sum_pool2((long long)g.B * g.M * g.Co, g.Ho, g.Wo, (const float*)y, (float*)y_pooled, as_stream(stream)));
@@ -239,6 +241,7 @@ int simnets_mex_forward_static_scratch(const simnets_mex_desc* d, const void* x,
     const int rc = mex_geometry(d, nullptr, &g);
     if (rc) return rc;
     if (!off || (g.B > 0 && (!x || !y))) return SIMNETS_E_NULL;
+    if (d->flags & SIMNETS_FLAG_MEX_NORMALIZED_OFFSETS) return SIMNETS_E_UNSUPPORTED;
     const bool f64 = d->dtype == SIMNETS_F64;
     if (!mex_use_tiled(g, f64, d->flags))        // these shapes run on kernels that need no scratch at all
         return from_cuda(launch_mex_fwd_direct(g, f64, x, off, y, as_stream(stream)));
@@ -252,6 +255,7 @@ int simnets_mex_input_grad(const simnets_mex_desc* d, const void* x, const void*
     if (rc) return rc;
     if (!off || (g.B > 0 && (!x || !y || !dy || !dx))) return SIMNETS_E_NULL;
     const bool f64 = d->dtype == SIMNETS_F64;
+    if ((d->flags & SIMNETS_FLAG_MEX_NORMALIZED_OFFSETS) && g.B > 0 && !mex_use_tiled(g, f64, d->flags)) return SIMNETS_E_UNSUPPORTED;
     if (mex_use_tiled(g, f64, d->flags)) {
         if (!ws || ws_bytes < mex_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;
         return from_cuda(launch_mex_dx_tiled(g, (const float*)x, (const float*)off, (const float*)y, (const float*)dy, (float*)dx,
@@ -267,6 +271,7 @@ int simnets_mex_offsets_grad(const simnets_mex_desc* d, const void* x, const voi
     if (rc) return rc;
     if (!off || !doff || (g.B > 0 && (!x || !y || !dy))) return SIMNETS_E_NULL;
     const bool f64 = d->dtype == SIMNETS_F64;
+    if ((d->flags & SIMNETS_FLAG_MEX_NORMALIZED_OFFSETS) && g.B > 0 && !mex_use_tiled(g, f64, d->flags)) return SIMNETS_E_UNSUPPORTED;
     const bool acc = (d->flags & SIMNETS_FLAG_ACCUMULATE) != 0;
     if (mex_use_tiled(g, f64, d->flags)) {
         if (!ws || ws_bytes < mex_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;
@@ -283,6 +288,7 @@ int simnets_mex_backward(const simnets_mex_desc* d, const void* x, const void* o
     if (rc) return rc;
     if (!off || !doff || (g.B > 0 && (!x || !y || !dy || !dx))) return SIMNETS_E_NULL;
     const bool f64 = d->dtype == SIMNETS_F64;
+    if ((d->flags & SIMNETS_FLAG_MEX_NORMALIZED_OFFSETS) && g.B > 0 && !mex_use_tiled(g, f64, d->flags)) return SIMNETS_E_UNSUPPORTED;
     const bool acc = (d->flags & SIMNETS_FLAG_ACCUMULATE) != 0;
     if (mex_use_tiled(g, f64, d->flags)) {
         if (!ws || ws_bytes < mex_workspace_bytes(g, f64, d->flags)) return SIMNETS_E_WORKSPACE;

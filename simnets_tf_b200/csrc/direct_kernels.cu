@@ -276,7 +276,7 @@ __global__ void __launch_bounds__(kThreads) mex_doff_direct(MexGeo g, const T* _
 // just fills the GPU keeps the usual case (every CTA reads the flag and returns) at a few microseconds
 inline int grid_for(long long total, bool gated = false) {
     const long long blocks = (total + kThreads - 1) / kThreads;
-    const long long cap = gated ? 148LL * 8 : 148LL * 32;
+    const long long cap = (long long)device_sm_count() * (gated ? 8 : 32);
     return int(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 

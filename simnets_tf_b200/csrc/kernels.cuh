@@ -107,6 +107,7 @@ bool mex_pair_aligned(const void*, const void*, const void*, const void*);
 int mex_pair_nt_fwd(const MexGeo&);
 int mex_pair_nt_dx(const MexGeo&);
 int mex_pair_doff_splits(const MexGeo&);
+size_t mex_pair_tile_floats(const MexGeo&);      // floats of one set of pre-split operand tiles as the pair-tile prepass writes them
 // pooled: when given, also the 2x2 sum pooling of y ([B, M * Co, Ho / 2, Wo / 2]; Ho and Wo even), added up by the epilogue
 cudaError_t launch_mex_fwd_pair(const MexGeo&, const float* x, const float* tiles, const float* mo, const float* mx, float* y,
                                 float* pooled, int* flag, int test_expire, cudaStream_t);

@@ -18,6 +18,9 @@ struct MexWs {           // workspace carve-up, every part 256-byte aligned
     float* part;         // [S][R][M][K] split-q partial sums of the offsets gradient
     float* tc_tiles;     // Eo split into TF32 hi / lo planes, tile by tile in the tensor-core operand layout
     float* tc_tiles_dx;  // the same for the input gradient of the pair-tile kernels (rows = taps), written together with tc_tiles
+    float* offn;         // [R][M][K] offsets minus their row's log-sum-exp, when the caller passes raw offsets
+    float* lse;          // [R][M] that log-sum-exp
+    float* dtmp;         // [R][M][K] offsets gradient with respect to the normalised rows (rows longer than 1024 taps only)
     size_t bytes;
     size_t fwd_bytes;    // bytes the forward pass touches (everything before `part`)
 };
@@ -90,26 +93,50 @@ __host__ inline bool use_tc_kernels(const MexGeo& g, uint32_t flags) {
 }
 __host__ inline bool use_smallk_kernels(const MexGeo& g, uint32_t flags) { return smallk_shape(g) && !use_tc_kernels(g, flags); }
 
-__host__ inline MexWs carve(const MexGeo& g, void* base) {
+// The layout must not depend on whether dy comes pooled: a forward call (full resolution) and the gradient calls that
+// reuse its workspace (possibly with a pooled dy, for which some kernel families are not used) must find every part in
+// the same place.  Sizes are therefore the larger of the two variants.
+__host__ inline MexWs carve(const MexGeo& g_in, void* base) {
     MexWs w;
     char* p = static_cast<char*>(base);
     size_t off = 0;
     auto take = [&](size_t bytes) { char* r = p ? p + off : nullptr; off += align256(bytes); return r; };
+    MexGeo g = g_in;                      // dy at full resolution
+    g.gp = 1; g.Ng = g.N;
+    MexGeo gq = g;                        // dy pooled 2 x 2, where the output size allows it
+    const bool poolable = g.Ho % 2 == 0 && g.Wo % 2 == 0;
+    if (poolable) { gq.gp = 2; gq.Ng = g.N / 4; }
     w.flag = reinterpret_cast<int*>(take(16));
     w.mo = reinterpret_cast<float*>(take(sizeof(float) * g.R * g.M));
     w.eo = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.M * pad4(g.K)));
     w.eot = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.K * pad4(g.M)));
     w.mx = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.B * g.N));
     w.fwd_bytes = off;
-    int max_splits = (tc_shape(g) || tc_smallk_shape(g)) ? std::max(doff_splits(g), mex_tc_doff_splits(g)) : doff_splits(g);
-    if ((tc_shape(g) || tc_smallk_shape(g)) && mex_pair_shape(g)) max_splits = std::max(max_splits, mex_pair_doff_splits(g));
-    if (mex_head_shape(g)) max_splits = std::max(max_splits, mex_head_splits(g));
+    auto splits_of = [](const MexGeo& q) {
+        int s = (tc_shape(q) || tc_smallk_shape(q)) ? std::max(doff_splits(q), mex_tc_doff_splits(q)) : doff_splits(q);
+        if ((tc_shape(q) || tc_smallk_shape(q)) && mex_pair_shape(q)) s = std::max(s, mex_pair_doff_splits(q));
+        if (mex_head_shape(q)) s = std::max(s, mex_head_splits(q));
+        return s;
+    };
+    const int max_splits = std::max(splits_of(g), splits_of(gq));
     size_t part_floats = (size_t)max_splits * g.R * g.M * g.K;
     if (mex_head_shape(g)) part_floats = std::max(part_floats, mex_head_fwd_scratch_floats(g));      // the head's forward pass parks its slice sums here
     w.part = reinterpret_cast<float*>(take(sizeof(float) * part_floats));
     if (mex_head_shape(g)) w.fwd_bytes = off;                      // (so the forward pass of that shape reaches this far)
-    w.tc_tiles = reinterpret_cast<float*>(take((tc_shape(g) || tc_smallk_shape(g)) ? sizeof(float) * mex_tc_tile_floats(g) : 0));
-    w.tc_tiles_dx = reinterpret_cast<float*>(take(((tc_shape(g) || tc_smallk_shape(g)) && mex_pair_shape(g)) ? sizeof(float) * mex_tc_tile_floats(g) : 0));
+    // (the pair-tile kernels tile with 64 or 128 rows where the one-region kernels may use 32: room for the larger of the two)
+    auto tiles_of = [](const MexGeo& q, bool* pair) {
+        const bool tc = tc_shape(q) || tc_smallk_shape(q);
+        *pair = *pair || (tc && mex_pair_shape(q));
+        return tc ? std::max(mex_tc_tile_floats(q), mex_pair_shape(q) ? mex_pair_tile_floats(q) : size_t(0)) : size_t(0);
+    };
+    bool pair = false;
+    const size_t tile_floats = std::max(tiles_of(g, &pair), tiles_of(gq, &pair));
+    w.tc_tiles = reinterpret_cast<float*>(take(sizeof(float) * tile_floats));
+    w.tc_tiles_dx = reinterpret_cast<float*>(take(pair ? sizeof(float) * tile_floats : 0));
+    // raw offsets (SIMNETS_FLAG_MEX_NORMALIZED_OFFSETS): the normalised rows for the exact kernels and each row's log-sum-exp
+    w.offn = reinterpret_cast<float*>(take(sizeof(float) * (size_t)g.R * g.M * g.K));
+    w.lse = reinterpret_cast<float*>(take(sizeof(float) * g.R * g.M));
+    w.dtmp = reinterpret_cast<float*>(take(g.K > 1024 ? sizeof(float) * (size_t)g.R * g.M * g.K : 0));
     w.bytes = off;
     return w;
 }

@@ -1174,6 +1174,13 @@ int mex_pair_nt_fwd(const MexGeo& g) { return pair_nt(g.M); }
 int mex_pair_nt_dx(const MexGeo& g) { return pair_nt(g.K); }
 int mex_pair_doff_splits(const MexGeo& g) { return dopair_plan(g).splits; }
 
+size_t mex_pair_tile_floats(const MexGeo& g) {
+    const int ntf = pair_nt(g.M), ntd = pair_nt(g.K);
+    const size_t fwd = (size_t)g.R * ((g.M + ntf - 1) / ntf) * ((g.K + kTcKT - 1) / kTcKT) * 2 * ntf * kTcKT;
+    const size_t dxf = (size_t)g.R * ((g.K + ntd - 1) / ntd) * ((g.M + kTcKT - 1) / kTcKT) * 2 * ntd * kTcKT;
+    return fwd > dxf ? fwd : dxf;
+}
+
 cudaError_t launch_mex_fwd_pair(const MexGeo& g, const float* x, const float* tiles, const float* mo, const float* mx, float* y,
                                 float* pooled, int* flag, int test_expire, cudaStream_t s) {
     if (pooled != nullptr) {           // the epilogue adds the two halves of every pooling window onto zeros

@@ -42,7 +42,8 @@ __device__ __forceinline__ int prep_core_offset(int row, int k) { return (row >>
 
 __global__ void __launch_bounds__(512) mex_prep_offsets(MexGeo g, int Mp, const float* __restrict__ off, float* __restrict__ mo,
                                                         float* __restrict__ eo, float* __restrict__ eot, int* __restrict__ flag,
-                                                        float* __restrict__ tf, int ntf, float* __restrict__ td, int ntd) {
+                                                        float* __restrict__ tf, int ntf, float* __restrict__ td, int ntd,
+                                                        float* __restrict__ offn, float* __restrict__ lse_out) {
     __shared__ float s_hi[512], s_lo[512];
     __shared__ int s_bad[512];
     const int nt = blockDim.x;                       // 128, or 512 for long rows
@@ -72,8 +73,28 @@ __global__ void __launch_bounds__(512) mex_prep_offsets(MexGeo g, int Mp, const 
     hi = s_hi[0]; lo = s_lo[0]; bad = s_bad[0];
     const float eps = float(g.eps);
     const float ref = eps > 0.f ? hi : lo;
+    // SIMNETS_FLAG_MEX_NORMALIZED_OFFSETS: the op works on offsets minus the log-sum-exp of their row.  Eo = exp(eps (o - ref))
+    // does not change; the row's reference value does, and the shifted row is kept for the exact kernels.
+    float lse = 0.f;
+    if (offn != nullptr) {
+        __syncthreads();
+        const float base = (hi == CUDART_INF_F || hi == -CUDART_INF_F) ? 0.f : hi;      // as a stable log-sum-exp treats infinite maxima
+        float sum = 0.f;
+        if (real) for (int k = threadIdx.x; k < g.K; k += nt) sum += expf(o[k] - base);
+        s_hi[threadIdx.x] = sum;
+        __syncthreads();
+        for (int s = nt / 2; s > 0; s >>= 1) {
+            if (threadIdx.x < s) s_hi[threadIdx.x] += s_hi[threadIdx.x + s];
+            __syncthreads();
+        }
+        lse = base + logf(s_hi[0]);
+        if (real) {
+            for (int k = threadIdx.x; k < g.K; k += nt) offn[(size_t)rm * g.K + k] = o[k] - lse;
+            if (threadIdx.x == 0) lse_out[rm] = lse;
+        }
+    }
     if (real && threadIdx.x == 0) {
-        mo[rm] = ref;
+        mo[rm] = ref - lse;
         if (bad || !(fabsf(eps) * (hi - lo) <= kSafeSpread)) atomicOr(flag, 1);
     }
     // taps up to the padding of the tiles: chunks of 16 for the forward tiles, whole tap tiles for the input-gradient tiles
@@ -415,6 +436,119 @@ __global__ void __launch_bounds__(256) mex_doff_reduce(long long n, int K, int s
     }
 }
 
+// The same reduction for offsets given raw (SIMNETS_FLAG_MEX_NORMALIZED_OFFSETS).  s[k] is the gradient with respect to the
+// normalised row (the split sums times Eo, or, when a status word is set, what the exact kernel left in the first R M K
+// floats of `part`); the gradient with respect to the raw row is s[k] - softmax(raw)[k] * sum_k s[k], with
+// softmax(raw)[k] = exp(raw[k] - lse).  Rows of up to 1024 taps: one CTA per (region, instance) row, every thread keeps its
+// EPT values of s in registers between the row sum and the final pass (the partial sums are read once).
+template <int EPT>
+__global__ void __launch_bounds__(128) mex_doff_reduce_norm(int K, int splits, long long n, const float* __restrict__ part, const float* __restrict__ eo,
+                                                            const float* __restrict__ raw, const float* __restrict__ lse,
+                                                            float* __restrict__ doff, int accumulate, const int* __restrict__ flag) {
+    __shared__ float red[128];
+    const bool exact = (flag[0] | flag[1]) != 0;
+    const long long row = blockIdx.x;
+    float sk[EPT];
+    float gs = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+        const int k = threadIdx.x + 128 * e;
+        sk[e] = 0.f;
+        if (k < K) {
+            const long long i = row * K + k;
+            if (exact) sk[e] = part[i];
+            else {
+                float a = 0.f;
+                for (int p = 0; p < splits; ++p) a += part[(size_t)p * n + i];
+                sk[e] = a * eo[row * pad4(K) + k];
+            }
+        }
+        gs += sk[e];
+    }
+    red[threadIdx.x] = gs;
+    __syncthreads();
+    for (int s = 64; s > 0; s >>= 1) {
+        if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+        __syncthreads();
+    }
+    gs = red[0];
+    const float l = lse[row];
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+        const int k = threadIdx.x + 128 * e;
+        if (k < K) {
+            const long long i = row * K + k;
+            const float v = sk[e] - expf(raw[i] - l) * gs;
+            doff[i] = accumulate ? doff[i] + v : v;
+        }
+    }
+}
+
+// Longer rows (the classifier head: 10 rows of 8192 taps): the element-parallel reduction into a scratch row set, then the
+// row pass.  `tmp` = gradient with respect to the normalised rows.
+__global__ void __launch_bounds__(256) mex_doff_reduce_tmp(long long n, int K, int splits, const float* __restrict__ part, const float* __restrict__ eo,
+                                                           float* __restrict__ tmp, const int* __restrict__ flag) {
+    const bool exact = (flag[0] | flag[1]) != 0;
+    for (long long i = blockIdx.x * 256LL + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
+        if (exact) { tmp[i] = part[i]; continue; }
+        float s = 0.f;
+        for (int p = 0; p < splits; ++p) s += part[(size_t)p * n + i];
+        tmp[i] = s * eo[(i / K) * pad4(K) + i % K];
+    }
+}
+
+__global__ void __launch_bounds__(256) mex_doff_norm_rows(int K, const float* __restrict__ tmp, const float* __restrict__ raw, const float* __restrict__ lse,
+                                                          float* __restrict__ doff, int accumulate) {
+    __shared__ float red[256];
+    const long long row = blockIdx.x;
+    const float* t = tmp + row * K;
+    float gs = 0.f;
+    for (int k = threadIdx.x; k < K; k += 256) gs += t[k];
+    red[threadIdx.x] = gs;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+        __syncthreads();
+    }
+    gs = red[0];
+    const float l = lse[row];
+    for (int k = threadIdx.x; k < K; k += 256) {
+        const long long i = row * K + k;
+        const float v = t[k] - expf(raw[i] - l) * gs;
+        doff[i] = accumulate ? doff[i] + v : v;
+    }
+}
+
+inline bool mex_norm(uint32_t flags) { return (flags & SIMNETS_FLAG_MEX_NORMALIZED_OFFSETS) != 0; }
+
+// The tail of every offsets-gradient path: the split partial sums become doff, and the exact kernel behind acts only when a
+// status word is set.  With raw offsets the exact kernel goes first, into `part`, and one launch reduces and normalises.
+cudaError_t finish_doff(const MexGeo& g, const MexWs& w, int splits, const float* x, const float* off, const float* y, const float* dy,
+                        float* doff, bool accumulate, uint32_t flags, cudaStream_t s) {
+    const long long n = (long long)g.R * g.M * g.K;
+    if (mex_norm(flags)) {
+        cudaError_t e = launch_mex_doff_direct(g, false, x, w.offn, y, dy, w.part, false, s, w.flag);
+        if (e != cudaSuccess) return e;
+        const int rows = g.R * g.M;
+        if (g.K <= 128) mex_doff_reduce_norm<1><<<rows, 128, 0, s>>>(g.K, splits, n, w.part, w.eo, off, w.lse, doff, accumulate, w.flag);
+        else if (g.K <= 256) mex_doff_reduce_norm<2><<<rows, 128, 0, s>>>(g.K, splits, n, w.part, w.eo, off, w.lse, doff, accumulate, w.flag);
+        else if (g.K <= 512) mex_doff_reduce_norm<4><<<rows, 128, 0, s>>>(g.K, splits, n, w.part, w.eo, off, w.lse, doff, accumulate, w.flag);
+        else if (g.K <= 1024) mex_doff_reduce_norm<8><<<rows, 128, 0, s>>>(g.K, splits, n, w.part, w.eo, off, w.lse, doff, accumulate, w.flag);
+        else {
+            mex_doff_reduce_tmp<<<int(std::min<long long>((n + 255) / 256, (long long)device_sm_count() * 8)), 256, 0, s>>>(n, g.K, splits, w.part, w.eo, w.dtmp, w.flag);
+            mex_doff_norm_rows<<<rows, 256, 0, s>>>(g.K, w.dtmp, off, w.lse, doff, accumulate);
+            count_launch();
+        }
+        count_launch();
+        return cudaGetLastError();
+    }
+    mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, (long long)device_sm_count() * 8)), 256, 0, s>>>(n, g.K, splits, w.part, w.eo, doff, accumulate, w.flag);
+    count_launch();
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
+}
+
 // Pair tiles: sibling regions alternate along the width and every tensor allows 8-byte accesses of pixel pairs.
 bool use_pair_kernels(const MexGeo& g, uint32_t flags, const void* a, const void* b, const void* c, const void* d) {
     return !(flags & (SIMNETS_FLAG_MEX_NO_PAIR_TILES | SIMNETS_FLAG_MEX_TC_ONE_TILE)) && mex_pair_shape(g) && mex_pair_aligned(a, b, c, d);
@@ -434,16 +568,18 @@ bool blocks_cover_input(const MexGeo& g) {
 }
 
 cudaError_t run_prepasses(const MexGeo& g, const MexWs& w, const float* x, const float* off, cudaStream_t s, bool need_mx = true,
-                          bool pair_tiles = false) {
+                          bool pair_tiles = false, bool normalize = false) {
     cudaError_t e = cudaMemsetAsync(w.flag, 0, 16, s);
     if (e != cudaSuccess) return e;
     if (pair_tiles) {
         // the pair-tile kernels' operand tiles (forward and input gradient) come out of the same launch
         const int ntf = mex_pair_nt_fwd(g), ntd = mex_pair_nt_dx(g);
         const int Mp = std::max(((g.M + ntf - 1) / ntf) * ntf, ((g.M + 15) / 16) * 16);
-        mex_prep_offsets<<<g.R * Mp, g.K >= 2048 ? 512 : 128, 0, s>>>(g, Mp, off, w.mo, w.eo, w.eot, w.flag, w.tc_tiles, ntf, w.tc_tiles_dx, ntd);
+        mex_prep_offsets<<<g.R * Mp, g.K >= 2048 ? 512 : 128, 0, s>>>(g, Mp, off, w.mo, w.eo, w.eot, w.flag, w.tc_tiles, ntf, w.tc_tiles_dx, ntd,
+                                                                      normalize ? w.offn : nullptr, w.lse);
     } else {
-        mex_prep_offsets<<<g.R * g.M, g.K >= 2048 ? 512 : 128, 0, s>>>(g, g.M, off, w.mo, w.eo, w.eot, w.flag, nullptr, 0, nullptr, 0);
+        mex_prep_offsets<<<g.R * g.M, g.K >= 2048 ? 512 : 128, 0, s>>>(g, g.M, off, w.mo, w.eo, w.eot, w.flag, nullptr, 0, nullptr, 0,
+                                                                       normalize ? w.offn : nullptr, w.lse);
     }
     if (!need_mx) { count_launch(); return cudaGetLastError(); }
     // long patches over few positions are contiguous per position: reduce them with one CTA each
@@ -506,22 +642,22 @@ static cudaError_t mex_fwd_tiled_body(const MexGeo& g, const float* x, const flo
                                       float* pooled, bool* pooled_done) {
     const MexWs w = carve(g, ws);
     if (use_smallk_kernels(g, flags)) {
-        cudaError_t e = run_prepasses(g, w, x, off, s, false);
+        cudaError_t e = run_prepasses(g, w, x, off, s, false, false, mex_norm(flags));
         if (e != cudaSuccess) return e;
         e = launch_mex_fwd_smallk(g, x, w.eo, w.mo, y, w.flag, s);
         if (e != cudaSuccess) return e;
-        return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);
+        return launch_mex_fwd_direct(g, false, x, mex_norm(flags) ? w.offn : off, y, s, w.flag);
     }
     if (smallm_shape(g)) {
-        cudaError_t e = run_prepasses(g, w, x, off, s, false);
+        cudaError_t e = run_prepasses(g, w, x, off, s, false, false, mex_norm(flags));
         if (e != cudaSuccess) return e;
         e = mex_head_shape(g) ? launch_mex_fwd_head(g, x, w.eo, w.eot, w.mo, w.mx, y, w.part, w.flag, s)        // (also leaves the maxima for the gradients)
                               : launch_mex_fwd_smallm(g, x, w.eot, w.mo, y, w.flag, s);
         if (e != cudaSuccess) return e;
-        return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);
+        return launch_mex_fwd_direct(g, false, x, mex_norm(flags) ? w.offn : off, y, s, w.flag);
     }
     // (the caller may have had the layer in front leave the per-position extrema in the workspace: SIMNETS_FLAG_MEX_MAXIMA_GIVEN)
-    cudaError_t e = run_prepasses(g, w, x, off, s, !(flags & SIMNETS_FLAG_MEX_MAXIMA_GIVEN), pair_prep(g, flags));
+    cudaError_t e = run_prepasses(g, w, x, off, s, !(flags & SIMNETS_FLAG_MEX_MAXIMA_GIVEN), pair_prep(g, flags), mex_norm(flags));
     if (e != cudaSuccess) return e;
     if (use_tc_kernels(g, flags)) {
         if (use_pair_kernels(g, flags, x, y, y, y)) {
@@ -529,7 +665,7 @@ static cudaError_t mex_fwd_tiled_body(const MexGeo& g, const float* x, const flo
             e = launch_mex_fwd_pair(g, x, w.tc_tiles, w.mo, w.mx, y, fuse ? pooled : nullptr, w.flag,
                                     (flags & SIMNETS_FLAG_MEX_TEST_EXPIRE_WAIT) != 0, s);
             if (e != cudaSuccess) return e;
-            e = launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);
+            e = launch_mex_fwd_direct(g, false, x, mex_norm(flags) ? w.offn : off, y, s, w.flag);
             if (e != cudaSuccess || !fuse) return e;
             *pooled_done = true;
             // if the exact kernel had to recompute y (a status word is set), the pooling is redone from y as well
@@ -540,7 +676,7 @@ static cudaError_t mex_fwd_tiled_body(const MexGeo& g, const float* x, const flo
         e = (flags & SIMNETS_FLAG_MEX_TC_ONE_TILE) ? launch_mex_fwd_tc(g, x, w.tc_tiles, w.mo, w.mx, y, w.flag, patches_inside_input(g), s)
                                                    : launch_mex_fwd_ws(g, x, w.tc_tiles, w.mo, w.mx, y, w.flag, patches_inside_input(g), s);
         if (e != cudaSuccess) return e;
-        return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);
+        return launch_mex_fwd_direct(g, false, x, mex_norm(flags) ? w.offn : off, y, s, w.flag);
     }
     const long long P = (long long)g.B * g.rs;
     const bool sp1 = g.bh == 1 && g.bw == 1;
@@ -559,7 +695,7 @@ static cudaError_t mex_fwd_tiled_body(const MexGeo& g, const float* x, const flo
     count_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    return launch_mex_fwd_direct(g, false, x, off, y, s, w.flag);       // runs only if the flag was raised
+    return launch_mex_fwd_direct(g, false, x, mex_norm(flags) ? w.offn : off, y, s, w.flag);       // runs only if the flag was raised
 }
 
 // --------------------------------------------- forward on library-owned scratch
@@ -595,16 +731,22 @@ int launch_mex_fwd_static(const MexGeo& g, const float* x, const float* off, flo
     // everything else in the scratch is fully rewritten by the prepasses before it is read.
     // The caller's flags stay in force; the tensor-core route is switched off on top of them, because the capacity
     // check above counts the CUDA-core route's scratch only (no operand tiles).
-    e = launch_mex_fwd_tiled(g, x, off, y, ptr, flags | SIMNETS_FLAG_MEX_NO_TENSORCORE, s);
+    e = launch_mex_fwd_tiled(g, x, off, y, ptr, (flags | SIMNETS_FLAG_MEX_NO_TENSORCORE) & ~uint32_t(SIMNETS_FLAG_MEX_MAXIMA_GIVEN), s);
     return e == cudaSuccess ? SIMNETS_OK : int(e);
 }
 
 cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* dx,
                                 void* ws, uint32_t flags, cudaStream_t s, bool prepped) {
-    if (!blocks_disjoint(g)) return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, nullptr);
     const MexWs w = carve(g, ws);
+    if (!blocks_disjoint(g)) {           // overlapping blocks: the exact kernel (on the normalised rows, if the offsets came raw)
+        if (mex_norm(flags) && !(prepped || forward_primes_workspace(g, flags))) {
+            const cudaError_t e0 = run_prepasses(g, w, x, off, s, false, false, true);
+            if (e0 != cudaSuccess) return e0;
+        }
+        return launch_mex_dx_direct(g, false, x, mex_norm(flags) ? w.offn : off, y, dy, dx, s, nullptr);
+    }
     const bool small = smallm_shape(g) || use_smallk_kernels(g, flags);
-    cudaError_t e = (prepped || forward_primes_workspace(g, flags)) ? cudaSuccess : run_prepasses(g, w, x, off, s, !small, pair_prep(g, flags));
+    cudaError_t e = (prepped || forward_primes_workspace(g, flags)) ? cudaSuccess : run_prepasses(g, w, x, off, s, !small, pair_prep(g, flags), mex_norm(flags));
     if (e != cudaSuccess) return e;
     if (!blocks_cover_input(g)) {
         e = cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)g.B * g.C * g.H * g.W, s);
@@ -613,12 +755,12 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
     if (use_smallk_kernels(g, flags)) {
         e = launch_mex_dx_smallk(g, x, w.eo, w.mo, y, dy, dx, w.flag, s);
         if (e != cudaSuccess) return e;
-        return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
+        return launch_mex_dx_direct(g, false, x, mex_norm(flags) ? w.offn : off, y, dy, dx, s, w.flag);
     }
     if (use_tc_kernels(g, flags) && use_pair_kernels(g, flags, x, y, dy, dx)) {
         e = launch_mex_dx_pair(g, x, w.tc_tiles_dx, w.mo, w.mx, y, dy, dx, w.flag, s);
         if (e != cudaSuccess) return e;
-        return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
+        return launch_mex_dx_direct(g, false, x, mex_norm(flags) ? w.offn : off, y, dy, dx, s, w.flag);
     }
     if (use_tc_kernels(g, flags)) {
         e = launch_mex_tc_prep(g, true, w.eot, w.tc_tiles, s);
@@ -628,7 +770,7 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
         e = ((flags & SIMNETS_FLAG_MEX_TC_ONE_TILE) || g.K <= 128) ? launch_mex_dx_tc(g, x, w.tc_tiles, w.mo, w.mx, y, dy, dx, w.flag, s)
                                                                    : launch_mex_dx_ws(g, x, w.tc_tiles, w.mo, w.mx, y, dy, dx, w.flag, s);
         if (e != cudaSuccess) return e;
-        return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
+        return launch_mex_dx_direct(g, false, x, mex_norm(flags) ? w.offn : off, y, dy, dx, s, w.flag);
     }
     if (small && smallm_shape(g) && mex_head_shape(g)) {
         if (!(prepped || forward_primes_workspace(g, flags))) {              // run_prepasses skipped the maxima for this family
@@ -637,12 +779,12 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
         }
         e = launch_mex_bwd_head(g, true, false, x, w.eo, w.mo, w.mx, y, dy, dx, nullptr, 1, w.flag, s);
         if (e != cudaSuccess) return e;
-        return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
+        return launch_mex_dx_direct(g, false, x, mex_norm(flags) ? w.offn : off, y, dy, dx, s, w.flag);
     }
     if (small) {
         e = launch_mex_dx_smallm(g, x, w.eo, w.mo, y, dy, dx, w.flag, s);
         if (e != cudaSuccess) return e;
-        return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
+        return launch_mex_dx_direct(g, false, x, mex_norm(flags) ? w.offn : off, y, dy, dx, s, w.flag);
     }
     const long long P = (long long)g.B * g.rs;
     const bool sp1 = g.bh == 1 && g.bw == 1;
@@ -656,57 +798,37 @@ cudaError_t launch_mex_dx_tiled(const MexGeo& g, const float* x, const float* of
     count_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    return launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
+    return launch_mex_dx_direct(g, false, x, mex_norm(flags) ? w.offn : off, y, dy, dx, s, w.flag);
 }
 
 cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* doff,
                                   bool accumulate, void* ws, uint32_t flags, cudaStream_t s, bool prepped) {
     const MexWs w = carve(g, ws);
-    cudaError_t e = (prepped || forward_primes_workspace(g, flags)) ? cudaSuccess : run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags), pair_prep(g, flags));
+    cudaError_t e = (prepped || forward_primes_workspace(g, flags)) ? cudaSuccess : run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags), pair_prep(g, flags), mex_norm(flags));
     if (e != cudaSuccess) return e;
     if (use_tc_kernels(g, flags)) {
         int tsplits = mex_tc_doff_splits(g);
         e = use_pair_kernels(g, flags, x, y, dy, dy) ? launch_mex_doff_pair(g, x, w.mo, w.mx, y, dy, w.part, &tsplits, w.flag, s)
                                                      : launch_mex_doff_tc(g, x, w.mo, w.mx, y, dy, w.part, tsplits, w.flag, s);
         if (e != cudaSuccess) return e;
-        const long long n = (long long)g.R * g.M * g.K;
-        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, (long long)device_sm_count() * 8)), 256, 0, s>>>(n, g.K, tsplits, w.part, w.eo, doff, accumulate, w.flag);
-        count_launch();
-        e = cudaGetLastError();
-        if (e != cudaSuccess) return e;
-        return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
+        return finish_doff(g, w, tsplits, x, off, y, dy, doff, accumulate, flags, s);
     }
     const int splits = doff_splits(g);
     if (use_smallk_kernels(g, flags)) {
         e = launch_mex_doff_smallk(g, x, w.mo, y, dy, w.part, splits, w.flag, s);
         if (e != cudaSuccess) return e;
-        const long long n = (long long)g.R * g.M * g.K;
-        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, (long long)device_sm_count() * 8)), 256, 0, s>>>(n, g.K, splits, w.part, w.eo, doff, accumulate, w.flag);
-        count_launch();
-        e = cudaGetLastError();
-        if (e != cudaSuccess) return e;
-        return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
+        return finish_doff(g, w, splits, x, off, y, dy, doff, accumulate, flags, s);
     }
     if (smallm_shape(g) && mex_head_shape(g)) {
         const int hs = mex_head_splits(g);
         e = launch_mex_bwd_head(g, false, true, x, w.eo, w.mo, w.mx, y, dy, nullptr, w.part, hs, w.flag, s);
         if (e != cudaSuccess) return e;
-        const long long n = (long long)g.R * g.M * g.K;
-        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, (long long)device_sm_count() * 8)), 256, 0, s>>>(n, g.K, hs, w.part, w.eo, doff, accumulate, w.flag);
-        count_launch();
-        e = cudaGetLastError();
-        if (e != cudaSuccess) return e;
-        return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
+        return finish_doff(g, w, hs, x, off, y, dy, doff, accumulate, flags, s);
     }
     if (smallm_shape(g)) {
         e = launch_mex_doff_smallm(g, x, w.mo, w.mx, y, dy, w.part, splits, w.flag, s);
         if (e != cudaSuccess) return e;
-        const long long n = (long long)g.R * g.M * g.K;
-        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, (long long)device_sm_count() * 8)), 256, 0, s>>>(n, g.K, splits, w.part, w.eo, doff, accumulate, w.flag);
-        count_launch();
-        e = cudaGetLastError();
-        if (e != cudaSuccess) return e;
-        return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
+        return finish_doff(g, w, splits, x, off, y, dy, doff, accumulate, flags, s);
     }
     const int tile = doff_big(g) ? 128 : 64;
     const long long blocks = (long long)((g.M + tile - 1) / tile) * ((g.K + tile - 1) / tile) * g.R * splits;
@@ -715,19 +837,17 @@ cudaError_t launch_mex_doff_tiled(const MexGeo& g, const float* x, const float* 
     if (doff_big(g)) { if (sp1) DOFF(128, 16, true); else DOFF(128, 16, false); }
     else { if (sp1) DOFF(64, 32, true); else DOFF(64, 32, false); }
 #undef DOFF
-    const long long n = (long long)g.R * g.M * g.K;
-    mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, (long long)device_sm_count() * 8)), 256, 0, s>>>(n, g.K, splits, w.part, w.eo, doff, accumulate, w.flag);
-    count_launch(2);
+    count_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
+    return finish_doff(g, w, splits, x, off, y, dy, doff, accumulate, flags, s);
 }
 
 // Both gradients of one layer in one call: the offsets prepass and the per-position maxima are computed once.
 cudaError_t launch_mex_backward_tiled(const MexGeo& g, const float* x, const float* off, const float* y, const float* dy, float* dx,
                                       float* doff, bool accumulate, void* ws, uint32_t flags, cudaStream_t s) {
     const MexWs w = carve(g, ws);
-    cudaError_t e = forward_primes_workspace(g, flags) ? cudaSuccess : run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags), pair_prep(g, flags));
+    cudaError_t e = forward_primes_workspace(g, flags) ? cudaSuccess : run_prepasses(g, w, x, off, s, !use_smallk_kernels(g, flags), pair_prep(g, flags), mex_norm(flags));
     if (e != cudaSuccess) return e;
     if (smallm_shape(g) && mex_head_shape(g) && blocks_disjoint(g)) {
         // the head: input gradient and the partial sums of the offsets gradient from one read of x
@@ -738,14 +858,9 @@ cudaError_t launch_mex_backward_tiled(const MexGeo& g, const float* x, const flo
         }
         e = launch_mex_bwd_head(g, true, true, x, w.eo, w.mo, w.mx, y, dy, dx, w.part, hs, w.flag, s);
         if (e != cudaSuccess) return e;
-        const long long n = (long long)g.R * g.M * g.K;
-        mex_doff_reduce<<<int(std::min<long long>((n + 255) / 256, (long long)device_sm_count() * 8)), 256, 0, s>>>(n, g.K, hs, w.part, w.eo, doff, accumulate, w.flag);
-        count_launch();
-        e = cudaGetLastError();
+        e = launch_mex_dx_direct(g, false, x, mex_norm(flags) ? w.offn : off, y, dy, dx, s, w.flag);
         if (e != cudaSuccess) return e;
-        e = launch_mex_dx_direct(g, false, x, off, y, dy, dx, s, w.flag);
-        if (e != cudaSuccess) return e;
-        return launch_mex_doff_direct(g, false, x, off, y, dy, doff, accumulate, s, w.flag);
+        return finish_doff(g, w, hs, x, off, y, dy, doff, accumulate, flags, s);
     }
     e = launch_mex_dx_tiled(g, x, off, y, dy, dx, ws, flags, s, true);
     if (e != cudaSuccess) return e;

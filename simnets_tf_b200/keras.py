@@ -237,6 +237,16 @@ class Mex(torch.nn.Module):
                     blocks_round_down=self.blocks_round_down, unshared_offset_region=self.unshared_offset_region,
                     epsilon=self.epsilon, softmax_mode=self.softmax_mode)
 
+    def _op_flags(self, dtype, device):
+        # float32 on the GPU: the op takes the raw offsets and normalises them in its own prepass (and its gradient comes back
+        # with respect to the raw values); otherwise effective_offsets() does it in front of the op
+        fused = self.normalize_offsets and dtype == torch.float32 and device.type == "cuda" and self.offsets is not None and \
+            self.offsets.dtype == torch.float32 and self.offsets.is_cuda
+        from . import _torch_glue
+        if _torch_glue.DEFAULT_FLAGS & (abi.FLAG_FORCE_DIRECT | abi.FLAG_MEX_EXACT):
+            fused = False           # those routes run without a workspace, which the fused normalisation needs
+        return abi.FLAG_MEX_NORMALIZED_OFFSETS if fused else 0
+
     def extrema_slot(self, input_shape, dtype, device, sum_pool2=False):
         """For a layer whose every patch is exactly the channels of one pixel (blocks [C, 1, 1], unit spatial strides, no
         padding): (workspace, device address, want_max) -- a layer workspace made ahead of the call and the place in it
@@ -250,8 +260,9 @@ class Mex(torch.nn.Module):
         b, c, h, w = [int(e) for e in input_shape]
         if list(self.blocks) != [c, 1, 1] or list(self.strides)[1:] != [1, 1] or any(int(p) != 0 for p in self.padding) or b == 0:
             return None
-        ws = _mex_layer_workspace_for((b, c, h, w), dtype, device, self.num_instances, pooled=sum_pool2, **self._op_attrs())
-        ptr = _mex_workspace_maxima((b, c, h, w), dtype, self.num_instances, ws, **self._op_attrs())
+        ws = _mex_layer_workspace_for((b, c, h, w), dtype, device, self.num_instances, pooled=sum_pool2, flags=self._op_flags(dtype, device),
+                                      **self._op_attrs())
+        ptr = _mex_workspace_maxima((b, c, h, w), dtype, self.num_instances, ws, flags=self._op_flags(dtype, device), **self._op_attrs())
         return None if ptr is None else (ws, ptr, float(self.epsilon) > 0)
 
     def forward(self, x, sum_pool2=False, layer_ws=None, maxima_given=False):
@@ -261,9 +272,11 @@ class Mex(torch.nn.Module):
             self.build(tuple(x.shape), x.device, x.dtype)
         if self.channels_last:
             x = x.permute(0, 3, 1, 2)
-        if layer_ws is not None:
-            y = _mex_in_workspace(x, self.effective_offsets(), self.num_instances, layer_ws,
-                                  fwd_flags=abi.FLAG_MEX_MAXIMA_GIVEN if maxima_given else 0, sum_pool2=sum_pool2, **self._op_attrs())
+        op_flags = self._op_flags(x.dtype, x.device) if x.shape[0] > 0 else 0
+        if layer_ws is not None or op_flags:
+            y = _mex_in_workspace(x, self.offsets if op_flags else self.effective_offsets(), self.num_instances, layer_ws,
+                                  fwd_flags=abi.FLAG_MEX_MAXIMA_GIVEN if maxima_given else 0, op_flags=op_flags, sum_pool2=sum_pool2,
+                                  **self._op_attrs())
             return y.permute(0, 2, 3, 1) if self.channels_last else y
         op = _mex_sum_pool2 if sum_pool2 else _mex
         y = op(x, self.effective_offsets(), self.num_instances, blocks=self.blocks, padding=self.padding,

@@ -251,7 +251,7 @@ def mex_backward(input, offsets, orig_output, output_grad, num_instances, flags=
 def _gradients(ctx, grad, pooled):
     input, offsets, y = ctx.saved_tensors
     gi = go = None
-    kw = dict(pooled=pooled, primed_workspace=ctx.layer_ws, **ctx.attrs)
+    kw = dict(pooled=pooled, primed_workspace=ctx.layer_ws, flags=ctx.op_flags, **ctx.attrs)
     if ctx.needs_input_grad[0] and ctx.needs_input_grad[1]:
         gi, go = mex_backward(input, offsets, y, grad, ctx.num_instances, **kw)
     elif ctx.needs_input_grad[0]:
@@ -261,12 +261,13 @@ def _gradients(ctx, grad, pooled):
     return gi, go, None, None
 
 
-def _forward_for_autograd(ctx, input, offsets, num_instances, attrs, pooled, layer_ws=None, fwd_flags=0):
+def _forward_for_autograd(ctx, input, offsets, num_instances, attrs, pooled, layer_ws=None, fwd_flags=0, op_flags=0):
     # a differentiated layer runs in a workspace of its own, which its gradient pass then finds primed
     # (layer_ws: the caller made that workspace already, e.g. to have the layer in front fill in the extrema)
-    ctx.layer_ws = layer_ws
+    ctx.layer_ws, ctx.op_flags = layer_ws, op_flags
+    fwd_flags |= op_flags
     if layer_ws is None and (ctx.needs_input_grad[0] or ctx.needs_input_grad[1]) and input.is_cuda and input.shape[0] > 0:
-        ctx.layer_ws = mex_layer_workspace(input, num_instances, pooled=pooled, **attrs)
+        ctx.layer_ws = mex_layer_workspace(input, num_instances, pooled=pooled, flags=op_flags, **attrs)
     if pooled and input.dtype == torch.float32 and input.shape[0] > 0:
         y, out = mex_forward_pool2(input, offsets, num_instances, flags=fwd_flags, workspace=ctx.layer_ws, **attrs)
     else:
@@ -280,12 +281,12 @@ def _forward_for_autograd(ctx, input, offsets, num_instances, attrs, pooled, lay
 
 class _Mex(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, input, offsets, num_instances, attrs, layer_ws=None, fwd_flags=0):
-        return _forward_for_autograd(ctx, input, offsets, num_instances, attrs, False, layer_ws, fwd_flags)
+    def forward(ctx, input, offsets, num_instances, attrs, layer_ws=None, fwd_flags=0, op_flags=0):
+        return _forward_for_autograd(ctx, input, offsets, num_instances, attrs, False, layer_ws, fwd_flags, op_flags)
 
     @staticmethod
     def backward(ctx, grad):
-        return _gradients(ctx, grad, False) + (None, None)
+        return _gradients(ctx, grad, False) + (None, None, None)
 
 
 def sum_pool2x2(y):
@@ -304,12 +305,12 @@ class _MexSumPool2(torch.autograd.Function):
     positions it summed) is never written out: the MEX gradient kernels read the pooled dy directly."""
 
     @staticmethod
-    def forward(ctx, input, offsets, num_instances, attrs, layer_ws=None, fwd_flags=0):
-        return _forward_for_autograd(ctx, input, offsets, num_instances, attrs, True, layer_ws, fwd_flags)
+    def forward(ctx, input, offsets, num_instances, attrs, layer_ws=None, fwd_flags=0, op_flags=0):
+        return _forward_for_autograd(ctx, input, offsets, num_instances, attrs, True, layer_ws, fwd_flags, op_flags)
 
     @staticmethod
     def backward(ctx, grad):
-        return _gradients(ctx, grad, True) + (None, None)
+        return _gradients(ctx, grad, True) + (None, None, None)
 
 
 def mex(input, offsets, num_instances, softmax_mode=None, padding=None, strides=None, blocks=None, epsilon=None,
@@ -328,7 +329,7 @@ def mex(input, offsets, num_instances, softmax_mode=None, padding=None, strides=
     return _Mex.apply(input, offsets, num_instances, attrs)
 
 
-def mex_sum_pool2(input, offsets, num_instances, layer_ws=None, fwd_flags=0, **kwargs):
+def mex_sum_pool2(input, offsets, num_instances, layer_ws=None, fwd_flags=0, op_flags=0, **kwargs):
     """`mex(...)` followed by a 2x2 sum pooling (the MEX + pooling pair of the reference's example networks,
     README.md:114-131, where the pooling is `4 * AveragePooling2D(2)`), with the pooling's backward folded into
     the MEX gradient kernels.  Same keyword arguments as `mex`.  Falls back to the two separate ops when the
@@ -336,14 +337,16 @@ def mex_sum_pool2(input, offsets, num_instances, layer_ws=None, fwd_flags=0, **k
     attrs = _attrs(**{k: v for k, v in kwargs.items() if k != "name"})
     g = _geometry(_desc(input, num_instances, attrs))
     if g.height_out % 2 or g.width_out % 2:
-        return torch.nn.functional.avg_pool2d(_Mex.apply(input, offsets, num_instances, attrs), 2) * 4.0
-    return _MexSumPool2.apply(input, offsets, num_instances, attrs, layer_ws, fwd_flags)
+        return torch.nn.functional.avg_pool2d(_Mex.apply(input, offsets, num_instances, attrs, layer_ws, fwd_flags, op_flags), 2) * 4.0
+    return _MexSumPool2.apply(input, offsets, num_instances, attrs, layer_ws, fwd_flags, op_flags)
 
 
-def mex_in_workspace(input, offsets, num_instances, layer_ws, fwd_flags=0, sum_pool2=False, **kwargs):
-    """`mex(...)` (or `mex_sum_pool2(...)`) run in a layer workspace the caller made (`mex_layer_workspace_for`), with extra
-    flags for the forward call only, e.g. abi.FLAG_MEX_MAXIMA_GIVEN after the layer in front has filled in the extrema."""
+def mex_in_workspace(input, offsets, num_instances, layer_ws=None, fwd_flags=0, op_flags=0, sum_pool2=False, **kwargs):
+    """`mex(...)` (or `mex_sum_pool2(...)`) with the library's extras: a layer workspace the caller made
+    (`mex_layer_workspace_for`), flags for the forward call only (abi.FLAG_MEX_MAXIMA_GIVEN after the layer in front has
+    filled in the extrema), flags for the forward and the gradient calls (abi.FLAG_MEX_NORMALIZED_OFFSETS: `offsets` are raw
+    and the gradient comes back with respect to them)."""
     attrs = _attrs(**{k: v for k, v in kwargs.items() if k != "name"})
     if sum_pool2:
-        return mex_sum_pool2(input, offsets, num_instances, layer_ws=layer_ws, fwd_flags=fwd_flags, **attrs)
-    return _Mex.apply(input, offsets, num_instances, attrs, layer_ws, fwd_flags)
+        return mex_sum_pool2(input, offsets, num_instances, layer_ws=layer_ws, fwd_flags=fwd_flags, op_flags=op_flags, **attrs)
+    return _Mex.apply(input, offsets, num_instances, attrs, layer_ws, fwd_flags, op_flags)

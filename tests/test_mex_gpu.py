@@ -416,3 +416,113 @@ def test_pooled_output_on_the_recomputing_routes(port, cuda_lib):
         assert (status[0], status[1]) == want
         cases.assert_parity(y.cpu().numpy(), ry, what="y")
         cases.assert_parity(yp.cpu().numpy(), _pool2(ry).astype(np.float32), tol=1e-5, what="pooled y")
+
+
+# ---- raw offsets, normalised inside the op (SIMNETS_FLAG_MEX_NORMALIZED_OFFSETS)
+def _normalise(off):
+    o = off.astype(np.float64)
+    flat = o.reshape(o.shape[0] * o.shape[1], -1)
+    m = flat.max(axis=1, keepdims=True)
+    lse = m + np.log(np.exp(flat - m).sum(axis=1, keepdims=True))
+    return (flat - lse).reshape(o.shape), np.exp(flat - lse)          # normalised offsets, softmax of every row
+
+
+_RAW = cases.MEX_PAIR[::2] + cases.MEX_HEAD[::2] + [c for c in cases.MEX_CONFIGS if not c["name"].startswith("cfg4")] + cases.MEX_SMALL[::5]
+
+
+@pytest.mark.parametrize("c", _RAW, ids=lambda c: c["name"])
+def test_raw_offsets_are_normalised_inside_the_op(port, c):
+    """Forward and input gradient as with offsets - logsumexp(row) in front of the op; the offsets gradient comes back with
+    respect to the raw values: d - softmax(row) * sum(d) of the oracle's gradient d."""
+    d = cases.mex_desc(c)
+    x, off, dy = cases.mex_inputs(c, port.mex_offsets_shape(d), port.mex_out_shape(d))
+    offn64, soft = _normalise(off)
+    offn = offn64.astype(np.float32)
+    ry = port.mex_forward(d, x, offn)
+    rdx = port.mex_input_grad(d, x, offn, ry, dy)
+    de = port.mex_offsets_grad(cases.mex_desc(c, dtype=abi.F64), x.astype(np.float64), offn64, ry.astype(np.float64), dy.astype(np.float64))
+    flat = de.reshape(soft.shape)
+    rdoff = (flat - soft * flat.sum(axis=1, keepdims=True)).reshape(off.shape)
+    xd, od, dyd, ryd = (gpu_util.dev(a) for a in (x, off, dy, ry))
+    attrs = cases.mex_attrs(c)
+    fl = c["flags"] | abi.FLAG_MEX_NORMALIZED_OFFSETS
+    cases.assert_parity(mex_ops.mex_forward(xd, od, c["M"], flags=fl, **attrs).cpu().numpy(), ry, what="y")
+    cases.assert_parity(mex_ops.mex_input_grad(xd, od, ryd, dyd, c["M"], flags=fl, **attrs).cpu().numpy(), rdx, tol=2e-5, what="dx")
+    cases.assert_parity(mex_ops.mex_offsets_grad(xd, od, ryd, dyd, c["M"], flags=fl, **attrs).cpu().numpy(), rdoff.astype(np.float32), tol=3e-5,
+                        what="doff (raw)")
+    bdx, bdoff = mex_ops.mex_backward(xd, od, ryd, dyd, c["M"], flags=fl, **attrs)
+    cases.assert_parity(bdx.cpu().numpy(), rdx, tol=2e-5, what="dx (fused call)")
+    cases.assert_parity(bdoff.cpu().numpy(), rdoff.astype(np.float32), tol=3e-5, what="doff (fused call)")
+    # accumulate into a caller tensor
+    acc = torch.full(off.shape, 2.0, device="cuda")
+    mex_ops.mex_offsets_grad(xd, od, ryd, dyd, c["M"], flags=fl | abi.FLAG_ACCUMULATE, out=acc, **attrs)
+    cases.assert_parity(acc.cpu().numpy() - 2.0, rdoff.astype(np.float32), tol=1e-4, what="doff accumulated")
+
+
+def test_raw_offsets_on_the_exact_route(port):
+    """A row spread that makes the factorisation unsafe: the exact kernels work on the normalised rows kept in the workspace."""
+    c = next(c for c in cases.MEX_CONFIGS if c["name"] == "cfg5_mex1_sub")
+    d = cases.mex_desc(c)
+    x, off, dy = cases.mex_inputs(c, port.mex_offsets_shape(d), port.mex_out_shape(d))
+    off = off.copy()
+    off[0, 0, 0] = 300.0
+    offn64, soft = _normalise(off)
+    offn = offn64.astype(np.float32)
+    ry = port.mex_forward(d, x, offn)
+    de = port.mex_offsets_grad(cases.mex_desc(c, dtype=abi.F64), x.astype(np.float64), offn64, ry.astype(np.float64), dy.astype(np.float64))
+    flat = de.reshape(soft.shape)
+    rdoff = (flat - soft * flat.sum(axis=1, keepdims=True)).reshape(off.shape)
+    xd, od, dyd, ryd = (gpu_util.dev(a) for a in (x, off, dy, ry))
+    attrs = cases.mex_attrs(c)
+    fl = abi.FLAG_MEX_NORMALIZED_OFFSETS
+    cases.assert_parity(mex_ops.mex_forward(xd, od, c["M"], flags=fl, **attrs).cpu().numpy(), ry, what="y")
+    dx, doff = mex_ops.mex_backward(xd, od, ryd, dyd, c["M"], flags=fl, **attrs)
+    cases.assert_parity(dx.cpu().numpy(), port.mex_input_grad(d, x, offn, ry, dy), tol=2e-5, what="dx")
+    cases.assert_parity(doff.cpu().numpy(), rdoff.astype(np.float32), tol=3e-5, what="doff (raw)")
+    with pytest.raises(RuntimeError):
+        mex_ops.mex_forward(xd, od, c["M"], flags=fl | abi.FLAG_FORCE_DIRECT, **attrs)
+
+
+def test_layer_with_fused_and_separate_normalisation():
+    from simnets_tf_b200 import keras as layers
+    torch.manual_seed(0)
+    x = torch.randn(4, 64, 8, 8, device="cuda")
+    kw = dict(num_instances=96, blocks=[64, 1, 1], strides=[64, 1, 1], softmax_mode=True, unshared_offset_region=[2], normalize_offsets=True)
+    a, b = layers.Mex(**kw), layers.Mex(**kw)
+    a.build(tuple(x.shape), device=x.device)
+    b.build(tuple(x.shape), device=x.device)
+    with torch.no_grad():
+        b.offsets.copy_(a.offsets)
+    ya = a(x, sum_pool2=True)
+    b._op_flags = lambda dtype, device: 0                 # the separate normalisation kernels in front of and behind the op
+    yb = b(x, sum_pool2=True)
+    assert torch.allclose(ya, yb, rtol=1e-5, atol=1e-5 * float(yb.abs().max()))
+    g = torch.randn_like(ya)
+    ya.backward(g)
+    yb.backward(g)
+    assert torch.allclose(a.offsets.grad, b.offsets.grad, rtol=1e-4, atol=3e-5 * float(b.offsets.grad.abs().max()))
+
+
+@pytest.mark.parametrize("shape,M", [((6, 32, 16, 16), 64), ((4, 64, 32, 32), 128), ((5, 40, 8, 16), 70)], ids=["K32", "cfg5_mex1", "ragged"])
+@pytest.mark.parametrize("norm", [0, abi.FLAG_MEX_NORMALIZED_OFFSETS], ids=["plain", "raw_offsets"])
+def test_results_do_not_depend_on_what_the_workspace_held(shape, M, norm):
+    """A forward call and the gradient calls that reuse its workspace (pooled dy) read nothing they did not write: a
+    workspace poisoned with NaN bytes or with large values gives the bits of a zeroed one.  (A layout that depended on
+    the pooled flag once made the gradient call look for the forward pass's tables in the wrong place.)"""
+    torch.manual_seed(0)
+    B, C, H, W = shape
+    attrs = dict(blocks=[C, 1, 1], strides=[C, 1, 1], softmax_mode=True, unshared_offset_region=[2])
+    x = torch.randn(B, C, H, W, device="cuda")
+    off = torch.randn(4, M, C, 1, 1, device="cuda")
+    dyp = torch.randn(B, M, H // 2, W // 2, device="cuda")
+
+    def run(fill):
+        ws = mex_ops.mex_layer_workspace(x, M, pooled=True, flags=norm, **attrs)
+        ws.fill_(fill)
+        y, yp = mex_ops.mex_forward_pool2(x, off, M, flags=norm, workspace=ws, **attrs)
+        dx, doff = mex_ops.mex_backward(x, off, y, dyp, M, flags=norm, primed_workspace=ws, pooled=True, **attrs)
+        return y, yp, dx, doff
+    ref = run(0)
+    for fill in (255, 127):
+        for a, b in zip(run(fill), ref):
+            assert torch.equal(a, b)
