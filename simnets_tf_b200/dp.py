@@ -26,6 +26,9 @@ class GradBucket(object):
         for p in self.params:
             v = self.flat[off:off + p.numel()].view_as(p)
             p.grad = v
+            # the layer classes pass this on to the library, whose parameter-gradient kernels then add into the bucket
+            # themselves (SIMNETS_FLAG_ACCUMULATE) instead of handing a tensor to autograd's accumulation
+            p._simnets_grad_sink = v
             self.views.append(v)
             off += p.numel()
 

@@ -21,6 +21,18 @@ from .ops.mex import mex_workspace_maxima as _mex_workspace_maxima
 from .ops.similarity import similarity_of_raw_weights as _similarity_of_raw_weights
 
 
+def _sinks(*params):
+    """The tensors that a data-parallel gradient bucket asked these parameters' gradients to be added to (dp.GradBucket), or
+    None unless every one of them has one and still holds it as its `.grad`."""
+    out = []
+    for p in params:
+        s = getattr(p, "_simnets_grad_sink", None)
+        if s is None or p.grad is None or p.grad.data_ptr() != s.data_ptr() or not torch.is_grad_enabled() or not p.requires_grad:
+            return None
+        out.append(s)
+    return tuple(out)
+
+
 def _init_tensor(spec, shape, device, dtype, generator=None):
     """Keras initializer names the reference's layers use ('random_normal' = N(0, 0.05), 'ones', 'zeros')
     or a callable `(shape, dtype) -> array-like`."""
@@ -99,7 +111,7 @@ class Similarity(torch.nn.Module):
                                        normalization_term=self.normalization_term,
                                        normalization_term_fudge=self.normalization_term_fudge,
                                        ignore_nan_input=self.ignore_nan_input, out_of_bounds_value=self.out_of_bounds_value,
-                                       extrema=extrema)
+                                       extrema=extrema, grad_sinks=_sinks(self.templates, self.sweights))
         return y.permute(0, 2, 3, 1) if self.channels_last else y
 
     def get_config(self):
@@ -274,9 +286,10 @@ class Mex(torch.nn.Module):
             x = x.permute(0, 3, 1, 2)
         op_flags = self._op_flags(x.dtype, x.device) if x.shape[0] > 0 else 0
         if layer_ws is not None or op_flags:
+            sink = _sinks(self.offsets) if op_flags else None       # (the raw offsets are the op's own input only when it normalises them)
             y = _mex_in_workspace(x, self.offsets if op_flags else self.effective_offsets(), self.num_instances, layer_ws,
                                   fwd_flags=abi.FLAG_MEX_MAXIMA_GIVEN if maxima_given else 0, op_flags=op_flags, sum_pool2=sum_pool2,
-                                  **self._op_attrs())
+                                  grad_sink=sink[0] if sink else None, **self._op_attrs())
             return y.permute(0, 2, 3, 1) if self.channels_last else y
         op = _mex_sum_pool2 if sum_pool2 else _mex
         y = op(x, self.effective_offsets(), self.num_instances, blocks=self.blocks, padding=self.padding,

@@ -224,7 +224,7 @@ def mex_offsets_grad(input, offsets, orig_output, output_grad, num_instances, fl
     return doff
 
 
-def mex_backward(input, offsets, orig_output, output_grad, num_instances, flags=0, primed_workspace=None, pooled=False, **attrs):
+def mex_backward(input, offsets, orig_output, output_grad, num_instances, flags=0, primed_workspace=None, pooled=False, doff_out=None, **attrs):
     """`MexInputGrad` and `MexOffsetsGrad` in one library call: (input_grad, offsets_grad).  `pooled` as in
     `mex_input_grad`.  `primed_workspace` (all three gradient ops): the buffer that `mex_forward` ran in for the same
     input and offsets, untouched since."""
@@ -236,7 +236,12 @@ def mex_backward(input, offsets, orig_output, output_grad, num_instances, flags=
     g = _geometry(d)
     _check_offsets(offsets, g, num_instances)
     _check_dy(dy, input, g, pooled)
-    dx, doff = torch.empty_like(input), torch.empty_like(offsets)
+    dx = torch.empty_like(input)
+    if doff_out is None:
+        doff = torch.empty_like(offsets)
+    else:                                   # (with FLAG_ACCUMULATE in `flags` the offsets gradient is added to it)
+        doff = doff_out
+        assert doff.is_contiguous() and doff.numel() == offsets.numel() and doff.dtype == offsets.dtype
     with torch.cuda.device(dev):
         ws, n = _ws(d, dev, primed_workspace)
         sig, nbytes, terms = _cost(d, g, "bwd")     # fused: x, offsets, y, dy read once, dx and doffsets written
@@ -252,19 +257,24 @@ def _gradients(ctx, grad, pooled):
     input, offsets, y = ctx.saved_tensors
     gi = go = None
     kw = dict(pooled=pooled, primed_workspace=ctx.layer_ws, flags=ctx.op_flags, **ctx.attrs)
+    sink = ctx.grad_sink
+    if sink is not None:                    # the offsets gradient is added straight into the caller's tensor (a gradient bucket)
+        kw["flags"] = kw["flags"] | abi.FLAG_ACCUMULATE
     if ctx.needs_input_grad[0] and ctx.needs_input_grad[1]:
-        gi, go = mex_backward(input, offsets, y, grad, ctx.num_instances, **kw)
+        gi, go = mex_backward(input, offsets, y, grad, ctx.num_instances, doff_out=sink, **kw)
     elif ctx.needs_input_grad[0]:
         gi = mex_input_grad(input, offsets, y, grad, ctx.num_instances, **kw)
     elif ctx.needs_input_grad[1]:
-        go = mex_offsets_grad(input, offsets, y, grad, ctx.num_instances, **kw)
+        go = mex_offsets_grad(input, offsets, y, grad, ctx.num_instances, out=sink, **kw)
+    if sink is not None:
+        go = None                           # nothing left for autograd to accumulate
     return gi, go, None, None
 
 
-def _forward_for_autograd(ctx, input, offsets, num_instances, attrs, pooled, layer_ws=None, fwd_flags=0, op_flags=0):
+def _forward_for_autograd(ctx, input, offsets, num_instances, attrs, pooled, layer_ws=None, fwd_flags=0, op_flags=0, grad_sink=None):
     # a differentiated layer runs in a workspace of its own, which its gradient pass then finds primed
     # (layer_ws: the caller made that workspace already, e.g. to have the layer in front fill in the extrema)
-    ctx.layer_ws, ctx.op_flags = layer_ws, op_flags
+    ctx.layer_ws, ctx.op_flags, ctx.grad_sink = layer_ws, op_flags, grad_sink
     fwd_flags |= op_flags
     if layer_ws is None and (ctx.needs_input_grad[0] or ctx.needs_input_grad[1]) and input.is_cuda and input.shape[0] > 0:
         ctx.layer_ws = mex_layer_workspace(input, num_instances, pooled=pooled, flags=op_flags, **attrs)
@@ -281,12 +291,12 @@ def _forward_for_autograd(ctx, input, offsets, num_instances, attrs, pooled, lay
 
 class _Mex(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, input, offsets, num_instances, attrs, layer_ws=None, fwd_flags=0, op_flags=0):
-        return _forward_for_autograd(ctx, input, offsets, num_instances, attrs, False, layer_ws, fwd_flags, op_flags)
+    def forward(ctx, input, offsets, num_instances, attrs, layer_ws=None, fwd_flags=0, op_flags=0, grad_sink=None):
+        return _forward_for_autograd(ctx, input, offsets, num_instances, attrs, False, layer_ws, fwd_flags, op_flags, grad_sink)
 
     @staticmethod
     def backward(ctx, grad):
-        return _gradients(ctx, grad, False) + (None, None, None)
+        return _gradients(ctx, grad, False) + (None, None, None, None)
 
 
 def sum_pool2x2(y):
@@ -305,12 +315,12 @@ class _MexSumPool2(torch.autograd.Function):
     positions it summed) is never written out: the MEX gradient kernels read the pooled dy directly."""
 
     @staticmethod
-    def forward(ctx, input, offsets, num_instances, attrs, layer_ws=None, fwd_flags=0, op_flags=0):
-        return _forward_for_autograd(ctx, input, offsets, num_instances, attrs, True, layer_ws, fwd_flags, op_flags)
+    def forward(ctx, input, offsets, num_instances, attrs, layer_ws=None, fwd_flags=0, op_flags=0, grad_sink=None):
+        return _forward_for_autograd(ctx, input, offsets, num_instances, attrs, True, layer_ws, fwd_flags, op_flags, grad_sink)
 
     @staticmethod
     def backward(ctx, grad):
-        return _gradients(ctx, grad, True) + (None, None, None)
+        return _gradients(ctx, grad, True) + (None, None, None, None)
 
 
 def mex(input, offsets, num_instances, softmax_mode=None, padding=None, strides=None, blocks=None, epsilon=None,
@@ -329,7 +339,7 @@ def mex(input, offsets, num_instances, softmax_mode=None, padding=None, strides=
     return _Mex.apply(input, offsets, num_instances, attrs)
 
 
-def mex_sum_pool2(input, offsets, num_instances, layer_ws=None, fwd_flags=0, op_flags=0, **kwargs):
+def mex_sum_pool2(input, offsets, num_instances, layer_ws=None, fwd_flags=0, op_flags=0, grad_sink=None, **kwargs):
     """`mex(...)` followed by a 2x2 sum pooling (the MEX + pooling pair of the reference's example networks,
     README.md:114-131, where the pooling is `4 * AveragePooling2D(2)`), with the pooling's backward folded into
     the MEX gradient kernels.  Same keyword arguments as `mex`.  Falls back to the two separate ops when the
@@ -337,16 +347,17 @@ def mex_sum_pool2(input, offsets, num_instances, layer_ws=None, fwd_flags=0, op_
     attrs = _attrs(**{k: v for k, v in kwargs.items() if k != "name"})
     g = _geometry(_desc(input, num_instances, attrs))
     if g.height_out % 2 or g.width_out % 2:
-        return torch.nn.functional.avg_pool2d(_Mex.apply(input, offsets, num_instances, attrs, layer_ws, fwd_flags, op_flags), 2) * 4.0
-    return _MexSumPool2.apply(input, offsets, num_instances, attrs, layer_ws, fwd_flags, op_flags)
+        return torch.nn.functional.avg_pool2d(_Mex.apply(input, offsets, num_instances, attrs, layer_ws, fwd_flags, op_flags, grad_sink), 2) * 4.0
+    return _MexSumPool2.apply(input, offsets, num_instances, attrs, layer_ws, fwd_flags, op_flags, grad_sink)
 
 
-def mex_in_workspace(input, offsets, num_instances, layer_ws=None, fwd_flags=0, op_flags=0, sum_pool2=False, **kwargs):
+def mex_in_workspace(input, offsets, num_instances, layer_ws=None, fwd_flags=0, op_flags=0, sum_pool2=False, grad_sink=None, **kwargs):
     """`mex(...)` (or `mex_sum_pool2(...)`) with the library's extras: a layer workspace the caller made
     (`mex_layer_workspace_for`), flags for the forward call only (abi.FLAG_MEX_MAXIMA_GIVEN after the layer in front has
     filled in the extrema), flags for the forward and the gradient calls (abi.FLAG_MEX_NORMALIZED_OFFSETS: `offsets` are raw
-    and the gradient comes back with respect to them)."""
+    and the gradient comes back with respect to them), a tensor that the offsets gradient is ADDED to instead of being
+    handed to autograd (`grad_sink`: the offsets' slice of a data-parallel gradient bucket)."""
     attrs = _attrs(**{k: v for k, v in kwargs.items() if k != "name"})
     if sum_pool2:
-        return mex_sum_pool2(input, offsets, num_instances, layer_ws=layer_ws, fwd_flags=fwd_flags, op_flags=op_flags, **attrs)
-    return _Mex.apply(input, offsets, num_instances, attrs, layer_ws, fwd_flags, op_flags)
+        return mex_sum_pool2(input, offsets, num_instances, layer_ws=layer_ws, fwd_flags=fwd_flags, op_flags=op_flags, grad_sink=grad_sink, **attrs)
+    return _Mex.apply(input, offsets, num_instances, attrs, layer_ws, fwd_flags, op_flags, grad_sink)

@@ -115,8 +115,8 @@ def similarity_parameters_grad(input, templates, weights, output_grad, flags=0, 
 
 class _Similarity(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, input, templates, weights, attrs, flags=0, extrema=None):
-        ctx.attrs, ctx.flags = attrs, flags
+    def forward(ctx, input, templates, weights, attrs, flags=0, extrema=None, grad_sinks=None):
+        ctx.attrs, ctx.flags, ctx.grad_sinks = attrs, flags, grad_sinks
         ctx.save_for_backward(input, templates, weights)
         return similarity_forward(input, templates, weights, flags=flags, extrema=extrema, **attrs)
 
@@ -127,8 +127,11 @@ class _Similarity(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             gi = similarity_input_grad(input, templates, weights, grad, flags=ctx.flags, **ctx.attrs)
         if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
-            gt, gw = similarity_parameters_grad(input, templates, weights, grad, flags=ctx.flags, **ctx.attrs)
-        return gi, gt, gw, None, None, None
+            if ctx.grad_sinks is not None:          # both parameter gradients are added straight into the caller's tensors
+                similarity_parameters_grad(input, templates, weights, grad, flags=ctx.flags | abi.FLAG_ACCUMULATE, out=ctx.grad_sinks, **ctx.attrs)
+            else:
+                gt, gw = similarity_parameters_grad(input, templates, weights, grad, flags=ctx.flags, **ctx.attrs)
+        return gi, gt, gw, None, None, None, None
 
 
 def similarity(input, templates, weights, similarity_function=None, blocks=None, strides=None, padding=None,
@@ -148,8 +151,8 @@ def similarity(input, templates, weights, similarity_function=None, blocks=None,
     return _Similarity.apply(input, templates, weights, attrs)
 
 
-def similarity_of_raw_weights(input, templates, raw_weights, flags=0, extrema=None, **attrs):
+def similarity_of_raw_weights(input, templates, raw_weights, flags=0, extrema=None, grad_sinks=None, **attrs):
     """`similarity(input, templates, abs(raw_weights), ...)`, differentiable w.r.t. all three tensors, with the absolute
     value and its gradient taken inside the library's kernels (abi.FLAG_SIM_ABS_WEIGHTS): what the reference's Keras
     layer computes with `K.abs(self.sweights)` in front of the op (python/simnets/keras.py:65)."""
-    return _Similarity.apply(input, templates, raw_weights, _attrs(**attrs), flags | abi.FLAG_SIM_ABS_WEIGHTS, extrema)
+    return _Similarity.apply(input, templates, raw_weights, _attrs(**attrs), flags | abi.FLAG_SIM_ABS_WEIGHTS, extrema, grad_sinks)
