@@ -703,7 +703,7 @@ struct DoPairPlan { int units, mgroups, ktiles, splits; };
 // Tensor maps of the offsets-gradient kernel's raw loader (LOAD == 2): y, dy, x and the per-position maxima seen as
 // (w, row parity class, row within the class, instance or channel, sample), so that the pixel pairs of one chunk -- a run
 // of one image row, or a few whole rows, of the region pair's rows -- times all instances are ONE box.  Plain per-CTA
-// tiled copies from this GPU's own tensors, no multicast.
+// tiled copies from this GPU's own tensors; each CTA fetches its own boxes, nothing is shared between CTAs.
 struct DoMaps { CUtensorMap y, dy, x, mx; };
 
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3, int c4) {
