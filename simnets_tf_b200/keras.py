@@ -3,8 +3,8 @@ reference's Keras layers (HUJI-Deep/simnets-tf python/simnets/keras.py:19-188).
 
 Keras and TensorFlow are not part of this stack; the layers are `torch.nn.Module`s that create their
 variables on first call (the counterpart of Keras' `build(input_shape)`) and run the CUDA operators.
-`perform_unsupervised_init` (k-means / GMM / PCA initialisation, pure TensorFlow graph code in the
-reference) is outside this library.
+`perform_unsupervised_init` (k-means / GMM initialisation of Similarity layers) lives in `unsupervised.py`, built on the
+Similarity operators; the reference's PCA branch serves Keras convolution layers, which do not exist here.
 """
 import ctypes as C
 import math
@@ -308,5 +308,7 @@ class Mex(torch.nn.Module):
         return {k: getattr(self, k) for k in names}
 
 
-def perform_unsupervised_init(model, kind='gmm', layers=[], data=None, batch_size=None):
-    raise NotImplementedError("unsupervised (k-means / GMM / PCA) initialisation is not part of the B200 operator library")
+def perform_unsupervised_init(model, kind='gmm', layers=[], data=None, batch_size=None, **kwargs):
+    """python/simnets/keras.py:191-238 for Similarity layers; see unsupervised.perform_unsupervised_init."""
+    from . import unsupervised
+    return unsupervised.perform_unsupervised_init(model, kind=kind, layers=layers, data=data, batch_size=batch_size, **kwargs)
