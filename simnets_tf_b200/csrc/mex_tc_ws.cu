@@ -133,24 +133,40 @@ __global__ void __launch_bounds__(kWsThreads, 1) mex_fwd_ws(MexGeo g, const floa
         float* mow = mo_w[warp - kWsProducerWarps];                              // this warp's slice of the item's offset maxima
         const float inv_eps = 1.f / float(g.eps), k_log = 0.69314718056f * inv_eps, c_add = float(g.cst) * inv_eps;
         const unsigned Nu = unsigned(g.N);                                       // distance between instances in y (32 N < 2^31)
+        // This warp's column of the first item; from then on the column of item li + 1 (an index division and a load of the
+        // position's maximum) is requested before the arithmetic of item li, so that its latency is not paid per item.
+        WsItem it = ws_item(plan, int(blockIdx.x));
+        Column col;
+        col.base = -1; col.mx = 0.f;
+        if (my_items > 0) col = column_of(g, it.r, (long long)it.jt * kTcPos + quarter * 32 + lane, P, mx);
+        int held_r = -1, held_mt = -1;                                           // whose offset maxima mow holds
         for (int li = 0; li < my_items; ++li) {
             const int buf = li & 1;
             if (sh.failed) break;
-            const WsItem it = ws_item(plan, int(blockIdx.x) + li * int(gridDim.x));
             const int m0 = it.mt * NT + half * (NT / 2);
-            for (int i = lane; i < NT / 2; i += 32) mow[i] = m0 + i < g.M ? __ldg(mo + it.r * g.M + m0 + i) : 0.f;
-            __syncwarp();
-            const Column col = column_of(g, it.r, (long long)it.jt * kTcPos + quarter * 32 + lane, P, mx);
+            if (it.r != held_r || it.mt != held_mt) {
+                __syncwarp();                                   // every lane is done with the previous contents
+                for (int i = lane; i < NT / 2; i += 32) mow[i] = m0 + i < g.M ? __ldg(mo + it.r * g.M + m0 + i) : 0.f;
+                __syncwarp();
+                held_r = it.r; held_mt = it.mt;
+            }
             const float cadd = col.mx + c_add;
-            float* yb = y + (col.base >= 0 ? col.base : 0) + (long long)m0 * g.N;
+            const bool live = col.base >= 0;
+            float* yb = y + (live ? col.base : 0) + (long long)m0 * g.N;
             const bool full = m0 + NT / 2 <= g.M;
+            WsItem nit = it;
+            Column ncol = col;
+            if (li + 1 < my_items) {
+                nit = ws_item(plan, int(blockIdx.x) + (li + 1) * int(gridDim.x));
+                ncol = column_of(g, nit.r, (long long)nit.jt * kTcPos + quarter * 32 + lane, P, mx);
+            }
             if (!mbar_wait(&sh.acc_full[buf], (uint32_t(li) >> 1) & 1u)) { sh.failed = 1; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (int c0 = 0; c0 < NT / 2; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem + uint32_t(buf * NT + half * (NT / 2) + c0) + (uint32_t(quarter * 32) << 16), v);
-                if (col.base >= 0) {
+                if (live) {
                     float* yp = yb + (size_t)c0 * Nu;                   // the 32 instances of the block: 32-bit offsets i * N
                     if (full) {
 #pragma unroll
@@ -170,7 +186,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) mex_fwd_ws(MexGeo g, const floa
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(&sh.acc_empty[buf]);
-            __syncwarp();                                   // every lane is done with this item's mow
+            it = nit;
+            col = ncol;
         }
     }
 

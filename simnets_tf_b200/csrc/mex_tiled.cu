@@ -145,6 +145,40 @@ __global__ void __launch_bounds__(256) mex_colmax(MexGeo g, const float* __restr
     }
 }
 
+// Short spatial blocks that tile the rows of the input (block width = stride along w, 2 or 4 wide, no padding, no patch
+// leaving the input): the taps of one block row are one aligned vector, consecutive positions read consecutive vectors,
+// and the bc * bh row loads of a position do not depend on one another, so they are issued together instead of tap by
+// tap with a division each.  Same values: max and min are associative and skip NaN taps either way.
+template <int BW>
+__global__ void __launch_bounds__(256) mex_colmax_rows(MexGeo g, const float* __restrict__ x, float* __restrict__ mx, const int* __restrict__ flag) {
+    if (*flag) return;
+    const long long total = (long long)g.B * g.N;
+    const bool up = g.eps > 0;
+    const int rows = g.bc * g.bh;
+    const size_t plane_step = (size_t)(g.H - g.bh + 1) * g.W;            // from the last row of a channel's block to the first of the next
+    for (long long idx = blockIdx.x * 256LL + threadIdx.x; idx < total; idx += (long long)gridDim.x * 256) {
+        const int pos = int(idx % g.N), n = int(idx / g.N);
+        const int w = pos % g.Wo, h = (pos / g.Wo) % g.Ho, c = pos / (g.Wo * g.Ho);
+        const float* rp = x + (size_t)n * g.C * g.H * g.W + ((size_t)(c * g.sc) * g.H + h * g.sh) * g.W + w * BW;
+        float v = up ? -CUDART_INF_F : CUDART_INF_F;
+        int kh = 0;
+#pragma unroll 8
+        for (int rr = 0; rr < rows; ++rr) {
+            float t;
+            if (BW == 2) {
+                const float2 q = __ldg(reinterpret_cast<const float2*>(rp));
+                t = up ? fmaxf(q.x, q.y) : fminf(q.x, q.y);
+            } else {
+                const float4 q = __ldg(reinterpret_cast<const float4*>(rp));
+                t = up ? fmaxf(fmaxf(q.x, q.y), fmaxf(q.z, q.w)) : fminf(fminf(q.x, q.y), fminf(q.z, q.w));
+            }
+            v = up ? fmaxf(v, t) : fminf(v, t);
+            if (++kh == g.bh) { kh = 0; rp += plane_step; } else rp += g.W;
+        }
+        mx[idx] = v;
+    }
+}
+
 // The same maxima with eight threads per position (warp w of a CTA takes taps w, w + 8, ...): layers with few
 // positions and long patches (8x8 maps under 256 channels) otherwise leave most of the GPU idle while each
 // thread walks its patch alone.  max and min are associative and NaN taps are skipped either way: same values.
@@ -591,6 +625,12 @@ cudaError_t run_prepasses(const MexGeo& g, const MexWs& w, const float* x, const
         const int grid = int(std::min<long long>((total + 31) / 32, (long long)device_sm_count() * 32));
         if (g.bh == 1 && g.bw == 1) mex_colmax_sliced<true><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
         else mex_colmax_sliced<false><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
+    } else if ((g.bw == 2 || g.bw == 4) && g.sw == g.bw && g.W % g.bw == 0 && patches_inside_input(g) &&
+               (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        // every vector load is aligned: rows start at multiples of W floats, W and the sample stride are multiples of bw
+        const int grid = int(std::min<long long>((total + 255) / 256, (long long)device_sm_count() * 16));
+        if (g.bw == 2) mex_colmax_rows<2><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
+        else mex_colmax_rows<4><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
     } else {
         const int grid = int(std::min<long long>((total + 255) / 256, (long long)device_sm_count() * 16));
         if (g.bh == 1 && g.bw == 1) mex_colmax<true><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);

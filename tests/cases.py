@@ -205,6 +205,16 @@ MEX_PAIR = [
 ]
 
 
+# Short spatial blocks that tile the input rows (block width = stride, 2 or 4): the per-position maxima are taken from
+# whole block rows.  A negative epsilon (minima), several channel blocks, a height that leaves a remainder, enough
+# instances for the tensor-core kernels and too few for them.
+MEX_ROWS = [
+    mex_case("rows_w4_neg", (3, 6, 9, 12), 9, (3, 2, 4), (3, 2, 4), eps=-0.8, softmax=True, seed=323),
+    mex_case("rows_w2_many", (2, 12, 6, 20), 40, (4, 3, 2), (4, 3, 2), eps=1.5, unshared=False, shared_region=(-1,), seed=324),
+    mex_case("rows_w2_tc", (2, 16, 8, 16), 64, (4, 2, 2), (4, 2, 2), eps=0.5, softmax=True, unshared=False, shared_region=(-1,), seed=325),
+]
+
+
 # Few instances over whole-sample patches with one offsets region: the classifier-head kernels (several positions per
 # CTA forward, both gradients from one read of x backward).  Tap counts off the tile sizes, 3 to 13 instances, several
 # channel blocks, a negative epsilon, no softmax.

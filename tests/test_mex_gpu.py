@@ -54,6 +54,12 @@ def test_pair_tile_shapes_on_one_region_kernels(port, c):
     gpu_util.check_mex_pooled_dy(port, c, flags=abi.FLAG_MEX_NO_PAIR_TILES)
 
 
+@pytest.mark.parametrize("c", cases.MEX_ROWS, ids=lambda c: c["name"])
+def test_row_tiling_blocks(port, c):
+    """Blocks as wide as their stride that tile the input rows: per-position extrema from whole block rows."""
+    gpu_util.check_mex(port, c, f64_tiebreak=True)
+
+
 @pytest.mark.parametrize("c", cases.MEX_HEAD, ids=lambda c: c["name"])
 def test_head_shapes(port, c):
     """Whole-sample patches under few instances and one offsets region: the head kernels."""
