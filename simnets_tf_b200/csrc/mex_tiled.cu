@@ -126,20 +126,32 @@ __global__ void __launch_bounds__(512) mex_prep_offsets(MexGeo g, int Mp, const 
 // mx[n][pos] = max (eps > 0) or min (eps < 0) over the K taps of the patch at pos; NaN taps are ignored,
 // as the reference's max pass ignores them (std::max(acc, NaN) keeps acc).
 template <bool SPATIAL1>
-__global__ void __launch_bounds__(256) mex_colmax(MexGeo g, const float* __restrict__ x, float* __restrict__ mx, const int* __restrict__ flag) {
+__global__ void __launch_bounds__(256) mex_colmax(MexGeo g, const float* __restrict__ x, float* __restrict__ mx, const int* __restrict__ flag,
+                                                  int interior) {
     if (*flag) return;
     const long long total = (long long)g.B * g.N;
     const bool up = g.eps > 0;
     const float oob = float(g.oob);
+    const size_t hw = (size_t)g.H * g.W;
     for (long long idx = blockIdx.x * 256LL + threadIdx.x; idx < total; idx += (long long)gridDim.x * 256) {
         const int pos = int(idx % g.N), n = int(idx / g.N);
         const int w = pos % g.Wo, h = (pos / g.Wo) % g.Ho, c = pos / (g.Wo * g.Ho);
         const float* xs = x + (size_t)n * g.C * g.H * g.W;
         const int c0 = c * g.sc - g.pc, h0 = h * g.sh - g.ph, w0 = w * g.sw - g.pw;
         float v = up ? -CUDART_INF_F : CUDART_INF_F;
-        for (int k = 0; k < g.K; ++k) {
-            const float t = patch_value<SPATIAL1>(g, xs, c0, h0, w0, k, oob);
-            v = up ? fmaxf(v, t) : fminf(v, t);
+        if (SPATIAL1 && interior) {
+            // 1x1 blocks inside the input: tap k is channel c0 + k of one pixel; eight independent loads at a time
+            const float* p = xs + ((size_t)c0 * g.H + h0) * g.W + w0;
+#pragma unroll 8
+            for (int k = 0; k < g.K; ++k) {
+                const float t = __ldg(p + k * hw);
+                v = up ? fmaxf(v, t) : fminf(v, t);
+            }
+        } else {
+            for (int k = 0; k < g.K; ++k) {
+                const float t = patch_value<SPATIAL1>(g, xs, c0, h0, w0, k, oob);
+                v = up ? fmaxf(v, t) : fminf(v, t);
+            }
         }
         mx[idx] = v;
     }
@@ -183,7 +195,8 @@ __global__ void __launch_bounds__(256) mex_colmax_rows(MexGeo g, const float* __
 // positions and long patches (8x8 maps under 256 channels) otherwise leave most of the GPU idle while each
 // thread walks its patch alone.  max and min are associative and NaN taps are skipped either way: same values.
 template <bool SPATIAL1>
-__global__ void __launch_bounds__(256) mex_colmax_sliced(MexGeo g, const float* __restrict__ x, float* __restrict__ mx, const int* __restrict__ flag) {
+__global__ void __launch_bounds__(256) mex_colmax_sliced(MexGeo g, const float* __restrict__ x, float* __restrict__ mx, const int* __restrict__ flag,
+                                                         int interior) {
     __shared__ float part[8][32];
     if (*flag) return;
     const long long total = (long long)g.B * g.N;
@@ -198,10 +211,20 @@ __global__ void __launch_bounds__(256) mex_colmax_sliced(MexGeo g, const float* 
             const int w = pos % g.Wo, h = (pos / g.Wo) % g.Ho, c = pos / (g.Wo * g.Ho);
             const float* xs = x + (size_t)n * g.C * g.H * g.W;
             const int c0 = c * g.sc - g.pc, h0 = h * g.sh - g.ph, w0 = w * g.sw - g.pw;
+            if (SPATIAL1 && interior) {
+                const size_t hw = (size_t)g.H * g.W;
+                const float* p = xs + ((size_t)c0 * g.H + h0) * g.W + w0;
+#pragma unroll 8
+                for (int k = slice; k < g.K; k += 8) {
+                    const float t = __ldg(p + k * hw);
+                    v = up ? fmaxf(v, t) : fminf(v, t);
+                }
+            } else {
 #pragma unroll 4
-            for (int k = slice; k < g.K; k += 8) {
-                const float t = patch_value<SPATIAL1>(g, xs, c0, h0, w0, k, oob);
-                v = up ? fmaxf(v, t) : fminf(v, t);
+                for (int k = slice; k < g.K; k += 8) {
+                    const float t = patch_value<SPATIAL1>(g, xs, c0, h0, w0, k, oob);
+                    v = up ? fmaxf(v, t) : fminf(v, t);
+                }
             }
         }
         part[slice][lane] = v;
@@ -619,13 +642,14 @@ cudaError_t run_prepasses(const MexGeo& g, const MexWs& w, const float* x, const
     // long patches over few positions are contiguous per position: reduce them with one CTA each
     if (g.K >= 256 && g.N <= 16) { count_launch(); return launch_mex_colmax_wide(g, x, w.mx, w.flag, s); }
     const long long total = (long long)g.B * g.N;
+    const int inside = patches_inside_input(g) ? 1 : 0;
     // (measured on 32x32x64, 16x16x128 and 8x8x256 maps at batches 256 and 2048: eight threads per position win for
     // long patches while one thread per position would not fill the GPU's thread slots: 2048 per multiprocessor)
     if (g.K >= 128 && total < (long long)device_sm_count() * 2048) {
         const int grid = int(std::min<long long>((total + 31) / 32, (long long)device_sm_count() * 32));
-        if (g.bh == 1 && g.bw == 1) mex_colmax_sliced<true><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
-        else mex_colmax_sliced<false><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
-    } else if ((g.bw == 2 || g.bw == 4) && g.sw == g.bw && g.W % g.bw == 0 && patches_inside_input(g) &&
+        if (g.bh == 1 && g.bw == 1) mex_colmax_sliced<true><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag, inside);
+        else mex_colmax_sliced<false><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag, inside);
+    } else if ((g.bw == 2 || g.bw == 4) && g.sw == g.bw && g.W % g.bw == 0 && inside &&
                (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
         // every vector load is aligned: rows start at multiples of W floats, W and the sample stride are multiples of bw
         const int grid = int(std::min<long long>((total + 255) / 256, (long long)device_sm_count() * 16));
@@ -633,8 +657,8 @@ cudaError_t run_prepasses(const MexGeo& g, const MexWs& w, const float* x, const
         else mex_colmax_rows<4><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
     } else {
         const int grid = int(std::min<long long>((total + 255) / 256, (long long)device_sm_count() * 16));
-        if (g.bh == 1 && g.bw == 1) mex_colmax<true><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
-        else mex_colmax<false><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag);
+        if (g.bh == 1 && g.bw == 1) mex_colmax<true><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag, inside);
+        else mex_colmax<false><<<grid, 256, 0, s>>>(g, x, w.mx, w.flag, inside);
     }
     count_launch(2);
     return cudaGetLastError();
