@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(kTcThreads) mex_fwd_tc(MexGeo g, const float* 
 constexpr int kDxMaxM = 2048;      // instances whose a * mo + c' fit the kernel's shared-memory table (larger M: CUDA-core kernels)
 
 template <int NT, bool SPATIAL1, bool INTERIOR>
-__global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4)) mex_dx_tc(MexGeo g, const float* __restrict__ x, const float* __restrict__ tiles,
+__global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : 3) mex_dx_tc(MexGeo g, const float* __restrict__ x, const float* __restrict__ tiles,
                                                        const float* __restrict__ mo, const float* __restrict__ mx,
                                                        const float* __restrict__ y, const float* __restrict__ dy,
                                                        float* __restrict__ dx, int* __restrict__ flag) {
@@ -171,36 +171,38 @@ __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4
     const float* btiles = tiles + ((size_t)r * ktiles + kt) * mchunks * 2 * NT * kTcKT;
     const int M = g.M;
 
-    float yv[8], gv[8], mv[8];
-    auto load = [&](int c) {
+    // two register sets of raw y / dy values: the loads of chunk c + 2 are issued as soon as chunk c has been consumed
+    float yv[2][8], gv[2][8];
+    auto load = [&](int c, auto parity) {
+        constexpr int S = decltype(parity)::value;
         const int m0 = c * kTcKT + mhalf * 8;
         if (m0 + 8 <= M) {
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                yv[u] = live ? __ldcs(yp + u * Nu) : 0.f;               // a dead row must not read a stranger's y: 0 * 2^(big) = NaN
-                gv[u] = live ? __ldcs(gp + u * Ngu) : 0.f;
+                yv[S][u] = live ? __ldcs(yp + u * Nu) : 0.f;            // a dead row must not read a stranger's y: 0 * 2^(big) = NaN
+                gv[S][u] = live ? __ldcs(gp + u * Ngu) : 0.f;
             }
-            const float4 m0123 = *reinterpret_cast<const float4*>(amo_s + m0), m4567 = *reinterpret_cast<const float4*>(amo_s + m0 + 4);
-            mv[0] = m0123.x; mv[1] = m0123.y; mv[2] = m0123.z; mv[3] = m0123.w;
-            mv[4] = m4567.x; mv[5] = m4567.y; mv[6] = m4567.z; mv[7] = m4567.w;
         } else {
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const bool in = m0 + u < M;
-                yv[u] = (in && live) ? __ldcs(yp + u * Nu) : 0.f;
-                gv[u] = (in && live) ? __ldcs(gp + u * Ngu) : 0.f;      // dy = 0: no contribution
-                mv[u] = amo_s[m0 + u];
+                yv[S][u] = (in && live) ? __ldcs(yp + u * Nu) : 0.f;
+                gv[S][u] = (in && live) ? __ldcs(gp + u * Ngu) : 0.f;   // dy = 0: no contribution
             }
         }
         yp += (size_t)kTcKT * Nu;
         gp += (size_t)kTcKT * Ngu;
     };
-    auto store = [&](int c, unsigned char* a_hi, unsigned char* a_lo, unsigned char* b_hi, unsigned char*) {
+    auto bcopy = [&](int c, unsigned char* b_hi) {
         const float* src = btiles + (size_t)c * 2 * NT * kTcKT;
         for (int v = threadIdx.x; v < 2 * NT * kTcKT / 4; v += kTcThreads) cp_async16(reinterpret_cast<float*>(b_hi) + v * 4, src + v * 4, 16);
+    };
+    auto store = [&](int c, auto parity, unsigned char* a_hi, unsigned char* a_lo) {
+        constexpr int S = decltype(parity)::value;
+        const float* mv = amo_s + c * kTcKT + mhalf * 8;                // (padded with zeros up to a whole chunk)
         float q[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) q[u] = gv[u] * ex2_ftz(fmaf(a, (mxv - yv[u]) + mv[u], c2));
+        for (int u = 0; u < 8; ++u) q[u] = gv[S][u] * ex2_ftz(fmaf(a, (mxv - yv[S][u]) + mv[u], c2));
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             float4 hi, lo;
@@ -211,7 +213,7 @@ __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : (NT == 128 ? 3 : 4
             *reinterpret_cast<float4*>(a_lo + off) = lo;
         }
     };
-    const bool good = tc_mainloop<NT, kTcKT, 128, 2>(sh, dsm, tmem_d, mchunks, load, store);
+    const bool good = tc_mainloop_ahead2<NT, kTcKT, 128>(sh, dsm, tmem_d, mchunks, load, store, bcopy);
 
     if (good) {
         const int quarter = warp & 3, half = warp >> 2;

@@ -1,6 +1,7 @@
 // tcgen05 building blocks shared by the tensor-core MEX kernels: bounded mbarrier waits, shared-memory matrix
 // descriptors, the TF32 MMA and its commit, tensor-memory allocation and loads, the split-TF32 main loop.
 #pragma once
+#include <type_traits>
 #include "mex_common.cuh"
 
 namespace simnets {
@@ -151,6 +152,70 @@ __device__ __forceinline__ bool tc_mainloop(TcShared& sh, unsigned char* dsm, ui
             }
             umma_commit(c + 1 < nchunks ? &sh.bar_free[stage] : &sh.bar_done);
         }
+    }
+    if (ok && nchunks > 0) ok = mbar_wait(&sh.bar_done, 0);
+    if (!ok) sh.failed = 1;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    __syncthreads();
+    return sh.failed == 0;
+}
+
+// The same loop with deeper prefetching, for kernels whose B operand is copied verbatim from global memory:
+//  * the global loads of the A operand are issued TWO chunks ahead: load(c, parity) fills register set c % 2 and
+//    store(c, parity, a_hi, a_lo) consumes it, so that a thread always has the loads of a whole chunk in flight (the
+//    parity is a compile-time tag, std::integral_constant, so both register sets stay in registers);
+//  * bcopy(c, b_hi) issues the cp.async copies of chunk c's B tile ONE chunk ahead, into the other stage, so that their
+//    latency is not waited for between store(c) and the MMAs of chunk c.
+// Two stages.
+template <int NT, int KT, int LBO, class Load, class Store, class BCopy>
+__device__ __forceinline__ bool tc_mainloop_ahead2(TcShared& sh, unsigned char* dsm, uint32_t tmem_d, int nchunks, Load load, Store store, BCopy bcopy) {
+    constexpr int SBO = (KT / 4) * LBO;
+    constexpr int A_BYTES = (128 / 8) * SBO, B_BYTES = (NT / 8) * SBO;
+    constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+    constexpr uint32_t idesc = umma_idesc(NT);
+    using Even = std::integral_constant<int, 0>;
+    using Odd = std::integral_constant<int, 1>;
+    bool ok = true;
+    if (nchunks > 0) {
+        load(0, Even{});
+        bcopy(0, dsm + 2 * A_BYTES);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    if (nchunks > 1) load(1, Odd{});
+    auto step = [&](int c, auto parity) {
+        const int stage = c & 1;
+        unsigned char* sA = dsm + stage * STAGE_BYTES;
+        unsigned char* sB = sA + 2 * A_BYTES;
+        store(c, parity, sA, sA + A_BYTES);              // this stage was found free one step ago (or is used for the first time)
+        if (c + 2 < nchunks) load(c + 2, parity);        // into the register set that store(c) just emptied
+        if (c + 1 < nchunks) {
+            // the other stage is free once the MMAs of chunk c - 1 are done
+            if (c >= 1 && ok) ok = mbar_wait(&sh.bar_free[stage ^ 1], uint32_t((c - 1) >> 1) & 1u);
+            bcopy(c + 1, dsm + (stage ^ 1) * STAGE_BYTES + 2 * A_BYTES);
+            asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 1;" ::: "memory");      // chunk c's tile has landed
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA's async proxy
+        __syncthreads();
+        if (threadIdx.x == 0 && ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_hi = smem_u32(sA), a_lo = a_hi + A_BYTES, b_hi = smem_u32(sB), b_lo = b_hi + B_BYTES;
+#pragma unroll
+            for (int ks = 0; ks < KT / 8; ++ks) {
+                const uint32_t o = ks * 2 * LBO;
+                const uint64_t dah = umma_desc(a_hi + o, LBO, SBO), dal = umma_desc(a_lo + o, LBO, SBO);
+                const uint64_t dbh = umma_desc(b_hi + o, LBO, SBO), dbl = umma_desc(b_lo + o, LBO, SBO);
+                umma_tf32(tmem_d, dal, dbh, idesc, (c | ks) != 0);
+                umma_tf32(tmem_d, dah, dbl, idesc, 1);
+                umma_tf32(tmem_d, dah, dbh, idesc, 1);
+            }
+            umma_commit(c + 1 < nchunks ? &sh.bar_free[stage] : &sh.bar_done);
+        }
+    };
+    for (int c = 0; c < nchunks; c += 2) {
+        step(c, Even{});
+        if (c + 1 < nchunks) step(c + 1, Odd{});
     }
     if (ok && nchunks > 0) ok = mbar_wait(&sh.bar_done, 0);
     if (!ok) sh.failed = 1;
