@@ -141,13 +141,16 @@ __global__ void __launch_bounds__(kTcThreads, NT == 256 ? 2 : 3) mex_dx_tc(MexGe
                                                        float* __restrict__ dx, int* __restrict__ flag) {
     extern __shared__ __align__(128) unsigned char dsm[];
     __shared__ TcShared sh;
-    __shared__ __align__(16) float amo_s[kDxMaxM];        // mo of every instance of the region (rounded up to a whole chunk)
     __shared__ int tap_tab[SPATIAL1 ? 1 : kTapTable];
     if (flag[0]) return;
     if (!SPATIAL1) fill_tap_table(g, tap_tab);            // (published by the barrier inside tc_begin)
     const bool tab_ok = tap_table_ok(g);
     const long long P = (long long)g.B * g.rs;
     const int ktiles = (g.K + NT - 1) / NT, mchunks = (g.M + kTcKT - 1) / kTcKT;
+    // mo of every instance of the region, rounded up to a whole chunk, behind the operand stages (sized by the launcher:
+    // a fixed table for the largest M would cost the fourth CTA per multiprocessor)
+    constexpr int kStages = tc_smem_bytes<NT, kTcKT, 128, 2>();
+    float* amo_s = reinterpret_cast<float*>(dsm + kStages);
     int bid = blockIdx.x;
     const int r = bid % g.R; bid /= g.R;
     const int kt = bid % ktiles;
@@ -430,13 +433,23 @@ cudaError_t launch_dx_nt(const MexGeo& g, const float* x, const float* tiles, co
     const long long P = (long long)g.B * g.rs;
     const long long blocks = ((P + kTcPos - 1) / kTcPos) * ((g.K + NT - 1) / NT) * g.R;
     if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    constexpr int smem = tc_smem_bytes<NT, kTcKT, 128, 2>();
+    if (g.M > kDxMaxM) return cudaErrorInvalidConfiguration;
+    constexpr int smem_max = tc_smem_bytes<NT, kTcKT, 128, 2>() + kDxMaxM * 4;
+    const int smem = tc_smem_bytes<NT, kTcKT, 128, 2>() + ((g.M + kTcKT - 1) / kTcKT) * kTcKT * 4;
+#define DX_RUN(KERNEL)                                                                              \
+    do {                                                                                            \
+        static bool attr_done = false;                                                              \
+        const cudaError_t e_ = set_smem_once(KERNEL, smem_max, attr_done);                          \
+        if (e_ != cudaSuccess) return e_;                                                           \
+        KERNEL<<<int(blocks), kTcThreads, smem, s>>>(g, x, tiles, mo, mx, y, dy, dx, flag);         \
+    } while (0)
     if (g.bh == 1 && g.bw == 1) {
-        if (patches_inside_input(g) && (long long)NT * g.H * g.W < 0x7fffffffLL) TC_RUN((mex_dx_tc<NT, true, true>), smem, int(blocks), g, x, tiles, mo, mx, y, dy, dx, flag);
-        else TC_RUN((mex_dx_tc<NT, true, false>), smem, int(blocks), g, x, tiles, mo, mx, y, dy, dx, flag);
+        if (patches_inside_input(g) && (long long)NT * g.H * g.W < 0x7fffffffLL) DX_RUN((mex_dx_tc<NT, true, true>));
+        else DX_RUN((mex_dx_tc<NT, true, false>));
     } else {
-        TC_RUN((mex_dx_tc<NT, false, false>), smem, int(blocks), g, x, tiles, mo, mx, y, dy, dx, flag);
+        DX_RUN((mex_dx_tc<NT, false, false>));
     }
+#undef DX_RUN
     count_launch();
     return cudaGetLastError();
 }

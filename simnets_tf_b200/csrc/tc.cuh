@@ -225,7 +225,7 @@ __device__ __forceinline__ bool tc_mainloop_ahead2(TcShared& sh, unsigned char* 
 }
 
 template <int NT, int KT, int LBO, int STAGES>
-constexpr int tc_smem_bytes() { return STAGES * (2 * (128 / 8) * (KT / 4) * LBO + 2 * (NT / 8) * (KT / 4) * LBO); }
+__host__ __device__ constexpr int tc_smem_bytes() { return STAGES * (2 * (128 / 8) * (KT / 4) * LBO + 2 * (NT / 8) * (KT / 4) * LBO); }
 
 // 32 consecutive tensor-memory columns of this thread's lane
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
